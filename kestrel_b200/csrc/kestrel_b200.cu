@@ -1,0 +1,92 @@
+// C ABI of the paged-KV library (see include/kestrel_b200.h for the contract).
+// One translation unit: the kernels live in the .cuh files next to this one.
+#include "common.cuh"
+#include "cache_ops.cuh"
+#include "paged_attention.cuh"
+
+using namespace kb200;
+
+#define KB200_ENTER(dev)                                                          \
+  DeviceGuard _guard(dev);                                                        \
+  if (!_guard.ok) return fail(KB200_ERR_CUDA, "cannot switch to CUDA device %d", (int)(dev))
+
+extern "C" {
+
+int kb200_abi_version(void) { return KB200_ABI_VERSION; }
+
+const char* kb200_last_error(void) { return err_buf(); }
+
+int kb200_device_status(int device, int32_t out[4], int clear) {
+  KB200_ENTER(device);
+  KB200_REQUIRE(out != nullptr, "out is null");
+  KB200_CUDA_OK(cudaDeviceSynchronize());
+  int host[4] = {0, 0, 0, 0};
+  KB200_CUDA_OK(cudaMemcpyFromSymbol(host, g_status, sizeof(host)));
+  for (int i = 0; i < 4; ++i) out[i] = host[i];
+  if (clear) {
+    int zero[4] = {0, 0, 0, 0};
+    KB200_CUDA_OK(cudaMemcpyToSymbol(g_status, zero, sizeof(zero)));
+  }
+  return KB200_OK;
+}
+
+int kb200_reshape_and_cache_flash(const void* key, const void* value, int64_t key_token_stride,
+                                  int64_t value_token_stride, void* key_cache, void* value_cache,
+                                  int64_t cache_page_stride, int64_t cache_token_stride,
+                                  int64_t cache_head_stride, const int64_t* slot_mapping,
+                                  int64_t num_tokens, int64_t n_pages, int32_t page_size,
+                                  int32_t n_kv_heads, int32_t head_dim, int32_t in_dtype,
+                                  int32_t cache_dtype, const float* k_scale, const float* v_scale,
+                                  int32_t n_scales, int32_t device, void* stream) {
+  KB200_ENTER(device);
+  return launch_append(key, value, key_token_stride, value_token_stride, key_cache, value_cache,
+                       cache_page_stride, cache_token_stride, cache_head_stride, slot_mapping, num_tokens,
+                       n_pages, page_size, n_kv_heads, head_dim, in_dtype, cache_dtype, k_scale, v_scale,
+                       n_scales, static_cast<cudaStream_t>(stream));
+}
+
+int kb200_build_slot_mapping(const int32_t* page_table, int64_t pt_row_stride, int64_t pt_rows,
+                             int64_t pt_cols, const void* batch_idx, int32_t batch_idx_is_i64,
+                             int32_t batch_per_row, int64_t row_len, const void* positions,
+                             int32_t positions_is_i64, int64_t* out_slots, int64_t n, int32_t page_size,
+                             int32_t device, void* stream) {
+  KB200_ENTER(device);
+  return launch_slot_mapping(page_table, pt_row_stride, pt_rows, pt_cols, batch_idx, batch_idx_is_i64,
+                             batch_per_row, row_len, positions, positions_is_i64, out_slots, n, page_size,
+                             static_cast<cudaStream_t>(stream));
+}
+
+int kb200_build_paged_kv_metadata(const int32_t* page_table, int64_t pt_row_stride, int64_t pt_rows,
+                                  int64_t pt_cols, const void* batch_idx, int32_t batch_idx_is_i64,
+                                  const int32_t* input_pos, int32_t* out_page_table, int64_t out_row_stride,
+                                  int64_t out_cols, int32_t* out_seqused_k, int64_t batch, int32_t page_size,
+                                  int32_t device, void* stream) {
+  KB200_ENTER(device);
+  return launch_metadata(page_table, pt_row_stride, pt_rows, pt_cols, batch_idx, batch_idx_is_i64, input_pos,
+                         out_page_table, out_row_stride, out_cols, out_seqused_k, batch, page_size,
+                         static_cast<cudaStream_t>(stream));
+}
+
+int kb200_copy_pages(void* const* caches, int32_t n_caches, int64_t page_bytes, int64_t page_stride_bytes,
+                     int64_t n_pages, const int32_t* src_pages, const int32_t* dst_pages, int64_t n_pairs,
+                     int32_t device, void* stream) {
+  KB200_ENTER(device);
+  return launch_copy_pages(caches, n_caches, page_bytes, page_stride_bytes, n_pages, src_pages, dst_pages,
+                           n_pairs, static_cast<cudaStream_t>(stream));
+}
+
+uint64_t kb200_attn_workspace_bytes(int64_t batch, int64_t total_q, int32_t n_q_heads, int32_t n_kv_heads,
+                                    int32_t head_dim, int32_t device) {
+  if (batch <= 0 || total_q <= 0 || n_q_heads <= 0 || n_kv_heads <= 0 || head_dim <= 0) return 0;
+  int sms = 0;
+  if (device_sm_count(device, &sms) != KB200_OK) return 0;
+  return attn_workspace_layout(batch, total_q, n_q_heads, n_kv_heads, head_dim, sms * kAttnWarps).total;
+}
+
+int kb200_paged_attention(const kb200_attn_args* args) {
+  if (!args) return fail(KB200_ERR_INVALID, "args is null");
+  KB200_ENTER(args->device);
+  return launch_paged_attention(args);
+}
+
+}  // extern "C"

@@ -1,0 +1,1040 @@
+// Paged split-KV decode attention for sm_100a.
+//
+// Work decomposition
+//   A *segment* is one (sequence b, KV head h, 16-row query block mb): the rows
+//   are the GQA group's query heads times the (few) query positions of the
+//   sequence, row r = j * group + g.  A segment's keys are cut into *tiles* of
+//   TILE_N tokens.  All tiles of all segments form one flat index space
+//   [0, T); worker w (one warp) owns the contiguous range
+//   [w*T/W, (w+1)*T/W), so every warp streams the same number of tiles (+-1)
+//   whatever the mix of context lengths.  A warp keeps the running
+//   (max, sum, O) of its current segment in registers; a segment that lies
+//   inside one warp's range is normalised and written straight to `out`, a
+//   segment cut by a range boundary leaves one partial per warp in scratch
+//   memory and a small merge kernel combines them.
+//
+// Data movement
+//   The pool view [n_pages, P, H_kv, D] is described to the TMA unit once per
+//   pool as a 4-D tensor map; a (page, head) tile of K or V is one
+//   cp.async.bulk.tensor box of P rows x 128 bytes (two boxes when a row is
+//   256 bytes), landing in 128-byte-swizzled shared memory so that ldmatrix is
+//   bank-conflict free.  Each warp owns a ring of kAttnStages stages and
+//   refills a stage as soon as it has read it, so 2 tiles per warp are always
+//   in flight behind the one being computed.  Page indices are read one tile
+//   ahead of the copy that needs them.  No multicast, no cluster.
+//
+// Math
+//   S = Q K^T and O += P V on mma.sync m16n8k16 (bf16 or f16 operands, fp32
+//   accumulate); FP8 e4m3 K/V are widened to f16 in registers (exact) and the
+//   per-head scales are folded into the softmax scale and the final
+//   normalisation.  Softmax is the usual online form in fp32, base 2.
+#pragma once
+
+#include <mutex>
+#include <unordered_map>
+#include <string>
+
+#include "common.cuh"
+
+namespace kb200 {
+
+constexpr int kAttnWarps = 4;
+constexpr int kAttnStages = 3;
+constexpr int kAttnThreads = kAttnWarps * 32;
+constexpr int kRowsPerSeg = 16;
+
+template <int KVB, int HD>
+struct AttnTile {
+  static constexpr int ROW_BYTES = HD * KVB;                      // bytes of one token row of one head
+  static constexpr int RB = ROW_BYTES > 128 ? 128 : ROW_BYTES;    // swizzled row width in smem
+  static constexpr int NH = ROW_BYTES / RB;                       // 128-byte halves per row
+  static constexpr int TILE_N = (KVB == 2 && HD == 128) ? 32 : 64;
+  static constexpr int KV_TILE_BYTES = TILE_N * ROW_BYTES;
+  static constexpr int STAGE_BYTES = 2 * KV_TILE_BYTES;           // K then V
+  static constexpr int SMEM_BYTES = kAttnWarps * kAttnStages * STAGE_BYTES + kAttnWarps * kAttnStages * 8 + 1024;
+};
+
+struct AttnParams {
+  const char* q;
+  char* out;
+  float* lse;
+  int64_t q_bs, q_rs, q_hs, o_bs, o_rs, o_hs;  // element strides
+  int64_t lse_bs, lse_hs;
+  const int32_t* page_table;
+  int64_t pt_rs;
+  const int32_t* seqused_k;
+  const int32_t* seqused_q;
+  const int32_t* cu_seqlens_q;
+  const float* ks_vec;
+  const float* vs_vec;
+  float ks, vs, softmax_scale;
+  // plan (written by attn_plan_kernel)
+  long long* tile_cum;  // [B+1]
+  int* seg_cum;         // [B+1]
+  int* nt;              // [B] tiles per segment
+  int* tile0;           // [B] first tile (sliding window)
+  int* sq;              // [B] valid query rows
+  int* qrow0;           // [B] first packed query row (0 in the padded layout)
+  int* klen;            // [B] keys
+  float* part_ml;       // [slots][16][2]  (scaled max in log2 units, sum)
+  float* part_o;        // [slots][16][HD] unnormalised
+  int64_t n_pages;
+  int batch, seqlen_q, hq, hkv, group, page_size, causal, window_left, q_is_bf16, n_workers, tile_n;
+};
+
+// ---------------------------------------------------------------------------
+// PTX helpers
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok;
+}
+__device__ __forceinline__ uint64_t global_timer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+// Waits for the phase with the given parity; gives up after ~2 s of wall time
+// and returns false (the caller records the failure and leaves the kernel).
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity) {
+  if (mbar_try_wait(bar, parity)) return true;
+  uint64_t start = 0;
+  for (uint32_t spins = 0;; ++spins) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((spins & 63) == 63) {
+      const uint64_t now = global_timer_ns();
+      if (start == 0) start = now;
+      else if (now - start > 2000000000ull) return false;
+    }
+  }
+}
+__device__ __forceinline__ void fence_barrier_init() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void fence_proxy_async() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* tm, uint32_t bar, int c0,
+                                            int c1, int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(tm)), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+__device__ __forceinline__ void ldsm_x4(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(addr));
+}
+template <bool BF16>
+__device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  if constexpr (BF16) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+  } else {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+  }
+}
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+// four e4m3 codes (one 32-bit word) -> two f16x2 words (bytes 0,1 and bytes 2,3); exact
+__device__ __forceinline__ void e4m3x4_to_f16x4(uint32_t x, uint32_t& lo, uint32_t& hi) {
+  asm("{\n\t.reg .b16 a, b;\n\t"
+      "mov.b32 {a, b}, %2;\n\t"
+      "cvt.rn.f16x2.e4m3x2 %0, a;\n\t"
+      "cvt.rn.f16x2.e4m3x2 %1, b;\n\t}"
+      : "=r"(lo), "=r"(hi)
+      : "r"(x));
+}
+template <bool BF16>
+__device__ __forceinline__ uint32_t pack2(float a, float b) {
+  if constexpr (BF16) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&v);
+  } else {
+    __half2 v = __floats2half2_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&v);
+  }
+}
+__device__ __forceinline__ float bf16_bits_to_float(uint32_t bits16) { return __uint_as_float(bits16 << 16); }
+
+// ---------------------------------------------------------------------------
+// Plan: per-sequence tile/segment counts and their exclusive prefix sums.
+// One block; sequences are scanned 256 at a time with a running carry.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) attn_plan_kernel(const AttnParams p) {
+  __shared__ long long warp_t[8];
+  __shared__ int warp_s[8];
+  __shared__ long long carry_t;
+  __shared__ int carry_s;
+  const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+  if (tid == 0) { carry_t = 0; carry_s = 0; }
+  __syncthreads();
+  for (int base = 0; base < p.batch; base += 256) {
+    const int b = base + tid;
+    long long cnt_t = 0;
+    int cnt_s = 0;
+    if (b < p.batch) {
+      int L = p.seqused_k[b];
+      if (L < 0) L = 0;
+      int sq, row0 = 0;
+      if (p.cu_seqlens_q) {
+        row0 = p.cu_seqlens_q[b];
+        sq = p.cu_seqlens_q[b + 1] - row0;
+      } else {
+        sq = p.seqlen_q;
+        if (p.seqused_q) sq = min(sq, p.seqused_q[b]);
+      }
+      if (sq < 0) sq = 0;
+      int t0 = 0;
+      if (p.window_left >= 0) {
+        int kmin = L - sq - p.window_left;
+        if (kmin > 0) t0 = kmin / p.tile_n;
+      }
+      int ntile = (sq > 0 && L > 0) ? (L + p.tile_n - 1) / p.tile_n - t0 : 0;
+      const int nmb = (p.group * sq + kRowsPerSeg - 1) / kRowsPerSeg;
+      cnt_s = p.hkv * nmb;
+      cnt_t = (long long)ntile * cnt_s;
+      p.nt[b] = ntile;
+      p.tile0[b] = t0;
+      p.sq[b] = sq;
+      p.qrow0[b] = row0;
+      p.klen[b] = L;
+    }
+    // inclusive warp scans
+    long long it = cnt_t;
+    int is = cnt_s;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      long long ut = __shfl_up_sync(0xffffffffu, it, d);
+      int us = __shfl_up_sync(0xffffffffu, is, d);
+      if (lane >= d) { it += ut; is += us; }
+    }
+    if (lane == 31) { warp_t[wid] = it; warp_s[wid] = is; }
+    __syncthreads();
+    long long off_t = carry_t;
+    int off_s = carry_s;
+    for (int w = 0; w < wid; ++w) { off_t += warp_t[w]; off_s += warp_s[w]; }
+    if (b < p.batch) {
+      p.tile_cum[b] = off_t + it - cnt_t;
+      p.seg_cum[b] = off_s + is - cnt_s;
+    }
+    __syncthreads();
+    if (tid == 255) { carry_t = off_t + it; carry_s = off_s + is; }
+    __syncthreads();
+  }
+  if (tid == 0) {
+    p.tile_cum[p.batch] = carry_t;
+    p.seg_cum[p.batch] = carry_s;
+  }
+}
+
+// Position of a warp inside the flat tile space (identical on all 32 lanes).
+struct Cursor {
+  int b, seg, nseg, t, nt, tile0, L, sq, nmb, segbase;
+};
+
+__device__ __forceinline__ void cursor_load_seq(const AttnParams& p, Cursor& c) {
+  c.nt = p.nt[c.b];
+  c.tile0 = p.tile0[c.b];
+  c.L = p.klen[c.b];
+  c.sq = p.sq[c.b];
+  c.nmb = (p.group * c.sq + kRowsPerSeg - 1) / kRowsPerSeg;
+  c.nseg = p.hkv * c.nmb;
+  c.segbase = p.seg_cum[c.b];
+}
+
+__device__ __forceinline__ void cursor_locate(const AttnParams& p, Cursor& c, long long g) {
+  int lo = 0, hi = p.batch;  // tile_cum[lo] <= g < tile_cum[hi]
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (p.tile_cum[mid] <= g) lo = mid; else hi = mid;
+  }
+  c.b = lo;
+  cursor_load_seq(p, c);
+  const long long off = g - p.tile_cum[lo];
+  c.seg = (int)(off / c.nt);
+  c.t = (int)(off - (long long)c.seg * c.nt);
+}
+
+// Moves to the next tile; only called while tiles remain, so a non-empty
+// sequence always follows.
+__device__ __forceinline__ void cursor_advance(const AttnParams& p, Cursor& c) {
+  if (++c.t < c.nt) return;
+  c.t = 0;
+  if (++c.seg < c.nseg) return;
+  c.seg = 0;
+  while (++c.b < p.batch) {
+    cursor_load_seq(p, c);
+    if (c.nt > 0 && c.nseg > 0) return;
+  }
+  c.b = p.batch - 1;  // not reached when the caller counts tiles correctly
+}
+
+template <int RB>
+__device__ __forceinline__ uint32_t swz(int row) {
+  if constexpr (RB == 128) return row & 7;
+  else if constexpr (RB == 64) return (row >> 1) & 3;
+  else return (row >> 2) & 1;
+}
+
+// ---------------------------------------------------------------------------
+// The attention kernel.  KVB: bytes per K/V element (2: bf16/f16, 1: e4m3);
+// BF16: operand type of the MMAs (bf16 when K/V are bf16, else f16).
+// ---------------------------------------------------------------------------
+template <int KVB, int HD, bool BF16>
+__global__ void __launch_bounds__(kAttnThreads, 1)
+paged_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+                  const __grid_constant__ AttnParams p) {
+  using T = AttnTile<KVB, HD>;
+  constexpr int TILE_N = T::TILE_N;
+  constexpr int RB = T::RB;
+  constexpr int NH = T::NH;
+  constexpr int NT8 = TILE_N / 8;    // score n-tiles per tile
+  constexpr int NKS = TILE_N / 16;   // k-steps of P V
+  constexpr int NOT = HD / 8;        // output n-tiles
+  constexpr int NQF = HD / 16;       // Q fragments (k-steps of Q K^T)
+  constexpr float kLog2e = 1.4426950408889634f;
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int c4 = lane & 3, g8 = lane >> 2;
+  const uint32_t my_stage0 = smem_base + (uint32_t)(warp * kAttnStages) * T::STAGE_BYTES;
+  const uint32_t bar0 = smem_base + (uint32_t)(kAttnWarps * kAttnStages) * T::STAGE_BYTES +
+                        (uint32_t)(warp * kAttnStages) * 8u;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kAttnWarps * kAttnStages; ++i)
+      mbar_init(smem_base + (uint32_t)(kAttnWarps * kAttnStages) * T::STAGE_BYTES + 8u * i, 1);
+    fence_barrier_init();
+    fence_proxy_async();
+  }
+  __syncthreads();
+  // No block-wide barrier below this line: warps are independent workers.
+
+  const long long total = p.tile_cum[p.batch];
+  const int w = blockIdx.x * kAttnWarps + warp;
+  const long long r0 = (long long)w * total / p.n_workers;
+  const long long r1 = (long long)(w + 1) * total / p.n_workers;
+  if (r0 >= r1) return;
+  const int my_tiles = (int)(r1 - r0);
+
+  const int P = p.page_size;
+  const int box_rows = P < TILE_N ? P : TILE_N;
+  const int boxes_per_tile = TILE_N / box_rows;
+  const int nbox = boxes_per_tile * NH * 2;
+
+  // ---- producer side: cursor of the next tile to copy, page index read one tile ahead
+  Cursor pc;
+  cursor_locate(p, pc, r0);
+  int issued = 0;
+  auto page_for = [&](const Cursor& c, int j) -> int {
+    const int i = j / (NH * 2);
+    const int key = (c.tile0 + c.t) * TILE_N + i * box_rows;
+    if (key >= c.L) return 0;
+    return p.page_table[(int64_t)c.b * p.pt_rs + key / P];
+  };
+  int pg = lane < nbox ? page_for(pc, lane) : 0;
+
+  auto issue = [&](int stage) {
+    const uint32_t sbase = my_stage0 + (uint32_t)stage * T::STAGE_BYTES;
+    const uint32_t bar = bar0 + 8u * stage;
+    const int k0 = (pc.tile0 + pc.t) * TILE_N;
+    const int h = pc.seg / pc.nmb;
+    int nvalid = pc.L - k0;
+    if (nvalid > TILE_N) nvalid = TILE_N;
+    const int nvb = (nvalid + box_rows - 1) / box_rows;
+    if (lane == 0) mbar_expect_tx(bar, (uint32_t)(nvb * box_rows * T::ROW_BYTES * 2));
+    __syncwarp();
+    for (int j = lane; j < nbox; j += 32) {
+      const int i = j / (NH * 2);
+      if (i >= nvb) continue;
+      const int sub = j - i * (NH * 2);
+      const int kv = sub / NH, half = sub - kv * NH;
+      const int key = k0 + i * box_rows;
+      const int page = (j == lane) ? pg : page_for(pc, j);
+      if ((unsigned)page >= (unsigned long long)p.n_pages) report(KB200_STATUS_BAD_PAGE, page, KID_ATTN);
+      const uint32_t dst = sbase + (uint32_t)kv * T::KV_TILE_BYTES + (uint32_t)half * (TILE_N * RB) +
+                           (uint32_t)(i * box_rows) * RB;
+      tma_load_4d(dst, kv ? &tmV : &tmK, bar, half * (RB / KVB), key % P, h, page);
+    }
+    ++issued;
+    if (issued < my_tiles) {
+      cursor_advance(p, pc);
+      pg = lane < nbox ? page_for(pc, lane) : 0;
+    }
+  };
+
+  for (int s = 0; s < kAttnStages && issued < my_tiles; ++s) issue(s);
+
+  // ---- consumer side
+  Cursor cc;
+  cursor_locate(p, cc, r0);
+
+  uint32_t qf[NQF][4];
+  float o[NOT][4];
+  float m0 = 0.f, m1 = 0.f, l0 = 0.f, l1 = 0.f;
+  float sl2 = 0.f, vscale = 1.f;
+  int lim0 = 0, lim1 = 0, row0 = 0, row1 = 0, h = 0;
+  bool valid0 = false, valid1 = false;
+  bool fresh = true;
+  long long piece_start = r0;
+
+  for (int it = 0; it < my_tiles; ++it) {
+    const long long g = r0 + it;
+    if (fresh) {
+      fresh = false;
+      piece_start = g;
+      const int mb = cc.seg % cc.nmb;
+      h = cc.seg / cc.nmb;
+      row0 = mb * kRowsPerSeg + g8;
+      row1 = row0 + 8;
+      const int nrows = p.group * cc.sq;
+      valid0 = row0 < nrows;
+      valid1 = row1 < nrows;
+      const int j0 = row0 / p.group, j1 = row1 / p.group;
+      const bool upper = p.causal || p.window_left >= 0;
+      lim0 = upper ? cc.L - cc.sq + j0 : cc.L - 1;
+      lim1 = upper ? cc.L - cc.sq + j1 : cc.L - 1;
+      const float ksc = p.ks_vec ? p.ks_vec[h] : p.ks;
+      vscale = p.vs_vec ? p.vs_vec[h] : p.vs;
+      sl2 = p.softmax_scale * ksc * kLog2e;
+      m0 = m1 = -INFINITY;
+      l0 = l1 = 0.f;
+#pragma unroll
+      for (int i = 0; i < NOT; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+      // Q fragments, straight from global memory (4 KB per segment at most)
+      const int64_t qb = (int64_t)cc.b * p.q_bs;
+      const char* q0 = p.q + 2 * (qb + (int64_t)(p.qrow0[cc.b] + j0) * p.q_rs +
+                                  (int64_t)(h * p.group + row0 % p.group) * p.q_hs);
+      const char* q1 = p.q + 2 * (qb + (int64_t)(p.qrow0[cc.b] + j1) * p.q_rs +
+                                  (int64_t)(h * p.group + row1 % p.group) * p.q_hs);
+      if constexpr (KVB == 2) {
+#pragma unroll
+        for (int ks = 0; ks < NQF; ++ks) {
+          const int d = 16 * ks + 2 * c4;
+          qf[ks][0] = valid0 ? *reinterpret_cast<const uint32_t*>(q0 + 2 * d) : 0u;
+          qf[ks][1] = valid1 ? *reinterpret_cast<const uint32_t*>(q1 + 2 * d) : 0u;
+          qf[ks][2] = valid0 ? *reinterpret_cast<const uint32_t*>(q0 + 2 * (d + 8)) : 0u;
+          qf[ks][3] = valid1 ? *reinterpret_cast<const uint32_t*>(q1 + 2 * (d + 8)) : 0u;
+        }
+      } else {
+        // e4m3 K rows are read four consecutive d per thread, so Q uses the same d order:
+        // k-slots (2c, 2c+1) <-> d = 16*ch + 4c + {0,1}; (2c+8, 2c+9) <-> d = 16*ch + 4c + {2,3}
+#pragma unroll
+        for (int ch = 0; ch < NQF; ++ch) {
+          const int d = 16 * ch + 4 * c4;
+          uint2 a = valid0 ? *reinterpret_cast<const uint2*>(q0 + 2 * d) : make_uint2(0u, 0u);
+          uint2 b = valid1 ? *reinterpret_cast<const uint2*>(q1 + 2 * d) : make_uint2(0u, 0u);
+          if (p.q_is_bf16) {
+            a.x = pack2<false>(bf16_bits_to_float(a.x & 0xffffu), bf16_bits_to_float(a.x >> 16));
+            a.y = pack2<false>(bf16_bits_to_float(a.y & 0xffffu), bf16_bits_to_float(a.y >> 16));
+            b.x = pack2<false>(bf16_bits_to_float(b.x & 0xffffu), bf16_bits_to_float(b.x >> 16));
+            b.y = pack2<false>(bf16_bits_to_float(b.y & 0xffffu), bf16_bits_to_float(b.y >> 16));
+          }
+          qf[ch][0] = a.x; qf[ch][1] = b.x; qf[ch][2] = a.y; qf[ch][3] = b.y;
+        }
+      }
+    }
+
+    const int stage = it % kAttnStages;
+    const uint32_t parity = (uint32_t)(it / kAttnStages) & 1u;
+    if (!mbar_wait_bounded(bar0 + 8u * stage, parity)) {
+      if (lane == 0) report(KB200_STATUS_WAIT_TIMEOUT, w, KID_ATTN);
+      return;
+    }
+    const uint32_t kbase = my_stage0 + (uint32_t)stage * T::STAGE_BYTES;
+    const uint32_t vbase = kbase + T::KV_TILE_BYTES;
+    const int key0 = (cc.tile0 + cc.t) * TILE_N;
+
+    // ---- S = Q K^T
+    float s[NT8][4];
+#pragma unroll
+    for (int n = 0; n < NT8; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+    if constexpr (KVB == 2) {
+#pragma unroll
+      for (int n = 0; n < NT8; ++n) {
+        const int r = n * 8 + (lane & 7);
+#pragma unroll
+        for (int q4 = 0; q4 < HD / 32; ++q4) {
+          const int ch = q4 * 4 + (lane >> 3);
+          const uint32_t addr = kbase + (uint32_t)(ch >> 3) * (TILE_N * 128) + (uint32_t)r * 128 +
+                                ((uint32_t)((ch & 7) ^ (r & 7)) << 4);
+          uint32_t b0, b1, b2, b3;
+          ldsm_x4(b0, b1, b2, b3, addr);
+          mma16816<BF16>(s[n], qf[2 * q4], b0, b1);
+          mma16816<BF16>(s[n], qf[2 * q4 + 1], b2, b3);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int n = 0; n < NT8; ++n) {
+        const int r = n * 8 + (lane & 7);
+#pragma unroll
+        for (int q4 = 0; q4 < HD / 64; ++q4) {
+          const int ch = q4 * 4 + (lane >> 3);
+          const uint32_t addr = kbase + (uint32_t)r * RB + ((uint32_t)(ch ^ swz<RB>(r)) << 4);
+          uint32_t x[4];
+          ldsm_x4(x[0], x[1], x[2], x[3], addr);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            uint32_t b0, b1;
+            e4m3x4_to_f16x4(x[i], b0, b1);
+            mma16816<false>(s[n], qf[q4 * 4 + i], b0, b1);
+          }
+        }
+      }
+    }
+
+    // ---- mask (only tiles that touch a boundary)
+    const int key_last = key0 + TILE_N - 1;
+    const int min_lim = (p.causal || p.window_left >= 0) ? cc.L - cc.sq : cc.L - 1;
+    const bool need_mask = key_last > min_lim || (p.window_left >= 0 && key0 < cc.L - 1 - p.window_left);
+    if (need_mask) {
+      const int lo0 = p.window_left >= 0 ? lim0 - p.window_left : 0;
+      const int lo1 = p.window_left >= 0 ? lim1 - p.window_left : 0;
+#pragma unroll
+      for (int n = 0; n < NT8; ++n) {
+        const int k = key0 + n * 8 + 2 * c4;
+        if (k > lim0 || k < lo0) s[n][0] = -INFINITY;
+        if (k + 1 > lim0 || k + 1 < lo0) s[n][1] = -INFINITY;
+        if (k > lim1 || k < lo1) s[n][2] = -INFINITY;
+        if (k + 1 > lim1 || k + 1 < lo1) s[n][3] = -INFINITY;
+      }
+    }
+
+    // ---- online softmax (base 2)
+    float t0 = -INFINITY, t1 = -INFINITY;
+#pragma unroll
+    for (int n = 0; n < NT8; ++n) {
+      t0 = fmaxf(t0, fmaxf(s[n][0], s[n][1]));
+      t1 = fmaxf(t1, fmaxf(s[n][2], s[n][3]));
+    }
+    t0 = fmaxf(t0, __shfl_xor_sync(0xffffffffu, t0, 1));
+    t0 = fmaxf(t0, __shfl_xor_sync(0xffffffffu, t0, 2));
+    t1 = fmaxf(t1, __shfl_xor_sync(0xffffffffu, t1, 1));
+    t1 = fmaxf(t1, __shfl_xor_sync(0xffffffffu, t1, 2));
+    const float mn0 = fmaxf(m0, t0), mn1 = fmaxf(m1, t1);
+    if (__any_sync(0xffffffffu, mn0 > m0 || mn1 > m1)) {
+      const float c0 = (m0 == -INFINITY) ? 0.f : ex2((m0 - mn0) * sl2);
+      const float c1 = (m1 == -INFINITY) ? 0.f : ex2((m1 - mn1) * sl2);
+      l0 *= c0;
+      l1 *= c1;
+#pragma unroll
+      for (int i = 0; i < NOT; ++i) {
+        o[i][0] *= c0; o[i][1] *= c0; o[i][2] *= c1; o[i][3] *= c1;
+      }
+      m0 = mn0;
+      m1 = mn1;
+    }
+    const float ms0 = (m0 == -INFINITY) ? 0.f : m0 * sl2;
+    const float ms1 = (m1 == -INFINITY) ? 0.f : m1 * sl2;
+    uint32_t pf[NKS][4];
+#pragma unroll
+    for (int n = 0; n < NT8; ++n) {
+      const float p0 = ex2(fmaf(s[n][0], sl2, -ms0));
+      const float p1 = ex2(fmaf(s[n][1], sl2, -ms0));
+      const float p2 = ex2(fmaf(s[n][2], sl2, -ms1));
+      const float p3 = ex2(fmaf(s[n][3], sl2, -ms1));
+      l0 += p0 + p1;
+      l1 += p2 + p3;
+      pf[n >> 1][(n & 1) * 2 + 0] = pack2<BF16>(p0, p1);
+      pf[n >> 1][(n & 1) * 2 + 1] = pack2<BF16>(p2, p3);
+    }
+
+    // ---- O += P V.  Rows of V past the sequence end may hold anything (NaN
+    // bit patterns included), so they are zeroed in the one tile that has them.
+    const bool need_vmask = key0 + TILE_N > cc.L;
+#pragma unroll
+    for (int ks = 0; ks < NKS; ++ks) {
+      uint32_t mk_lo = 0xffffffffu, mk_hi = 0xffffffffu;
+      if (need_vmask) {
+        const int kv_left = cc.L - (key0 + 16 * ks);  // valid keys in this 16-key block
+        mk_lo = (2 * c4 < kv_left ? 0x0000ffffu : 0u) | (2 * c4 + 1 < kv_left ? 0xffff0000u : 0u);
+        mk_hi = (2 * c4 + 8 < kv_left ? 0x0000ffffu : 0u) | (2 * c4 + 9 < kv_left ? 0xffff0000u : 0u);
+      }
+      const int row = ks * 16 + ((lane >> 3) & 1) * 8 + (lane & 7);
+      if constexpr (KVB == 2) {
+#pragma unroll
+        for (int q2 = 0; q2 < HD / 16; ++q2) {
+          const int ch = q2 * 2 + (lane >> 4);
+          const uint32_t addr = vbase + (uint32_t)(ch >> 3) * (TILE_N * 128) + (uint32_t)row * 128 +
+                                ((uint32_t)((ch & 7) ^ (row & 7)) << 4);
+          uint32_t b0, b1, b2, b3;
+          ldsm_x4_t(b0, b1, b2, b3, addr);
+          mma16816<BF16>(o[2 * q2], pf[ks], b0 & mk_lo, b1 & mk_hi);
+          mma16816<BF16>(o[2 * q2 + 1], pf[ks], b2 & mk_lo, b3 & mk_hi);
+        }
+      } else {
+#pragma unroll
+        for (int q2 = 0; q2 < HD / 32; ++q2) {
+          const int ch = q2 * 2 + (lane >> 4);
+          const uint32_t addr = vbase + (uint32_t)row * RB + ((uint32_t)(ch ^ swz<RB>(row)) << 4);
+          uint32_t x0, x1, x2, x3;
+          ldsm_x4_t(x0, x1, x2, x3, addr);
+          // word = [key 2c: d, d+1 | key 2c+1: d, d+1]  ->  [d: key 2c, 2c+1 | d+1: key 2c, 2c+1]
+          x0 = __byte_perm(x0 & mk_lo, 0, 0x3120);
+          x1 = __byte_perm(x1 & mk_hi, 0, 0x3120);
+          x2 = __byte_perm(x2 & mk_lo, 0, 0x3120);
+          x3 = __byte_perm(x3 & mk_hi, 0, 0x3120);
+          uint32_t e0, o0, e1, o1;
+          e4m3x4_to_f16x4(x0, e0, o0);
+          e4m3x4_to_f16x4(x1, e1, o1);
+          mma16816<false>(o[4 * q2 + 0], pf[ks], e0, e1);  // d = 16*(2*q2)   + 2g
+          mma16816<false>(o[4 * q2 + 1], pf[ks], o0, o1);  // d = 16*(2*q2)   + 2g + 1
+          e4m3x4_to_f16x4(x2, e0, o0);
+          e4m3x4_to_f16x4(x3, e1, o1);
+          mma16816<false>(o[4 * q2 + 2], pf[ks], e0, e1);  // d = 16*(2*q2+1) + 2g
+          mma16816<false>(o[4 * q2 + 3], pf[ks], o0, o1);  // d = 16*(2*q2+1) + 2g + 1
+        }
+      }
+    }
+
+    // ---- this stage has been read: refill it with the tile kAttnStages ahead
+    __syncwarp();
+    if (issued < my_tiles) {
+      fence_proxy_async();
+      issue(stage);
+    }
+
+    // ---- end of this warp's piece of the segment?
+    const bool seg_end = cc.t == cc.nt - 1;
+    if (seg_end || it == my_tiles - 1) {
+      l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+      l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+      l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+      l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+      const bool whole = seg_end && (g - piece_start == cc.nt - 1);
+      const int seg_id = cc.segbase + cc.seg;
+      if (whole) {
+        const float i0 = l0 > 0.f ? vscale / l0 : 0.f;
+        const float i1 = l1 > 0.f ? vscale / l1 : 0.f;
+        const int64_t ob = (int64_t)cc.b * p.o_bs;
+        const int qr = p.qrow0[cc.b];
+        const int j0 = row0 / p.group, j1 = row1 / p.group;
+        const int hq0 = h * p.group + row0 % p.group, hq1 = h * p.group + row1 % p.group;
+        char* out0 = p.out + 2 * (ob + (int64_t)(qr + j0) * p.o_rs + (int64_t)hq0 * p.o_hs);
+        char* out1 = p.out + 2 * (ob + (int64_t)(qr + j1) * p.o_rs + (int64_t)hq1 * p.o_hs);
+        const bool obf = KVB == 2 ? BF16 : (p.q_is_bf16 != 0);
+        if constexpr (KVB == 2) {
+#pragma unroll
+          for (int i = 0; i < NOT; ++i) {
+            const int d = 8 * i + 2 * c4;
+            if (valid0) *reinterpret_cast<uint32_t*>(out0 + 2 * d) = pack2<BF16>(o[i][0] * i0, o[i][1] * i0);
+            if (valid1) *reinterpret_cast<uint32_t*>(out1 + 2 * d) = pack2<BF16>(o[i][2] * i1, o[i][3] * i1);
+          }
+        } else {
+#pragma unroll
+          for (int ch = 0; ch < HD / 16; ++ch) {
+            const int d = 16 * ch + 4 * c4;
+            const float a0 = o[2 * ch][0] * i0, a1 = o[2 * ch + 1][0] * i0, a2 = o[2 * ch][1] * i0, a3 = o[2 * ch + 1][1] * i0;
+            const float b0 = o[2 * ch][2] * i1, b1 = o[2 * ch + 1][2] * i1, b2 = o[2 * ch][3] * i1, b3 = o[2 * ch + 1][3] * i1;
+            if (valid0)
+              *reinterpret_cast<uint2*>(out0 + 2 * d) = obf ? make_uint2(pack2<true>(a0, a1), pack2<true>(a2, a3))
+                                                            : make_uint2(pack2<false>(a0, a1), pack2<false>(a2, a3));
+            if (valid1)
+              *reinterpret_cast<uint2*>(out1 + 2 * d) = obf ? make_uint2(pack2<true>(b0, b1), pack2<true>(b2, b3))
+                                                            : make_uint2(pack2<false>(b0, b1), pack2<false>(b2, b3));
+          }
+        }
+        if (p.lse && c4 == 0) {
+          constexpr float kLn2 = 0.6931471805599453f;
+          if (valid0) p.lse[(int64_t)cc.b * p.lse_bs + (int64_t)hq0 * p.lse_hs + qr + j0] =
+              l0 > 0.f ? m0 * sl2 * kLn2 + logf(l0) : -INFINITY;
+          if (valid1) p.lse[(int64_t)cc.b * p.lse_bs + (int64_t)hq1 * p.lse_hs + qr + j1] =
+              l1 > 0.f ? m1 * sl2 * kLn2 + logf(l1) : -INFINITY;
+        }
+      } else {
+        const int64_t slot = (int64_t)seg_id + w;
+        float* po = p.part_o + slot * (kRowsPerSeg * HD);
+        float* pml = p.part_ml + slot * (kRowsPerSeg * 2);
+        if (c4 == 0) {
+          pml[g8 * 2 + 0] = (m0 == -INFINITY) ? -INFINITY : m0 * sl2;
+          pml[g8 * 2 + 1] = l0;
+          pml[(g8 + 8) * 2 + 0] = (m1 == -INFINITY) ? -INFINITY : m1 * sl2;
+          pml[(g8 + 8) * 2 + 1] = l1;
+        }
+        if constexpr (KVB == 2) {
+#pragma unroll
+          for (int i = 0; i < NOT; ++i) {
+            const int d = 8 * i + 2 * c4;
+            *reinterpret_cast<float2*>(po + g8 * HD + d) = make_float2(o[i][0], o[i][1]);
+            *reinterpret_cast<float2*>(po + (g8 + 8) * HD + d) = make_float2(o[i][2], o[i][3]);
+          }
+        } else {
+#pragma unroll
+          for (int ch = 0; ch < HD / 16; ++ch) {
+            const int d = 16 * ch + 4 * c4;
+            *reinterpret_cast<float4*>(po + g8 * HD + d) =
+                make_float4(o[2 * ch][0], o[2 * ch + 1][0], o[2 * ch][1], o[2 * ch + 1][1]);
+            *reinterpret_cast<float4*>(po + (g8 + 8) * HD + d) =
+                make_float4(o[2 * ch][2], o[2 * ch + 1][2], o[2 * ch][3], o[2 * ch + 1][3]);
+          }
+        }
+      }
+      fresh = true;
+    }
+    if (it + 1 < my_tiles) cursor_advance(p, cc);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Merge: one block per segment.  Segments written directly are skipped,
+// segments without keys are zero-filled, the others combine their partials.
+// ---------------------------------------------------------------------------
+template <int HD>
+__global__ void __launch_bounds__(128) attn_merge_kernel(const AttnParams p) {
+  const int seg = blockIdx.x;
+  const int nseg_total = p.seg_cum[p.batch];
+  if (seg >= nseg_total) return;
+  int lo = 0, hi = p.batch;
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (p.seg_cum[mid] <= seg) lo = mid; else hi = mid;
+  }
+  const int b = lo;
+  const int sq = p.sq[b];
+  const int nmb = (p.group * sq + kRowsPerSeg - 1) / kRowsPerSeg;
+  const int sib = seg - p.seg_cum[b];
+  const int h = sib / nmb, mb = sib - h * nmb;
+  const int nt = p.nt[b];
+  const long long total = p.tile_cum[p.batch];
+  int wf = 0, wl = -1;
+  if (nt > 0) {
+    const long long t0 = p.tile_cum[b] + (long long)sib * nt;
+    const long long t1 = t0 + nt;
+    wf = (int)(((t0 + 1) * p.n_workers - 1) / total);
+    wl = (int)((t1 * p.n_workers - 1) / total);
+    if (wf == wl) return;  // written by the attention kernel itself
+  }
+  const int nrows = p.group * sq;
+  const float vscale = p.vs_vec ? p.vs_vec[h] : p.vs;
+  const int qr = p.qrow0[b];
+  constexpr float kLn2 = 0.6931471805599453f;
+  for (int e = threadIdx.x; e < kRowsPerSeg * HD; e += 128) {
+    const int rl = e / HD, d = e - rl * HD;
+    const int row = mb * kRowsPerSeg + rl;
+    if (row >= nrows) continue;
+    float M = -INFINITY;
+    for (int wi = wf; wi <= wl; ++wi) M = fmaxf(M, p.part_ml[((int64_t)seg + wi) * (kRowsPerSeg * 2) + rl * 2]);
+    float L = 0.f, acc = 0.f;
+    if (M != -INFINITY) {
+      for (int wi = wf; wi <= wl; ++wi) {
+        const int64_t slot = (int64_t)seg + wi;
+        const float mi = p.part_ml[slot * (kRowsPerSeg * 2) + rl * 2];
+        if (mi == -INFINITY) continue;
+        const float wgt = ex2(mi - M);
+        L += wgt * p.part_ml[slot * (kRowsPerSeg * 2) + rl * 2 + 1];
+        acc += wgt * p.part_o[slot * (kRowsPerSeg * HD) + rl * HD + d];
+      }
+    }
+    const float val = L > 0.f ? acc * vscale / L : 0.f;
+    const int j = row / p.group, hq = h * p.group + row % p.group;
+    const int64_t oi = (int64_t)b * p.o_bs + (int64_t)(qr + j) * p.o_rs + (int64_t)hq * p.o_hs + d;
+    if (p.q_is_bf16) reinterpret_cast<__nv_bfloat16*>(p.out)[oi] = __float2bfloat16_rn(val);
+    else reinterpret_cast<__half*>(p.out)[oi] = __float2half_rn(val);
+    if (p.lse && d == 0)
+      p.lse[(int64_t)b * p.lse_bs + (int64_t)hq * p.lse_hs + qr + j] = L > 0.f ? M * kLn2 + logf(L) : -INFINITY;
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+inline EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = [] {
+    void* f = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      f = nullptr;
+    return reinterpret_cast<EncodeTiledFn>(f);
+  }();
+  return fn;
+}
+
+struct TmapKey {
+  const void* base;
+  int64_t page_stride, token_stride, head_stride, n_pages;
+  int32_t page_size, hkv, hd, dtype, device;
+  bool operator==(const TmapKey& o) const {
+    return base == o.base && page_stride == o.page_stride && token_stride == o.token_stride &&
+           head_stride == o.head_stride && n_pages == o.n_pages && page_size == o.page_size &&
+           hkv == o.hkv && hd == o.hd && dtype == o.dtype && device == o.device;
+  }
+};
+struct TmapKeyHash {
+  size_t operator()(const TmapKey& k) const {
+    size_t h = std::hash<const void*>()(k.base);
+    auto mix = [&](uint64_t v) { h ^= v + 0x9e3779b97f4a7c15ull + (h << 6) + (h >> 2); };
+    mix((uint64_t)k.page_stride); mix((uint64_t)k.token_stride); mix((uint64_t)k.head_stride);
+    mix((uint64_t)k.n_pages); mix((uint64_t)k.page_size); mix((uint64_t)k.hkv); mix((uint64_t)k.hd);
+    mix((uint64_t)k.dtype); mix((uint64_t)k.device);
+    return h;
+  }
+};
+
+// One tensor map per pool view: dims (innermost first) D, P, H_kv, n_pages;
+// box = (128 bytes of D, min(P, TILE_N) tokens, 1 head, 1 page), 128-byte swizzle.
+inline int get_pool_tmap(const TmapKey& key, int tile_n, CUtensorMap* out) {
+  static std::mutex mu;
+  static std::unordered_map<TmapKey, CUtensorMap, TmapKeyHash> cache;
+  {
+    std::lock_guard<std::mutex> lk(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) { *out = it->second; return KB200_OK; }
+  }
+  EncodeTiledFn enc = encode_tiled_fn();
+  if (!enc) return fail(KB200_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  const int es = dtype_size(key.dtype);
+  const int row_bytes = key.hd * es;
+  const int rb = row_bytes > 128 ? 128 : row_bytes;
+  const int box_rows = key.page_size < tile_n ? key.page_size : tile_n;
+  cuuint64_t dims[4] = {(cuuint64_t)key.hd, (cuuint64_t)key.page_size, (cuuint64_t)key.hkv, (cuuint64_t)key.n_pages};
+  cuuint64_t strides[3] = {(cuuint64_t)(key.token_stride * es), (cuuint64_t)(key.head_stride * es),
+                           (cuuint64_t)(key.page_stride * es)};
+  cuuint32_t box[4] = {(cuuint32_t)(rb / es), (cuuint32_t)box_rows, 1u, 1u};
+  cuuint32_t estr[4] = {1u, 1u, 1u, 1u};
+  CUtensorMapDataType dt = key.dtype == KB200_DTYPE_E4M3 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                           : key.dtype == KB200_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                           : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  CUtensorMapSwizzle sw = rb == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
+                          : rb == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B;
+  CUtensorMap tm;
+  CUresult r = enc(&tm, dt, 4, const_cast<void*>(key.base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(KB200_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
+  {
+    std::lock_guard<std::mutex> lk(mu);
+    if (cache.size() > 4096) cache.clear();
+    cache.emplace(key, tm);
+  }
+  *out = tm;
+  return KB200_OK;
+}
+
+struct DeviceInfo { int sms = 0; bool smem_set[3][2] = {{false, false}, {false, false}, {false, false}}; };
+inline DeviceInfo& device_info(int dev) {
+  static DeviceInfo info[64];
+  return info[dev & 63];
+}
+
+inline int tile_n_for(int kv_dtype, int head_dim) {
+  return (dtype_size(kv_dtype) == 2 && head_dim == 128) ? 32 : 64;
+}
+
+struct AttnWorkspace {
+  size_t tile_cum, seg_cum, nt, tile0, sq, qrow0, klen, part_ml, part_o, total;
+};
+
+inline int64_t attn_max_segments(int64_t batch, int64_t total_q, int hq, int hkv) {
+  const int group = hq / hkv;
+  // sum over sequences of ceil(group * sq_b / 16) <= group * total_q / 16 + batch
+  return (int64_t)hkv * ((group * total_q + kRowsPerSeg - 1) / kRowsPerSeg + batch);
+}
+
+inline AttnWorkspace attn_workspace_layout(int64_t batch, int64_t total_q, int hq, int hkv, int hd, int n_workers) {
+  auto up = [](size_t x) { return (x + 255) & ~size_t(255); };
+  AttnWorkspace w;
+  size_t off = 0;
+  w.tile_cum = off; off = up(off + sizeof(long long) * (batch + 1));
+  w.seg_cum = off; off = up(off + sizeof(int) * (batch + 1));
+  w.nt = off; off = up(off + sizeof(int) * batch);
+  w.tile0 = off; off = up(off + sizeof(int) * batch);
+  w.sq = off; off = up(off + sizeof(int) * batch);
+  w.qrow0 = off; off = up(off + sizeof(int) * batch);
+  w.klen = off; off = up(off + sizeof(int) * batch);
+  const int64_t slots = attn_max_segments(batch, total_q, hq, hkv) + n_workers;
+  w.part_ml = off; off = up(off + sizeof(float) * slots * kRowsPerSeg * 2);
+  w.part_o = off; off = up(off + sizeof(float) * slots * kRowsPerSeg * hd);
+  w.total = off;
+  return w;
+}
+
+inline int device_sm_count(int dev, int* sms) {
+  DeviceInfo& di = device_info(dev);
+  if (di.sms == 0) {
+    int n = 0;
+    KB200_CUDA_OK(cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev));
+    di.sms = n;
+  }
+  *sms = di.sms;
+  return KB200_OK;
+}
+
+template <int KVB, int HD, bool BF16>
+inline int launch_attn_variant(const CUtensorMap& tmK, const CUtensorMap& tmV, const AttnParams& p, int grid,
+                               int dev, int variant_idx, cudaStream_t stream) {
+  using T = AttnTile<KVB, HD>;
+  auto kern = paged_attn_kernel<KVB, HD, BF16>;
+  DeviceInfo& di = device_info(dev);
+  bool& done = di.smem_set[variant_idx][HD == 128 ? 1 : 0];
+  if (!done) {
+    KB200_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM_BYTES));
+    done = true;
+  }
+  kern<<<grid, kAttnThreads, T::SMEM_BYTES, stream>>>(tmK, tmV, p);
+  KB200_CUDA_OK(cudaGetLastError());
+  return KB200_OK;
+}
+
+inline int launch_paged_attention(const kb200_attn_args* a) {
+  KB200_REQUIRE(a != nullptr, "args is null");
+  KB200_REQUIRE(a->struct_bytes == sizeof(kb200_attn_args), "kb200_attn_args size mismatch: got %u, built with %zu",
+                a->struct_bytes, sizeof(kb200_attn_args));
+  if (a->batch == 0 || a->total_q == 0) return KB200_OK;
+  KB200_REQUIRE(a->batch > 0 && a->batch < (1 << 30), "batch out of range");
+  KB200_REQUIRE(a->q && a->out && a->k_cache && a->v_cache && a->page_table && a->seqused_k, "null pointer argument");
+  KB200_REQUIRE(a->q_dtype == KB200_DTYPE_F16 || a->q_dtype == KB200_DTYPE_BF16, "q must be F16 or BF16");
+  KB200_REQUIRE(a->kv_dtype == KB200_DTYPE_E4M3 || a->kv_dtype == a->q_dtype,
+                "K/V dtype must equal q dtype or be E4M3");
+  if (a->head_dim != 64 && a->head_dim != 128)
+    return fail(KB200_ERR_UNSUPPORTED, "head_dim %d is not supported (64 or 128)", a->head_dim);
+  KB200_REQUIRE(a->n_kv_heads > 0 && a->n_q_heads > 0 && a->n_q_heads % a->n_kv_heads == 0,
+                "n_q_heads must be a positive multiple of n_kv_heads");
+  const int P = a->page_size;
+  if (P <= 0 || P > 256 || (P & (P - 1)) != 0)
+    return fail(KB200_ERR_UNSUPPORTED, "page_size %d is not supported (power of two, at most 256)", P);
+  KB200_REQUIRE(a->seqlen_q > 0 && a->total_q > 0, "seqlen_q and total_q must be positive");
+  KB200_REQUIRE(a->n_pages > 0, "n_pages must be positive");
+  const int es = dtype_size(a->kv_dtype);
+  KB200_REQUIRE(aligned16(a->k_cache) && aligned16(a->v_cache), "K/V pools must be 16-byte aligned");
+  KB200_REQUIRE((a->kv_page_stride * es) % 16 == 0 && (a->kv_token_stride * es) % 16 == 0 &&
+                    (a->kv_head_stride * es) % 16 == 0,
+                "K/V pool strides must be multiples of 16 bytes");
+  KB200_REQUIRE(aligned16(a->q) && aligned16(a->out), "q and out must be 16-byte aligned");
+  KB200_REQUIRE(a->q_row_stride % 8 == 0 && a->q_head_stride % 8 == 0 && a->q_batch_stride % 8 == 0 &&
+                    a->o_row_stride % 8 == 0 && a->o_head_stride % 8 == 0 && a->o_batch_stride % 8 == 0,
+                "q/out strides must be multiples of 8 elements");
+  KB200_REQUIRE(a->softmax_scale > 0.f, "softmax_scale must be positive");
+
+  int sms = 0;
+  if (int rc = device_sm_count(a->device, &sms)) return rc;
+  const int grid = sms;
+  const int n_workers = grid * kAttnWarps;
+  const int group = a->n_q_heads / a->n_kv_heads;
+  const AttnWorkspace wl = attn_workspace_layout(a->batch, a->total_q, a->n_q_heads, a->n_kv_heads, a->head_dim, n_workers);
+  if (!a->workspace || a->workspace_bytes < wl.total)
+    return fail(KB200_ERR_WORKSPACE, "workspace too small: need %zu bytes, got %llu", wl.total,
+                (unsigned long long)a->workspace_bytes);
+  KB200_REQUIRE((reinterpret_cast<uintptr_t>(a->workspace) & 255) == 0, "workspace must be 256-byte aligned");
+
+  const int tile_n = tile_n_for(a->kv_dtype, a->head_dim);
+  TmapKey key{a->k_cache, a->kv_page_stride, a->kv_token_stride, a->kv_head_stride, a->n_pages,
+              P, a->n_kv_heads, a->head_dim, a->kv_dtype, a->device};
+  CUtensorMap tmK, tmV;
+  if (int rc = get_pool_tmap(key, tile_n, &tmK)) return rc;
+  key.base = a->v_cache;
+  if (int rc = get_pool_tmap(key, tile_n, &tmV)) return rc;
+
+  char* ws = static_cast<char*>(a->workspace);
+  AttnParams p;
+  p.q = static_cast<const char*>(a->q);
+  p.out = static_cast<char*>(a->out);
+  p.lse = a->lse;
+  const bool packed = a->cu_seqlens_q != nullptr;
+  p.q_bs = packed ? 0 : a->q_batch_stride;
+  p.q_rs = a->q_row_stride;
+  p.q_hs = a->q_head_stride;
+  p.o_bs = packed ? 0 : a->o_batch_stride;
+  p.o_rs = a->o_row_stride;
+  p.o_hs = a->o_head_stride;
+  p.lse_bs = packed ? 0 : (int64_t)a->n_q_heads * a->seqlen_q;
+  p.lse_hs = packed ? a->total_q : a->seqlen_q;
+  p.page_table = a->page_table;
+  p.pt_rs = a->pt_row_stride;
+  p.seqused_k = a->seqused_k;
+  p.seqused_q = packed ? nullptr : a->seqused_q;
+  p.cu_seqlens_q = a->cu_seqlens_q;
+  p.ks_vec = a->kv_dtype == KB200_DTYPE_E4M3 ? a->k_scale_per_head : nullptr;
+  p.vs_vec = a->kv_dtype == KB200_DTYPE_E4M3 ? a->v_scale_per_head : nullptr;
+  p.ks = a->kv_dtype == KB200_DTYPE_E4M3 ? a->k_scale : 1.f;
+  p.vs = a->kv_dtype == KB200_DTYPE_E4M3 ? a->v_scale : 1.f;
+  p.softmax_scale = a->softmax_scale;
+  p.tile_cum = reinterpret_cast<long long*>(ws + wl.tile_cum);
+  p.seg_cum = reinterpret_cast<int*>(ws + wl.seg_cum);
+  p.nt = reinterpret_cast<int*>(ws + wl.nt);
+  p.tile0 = reinterpret_cast<int*>(ws + wl.tile0);
+  p.sq = reinterpret_cast<int*>(ws + wl.sq);
+  p.qrow0 = reinterpret_cast<int*>(ws + wl.qrow0);
+  p.klen = reinterpret_cast<int*>(ws + wl.klen);
+  p.part_ml = reinterpret_cast<float*>(ws + wl.part_ml);
+  p.part_o = reinterpret_cast<float*>(ws + wl.part_o);
+  p.n_pages = a->n_pages;
+  p.batch = (int)a->batch;
+  p.seqlen_q = a->seqlen_q;
+  p.hq = a->n_q_heads;
+  p.hkv = a->n_kv_heads;
+  p.group = group;
+  p.page_size = P;
+  p.causal = a->causal != 0;
+  p.window_left = a->window_left;
+  p.q_is_bf16 = a->q_dtype == KB200_DTYPE_BF16;
+  p.n_workers = n_workers;
+  p.tile_n = tile_n;
+
+  cudaStream_t stream = static_cast<cudaStream_t>(a->stream);
+  attn_plan_kernel<<<1, 256, 0, stream>>>(p);
+  KB200_CUDA_OK(cudaGetLastError());
+
+  int rc;
+  const bool d128 = a->head_dim == 128;
+  if (a->kv_dtype == KB200_DTYPE_E4M3) {
+    rc = d128 ? launch_attn_variant<1, 128, false>(tmK, tmV, p, grid, a->device, 0, stream)
+              : launch_attn_variant<1, 64, false>(tmK, tmV, p, grid, a->device, 0, stream);
+  } else if (a->kv_dtype == KB200_DTYPE_BF16) {
+    rc = d128 ? launch_attn_variant<2, 128, true>(tmK, tmV, p, grid, a->device, 1, stream)
+              : launch_attn_variant<2, 64, true>(tmK, tmV, p, grid, a->device, 1, stream);
+  } else {
+    rc = d128 ? launch_attn_variant<2, 128, false>(tmK, tmV, p, grid, a->device, 2, stream)
+              : launch_attn_variant<2, 64, false>(tmK, tmV, p, grid, a->device, 2, stream);
+  }
+  if (rc) return rc;
+
+  const int64_t max_seg = packed ? attn_max_segments(a->batch, a->total_q, a->n_q_heads, a->n_kv_heads)
+                                 : a->batch * a->n_kv_heads * ((group * (int64_t)a->seqlen_q + kRowsPerSeg - 1) / kRowsPerSeg);
+  KB200_REQUIRE(max_seg <= 0x7fffffff, "too many segments");
+  if (d128) attn_merge_kernel<128><<<(int)max_seg, 128, 0, stream>>>(p);
+  else attn_merge_kernel<64><<<(int)max_seg, 128, 0, stream>>>(p);
+  KB200_CUDA_OK(cudaGetLastError());
+  return KB200_OK;
+}
+
+}  // namespace kb200

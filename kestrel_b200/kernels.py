@@ -1,0 +1,499 @@
+"""``kestrel_kernels``-compatible runtime object for the paged-KV path.
+
+The reference binds its kernels at import time with
+``from kestrel_kernels import get_runtime`` and then calls
+``get_runtime().cache.reshape_and_cache_flash``,
+``get_runtime().cache.build_paged_kv_metadata`` (``kestrel/kv_cache.py:10-17``) and
+``get_runtime().attention.flash_attn_fwd`` (``kestrel/ops/attention.py:69``,
+``kestrel/models/moondream/text.py:30-31``).  :func:`get_runtime` returns an
+object with exactly those attributes, backed by the sm_100a library through its
+C ABI; :func:`install_as_kestrel_kernels` registers this module under the name
+``kestrel_kernels`` so the reference's own ``kv_cache.py`` / ``ops/attention.py``
+run on it unmodified.
+
+Every function here takes CUDA tensors and enqueues on the current stream of
+the tensors' device.  There is no CPU path: CPU tensors raise.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+import math
+import sys
+from typing import Any, Optional, Sequence
+
+import torch
+
+from . import _native
+
+_TORCH_TO_DTYPE = {
+    torch.float32: _native.DTYPE_F32,
+    torch.float16: _native.DTYPE_F16,
+    torch.bfloat16: _native.DTYPE_BF16,
+    torch.float8_e4m3fn: _native.DTYPE_E4M3,
+    torch.uint8: _native.DTYPE_E4M3,  # the reference passes FP8 pools viewed as uint8
+}
+
+
+def _require_cuda(name: str, t: torch.Tensor) -> int:
+    if not isinstance(t, torch.Tensor) or t.device.type != "cuda":
+        dev = getattr(t, "device", type(t).__name__)
+        raise RuntimeError(
+            f"{name} must be a CUDA tensor (got {dev}); the kestrel_b200 kernels have no CPU fallback"
+        )
+    return t.device.index if t.device.index is not None else torch.cuda.current_device()
+
+
+def _stream(device_index: int) -> int:
+    return torch.cuda.current_stream(device_index).cuda_stream
+
+
+def _cache_view_geometry(name: str, cache: torch.Tensor) -> tuple[int, int, int, int, int, int, int]:
+    """(n_pages, page_size, n_heads, head_dim, page_stride, token_stride, head_stride) of a
+    ``[n_pages, page_size, n_heads, head_dim]`` cache view."""
+    if cache.ndim != 4:
+        raise ValueError(f"{name} must have shape [n_pages, page_size, n_heads, head_dim]")
+    if cache.stride(3) != 1:
+        raise ValueError(f"{name} must be contiguous in head_dim")
+    n_pages, page_size, n_heads, head_dim = cache.shape
+    return (n_pages, page_size, n_heads, head_dim, cache.stride(0), cache.stride(1), cache.stride(2))
+
+
+# ---------------------------------------------------------------------------
+# cache ops
+# ---------------------------------------------------------------------------
+
+def reshape_and_cache_flash(key: torch.Tensor, value: torch.Tensor, key_cache: torch.Tensor,
+                            value_cache: torch.Tensor, slot_mapping: torch.Tensor,
+                            kv_cache_dtype: str, k_scale: torch.Tensor, v_scale: torch.Tensor) -> None:
+    """Append token rows to the paged pools (call shape of ``kestrel/kv_cache.py:222-231``).
+
+    ``key, value [T, H_kv, D]`` (token stride free, heads and D compact);
+    ``key_cache, value_cache`` the ``[n_pages, P, H_kv, D]`` views (uint8 or
+    float8_e4m3fn when ``kv_cache_dtype`` starts with ``"fp8"``);
+    ``slot_mapping int64 [T]``; ``k_scale, v_scale`` fp32 device tensors with 1 or
+    ``H_kv`` elements (used only for FP8).  Rows with a negative slot are skipped.
+    """
+    dev = _require_cuda("key", key)
+    for nm, t in (("value", value), ("key_cache", key_cache), ("value_cache", value_cache),
+                  ("slot_mapping", slot_mapping)):
+        if _require_cuda(nm, t) != dev:
+            raise ValueError(f"{nm} lives on a different device than key")
+    if key.ndim != 3 or value.ndim != 3 or key.shape != value.shape:
+        raise ValueError("key and value must both have shape [num_tokens, n_kv_heads, head_dim]")
+    T, H, D = key.shape
+    for nm, t in (("key", key), ("value", value)):
+        if t.stride(2) != 1 or t.stride(1) != D:
+            raise ValueError(f"{nm} must be compact across heads/head_dim; got stride={t.stride()}")
+    n_pages, P, Hc, Dc, ps, ts, hs = _cache_view_geometry("key_cache", key_cache)
+    if _cache_view_geometry("value_cache", value_cache) != (n_pages, P, Hc, Dc, ps, ts, hs):
+        raise ValueError("key_cache and value_cache must have the same shape and strides")
+    if (Hc, Dc) != (H, D):
+        raise ValueError(f"cache heads/head_dim {(Hc, Dc)} do not match the rows {(H, D)}")
+    if slot_mapping.dtype != torch.int64 or slot_mapping.ndim != 1 or not slot_mapping.is_contiguous():
+        raise ValueError("slot_mapping must be a contiguous 1-D int64 tensor")
+    if slot_mapping.numel() != T:
+        raise RuntimeError("slot_mapping size does not match the number of token rows")
+    if T == 0:
+        return
+    quant = str(kv_cache_dtype).startswith("fp8")
+    if quant:
+        if key_cache.dtype not in (torch.uint8, torch.float8_e4m3fn):
+            raise ValueError("fp8 kv_cache_dtype needs uint8 or float8_e4m3fn caches")
+        cache_dt = _native.DTYPE_E4M3
+        for nm, s in (("k_scale", k_scale), ("v_scale", v_scale)):
+            if s is None or s.dtype != torch.float32 or _require_cuda(nm, s) != dev:
+                raise ValueError(f"{nm} must be an fp32 tensor on the cache device")
+            if s.numel() not in (1, H) or not s.is_contiguous():
+                raise ValueError(f"{nm} must hold 1 or n_kv_heads contiguous values")
+        if k_scale.numel() != v_scale.numel():
+            raise ValueError("k_scale and v_scale must have the same number of elements")
+        n_scales = k_scale.numel()
+        ks_ptr, vs_ptr = k_scale.data_ptr(), v_scale.data_ptr()
+    else:
+        if key_cache.dtype != key.dtype:
+            raise ValueError(f"cache dtype {key_cache.dtype} does not match row dtype {key.dtype}")
+        cache_dt = _TORCH_TO_DTYPE.get(key_cache.dtype)
+        if cache_dt is None or key_cache.dtype in (torch.uint8, torch.float8_e4m3fn):
+            raise ValueError(f"unsupported cache dtype {key_cache.dtype}")
+        n_scales, ks_ptr, vs_ptr = 1, None, None
+    in_dt = _TORCH_TO_DTYPE.get(key.dtype)
+    if in_dt is None or key.dtype in (torch.uint8, torch.float8_e4m3fn) or value.dtype != key.dtype:
+        raise ValueError(f"unsupported row dtype {key.dtype}/{value.dtype}")
+    lib = _native.load()
+    _native.check(lib.kb200_reshape_and_cache_flash(
+        key.data_ptr(), value.data_ptr(), key.stride(0), value.stride(0),
+        key_cache.data_ptr(), value_cache.data_ptr(), ps, ts, hs,
+        slot_mapping.data_ptr(), T, n_pages, P, H, D, in_dt, cache_dt,
+        ks_ptr, vs_ptr, n_scales, dev, _stream(dev)))
+
+
+def build_slot_mapping(page_table: torch.Tensor, batch_idx: torch.Tensor, positions: torch.Tensor,
+                       page_size: int, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``slots = page_table[batch, pos // P] * P + pos % P`` as int64, shaped like ``positions``
+    (one launch for ``kestrel/kv_cache.py:524-551``)."""
+    dev = _require_cuda("page_table", page_table)
+    if _require_cuda("batch_idx", batch_idx) != dev or _require_cuda("positions", positions) != dev:
+        raise ValueError("page_table, batch_idx and positions must live on one device")
+    if page_table.dtype != torch.int32 or page_table.ndim != 2 or page_table.stride(1) != 1:
+        raise ValueError("page_table must be int32 [rows, pages] contiguous in the last dimension")
+    if batch_idx.ndim == 1:
+        if positions.ndim != 2 or positions.shape[0] != batch_idx.shape[0]:
+            raise ValueError("1-D batch_idx needs positions of shape [batch, seq]")
+        per_row, row_len = 1, positions.shape[1]
+    else:
+        if batch_idx.shape != positions.shape:
+            raise ValueError("batch_idx and positions shape mismatch")
+        per_row, row_len = 0, 1
+    for nm, t in (("batch_idx", batch_idx), ("positions", positions)):
+        if t.dtype not in (torch.int32, torch.int64):
+            raise ValueError(f"{nm} must be int32 or int64")
+    batch_idx = batch_idx.contiguous()
+    positions_c = positions.contiguous()
+    if out is None:
+        out = torch.empty(positions.shape, dtype=torch.int64, device=positions.device)
+    elif out.dtype != torch.int64 or out.shape != positions.shape or not out.is_contiguous():
+        raise ValueError("out must be a contiguous int64 tensor shaped like positions")
+    n = positions_c.numel()
+    if n == 0:
+        return out
+    if per_row and row_len == 0:
+        return out
+    lib = _native.load()
+    _native.check(lib.kb200_build_slot_mapping(
+        page_table.data_ptr(), page_table.stride(0), page_table.shape[0], page_table.shape[1],
+        batch_idx.data_ptr(), int(batch_idx.dtype == torch.int64), per_row, row_len,
+        positions_c.data_ptr(), int(positions_c.dtype == torch.int64), out.data_ptr(), n,
+        int(page_size), dev, _stream(dev)))
+    return out
+
+
+def build_paged_kv_metadata(page_table: torch.Tensor, batch_idx: torch.Tensor, input_pos: torch.Tensor,
+                            out_page_table: torch.Tensor, out_seqused_k: torch.Tensor,
+                            page_size: int) -> None:
+    """Decode metadata (call shape of ``kestrel/kv_cache.py:515-522``): ``out_seqused_k = input_pos + 1``
+    and the live prefix of each active page-table row copied into ``out_page_table``."""
+    dev = _require_cuda("page_table", page_table)
+    for nm, t in (("batch_idx", batch_idx), ("input_pos", input_pos), ("out_page_table", out_page_table),
+                  ("out_seqused_k", out_seqused_k)):
+        if _require_cuda(nm, t) != dev:
+            raise ValueError(f"{nm} must live on the page table's device")
+    if page_table.dtype != torch.int32 or out_page_table.dtype != torch.int32:
+        raise ValueError("page tables must be int32")
+    if input_pos.dtype != torch.int32 or out_seqused_k.dtype != torch.int32:
+        raise ValueError("input_pos and out_seqused_k must be int32")
+    if batch_idx.dtype not in (torch.int32, torch.int64):
+        raise ValueError("batch_idx must be int32 or int64")
+    if page_table.ndim != 2 or out_page_table.ndim != 2 or page_table.stride(1) != 1 or out_page_table.stride(1) != 1:
+        raise ValueError("page tables must be 2-D and contiguous in the last dimension")
+    B = batch_idx.shape[0]
+    if input_pos.shape[0] != B or out_page_table.shape[0] < B or out_seqused_k.shape[0] < B:
+        raise ValueError("metadata buffers are smaller than the batch")
+    if B == 0:
+        return
+    batch_idx = batch_idx.contiguous()
+    input_pos = input_pos.contiguous()
+    if not out_seqused_k.is_contiguous():
+        raise ValueError("out_seqused_k must be contiguous")
+    lib = _native.load()
+    _native.check(lib.kb200_build_paged_kv_metadata(
+        page_table.data_ptr(), page_table.stride(0), page_table.shape[0], page_table.shape[1],
+        batch_idx.data_ptr(), int(batch_idx.dtype == torch.int64), input_pos.data_ptr(),
+        out_page_table.data_ptr(), out_page_table.stride(0), out_page_table.shape[1],
+        out_seqused_k.data_ptr(), B, int(page_size), dev, _stream(dev)))
+
+
+def copy_pages(caches: Sequence[torch.Tensor], src_pages, dst_pages) -> None:
+    """Copy-on-write: copy physical page ``src_pages[i]`` onto ``dst_pages[i]`` in every pool of
+    ``caches`` (each ``[n_pages, ...]`` with contiguous pages; all the same geometry) in one launch.
+
+    ``src_pages`` / ``dst_pages`` are int sequences or int32 device tensors; destinations
+    must be distinct and disjoint from the sources.  The reference has no such op.
+    """
+    if len(caches) == 0:
+        return
+    first = caches[0]
+    dev = _require_cuda("caches[0]", first)
+    page_elems = math.prod(first.shape[1:])
+    page_bytes = page_elems * first.element_size()
+    stride_bytes = first.stride(0) * first.element_size()
+    ptrs = (C.c_void_p * len(caches))()
+    for i, c in enumerate(caches):
+        if _require_cuda(f"caches[{i}]", c) != dev:
+            raise ValueError("all pools must live on one device")
+        if c.shape != first.shape or c.stride() != first.stride() or c.dtype != first.dtype:
+            raise ValueError("all pools must share shape, strides and dtype")
+        if not c[0].is_contiguous():
+            raise ValueError("pages of a pool must be contiguous")
+        ptrs[i] = c.data_ptr()
+
+    def as_dev(x, nm):
+        if isinstance(x, torch.Tensor):
+            if x.dtype != torch.int32 or x.ndim != 1 or not x.is_contiguous() or _require_cuda(nm, x) != dev:
+                raise ValueError(f"{nm} must be a contiguous 1-D int32 tensor on the pools' device")
+            return x
+        return torch.tensor(list(x), dtype=torch.int32, device=first.device)
+
+    if not isinstance(src_pages, torch.Tensor) and not isinstance(dst_pages, torch.Tensor):
+        s_l, d_l = [int(v) for v in src_pages], [int(v) for v in dst_pages]
+        if len(s_l) != len(d_l):
+            raise ValueError("src_pages and dst_pages differ in length")
+        if len(set(d_l)) != len(d_l) or set(d_l) & set(s_l):
+            raise ValueError("destination pages must be distinct and disjoint from the sources")
+        n_pages = first.shape[0]
+        if any(p < 0 or p >= n_pages for p in s_l + d_l):
+            raise ValueError("page index out of range")
+        src_pages, dst_pages = s_l, d_l
+    src_t, dst_t = as_dev(src_pages, "src_pages"), as_dev(dst_pages, "dst_pages")
+    if src_t.numel() != dst_t.numel():
+        raise ValueError("src_pages and dst_pages differ in length")
+    if src_t.numel() == 0:
+        return
+    lib = _native.load()
+    _native.check(lib.kb200_copy_pages(ptrs, len(caches), page_bytes, stride_bytes, first.shape[0],
+                                       src_t.data_ptr(), dst_t.data_ptr(), src_t.numel(), dev, _stream(dev)))
+
+
+# ---------------------------------------------------------------------------
+# attention
+# ---------------------------------------------------------------------------
+
+_workspaces: dict[tuple[int, int], torch.Tensor] = {}
+_ws_bytes_cache: dict[tuple, int] = {}
+
+
+def _workspace(dev: int, stream: int, nbytes: int) -> torch.Tensor:
+    key = (dev, stream)
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < nbytes:
+        # grow geometrically so steady-state decode never reallocates
+        size = max(nbytes, 2 * ws.numel() if ws is not None else 0, 1 << 20)
+        ws = torch.empty(size, dtype=torch.uint8, device=torch.device("cuda", dev))
+        _workspaces[key] = ws
+    return ws
+
+
+def reserve_attention_workspace(*, batch: int, total_q: int, n_q_heads: int, n_kv_heads: int,
+                                head_dim: int, device: torch.device | int | None = None) -> int:
+    """Pre-size the scratch buffer of the current stream (call before CUDA-graph capture so that
+    no allocation happens inside it).  Returns the byte count."""
+    dev = torch.cuda.current_device() if device is None else torch.device(device).index if not isinstance(device, int) else device
+    if dev is None:
+        dev = torch.cuda.current_device()
+    n = int(_native.load().kb200_attn_workspace_bytes(batch, total_q, n_q_heads, n_kv_heads, head_dim, dev))
+    _workspace(dev, _stream(dev), n)
+    return n
+
+
+def flash_attn_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *,
+                   page_table: Optional[torch.Tensor] = None,
+                   cu_seqlens_q: Optional[torch.Tensor] = None,
+                   cu_seqlens_k: Optional[torch.Tensor] = None,
+                   seqused_q: Optional[torch.Tensor] = None,
+                   seqused_k: Optional[torch.Tensor] = None,
+                   paged_kv_non_tma: bool = False,
+                   causal: bool = False,
+                   window_size_left: Optional[int] = None,
+                   window_size_right: Optional[int] = None,
+                   softmax_scale: Optional[float] = None,
+                   k_scale: Any = None, v_scale: Any = None,
+                   pack_gqa: Optional[bool] = None,
+                   mask_mod: Any = None, aux_tensors: Any = None,
+                   out: Optional[torch.Tensor] = None,
+                   return_lse: bool = False,
+                   max_seqlen_q: Optional[int] = None):
+    """Paged attention with the call surface the reference uses for ``flash_attn_fwd``
+    (``kestrel/ops/attention.py:69-86``, ``kestrel/models/moondream/text.py:158-185``).
+
+    ``q [B, Sq, H_q, D]`` (or ``[total_q, H_q, D]`` with ``cu_seqlens_q``), fp16/bf16;
+    ``k, v`` the ``[n_pages, P, H_kv, D]`` pool views (q's dtype, or FP8 e4m3 as
+    float8_e4m3fn / uint8); ``page_table int32 [B, >= ceil(L/P)]``; ``seqused_k int32 [B]``.
+    ``k_scale`` / ``v_scale``: python floats (as the reference passes) or fp32 device
+    tensors with ``H_kv`` entries.  ``paged_kv_non_tma`` and ``pack_gqa`` are accepted and
+    ignored (hints to the reference's kernel).  Returns ``(out, lse_or_None)``.
+
+    Not implemented (raise ``NotImplementedError``): dense K/V (``page_table=None``),
+    ``cu_seqlens_k``, ``mask_mod`` / ``aux_tensors``, a non-zero right window.
+    """
+    if page_table is None:
+        raise NotImplementedError("dense (non-paged) attention is outside the paged-KV path")
+    if cu_seqlens_k is not None:
+        raise NotImplementedError("cu_seqlens_k is not supported; pass seqused_k")
+    if mask_mod is not None or aux_tensors is not None:
+        raise NotImplementedError("mask_mod / aux_tensors (prefix-LM prefill masks) are not supported")
+    if seqused_k is None:
+        raise ValueError("paged attention requires seqused_k")
+    if window_size_right not in (None, 0, -1) :
+        raise NotImplementedError("only window_size_right in (None, 0) is supported")
+    dev = _require_cuda("q", q)
+    for nm, t in (("k", k), ("v", v), ("page_table", page_table), ("seqused_k", seqused_k)):
+        if _require_cuda(nm, t) != dev:
+            raise ValueError(f"{nm} must live on q's device")
+    if q.dtype not in (torch.float16, torch.bfloat16):
+        raise RuntimeError(f"paged attention requires fp16/bf16 query, got {q.dtype}")
+    packed = cu_seqlens_q is not None
+    if packed:
+        if q.ndim != 3:
+            raise ValueError("with cu_seqlens_q, q must have shape [total_q, n_heads, head_dim]")
+        total_q, Hq, D = q.shape
+        B = cu_seqlens_q.shape[0] - 1
+        if cu_seqlens_q.dtype != torch.int32 or not cu_seqlens_q.is_contiguous() or _require_cuda("cu_seqlens_q", cu_seqlens_q) != dev:
+            raise ValueError("cu_seqlens_q must be a contiguous int32 tensor on q's device")
+        Sq = int(max_seqlen_q) if max_seqlen_q is not None else total_q
+        q_strides = (0, q.stride(0), q.stride(1))
+    else:
+        if q.ndim != 4:
+            raise ValueError("q must have shape [batch, seqlen_q, n_heads, head_dim]")
+        B, Sq, Hq, D = q.shape
+        total_q = B * Sq
+        q_strides = (q.stride(0), q.stride(1), q.stride(2))
+    if q.stride(-1) != 1:
+        raise ValueError("q must be contiguous in head_dim")
+    n_pages, P, Hkv, Dk, ps, ts, hs = _cache_view_geometry("k", k)
+    if _cache_view_geometry("v", v) != (n_pages, P, Hkv, Dk, ps, ts, hs):
+        raise ValueError("k and v must have the same shape and strides")
+    if Dk != D:
+        raise ValueError(f"head_dim mismatch: q has {D}, K/V have {Dk}")
+    if k.dtype != v.dtype:
+        raise ValueError("k and v must share a dtype")
+    fp8 = k.dtype in (torch.float8_e4m3fn, torch.uint8)
+    if not fp8 and k.dtype != q.dtype:
+        raise ValueError(f"K/V dtype {k.dtype} must equal the query dtype {q.dtype} or be FP8 e4m3")
+    if page_table.dtype != torch.int32 or page_table.ndim != 2 or page_table.stride(1) != 1:
+        raise ValueError("page_table must be int32 [batch, pages], contiguous in the last dimension")
+    if page_table.shape[0] < B:
+        raise ValueError("page_table has fewer rows than the batch")
+    if seqused_k.dtype != torch.int32 or seqused_k.ndim != 1 or seqused_k.shape[0] < B or not seqused_k.is_contiguous():
+        raise ValueError("seqused_k must be a contiguous int32 tensor with one entry per sequence")
+    if seqused_q is not None:
+        if packed:
+            raise ValueError("seqused_q cannot be combined with cu_seqlens_q")
+        if seqused_q.dtype != torch.int32 or seqused_q.shape[0] < B or not seqused_q.is_contiguous() or _require_cuda("seqused_q", seqused_q) != dev:
+            raise ValueError("seqused_q must be a contiguous int32 tensor on q's device")
+    if out is None:
+        out = torch.empty_like(q)
+    elif out.shape != q.shape or out.dtype != q.dtype or out.stride(-1) != 1 or _require_cuda("out", out) != dev:
+        raise ValueError("out must match q in shape, dtype and device")
+    lse = None
+    if return_lse:
+        lse = torch.empty((Hq, total_q) if packed else (B, Hq, Sq), dtype=torch.float32, device=q.device)
+    if B == 0 or total_q == 0:
+        return out, lse
+    o_strides = (0, out.stride(0), out.stride(1)) if packed else (out.stride(0), out.stride(1), out.stride(2))
+
+    ks_f = vs_f = 1.0
+    ks_ptr = vs_ptr = None
+    if fp8:
+        def scale_arg(s, nm):
+            if s is None:
+                return 1.0, None
+            if isinstance(s, torch.Tensor):
+                if s.numel() == 1 and s.device.type != "cuda":
+                    return float(s), None
+                if s.dtype != torch.float32 or not s.is_contiguous() or _require_cuda(nm, s) != dev or s.numel() != Hkv:
+                    raise ValueError(f"{nm} tensor must be contiguous fp32 with n_kv_heads entries on q's device")
+                return 1.0, s.data_ptr()
+            return float(s), None
+        ks_f, ks_ptr = scale_arg(k_scale, "k_scale")
+        vs_f, vs_ptr = scale_arg(v_scale, "v_scale")
+
+    stream = _stream(dev)
+    wkey = (B, total_q, Hq, Hkv, D, dev)
+    nbytes = _ws_bytes_cache.get(wkey)
+    lib = _native.load()
+    if nbytes is None:
+        nbytes = int(lib.kb200_attn_workspace_bytes(B, total_q, Hq, Hkv, D, dev))
+        _ws_bytes_cache[wkey] = nbytes
+    ws = _workspace(dev, stream, nbytes)
+
+    a = _native.AttnArgs()
+    a.struct_bytes = C.sizeof(_native.AttnArgs)
+    a.device = dev
+    a.stream = stream
+    a.q = q.data_ptr()
+    a.out = out.data_ptr()
+    a.lse = lse.data_ptr() if lse is not None else None
+    a.q_batch_stride, a.q_row_stride, a.q_head_stride = q_strides
+    a.o_batch_stride, a.o_row_stride, a.o_head_stride = o_strides
+    a.k_cache = k.data_ptr()
+    a.v_cache = v.data_ptr()
+    a.kv_page_stride, a.kv_token_stride, a.kv_head_stride = ps, ts, hs
+    a.n_pages = n_pages
+    a.page_table = page_table.data_ptr()
+    a.pt_row_stride = page_table.stride(0)
+    a.seqused_k = seqused_k.data_ptr()
+    a.seqused_q = seqused_q.data_ptr() if seqused_q is not None else None
+    a.cu_seqlens_q = cu_seqlens_q.data_ptr() if packed else None
+    a.batch = B
+    a.total_q = total_q
+    a.seqlen_q = Sq
+    a.n_q_heads, a.n_kv_heads, a.head_dim, a.page_size = Hq, Hkv, D, P
+    a.q_dtype = _TORCH_TO_DTYPE[q.dtype]
+    a.kv_dtype = _native.DTYPE_E4M3 if fp8 else _TORCH_TO_DTYPE[k.dtype]
+    a.softmax_scale = float(softmax_scale) if softmax_scale is not None else 1.0 / math.sqrt(D)
+    a.causal = 1 if causal else 0
+    a.window_left = int(window_size_left) if window_size_left is not None and window_size_left >= 0 else -1
+    a.k_scale, a.v_scale = ks_f, vs_f
+    a.k_scale_per_head, a.v_scale_per_head = ks_ptr, vs_ptr
+    a.workspace = ws.data_ptr()
+    a.workspace_bytes = ws.numel()
+    _native.check(lib.kb200_paged_attention(C.byref(a)))
+    return out, lse
+
+
+# ---------------------------------------------------------------------------
+# runtime object
+# ---------------------------------------------------------------------------
+
+class _Unavailable:
+    """Namespace whose every attribute raises: kernels outside the paged-KV path."""
+
+    def __init__(self, name: str) -> None:
+        self._name = name
+
+    def __getattr__(self, item: str):
+        raise NotImplementedError(
+            f"kestrel_kernels.{self._name}.{item} is outside the paged-KV path this library implements"
+        )
+
+
+class _CacheOps:
+    reshape_and_cache_flash = staticmethod(reshape_and_cache_flash)
+    build_paged_kv_metadata = staticmethod(build_paged_kv_metadata)
+    build_slot_mapping = staticmethod(build_slot_mapping)
+    copy_pages = staticmethod(copy_pages)
+
+
+class _AttentionOps:
+    flash_attn_fwd = staticmethod(flash_attn_fwd)
+
+    def __getattr__(self, item: str):
+        raise NotImplementedError(f"kestrel_kernels.attention.{item} is outside the paged-KV path")
+
+
+class Runtime:
+    """What ``kestrel_kernels.get_runtime()`` returns, restricted to the paged-KV path."""
+
+    def __init__(self) -> None:
+        self.cache = _CacheOps()
+        self.attention = _AttentionOps()
+        for name in ("rotary", "linear", "vision", "dense", "tau", "moe", "gated_delta", "sampling",
+                     "megakernel", "generated_decode", "linear_ops"):
+            setattr(self, name, _Unavailable(name))
+
+
+_RUNTIME: Optional[Runtime] = None
+
+
+def get_runtime() -> Runtime:
+    """Load the native library (raising if it is missing) and return the runtime object."""
+    global _RUNTIME
+    if _RUNTIME is None:
+        _native.load()
+        _RUNTIME = Runtime()
+    return _RUNTIME
+
+
+def install_as_kestrel_kernels() -> None:
+    """Register this module as ``kestrel_kernels`` so Kestrel's own modules bind to it."""
+    sys.modules["kestrel_kernels"] = sys.modules[__name__]
