@@ -1,0 +1,631 @@
+"""Benchmark of the paged-KV hot path: append + paged decode attention over a KV stack.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload cfg2|cfg3|cfg4|cfg5] [--impl reference]
+
+One *step* is one decode step of the whole KV stack of the workload: decode metadata and slot
+mapping once, then per layer the append of the new tokens' K/V rows (quantised to FP8 where the
+workload says so) and the paged attention of the new queries over the grown context.  Inputs are
+seeded synthetic tensors with the shapes and value distributions of the named configuration.
+
+Default workload ``cfg3``: FP8 e4m3 KV with per-(layer, KV-head) scales, 24 layers, batch 256,
+contexts U[4096, 32768], 32 query / 8 KV heads, head_dim 128, page size 16, inputs N(0,1) with
+1 % outliers x20.  24 layers of that context need about 232 GB of KV, more than one GPU holds, so
+the stack keeps as many *distinct* layer pools as fit (``config.n_layer_pools``) and layer ``i``
+uses pool ``i mod n``: every layer still streams its whole KV from HBM (a pool is ~10 GB, far
+beyond L2).
+
+With N > 1 (launched by torchrun, one rank per GPU) every rank runs the same workload on its own
+sequences (requests shard by sequence; no collective on the data path); the time is the max over
+ranks and ``value`` is the sum over ranks: weak scaling.
+
+The one JSON line printed by rank 0 carries the whole-job HBM GB/s (``value``), tokens/s, the
+end-to-end number with host buffers (``e2e``), the roofline of the attention kernel, the clocks
+seen during the timed region and a CPU baseline (the oracle timed on the host cores).
+``--impl reference`` times the CPU restatement of the reference's torch path instead.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+NOMINAL_HBM_GBS = 8000.0
+FALLBACK_HBM_GBS = 6650.0
+
+WORKLOADS = {
+    # name: batch, len range, layers, kv dtype, head_dim, seqlen_q, outliers, pool factor
+    "cfg2": dict(batch=64, lo=1024, hi=8192, layers=1, kv="bf16", head_dim=128, sq=1, outliers=0.0, pool=1.25,
+                 desc="bf16, batch 64, ctx U[1024,8192], 1 layer, 32/8 heads, D=128, page 16, pool 1.25x"),
+    "cfg3": dict(batch=256, lo=4096, hi=32768, layers=24, kv="fp8", head_dim=128, sq=1, outliers=0.01, pool=1.02,
+                 desc="FP8 e4m3 KV (per layer+head scales, quantise on append), 24 layers, batch 256, "
+                      "ctx U[4096,32768], 32/8 heads, D=128, page 16, N(0,1)+1% outliers x20"),
+    "cfg4": dict(batch=512, lo=32, hi=256, layers=1, kv="bf16", head_dim=64, sq=1, outliers=0.0, pool=1.25, prefix=729,
+                 desc="bf16, 512 requests sharing a 729-token prefix (COW of the partial page) + suffix U[32,256], "
+                      "decode steps, 32/8 heads, D=64, page 16"),
+    "cfg5": dict(batch=256, lo=2048, hi=16384, layers=24, kv="bf16", head_dim=128, sq=4, outliers=0.0, pool=1.02,
+                 desc="bf16, 24 layers, 256 sequences per GPU, ctx U[2048,16384], 4-token verify + 4-token append, "
+                      "32/8 heads, D=128, page 16"),
+}
+HQ, HKV, PAGE = 32, 8, 16
+
+
+# ----------------------------------------------------------------------------------------------
+# helpers
+# ----------------------------------------------------------------------------------------------
+
+def measured_hbm_peak() -> tuple[float, str]:
+    f = ROOT / "MEASURED_PEAKS.json"
+    if f.exists():
+        try:
+            return float(json.loads(f.read_text())["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.lines: list[str] = []
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.gpu_index)],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except Exception:
+            self.proc = None
+            return
+        def pump():
+            for line in self.proc.stdout:
+                self.lines.append(line.strip())
+        self.thread = threading.Thread(target=pump, daemon=True)
+        self.thread.start()
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            self.proc.kill()
+        sm, mx, power, reasons = [], [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            parts = [p.strip() for p in ln.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                mx.append(float(parts[2]))
+                power.append(float(parts[3]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "power_w_max": max(power),
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def physical_gpu_index(local: int) -> int:
+    vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+    if vis:
+        try:
+            return int(vis.split(",")[local])
+        except Exception:
+            return local
+    return local
+
+
+def algorithmic_bytes(lengths_after: torch.Tensor, *, layers: int, kv_bytes: int, head_dim: int, sq: int,
+                      batch: int) -> dict:
+    """Bytes one step must move, per the formula of the measurement plan: K+V actually attended (tokens,
+    not pages), Q read, O written, compact page table + lengths read, appended rows read (bf16) and
+    written (KV dtype), slot map."""
+    tok = int(lengths_after.sum())
+    kv = tok * 2 * HKV * head_dim * kv_bytes
+    qo = 2 * batch * sq * HQ * head_dim * 2
+    table = int(((lengths_after + PAGE - 1) // PAGE).sum()) * 4 + batch * 4
+    append = batch * sq * 2 * HKV * head_dim * (2 + kv_bytes) + batch * sq * 8
+    per_layer = kv + qo + table + append
+    return {"per_layer": per_layer, "per_step": per_layer * layers, "attn_per_launch": kv + qo + table}
+
+
+# ----------------------------------------------------------------------------------------------
+# GPU workload
+# ----------------------------------------------------------------------------------------------
+
+class GpuWorkload:
+    def __init__(self, name: str, device: torch.device, rank: int, total_steps: int, budget_frac: float = 0.78):
+        from kestrel_b200.kv_cache import KVMemoryPool, PagedKVCache, PageTable, copy_kv_pages
+        from kestrel_b200 import kernels
+
+        self.kernels = kernels
+        self.cfg = cfg = WORKLOADS[name]
+        self.name, self.device = name, device
+        self.B, self.D, self.sq, self.layers_n = cfg["batch"], cfg["head_dim"], cfg["sq"], cfg["layers"]
+        self.kv_dtype = torch.float8_e4m3fn if cfg["kv"] == "fp8" else torch.bfloat16
+        self.kv_bytes = 1 if cfg["kv"] == "fp8" else 2
+        g = torch.Generator().manual_seed(1000 + int(name[3:]) + 7919 * rank)
+        prefix = cfg.get("prefix", 0)
+        suffix = torch.randint(cfg["lo"], cfg["hi"] + 1, (self.B,), generator=g)
+        self.len0 = suffix + prefix                      # context before the first timed/warm-up step
+        grow = total_steps * self.sq + 1
+        final = self.len0 + grow
+        if prefix:
+            shared_pages = prefix // PAGE
+            own_pages = ((final + PAGE - 1) // PAGE - shared_pages)
+            total_pages = int(own_pages.sum()) + shared_pages + 1
+        else:
+            total_pages = int(((final + PAGE - 1) // PAGE).sum())
+        self.n_pages = int(total_pages * cfg["pool"]) + 16
+        per_layer = 2 * self.n_pages * HKV * PAGE * self.D * self.kv_bytes
+        free, _ = torch.cuda.mem_get_info(device)
+        table_bytes = 3 * (self.B + 2) * self.n_pages * 4
+        budget = min(int(free * budget_frac), 150 * 2 ** 30) - table_bytes - (2 << 30)
+        self.n_pools = max(1, min(self.layers_n, budget // per_layer))
+        self.pool = KVMemoryPool(device=device)
+        shared_cache = None
+        if prefix:
+            class _Owner:  # stands in for the radix tree: owns the shared prefix pages
+                page_granular = True
+                _free_pages_sink = None
+                def evict(self, n): return 0
+                def evictable_page_count(self): return 0
+                def reclaimable_page_count(self): return 0
+            shared_cache = _Owner()
+        self.pt = PageTable(n_pages=self.n_pages, page_size=PAGE, max_batch_size=self.B + 2, device=device,
+                            prefix_cache=shared_cache)
+        # pages scattered by a seeded permutation of the free list
+        order = torch.randperm(len(self.pt.free_pages), generator=g).tolist()
+        self.pt.free_pages = [self.pt.free_pages[i] for i in order]
+
+        dg = torch.Generator(device=device).manual_seed(4242 + rank)
+        self.dg = dg
+        self.caches = []
+        scales = None
+        for l in range(self.n_pools):
+            kw = {}
+            if self.kv_dtype == torch.float8_e4m3fn:
+                kw = dict(k_scale=[1.0] * HKV, v_scale=[1.0] * HKV)  # set after the absmax pass
+            self.caches.append(PagedKVCache(self.pt, n_heads=HKV, head_dim=self.D, dtype=self.kv_dtype,
+                                            pool=self.pool, **kw))
+        # rows and pages
+        self.rows = []
+        if prefix:
+            owner = self.pt.allocate()
+            self.pt.reserve(owner, prefix)
+            shared = list(self.pt.page_table_cpu[owner])
+            self.owner_row = owner
+            for b in range(self.B):
+                r = self.pt.allocate() if self.pt.free_batch_idx else None
+                if r is None:
+                    raise RuntimeError("page table has too few rows")
+                self.pt.map_pages(r, 0, shared)
+                if prefix % PAGE:
+                    self.pt.cow_page(r, len(shared) - 1)
+                self.pt.reserve(r, int(final[b]))
+                self.rows.append(r)
+        else:
+            for b in range(self.B):
+                r = self.pt.allocate()
+                self.pt.reserve(r, int(final[b]))
+                self.rows.append(r)
+        self.pt.commit_block_table()
+        self.batch_idx = torch.tensor(self.rows, dtype=torch.int64, device=device)
+        self._fill(prefix, copy_kv_pages)
+        # per-step inputs, resident in HBM (one set per layer so no layer reuses another's rows)
+        self.q = [self._randn(self.B, self.sq, HQ, self.D).to(torch.bfloat16) for _ in range(self.layers_n)]
+        self.k_new = [self._randn(self.B, self.sq, HKV, self.D).to(torch.bfloat16) for _ in range(self.layers_n)]
+        self.v_new = [self._randn(self.B, self.sq, HKV, self.D).to(torch.bfloat16) for _ in range(self.layers_n)]
+        self.out = [torch.empty_like(q) for q in self.q]
+        self.meta_pt = torch.zeros(self.B, self.n_pages, dtype=torch.int32, device=device)
+        self.meta_sk = torch.zeros(self.B, dtype=torch.int32, device=device)
+        self.pos = torch.zeros(self.B, self.sq, dtype=torch.int64, device=device)
+        self.step_no = 0
+        kernels.reserve_attention_workspace(batch=self.B, total_q=self.B * self.sq, n_q_heads=HQ, n_kv_heads=HKV,
+                                            head_dim=self.D, device=device)
+        # host staging for the end-to-end variant
+        self.h_in = [torch.empty(self.B, self.sq, (HQ + 2 * HKV) * self.D, dtype=torch.bfloat16).pin_memory()
+                     for _ in range(self.layers_n)]
+        for h in self.h_in:
+            h.normal_()
+        self.d_in = [torch.empty(self.B, self.sq, (HQ + 2 * HKV) * self.D, dtype=torch.bfloat16, device=device)
+                     for _ in range(2)]
+        self.h_out = torch.empty(self.layers_n, self.B, self.sq, HQ, self.D, dtype=torch.bfloat16).pin_memory()
+        self.h_pos = torch.zeros(self.B, self.sq, dtype=torch.int64).pin_memory()
+        self.attn_events: list[tuple[torch.cuda.Event, torch.cuda.Event]] = []
+        self.launches_per_step = 2 + self.layers_n * 4
+
+    def _randn(self, *shape):
+        x = torch.randn(*shape, generator=self.dg, device=self.device)
+        if self.cfg["outliers"] > 0:
+            m = torch.rand(*shape, generator=self.dg, device=self.device) < self.cfg["outliers"]
+            x = torch.where(m, x * 20.0, x)
+        return x
+
+    def _fill(self, prefix: int, copy_kv_pages) -> None:
+        """Store the initial contexts through the library's own append (quantising where needed)."""
+        dev = self.device
+        chunk_tokens = 1 << 18
+        # flat (row, position) list of every context token
+        if prefix:
+            seqs = [(self.owner_row, 0, prefix)] + [(r, prefix, int(L)) for r, L in zip(self.rows, self.len0.tolist())]
+        else:
+            seqs = [(r, 0, int(L)) for r, L in zip(self.rows, self.len0.tolist())]
+        rows = torch.cat([torch.full((e - s,), r, dtype=torch.int32) for r, s, e in seqs]).to(dev)
+        pos = torch.cat([torch.arange(s, e, dtype=torch.int32) for r, s, e in seqs]).to(dev)
+        slots = self.kernels.build_slot_mapping(self.pt.page_table, rows, pos.view(-1, 1).contiguous().view(-1), PAGE) \
+            if False else self.kernels.build_slot_mapping(self.pt.page_table, rows.view(-1, 1), pos.view(-1, 1), PAGE).view(-1)
+        T = slots.numel()
+        for l, cache in enumerate(self.caches):
+            seeds = [(l * 1000003 + c) for c in range((T + chunk_tokens - 1) // chunk_tokens)]
+            if self.kv_dtype == torch.float8_e4m3fn:
+                kmax = torch.zeros(HKV, device=dev)
+                vmax = torch.zeros(HKV, device=dev)
+                for c, seed in enumerate(seeds):
+                    n = min(chunk_tokens, T - c * chunk_tokens)
+                    self.dg.manual_seed(seed)
+                    k = self._randn(n, HKV, self.D).to(torch.bfloat16)
+                    v = self._randn(n, HKV, self.D).to(torch.bfloat16)
+                    kmax = torch.maximum(kmax, k.float().abs().amax(dim=(0, 2)))
+                    vmax = torch.maximum(vmax, v.float().abs().amax(dim=(0, 2)))
+                cache.k_scale_tensor.copy_(kmax / 448.0)
+                cache.v_scale_tensor.copy_(vmax / 448.0)
+            for c, seed in enumerate(seeds):
+                n = min(chunk_tokens, T - c * chunk_tokens)
+                self.dg.manual_seed(seed)
+                k = self._randn(n, HKV, self.D).to(torch.bfloat16)
+                v = self._randn(n, HKV, self.D).to(torch.bfloat16)
+                sl = slots[c * chunk_tokens: c * chunk_tokens + n]
+                cache.update(sl.view(1, n), k.view(1, n, HKV, self.D), v.view(1, n, HKV, self.D),
+                             slot_mapping=sl.view(1, n))
+            del k, v
+        if prefix and prefix % PAGE:
+            # the prefix was stored in the owner's pages; give every request its copy of the partial page.
+            src, dst = self.pt.take_pending_page_copies()
+            # cow_page ran before the owner's page was filled, so run the queued copies now
+            copy_kv_pages(self.caches, src, dst)
+            self.cow_pairs = len(dst)
+        torch.cuda.synchronize(dev)
+        self.dg.manual_seed(99)
+
+    # ---- one step, inputs resident in HBM
+    def lengths_after(self, step_no: int) -> torch.Tensor:
+        return self.len0 + (step_no + 1) * self.sq
+
+    def step_device(self, record_attn: bool = False) -> None:
+        t = self.step_no
+        base = (self.len0 + t * self.sq).to(self.device, non_blocking=True)
+        self.pos.copy_(base.view(-1, 1) + torch.arange(self.sq, device=self.device).view(1, -1))
+        self._run_layers(self.pos, record_attn, host=False)
+        self.step_no += 1
+
+    # ---- one step through the public API with host buffers
+    def step_e2e(self) -> None:
+        t = self.step_no
+        for b, r in enumerate(self.rows):
+            self.pt.reserve(r, int(self.len0[b]) + (t + 1) * self.sq)
+        self.pt.commit_block_table(self.rows)
+        self.h_pos.copy_((self.len0 + t * self.sq).view(-1, 1) + torch.arange(self.sq).view(1, -1))
+        self.pos.copy_(self.h_pos, non_blocking=True)
+        self._run_layers(self.pos, False, host=True)
+        torch.cuda.current_stream(self.device).synchronize()
+        self.step_no += 1
+
+    def _run_layers(self, pos: torch.Tensor, record_attn: bool, host: bool) -> None:
+        from kestrel_b200.attention import paged_attention
+        slots = self.pt.build_slot_mapping(self.batch_idx, pos)
+        self.pt.populate_paged_kv_metadata(batch_idx=self.batch_idx, input_pos=pos[:, -1].to(torch.int32),
+                                           out_page_table=self.meta_pt, out_seqused_k=self.meta_sk)
+        scale = 1.0 / math.sqrt(self.D)
+        for l in range(self.layers_n):
+            cache = self.caches[l % self.n_pools]
+            if host:
+                d = self.d_in[l & 1]
+                d.copy_(self.h_in[l], non_blocking=True)
+                q, k, v = d.split([HQ * self.D, HKV * self.D, HKV * self.D], dim=-1)
+                q = q.view(self.B, self.sq, HQ, self.D)
+                k = k.view(self.B, self.sq, HKV, self.D)
+                v = v.view(self.B, self.sq, HKV, self.D)
+            else:
+                q, k, v = self.q[l], self.k_new[l], self.v_new[l]
+            cache.update(pos, k, v, slot_mapping=slots)
+            if record_attn:
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+            out, _ = self.kernels.flash_attn_fwd(
+                q, cache.k_cache.permute(0, 2, 1, 3), cache.v_cache.permute(0, 2, 1, 3), page_table=self.meta_pt,
+                seqused_k=self.meta_sk, causal=True, softmax_scale=scale, k_scale=cache.k_scale, v_scale=cache.v_scale,
+                out=self.out[l])
+            if record_attn:
+                e1.record()
+                self.attn_events.append((e0, e1))
+            if host:
+                self.h_out[l].copy_(out, non_blocking=True)
+
+    def e2e_bytes(self) -> tuple[int, int]:
+        h2d = self.layers_n * self.h_in[0].numel() * 2 + self.h_pos.numel() * 8
+        d2h = self.h_out.numel() * 2
+        return h2d, d2h
+
+
+# ----------------------------------------------------------------------------------------------
+# CPU arm: the oracle (a port of the reference's torch path) on a bounded sample of the workload
+# ----------------------------------------------------------------------------------------------
+
+class CpuWorkload:
+    def __init__(self, name: str, sample_batch: int, seed_rank: int = 0):
+        from oracle import paged_kv_oracle as O
+        self.O = O
+        self.cfg = cfg = WORKLOADS[name]
+        self.B = min(sample_batch, cfg["batch"])
+        self.D, self.sq = cfg["head_dim"], cfg["sq"]
+        self.kv_bytes = 1 if cfg["kv"] == "fp8" else 2
+        g = torch.Generator().manual_seed(1000 + int(name[3:]))
+        prefix = cfg.get("prefix", 0)
+        full = torch.randint(cfg["lo"], cfg["hi"] + 1, (cfg["batch"],), generator=g) + prefix
+        self.len0 = full[: self.B]
+        pages = int(((self.len0 + 64 + PAGE - 1) // PAGE).sum()) + 2
+        perm = (torch.randperm(pages - 1, generator=g) + 1).to(torch.int32)
+        width = int(((self.len0 + 64 + PAGE - 1) // PAGE).max())
+        self.table = torch.zeros(self.B + 1, width, dtype=torch.int32)
+        cur = 0
+        for b in range(self.B):
+            n = int((self.len0[b] + 64 + PAGE - 1) // PAGE)
+            self.table[b + 1, :n] = perm[cur:cur + n]
+            cur += n
+        shape = (pages, HKV, PAGE, self.D)
+        if cfg["kv"] == "fp8":
+            self.kc = torch.randint(0, 0x77, shape, generator=g, dtype=torch.uint8)
+            self.vc = torch.randint(0, 0x77, shape, generator=g, dtype=torch.uint8)
+            self.ks = torch.full((HKV,), 0.2)
+            self.vs = torch.full((HKV,), 0.2)
+        else:
+            self.kc = torch.randn(shape, generator=g).to(torch.bfloat16)
+            self.vc = torch.randn(shape, generator=g).to(torch.bfloat16)
+            self.ks = self.vs = None
+        self.q = torch.randn(self.B, self.sq, HQ, self.D, generator=g).to(torch.bfloat16)
+        self.k_new = torch.randn(self.B, self.sq, HKV, self.D, generator=g).to(torch.bfloat16)
+        self.v_new = torch.randn(self.B, self.sq, HKV, self.D, generator=g).to(torch.bfloat16)
+        self.step_no = 0
+
+    def lengths_after(self, step_no: int) -> torch.Tensor:
+        return self.len0 + (step_no % 8 + 1) * self.sq
+
+    def step(self) -> None:
+        """One layer of one step: slot mapping, append, metadata, gather + attention."""
+        t = self.step_no % 8
+        pos = (self.len0 + t * self.sq).view(-1, 1) + torch.arange(self.sq).view(1, -1)
+        self.O.decode_step(self.q.float(), self.k_new, self.v_new, self.kc, self.vc, self.table,
+                           torch.arange(1, self.B + 1), pos, k_scale=self.ks, v_scale=self.vs)
+        self.step_no += 1
+
+
+def time_cpu(name: str, steps: int, warmup: int, target_seconds: float = 12.0) -> dict:
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    cfg = WORKLOADS[name]
+    sample_b = 2 if cfg["hi"] >= 16384 else 4
+    w = CpuWorkload(name, sample_b)
+    for _ in range(max(1, min(warmup, 2))):
+        w.step()
+    t0 = time.perf_counter()
+    w.step()
+    one = time.perf_counter() - t0
+    reps = max(1, min(steps, int(target_seconds / max(one, 1e-3))))
+    times = []
+    byts = []
+    for _ in range(reps):
+        n = w.step_no
+        t0 = time.perf_counter()
+        w.step()
+        times.append(time.perf_counter() - t0)
+        byts.append(algorithmic_bytes(w.lengths_after(n), layers=1, kv_bytes=w.kv_bytes, head_dim=w.D, sq=w.sq,
+                                      batch=w.B)["per_step"])
+    med = statistics.median(times)
+    gbs = statistics.median(byts) / med / 1e9
+    return {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "port",
+            "sample": f"{w.B} of {cfg['batch']} sequences, 1 of {cfg['layers']} layers, {reps} steps "
+                      f"(oracle: torch CPU restatement of the reference path, {cores} threads)",
+            "ms_per_sample_step": med * 1e3, "tokens_per_s": w.B * w.sq / med / cfg["layers"],
+            "steps": reps}
+
+
+# ----------------------------------------------------------------------------------------------
+# main
+# ----------------------------------------------------------------------------------------------
+
+def run_reference_arm(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    res = time_cpu(args.workload, args.steps, args.warmup, target_seconds=25.0)
+    cfg = WORKLOADS[args.workload]
+    line = {
+        "impl": "reference", "metric": "paged append+decode-attn HBM GB/s", "value": res["value"], "unit": "GB/s",
+        "n_gpus": args.gpus, "steps": res["steps"], "warmup": args.warmup, "ms_per_step": res["ms_per_sample_step"],
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": cfg["kv"], "data": "synthetic",
+        "config": {"workload": f"{args.workload}: {cfg['desc']}", "timing": "host wall clock on a bounded sample"},
+        "tokens_per_s": res["tokens_per_s"],
+        "cpu_baseline": {k: res[k] for k in ("value", "unit", "cores", "kind", "sample")},
+        "e2e": {"value": res["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--workload", default="cfg3", choices=sorted(WORKLOADS))
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+        return
+    if args.warmup < 3:
+        args.warmup = 3
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (the kernels have no CPU fallback)")
+    device = torch.device("cuda", local)
+    torch.cuda.set_device(device)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=device)
+
+    from kestrel_b200 import _native
+    _native.load()
+    cfg = WORKLOADS[args.workload]
+    e2e_steps = 0 if args.no_e2e else max(3, min(args.steps, 5))
+    total_steps = 2 * args.warmup + args.steps + e2e_steps + 2
+    wl = GpuWorkload(args.workload, device, rank, total_steps)
+
+    def barrier():
+        torch.cuda.synchronize(device)
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize(device)
+
+    for _ in range(args.warmup):
+        wl.step_device()
+    barrier()
+    sampler = ClockSampler(physical_gpu_index(local))
+    if rank == 0:
+        sampler.start()
+    first_step = wl.step_no
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(args.steps):
+        wl.step_device(record_attn=True)
+    stop.record()
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    elapsed_ms = start.elapsed_time(stop)
+    step_bytes = [algorithmic_bytes(wl.lengths_after(first_step + i), layers=wl.layers_n, kv_bytes=wl.kv_bytes,
+                                    head_dim=wl.D, sq=wl.sq, batch=wl.B) for i in range(args.steps)]
+    total_bytes = sum(b["per_step"] for b in step_bytes)
+    attn_ms = [a.elapsed_time(b) for a, b in wl.attn_events]
+    attn_bytes = sum(b["attn_per_launch"] for b in step_bytes) / len(step_bytes)
+    wl.attn_events.clear()
+
+    # end-to-end: host buffers in, host result out, every step
+    e2e = None
+    if e2e_steps:
+        for _ in range(args.warmup):
+            wl.step_e2e()
+        barrier()
+        first_e2e = wl.step_no
+        t0 = torch.cuda.Event(enable_timing=True)
+        t1 = torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for _ in range(e2e_steps):
+            wl.step_e2e()
+        t1.record()
+        barrier()
+        e2e_ms = t0.elapsed_time(t1)
+        e2e_bytes = sum(algorithmic_bytes(wl.lengths_after(first_e2e + i), layers=wl.layers_n, kv_bytes=wl.kv_bytes,
+                                          head_dim=wl.D, sq=wl.sq, batch=wl.B)["per_step"] for i in range(e2e_steps))
+        e2e = (e2e_ms, e2e_bytes)
+
+    flags = _native.device_status(local, clear=True)
+    if flags[0] != 0:
+        raise SystemExit(f"kernel diagnostics reported a problem: {flags}")
+
+    # aggregate over ranks: max time, summed bytes
+    stats = torch.tensor([elapsed_ms, float(total_bytes), e2e[0] if e2e else 0.0, float(e2e[1]) if e2e else 0.0,
+                          float(statistics.mean(attn_ms)), float(attn_bytes)], dtype=torch.float64, device=device)
+    if dist is not None:
+        mx = stats.clone()
+        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+        sm = stats.clone()
+        dist.all_reduce(sm, op=dist.ReduceOp.SUM)
+        elapsed_ms, total_bytes = mx[0].item(), sm[1].item()
+        e2e_ms_all, e2e_bytes_all = mx[2].item(), sm[3].item()
+    else:
+        e2e_ms_all, e2e_bytes_all = stats[2].item(), stats[3].item()
+    if rank != 0:
+        if dist is not None:
+            dist.destroy_process_group()
+        return
+
+    peak, peak_kind = measured_hbm_peak()
+    value = total_bytes / (elapsed_ms * 1e-3) / 1e9
+    ms_per_step = elapsed_ms / args.steps
+    tok_s = world * wl.B * wl.sq / (ms_per_step * 1e-3)
+    attn_avg_ms = statistics.mean(attn_ms)
+    achieved = attn_bytes / (attn_avg_ms * 1e-3) / 1e9
+    h2d, d2h = wl.e2e_bytes()
+    line = {
+        "metric": "paged append+decode-attn HBM GB/s", "value": value, "unit": "GB/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "fp8_e4m3 KV, bf16 q/out, f16 mma, fp32 softmax"
+        if cfg["kv"] == "fp8" else "bf16", "data": "synthetic",
+        "config": {"workload": f"{args.workload}: {cfg['desc']}", "n_layer_pools": wl.n_pools,
+                   "layers": wl.layers_n, "pool_pages": wl.n_pages, "sequences_per_gpu": wl.B,
+                   "l2_policy": "inputs larger than L2 (every layer streams a multi-GB pool)"
+                   if wl.n_pages * HKV * PAGE * wl.D * wl.kv_bytes * 2 > 256e6 else
+                   "working set near L2 size; see tokens/s rather than GB/s"},
+        "tokens_per_s": tok_s, "pct_of_8TBps": 100.0 * value / world / NOMINAL_HBM_GBS,
+        "pct_of_measured_hbm": 100.0 * value / world / peak,
+        "gpu_launches": wl.launches_per_step * args.steps,
+        "clocks": clocks,
+        "roofline": {"bound": "hbm", "kernel": "paged_attn_kernel (+ its plan and merge launches)",
+                     "achieved": achieved, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
+                     "frac": achieved / peak, "traffic": None,
+                     "launch_ms_avg": attn_avg_ms, "algorithmic_bytes_per_launch": attn_bytes},
+    }
+    if e2e_steps:
+        e2e_val = e2e_bytes_all / (e2e_ms_all * 1e-3) / 1e9
+        line["e2e"] = {"value": e2e_val, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                       "ms_per_step": e2e_ms_all / e2e_steps, "steps": e2e_steps,
+                       "tokens_per_s": world * wl.B * wl.sq / (e2e_ms_all / e2e_steps * 1e-3)}
+    if world == 1 and not args.no_cpu_baseline:
+        cb = time_cpu(args.workload, steps=50, warmup=1)
+        line["cpu_baseline"] = {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")}
+        line["cpu_baseline"]["tokens_per_s"] = cb["tokens_per_s"]
+    print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

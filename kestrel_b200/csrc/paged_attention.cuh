@@ -30,6 +30,7 @@
 //   normalisation.  Softmax is the usual online form in fp32, base 2.
 #pragma once
 
+#include <cstdlib>
 #include <mutex>
 #include <unordered_map>
 #include <string>
@@ -38,20 +39,24 @@
 
 namespace kb200 {
 
-constexpr int kAttnWarps = 4;
 constexpr int kAttnStages = 3;
-constexpr int kAttnThreads = kAttnWarps * 32;
+constexpr int kAttnMaxWarps = 8;
 constexpr int kRowsPerSeg = 16;
+constexpr int kAttnRingBytes = 192 * 1024;  // shared memory given to the K/V rings of one CTA
 
-template <int KVB, int HD>
+// NW worker warps per CTA share the ring: each gets kAttnStages stages of
+// kAttnRingBytes / (NW * kAttnStages) bytes (16 KB with 4 warps, 8 KB with 8).
+template <int KVB, int HD, int NW>
 struct AttnTile {
   static constexpr int ROW_BYTES = HD * KVB;                      // bytes of one token row of one head
   static constexpr int RB = ROW_BYTES > 128 ? 128 : ROW_BYTES;    // swizzled row width in smem
   static constexpr int NH = ROW_BYTES / RB;                       // 128-byte halves per row
-  static constexpr int TILE_N = (KVB == 2 && HD == 128) ? 32 : 64;
+  static constexpr int STAGE_TARGET = kAttnRingBytes / (NW * kAttnStages);
+  static constexpr int TILE_RAW = STAGE_TARGET / (2 * ROW_BYTES);
+  static constexpr int TILE_N = TILE_RAW > 64 ? 64 : TILE_RAW;
   static constexpr int KV_TILE_BYTES = TILE_N * ROW_BYTES;
   static constexpr int STAGE_BYTES = 2 * KV_TILE_BYTES;           // K then V
-  static constexpr int SMEM_BYTES = kAttnWarps * kAttnStages * STAGE_BYTES + kAttnWarps * kAttnStages * 8 + 1024;
+  static constexpr int SMEM_BYTES = NW * kAttnStages * STAGE_BYTES + NW * kAttnStages * 8 + 1024;
 };
 
 struct AttnParams {
@@ -312,11 +317,12 @@ __device__ __forceinline__ uint32_t swz(int row) {
 // The attention kernel.  KVB: bytes per K/V element (2: bf16/f16, 1: e4m3);
 // BF16: operand type of the MMAs (bf16 when K/V are bf16, else f16).
 // ---------------------------------------------------------------------------
-template <int KVB, int HD, bool BF16>
-__global__ void __launch_bounds__(kAttnThreads, 1)
+template <int KVB, int HD, bool BF16, int NW>
+__global__ void __launch_bounds__(NW * 32, 1)
 paged_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                   const __grid_constant__ AttnParams p) {
-  using T = AttnTile<KVB, HD>;
+  using T = AttnTile<KVB, HD, NW>;
+  constexpr int kAttnWarps = NW;
   constexpr int TILE_N = T::TILE_N;
   constexpr int RB = T::RB;
   constexpr int NH = T::NH;
@@ -746,11 +752,17 @@ __global__ void __launch_bounds__(128) attn_merge_kernel(const AttnParams p) {
     const int rl = e / HD, d = e - rl * HD;
     const int row = mb * kRowsPerSeg + rl;
     if (row >= nrows) continue;
+    // A worker between wf and wl whose range is empty (fewer tiles than workers) wrote nothing.
+    auto has_tiles = [&](int wi) {
+      return (long long)wi * total / p.n_workers < (long long)(wi + 1) * total / p.n_workers;
+    };
     float M = -INFINITY;
-    for (int wi = wf; wi <= wl; ++wi) M = fmaxf(M, p.part_ml[((int64_t)seg + wi) * (kRowsPerSeg * 2) + rl * 2]);
+    for (int wi = wf; wi <= wl; ++wi)
+      if (has_tiles(wi)) M = fmaxf(M, p.part_ml[((int64_t)seg + wi) * (kRowsPerSeg * 2) + rl * 2]);
     float L = 0.f, acc = 0.f;
     if (M != -INFINITY) {
       for (int wi = wf; wi <= wl; ++wi) {
+        if (!has_tiles(wi)) continue;
         const int64_t slot = (int64_t)seg + wi;
         const float mi = p.part_ml[slot * (kRowsPerSeg * 2) + rl * 2];
         if (mi == -INFINITY) continue;
@@ -850,14 +862,29 @@ inline int get_pool_tmap(const TmapKey& key, int tile_n, CUtensorMap* out) {
   return KB200_OK;
 }
 
-struct DeviceInfo { int sms = 0; bool smem_set[3][2] = {{false, false}, {false, false}, {false, false}}; };
+struct DeviceInfo { int sms = 0; bool smem_set[3][2][2] = {}; };
 inline DeviceInfo& device_info(int dev) {
   static DeviceInfo info[64];
   return info[dev & 63];
 }
 
-inline int tile_n_for(int kv_dtype, int head_dim) {
-  return (dtype_size(kv_dtype) == 2 && head_dim == 128) ? 32 : 64;
+inline int tile_n_for(int kv_dtype, int head_dim, int nw) {
+  const int raw = kAttnRingBytes / (nw * kAttnStages) / (2 * head_dim * dtype_size(kv_dtype));
+  return raw > 64 ? 64 : raw;
+}
+
+// Worker warps per CTA.  8 warps (two per scheduler, 8 KB stages) beat 4 warps (16 KB stages) on
+// every measured shape: one warp per scheduler cannot hide its own MMA/ALU latencies.
+inline int attn_warps_for(int kv_dtype, int head_dim) {
+  static const int forced = [] {
+    const char* e = getenv("KB200_ATTN_WARPS");
+    const int v = e ? atoi(e) : 0;
+    return (v == 4 || v == 8) ? v : 0;
+  }();
+  if (forced) return forced;
+  (void)head_dim;
+  (void)kv_dtype;
+  return 8;
 }
 
 struct AttnWorkspace {
@@ -899,20 +926,30 @@ inline int device_sm_count(int dev, int* sms) {
   return KB200_OK;
 }
 
-template <int KVB, int HD, bool BF16>
+template <int KVB, int HD, bool BF16, int NW>
 inline int launch_attn_variant(const CUtensorMap& tmK, const CUtensorMap& tmV, const AttnParams& p, int grid,
                                int dev, int variant_idx, cudaStream_t stream) {
-  using T = AttnTile<KVB, HD>;
-  auto kern = paged_attn_kernel<KVB, HD, BF16>;
+  using T = AttnTile<KVB, HD, NW>;
+  auto kern = paged_attn_kernel<KVB, HD, BF16, NW>;
   DeviceInfo& di = device_info(dev);
-  bool& done = di.smem_set[variant_idx][HD == 128 ? 1 : 0];
+  bool& done = di.smem_set[variant_idx][HD == 128 ? 1 : 0][NW == 8 ? 1 : 0];
   if (!done) {
     KB200_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM_BYTES));
     done = true;
   }
-  kern<<<grid, kAttnThreads, T::SMEM_BYTES, stream>>>(tmK, tmV, p);
+  kern<<<grid, NW * 32, T::SMEM_BYTES, stream>>>(tmK, tmV, p);
   KB200_CUDA_OK(cudaGetLastError());
   return KB200_OK;
+}
+
+template <int KVB, bool BF16>
+inline int launch_attn_dispatch(bool d128, int nw, const CUtensorMap& tmK, const CUtensorMap& tmV,
+                                const AttnParams& p, int grid, int dev, int variant_idx, cudaStream_t stream) {
+  if (d128)
+    return nw == 8 ? launch_attn_variant<KVB, 128, BF16, 8>(tmK, tmV, p, grid, dev, variant_idx, stream)
+                   : launch_attn_variant<KVB, 128, BF16, 4>(tmK, tmV, p, grid, dev, variant_idx, stream);
+  return nw == 8 ? launch_attn_variant<KVB, 64, BF16, 8>(tmK, tmV, p, grid, dev, variant_idx, stream)
+                 : launch_attn_variant<KVB, 64, BF16, 4>(tmK, tmV, p, grid, dev, variant_idx, stream);
 }
 
 inline int launch_paged_attention(const kb200_attn_args* a) {
@@ -948,15 +985,25 @@ inline int launch_paged_attention(const kb200_attn_args* a) {
   int sms = 0;
   if (int rc = device_sm_count(a->device, &sms)) return rc;
   const int grid = sms;
-  const int n_workers = grid * kAttnWarps;
+  const int nw = attn_warps_for(a->kv_dtype, a->head_dim);
+  const int n_workers = grid * nw;
   const int group = a->n_q_heads / a->n_kv_heads;
-  const AttnWorkspace wl = attn_workspace_layout(a->batch, a->total_q, a->n_q_heads, a->n_kv_heads, a->head_dim, n_workers);
+  const AttnWorkspace wl = attn_workspace_layout(a->batch, a->total_q, a->n_q_heads, a->n_kv_heads, a->head_dim,
+                                                 grid * kAttnMaxWarps);
   if (!a->workspace || a->workspace_bytes < wl.total)
     return fail(KB200_ERR_WORKSPACE, "workspace too small: need %zu bytes, got %llu", wl.total,
                 (unsigned long long)a->workspace_bytes);
   KB200_REQUIRE((reinterpret_cast<uintptr_t>(a->workspace) & 255) == 0, "workspace must be 256-byte aligned");
 
-  const int tile_n = tile_n_for(a->kv_dtype, a->head_dim);
+  const int tile_n = tile_n_for(a->kv_dtype, a->head_dim, nw);
+  {
+    // every copy lands on a 128-byte boundary of shared memory
+    const int row_bytes = a->head_dim * es;
+    const int rb = row_bytes > 128 ? 128 : row_bytes;
+    const int box_rows = P < tile_n ? P : tile_n;
+    if ((box_rows * rb) % 128 != 0)
+      return fail(KB200_ERR_UNSUPPORTED, "page_size %d with %d-byte rows is not supported", P, row_bytes);
+  }
   TmapKey key{a->k_cache, a->kv_page_stride, a->kv_token_stride, a->kv_head_stride, a->n_pages,
               P, a->n_kv_heads, a->head_dim, a->kv_dtype, a->device};
   CUtensorMap tmK, tmV;
@@ -1016,16 +1063,12 @@ inline int launch_paged_attention(const kb200_attn_args* a) {
 
   int rc;
   const bool d128 = a->head_dim == 128;
-  if (a->kv_dtype == KB200_DTYPE_E4M3) {
-    rc = d128 ? launch_attn_variant<1, 128, false>(tmK, tmV, p, grid, a->device, 0, stream)
-              : launch_attn_variant<1, 64, false>(tmK, tmV, p, grid, a->device, 0, stream);
-  } else if (a->kv_dtype == KB200_DTYPE_BF16) {
-    rc = d128 ? launch_attn_variant<2, 128, true>(tmK, tmV, p, grid, a->device, 1, stream)
-              : launch_attn_variant<2, 64, true>(tmK, tmV, p, grid, a->device, 1, stream);
-  } else {
-    rc = d128 ? launch_attn_variant<2, 128, false>(tmK, tmV, p, grid, a->device, 2, stream)
-              : launch_attn_variant<2, 64, false>(tmK, tmV, p, grid, a->device, 2, stream);
-  }
+  if (a->kv_dtype == KB200_DTYPE_E4M3)
+    rc = launch_attn_dispatch<1, false>(d128, nw, tmK, tmV, p, grid, a->device, 0, stream);
+  else if (a->kv_dtype == KB200_DTYPE_BF16)
+    rc = launch_attn_dispatch<2, true>(d128, nw, tmK, tmV, p, grid, a->device, 1, stream);
+  else
+    rc = launch_attn_dispatch<2, false>(d128, nw, tmK, tmV, p, grid, a->device, 2, stream);
   if (rc) return rc;
 
   const int64_t max_seg = packed ? attn_max_segments(a->batch, a->total_q, a->n_q_heads, a->n_kv_heads)
