@@ -314,6 +314,69 @@ __device__ __forceinline__ uint32_t swz(int row) {
 }
 
 // ---------------------------------------------------------------------------
+// Copy side of a worker warp: walks the warp's tile range ahead of the math,
+// one TMA box per (page, head, K|V, 128-byte half), page indices read one tile
+// before the copy that needs them.
+// ---------------------------------------------------------------------------
+template <typename T, int KVB>
+struct TileProducer {
+  static constexpr int TILE_N = T::TILE_N;
+  static constexpr int RB = T::RB;
+  static constexpr int NH = T::NH;
+  const AttnParams& p;
+  const CUtensorMap* tmK;
+  const CUtensorMap* tmV;
+  uint32_t stage0, bar0;
+  int lane, P, box_rows, nbox, my_tiles, issued, pg;
+  Cursor pc;
+
+  __device__ __forceinline__ TileProducer(const AttnParams& p_, const CUtensorMap* k, const CUtensorMap* v,
+                                          uint32_t stage0_, uint32_t bar0_, int lane_, long long r0, int my_tiles_)
+      : p(p_), tmK(k), tmV(v), stage0(stage0_), bar0(bar0_), lane(lane_), my_tiles(my_tiles_), issued(0) {
+    P = p.page_size;
+    box_rows = P < TILE_N ? P : TILE_N;
+    nbox = (TILE_N / box_rows) * NH * 2;
+    cursor_locate(p, pc, r0);
+    pg = lane < nbox ? page_for(lane) : 0;
+  }
+  __device__ __forceinline__ int page_for(int j) const {
+    const int i = j / (NH * 2);
+    const int key = (pc.tile0 + pc.t) * TILE_N + i * box_rows;
+    if (key >= pc.L) return 0;
+    return p.page_table[(int64_t)pc.b * p.pt_rs + key / P];
+  }
+  __device__ __forceinline__ void issue(int stage) {
+    const uint32_t sbase = stage0 + (uint32_t)stage * T::STAGE_BYTES;
+    const uint32_t bar = bar0 + 8u * stage;
+    const int k0 = (pc.tile0 + pc.t) * TILE_N;
+    const int h = pc.seg / pc.nmb;
+    int nvalid = pc.L - k0;
+    if (nvalid > TILE_N) nvalid = TILE_N;
+    const int nvb = (nvalid + box_rows - 1) / box_rows;
+    if (lane == 0) mbar_expect_tx(bar, (uint32_t)(nvb * box_rows * T::ROW_BYTES * 2));
+    __syncwarp();
+    for (int j = lane; j < nbox; j += 32) {
+      const int i = j / (NH * 2);
+      if (i >= nvb) continue;
+      const int sub = j - i * (NH * 2);
+      const int kv = sub / NH, half = sub - kv * NH;
+      const int key = k0 + i * box_rows;
+      const int page = (j == lane) ? pg : page_for(j);
+      if ((unsigned)page >= (unsigned long long)p.n_pages) report(KB200_STATUS_BAD_PAGE, page, KID_ATTN);
+      const uint32_t dst = sbase + (uint32_t)kv * T::KV_TILE_BYTES + (uint32_t)half * (TILE_N * RB) +
+                           (uint32_t)(i * box_rows) * RB;
+      tma_load_4d(dst, kv ? tmV : tmK, bar, half * (RB / KVB), key % P, h, page);
+    }
+    ++issued;
+    if (issued < my_tiles) {
+      cursor_advance(p, pc);
+      pg = lane < nbox ? page_for(lane) : 0;
+    }
+  }
+  __device__ __forceinline__ bool more() const { return issued < my_tiles; }
+};
+
+// ---------------------------------------------------------------------------
 // The attention kernel.  KVB: bytes per K/V element (2: bf16/f16, 1: e4m3);
 // BF16: operand type of the MMAs (bf16 when K/V are bf16, else f16).
 // ---------------------------------------------------------------------------
@@ -356,53 +419,8 @@ paged_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
   if (r0 >= r1) return;
   const int my_tiles = (int)(r1 - r0);
 
-  const int P = p.page_size;
-  const int box_rows = P < TILE_N ? P : TILE_N;
-  const int boxes_per_tile = TILE_N / box_rows;
-  const int nbox = boxes_per_tile * NH * 2;
-
-  // ---- producer side: cursor of the next tile to copy, page index read one tile ahead
-  Cursor pc;
-  cursor_locate(p, pc, r0);
-  int issued = 0;
-  auto page_for = [&](const Cursor& c, int j) -> int {
-    const int i = j / (NH * 2);
-    const int key = (c.tile0 + c.t) * TILE_N + i * box_rows;
-    if (key >= c.L) return 0;
-    return p.page_table[(int64_t)c.b * p.pt_rs + key / P];
-  };
-  int pg = lane < nbox ? page_for(pc, lane) : 0;
-
-  auto issue = [&](int stage) {
-    const uint32_t sbase = my_stage0 + (uint32_t)stage * T::STAGE_BYTES;
-    const uint32_t bar = bar0 + 8u * stage;
-    const int k0 = (pc.tile0 + pc.t) * TILE_N;
-    const int h = pc.seg / pc.nmb;
-    int nvalid = pc.L - k0;
-    if (nvalid > TILE_N) nvalid = TILE_N;
-    const int nvb = (nvalid + box_rows - 1) / box_rows;
-    if (lane == 0) mbar_expect_tx(bar, (uint32_t)(nvb * box_rows * T::ROW_BYTES * 2));
-    __syncwarp();
-    for (int j = lane; j < nbox; j += 32) {
-      const int i = j / (NH * 2);
-      if (i >= nvb) continue;
-      const int sub = j - i * (NH * 2);
-      const int kv = sub / NH, half = sub - kv * NH;
-      const int key = k0 + i * box_rows;
-      const int page = (j == lane) ? pg : page_for(pc, j);
-      if ((unsigned)page >= (unsigned long long)p.n_pages) report(KB200_STATUS_BAD_PAGE, page, KID_ATTN);
-      const uint32_t dst = sbase + (uint32_t)kv * T::KV_TILE_BYTES + (uint32_t)half * (TILE_N * RB) +
-                           (uint32_t)(i * box_rows) * RB;
-      tma_load_4d(dst, kv ? &tmV : &tmK, bar, half * (RB / KVB), key % P, h, page);
-    }
-    ++issued;
-    if (issued < my_tiles) {
-      cursor_advance(p, pc);
-      pg = lane < nbox ? page_for(pc, lane) : 0;
-    }
-  };
-
-  for (int s = 0; s < kAttnStages && issued < my_tiles; ++s) issue(s);
+  TileProducer<T, KVB> prod(p, &tmK, &tmV, my_stage0, bar0, lane, r0, my_tiles);
+  for (int s = 0; s < kAttnStages && prod.more(); ++s) prod.issue(s);
 
   // ---- consumer side
   Cursor cc;
@@ -629,9 +647,9 @@ paged_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
 
     // ---- this stage has been read: refill it with the tile kAttnStages ahead
     __syncwarp();
-    if (issued < my_tiles) {
+    if (prod.more()) {
       fence_proxy_async();
-      issue(stage);
+      prod.issue(stage);
     }
 
     // ---- end of this warp's piece of the segment?

@@ -106,7 +106,8 @@ def test_decode_fp8_kv(head_dim, per_head, qdtype):
     assert_close(out, want, f"fp8 D={head_dim} per_head={per_head}")
 
 
-@pytest.mark.parametrize("seqlen_q,group,heads_kv", [(4, 4, 8), (2, 4, 2), (4, 8, 2), (1, 1, 8), (3, 16, 1), (1, 6, 2), (16, 1, 2)])
+@pytest.mark.parametrize("seqlen_q,group,heads_kv", [(4, 4, 8), (2, 4, 2), (4, 8, 2), (1, 1, 8), (3, 16, 1), (1, 6, 2), (16, 1, 2),
+                                                      (2, 2, 4), (4, 1, 8), (3, 1, 2), (1, 3, 4)])
 @pytest.mark.parametrize("kv", ["same", "fp8"])
 def test_multi_query_causal_and_gqa_shapes(seqlen_q, group, heads_kv, kv):
     lengths = [1, 3, 4, 5, 16, 17, 40, 64, 65, 333]
@@ -139,11 +140,11 @@ def test_seqused_q_and_non_causal_and_lse():
 
 
 @pytest.mark.parametrize("window", [0, 5, 31, 32, 100, 4000])
-@pytest.mark.parametrize("kv", ["same", "fp8"])
-def test_sliding_window(window, kv):
+@pytest.mark.parametrize("kv,seqlen_q", [("same", 2), ("fp8", 2), ("fp8", 1)])
+def test_sliding_window(window, kv, seqlen_q):
     lengths = [1, 30, 33, 64, 100, 101, 700]
     p = make_paged_problem(seed=11, batch=len(lengths), len_lo=0, len_hi=0, n_q_heads=8, n_kv_heads=2, head_dim=128,
-                           page_size=16, seqlen_q=2, dtype=torch.bfloat16, lengths=lengths)
+                           page_size=16, seqlen_q=seqlen_q, dtype=torch.bfloat16, lengths=lengths)
     out, want = run_case(p, torch.bfloat16, kv=kv, window=window, causal=False,
                          scales=(0.02, 0.02) if kv == "fp8" else None)
     assert_close(out, want, f"window={window}")
