@@ -18,7 +18,7 @@
 //   pool as a 4-D tensor map; a (page, head) tile of K or V is one
 //   cp.async.bulk.tensor box of P rows x 128 bytes (two boxes when a row is
 //   256 bytes), landing in 128-byte-swizzled shared memory so that ldmatrix is
-//   bank-conflict free.  Each warp owns a ring of kAttnStages stages and
+//   bank-conflict free.  Each warp owns a ring of NS stages and
 //   refills a stage as soon as it has read it, so 2 tiles per warp are always
 //   in flight behind the one being computed.  Page indices are read one tile
 //   ahead of the copy that needs them.  No multicast, no cluster.
@@ -31,6 +31,7 @@
 #pragma once
 
 #include <cstdlib>
+#include <type_traits>
 #include <mutex>
 #include <unordered_map>
 #include <string>
@@ -39,24 +40,25 @@
 
 namespace kb200 {
 
-constexpr int kAttnStages = 3;
-constexpr int kAttnMaxWarps = 8;
-constexpr int kRowsPerSeg = 16;
+constexpr int kAttnMaxWarps = 12;
+constexpr int kRowsPerSeg = 16;   // query rows per segment, general kernel (also the stride of scratch slots)
+constexpr int kDecodeRows = 8;    // query rows per segment, decode kernel
 constexpr int kAttnRingBytes = 192 * 1024;  // shared memory given to the K/V rings of one CTA
 
-// NW worker warps per CTA share the ring: each gets kAttnStages stages of
-// kAttnRingBytes / (NW * kAttnStages) bytes (16 KB with 4 warps, 8 KB with 8).
-template <int KVB, int HD, int NW>
+// NW worker warps per CTA share the ring: each gets NS stages of
+// kAttnRingBytes / (NW * NS) bytes (8 KB with 8 warps x 3 stages or 12 warps x 2 stages).
+template <int KVB, int HD, int NW, int NS>
 struct AttnTile {
+  static constexpr int STAGES = NS;
   static constexpr int ROW_BYTES = HD * KVB;                      // bytes of one token row of one head
   static constexpr int RB = ROW_BYTES > 128 ? 128 : ROW_BYTES;    // swizzled row width in smem
   static constexpr int NH = ROW_BYTES / RB;                       // 128-byte halves per row
-  static constexpr int STAGE_TARGET = kAttnRingBytes / (NW * kAttnStages);
+  static constexpr int STAGE_TARGET = kAttnRingBytes / (NW * NS);
   static constexpr int TILE_RAW = STAGE_TARGET / (2 * ROW_BYTES);
   static constexpr int TILE_N = TILE_RAW > 64 ? 64 : TILE_RAW;
   static constexpr int KV_TILE_BYTES = TILE_N * ROW_BYTES;
   static constexpr int STAGE_BYTES = 2 * KV_TILE_BYTES;           // K then V
-  static constexpr int SMEM_BYTES = NW * kAttnStages * STAGE_BYTES + NW * kAttnStages * 8 + 1024;
+  static constexpr int SMEM_BYTES = NW * NS * STAGE_BYTES + NW * NS * 8 + 1024;
 };
 
 struct AttnParams {
@@ -85,6 +87,7 @@ struct AttnParams {
   float* part_o;        // [slots][16][HD] unnormalised
   int64_t n_pages;
   int batch, seqlen_q, hq, hkv, group, page_size, causal, window_left, q_is_bf16, n_workers, tile_n;
+  int rows_per_seg;  // query rows per segment: 16 (general kernel) or 8 (decode kernel)
 };
 
 // ---------------------------------------------------------------------------
@@ -227,7 +230,7 @@ __global__ void __launch_bounds__(256) attn_plan_kernel(const AttnParams p) {
         if (kmin > 0) t0 = kmin / p.tile_n;
       }
       int ntile = (sq > 0 && L > 0) ? (L + p.tile_n - 1) / p.tile_n - t0 : 0;
-      const int nmb = (p.group * sq + kRowsPerSeg - 1) / kRowsPerSeg;
+      const int nmb = (p.group * sq + p.rows_per_seg - 1) / p.rows_per_seg;
       cnt_s = p.hkv * nmb;
       cnt_t = (long long)ntile * cnt_s;
       p.nt[b] = ntile;
@@ -274,7 +277,7 @@ __device__ __forceinline__ void cursor_load_seq(const AttnParams& p, Cursor& c) 
   c.tile0 = p.tile0[c.b];
   c.L = p.klen[c.b];
   c.sq = p.sq[c.b];
-  c.nmb = (p.group * c.sq + kRowsPerSeg - 1) / kRowsPerSeg;
+  c.nmb = (p.group * c.sq + p.rows_per_seg - 1) / p.rows_per_seg;
   c.nseg = p.hkv * c.nmb;
   c.segbase = p.seg_cum[c.b];
 }
@@ -380,11 +383,11 @@ struct TileProducer {
 // The attention kernel.  KVB: bytes per K/V element (2: bf16/f16, 1: e4m3);
 // BF16: operand type of the MMAs (bf16 when K/V are bf16, else f16).
 // ---------------------------------------------------------------------------
-template <int KVB, int HD, bool BF16, int NW>
+template <int KVB, int HD, bool BF16, int NW, int NS>
 __global__ void __launch_bounds__(NW * 32, 1)
 paged_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                   const __grid_constant__ AttnParams p) {
-  using T = AttnTile<KVB, HD, NW>;
+  using T = AttnTile<KVB, HD, NW, NS>;
   constexpr int kAttnWarps = NW;
   constexpr int TILE_N = T::TILE_N;
   constexpr int RB = T::RB;
@@ -399,13 +402,13 @@ paged_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int c4 = lane & 3, g8 = lane >> 2;
-  const uint32_t my_stage0 = smem_base + (uint32_t)(warp * kAttnStages) * T::STAGE_BYTES;
-  const uint32_t bar0 = smem_base + (uint32_t)(kAttnWarps * kAttnStages) * T::STAGE_BYTES +
-                        (uint32_t)(warp * kAttnStages) * 8u;
+  const uint32_t my_stage0 = smem_base + (uint32_t)(warp * NS) * T::STAGE_BYTES;
+  const uint32_t bar0 = smem_base + (uint32_t)(kAttnWarps * NS) * T::STAGE_BYTES +
+                        (uint32_t)(warp * NS) * 8u;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < kAttnWarps * kAttnStages; ++i)
-      mbar_init(smem_base + (uint32_t)(kAttnWarps * kAttnStages) * T::STAGE_BYTES + 8u * i, 1);
+    for (int i = 0; i < kAttnWarps * NS; ++i)
+      mbar_init(smem_base + (uint32_t)(kAttnWarps * NS) * T::STAGE_BYTES + 8u * i, 1);
     fence_barrier_init();
     fence_proxy_async();
   }
@@ -420,7 +423,7 @@ paged_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
   const int my_tiles = (int)(r1 - r0);
 
   TileProducer<T, KVB> prod(p, &tmK, &tmV, my_stage0, bar0, lane, r0, my_tiles);
-  for (int s = 0; s < kAttnStages && prod.more(); ++s) prod.issue(s);
+  for (int s = 0; s < NS && prod.more(); ++s) prod.issue(s);
 
   // ---- consumer side
   Cursor cc;
@@ -492,8 +495,8 @@ paged_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
       }
     }
 
-    const int stage = it % kAttnStages;
-    const uint32_t parity = (uint32_t)(it / kAttnStages) & 1u;
+    const int stage = it % NS;
+    const uint32_t parity = (uint32_t)(it / NS) & 1u;
     if (!mbar_wait_bounded(bar0 + 8u * stage, parity)) {
       if (lane == 0) report(KB200_STATUS_WAIT_TIMEOUT, w, KID_ATTN);
       return;
@@ -598,54 +601,61 @@ paged_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
     }
 
     // ---- O += P V.  Rows of V past the sequence end may hold anything (NaN
-    // bit patterns included), so they are zeroed in the one tile that has them.
-    const bool need_vmask = key0 + TILE_N > cc.L;
+    // bit patterns included), so they are zeroed in the one tile that has them;
+    // every other tile runs the mask-free instantiation.
+    auto pv = [&](auto masked_tag) {
+      constexpr bool MASKED = decltype(masked_tag)::value;
 #pragma unroll
-    for (int ks = 0; ks < NKS; ++ks) {
-      uint32_t mk_lo = 0xffffffffu, mk_hi = 0xffffffffu;
-      if (need_vmask) {
-        const int kv_left = cc.L - (key0 + 16 * ks);  // valid keys in this 16-key block
-        mk_lo = (2 * c4 < kv_left ? 0x0000ffffu : 0u) | (2 * c4 + 1 < kv_left ? 0xffff0000u : 0u);
-        mk_hi = (2 * c4 + 8 < kv_left ? 0x0000ffffu : 0u) | (2 * c4 + 9 < kv_left ? 0xffff0000u : 0u);
-      }
-      const int row = ks * 16 + ((lane >> 3) & 1) * 8 + (lane & 7);
-      if constexpr (KVB == 2) {
-#pragma unroll
-        for (int q2 = 0; q2 < HD / 16; ++q2) {
-          const int ch = q2 * 2 + (lane >> 4);
-          const uint32_t addr = vbase + (uint32_t)(ch >> 3) * (TILE_N * 128) + (uint32_t)row * 128 +
-                                ((uint32_t)((ch & 7) ^ (row & 7)) << 4);
-          uint32_t b0, b1, b2, b3;
-          ldsm_x4_t(b0, b1, b2, b3, addr);
-          mma16816<BF16>(o[2 * q2], pf[ks], b0 & mk_lo, b1 & mk_hi);
-          mma16816<BF16>(o[2 * q2 + 1], pf[ks], b2 & mk_lo, b3 & mk_hi);
+      for (int ks = 0; ks < NKS; ++ks) {
+        uint32_t mk_lo = 0xffffffffu, mk_hi = 0xffffffffu;
+        if constexpr (MASKED) {
+          const int kv_left = cc.L - (key0 + 16 * ks);  // valid keys in this 16-key block
+          mk_lo = (2 * c4 < kv_left ? 0x0000ffffu : 0u) | (2 * c4 + 1 < kv_left ? 0xffff0000u : 0u);
+          mk_hi = (2 * c4 + 8 < kv_left ? 0x0000ffffu : 0u) | (2 * c4 + 9 < kv_left ? 0xffff0000u : 0u);
         }
-      } else {
+        const int row = ks * 16 + ((lane >> 3) & 1) * 8 + (lane & 7);
+        if constexpr (KVB == 2) {
 #pragma unroll
-        for (int q2 = 0; q2 < HD / 32; ++q2) {
-          const int ch = q2 * 2 + (lane >> 4);
-          const uint32_t addr = vbase + (uint32_t)row * RB + ((uint32_t)(ch ^ swz<RB>(row)) << 4);
-          uint32_t x0, x1, x2, x3;
-          ldsm_x4_t(x0, x1, x2, x3, addr);
-          // word = [key 2c: d, d+1 | key 2c+1: d, d+1]  ->  [d: key 2c, 2c+1 | d+1: key 2c, 2c+1]
-          x0 = __byte_perm(x0 & mk_lo, 0, 0x3120);
-          x1 = __byte_perm(x1 & mk_hi, 0, 0x3120);
-          x2 = __byte_perm(x2 & mk_lo, 0, 0x3120);
-          x3 = __byte_perm(x3 & mk_hi, 0, 0x3120);
-          uint32_t e0, o0, e1, o1;
-          e4m3x4_to_f16x4(x0, e0, o0);
-          e4m3x4_to_f16x4(x1, e1, o1);
-          mma16816<false>(o[4 * q2 + 0], pf[ks], e0, e1);  // d = 16*(2*q2)   + 2g
-          mma16816<false>(o[4 * q2 + 1], pf[ks], o0, o1);  // d = 16*(2*q2)   + 2g + 1
-          e4m3x4_to_f16x4(x2, e0, o0);
-          e4m3x4_to_f16x4(x3, e1, o1);
-          mma16816<false>(o[4 * q2 + 2], pf[ks], e0, e1);  // d = 16*(2*q2+1) + 2g
-          mma16816<false>(o[4 * q2 + 3], pf[ks], o0, o1);  // d = 16*(2*q2+1) + 2g + 1
+          for (int q2 = 0; q2 < HD / 16; ++q2) {
+            const int ch = q2 * 2 + (lane >> 4);
+            const uint32_t addr = vbase + (uint32_t)(ch >> 3) * (TILE_N * 128) + (uint32_t)row * 128 +
+                                  ((uint32_t)((ch & 7) ^ (row & 7)) << 4);
+            uint32_t b0, b1, b2, b3;
+            ldsm_x4_t(b0, b1, b2, b3, addr);
+            if constexpr (MASKED) { b0 &= mk_lo; b1 &= mk_hi; b2 &= mk_lo; b3 &= mk_hi; }
+            mma16816<BF16>(o[2 * q2], pf[ks], b0, b1);
+            mma16816<BF16>(o[2 * q2 + 1], pf[ks], b2, b3);
+          }
+        } else {
+#pragma unroll
+          for (int q2 = 0; q2 < HD / 32; ++q2) {
+            const int ch = q2 * 2 + (lane >> 4);
+            const uint32_t addr = vbase + (uint32_t)row * RB + ((uint32_t)(ch ^ swz<RB>(row)) << 4);
+            uint32_t x0, x1, x2, x3;
+            ldsm_x4_t(x0, x1, x2, x3, addr);
+            if constexpr (MASKED) { x0 &= mk_lo; x1 &= mk_hi; x2 &= mk_lo; x3 &= mk_hi; }
+            // word = [key 2c: d, d+1 | key 2c+1: d, d+1]  ->  [d: key 2c, 2c+1 | d+1: key 2c, 2c+1]
+            x0 = __byte_perm(x0, 0, 0x3120);
+            x1 = __byte_perm(x1, 0, 0x3120);
+            x2 = __byte_perm(x2, 0, 0x3120);
+            x3 = __byte_perm(x3, 0, 0x3120);
+            uint32_t e0, o0, e1, o1;
+            e4m3x4_to_f16x4(x0, e0, o0);
+            e4m3x4_to_f16x4(x1, e1, o1);
+            mma16816<false>(o[4 * q2 + 0], pf[ks], e0, e1);  // d = 16*(2*q2)   + 2g
+            mma16816<false>(o[4 * q2 + 1], pf[ks], o0, o1);  // d = 16*(2*q2)   + 2g + 1
+            e4m3x4_to_f16x4(x2, e0, o0);
+            e4m3x4_to_f16x4(x3, e1, o1);
+            mma16816<false>(o[4 * q2 + 2], pf[ks], e0, e1);  // d = 16*(2*q2+1) + 2g
+            mma16816<false>(o[4 * q2 + 3], pf[ks], o0, o1);  // d = 16*(2*q2+1) + 2g + 1
+          }
         }
       }
-    }
+    };
+    if (key0 + TILE_N > cc.L) pv(std::true_type{});
+    else pv(std::false_type{});
 
-    // ---- this stage has been read: refill it with the tile kAttnStages ahead
+    // ---- this stage has been read: refill it with the tile NS ahead
     __syncwarp();
     if (prod.more()) {
       fence_proxy_async();
@@ -734,6 +744,397 @@ paged_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
 }
 
 // ---------------------------------------------------------------------------
+// Decode kernel: segments of at most 8 query rows (GQA group x query positions),
+// computed in the transposed form so that the 16-wide MMA dimension carries keys
+// (for Q K^T) or head_dim (for P V) instead of mostly empty query rows:
+//
+//   S^T[keys x q] = K[keys x d] . Q^T[d x q]        A = K tile (ldmatrix), B = Q^T (registers)
+//   O^T[d x q]   += V^T[d x keys] . P^T[keys x q]   A = V^T (ldmatrix.trans), B = P^T
+//
+// Compared with the general kernel this halves the MMAs per key, halves the
+// accumulator registers (O^T is head_dim x 8) and drops the unused-row math.
+// The softmax weights come out of the first product with keys along the thread's
+// row index; movmatrix.trans turns them into the B fragment of the second.
+// e4m3 K/V are widened to f16 in registers as in the general kernel; the d-order
+// inside each 16-wide slice is permuted consistently between the operands
+// (K: bytes 4c..4c+3 of a 16-byte chunk feed k-slots 2c,2c+1 and 2c+8,2c+9;
+//  V: MMA row g is d = 16*chunk + 2g, row g+8 is d = 16*chunk + 2g + 1).
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t x) {
+  uint32_t y;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(y) : "r"(x));
+  return y;
+}
+template <bool BF16>
+__device__ __forceinline__ void mma16816r(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                          uint32_t b0, uint32_t b1) {
+  if constexpr (BF16) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+  } else {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+  }
+}
+
+template <int KVB, int HD, bool BF16, int NW, int NS>
+__global__ void __launch_bounds__(NW * 32, 1)
+paged_attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+                         const __grid_constant__ AttnParams p) {
+  using T = AttnTile<KVB, HD, NW, NS>;
+  constexpr int TILE_N = T::TILE_N;
+  constexpr int RB = T::RB;
+  constexpr int NMT = TILE_N / 16;  // 16-key blocks per tile
+  constexpr int NDT = HD / 16;      // 16-wide head_dim slices
+  constexpr float kLog2e = 1.4426950408889634f;
+  static_assert(TILE_N % 16 == 0, "tile must hold whole 16-key blocks");
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int c4 = lane & 3, g8 = lane >> 2;
+  const uint32_t my_stage0 = smem_base + (uint32_t)(warp * NS) * T::STAGE_BYTES;
+  const uint32_t bar0 = smem_base + (uint32_t)(NW * NS) * T::STAGE_BYTES + (uint32_t)(warp * NS) * 8u;
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < NW * NS; ++i) mbar_init(smem_base + (uint32_t)(NW * NS) * T::STAGE_BYTES + 8u * i, 1);
+    fence_barrier_init();
+    fence_proxy_async();
+  }
+  __syncthreads();
+  // No block-wide barrier below this line: warps are independent workers.
+
+  const long long total = p.tile_cum[p.batch];
+  const int w = blockIdx.x * NW + warp;
+  const long long r0 = (long long)w * total / p.n_workers;
+  const long long r1 = (long long)(w + 1) * total / p.n_workers;
+  if (r0 >= r1) return;
+  const int my_tiles = (int)(r1 - r0);
+
+  TileProducer<T, KVB> prod(p, &tmK, &tmV, my_stage0, bar0, lane, r0, my_tiles);
+  for (int s = 0; s < NS && prod.more(); ++s) prod.issue(s);
+
+  Cursor cc;
+  cursor_locate(p, cc, r0);
+
+  // lane-constant parts of the ldmatrix addresses
+  const int mi = lane >> 3;                                  // which of the four 8x8 matrices this lane addresses
+  const int k_row = (mi & 1) * 8 + (lane & 7);               // K: matrices (keys lo|hi) x (chunk, chunk+1)
+  const int k_chunk = mi >> 1;
+  const int v_row = KVB == 2 ? (mi >> 1) * 8 + (lane & 7) : (mi & 1) * 8 + (lane & 7);
+  const int v_chunk = KVB == 2 ? (mi & 1) : (mi >> 1);
+
+  uint32_t qb[NDT][2];   // Q^T B fragments: row g8 of the segment, one 16-wide d slice each
+  float o[NDT][4];       // O^T: [d slice][ (d row g, q 2c) (d row g, q 2c+1) (d row g+8, q 2c) (d row g+8, q 2c+1) ]
+  float m0 = 0.f, m1 = 0.f, l0 = 0.f, l1 = 0.f;   // running max / partial sum of query rows 2c and 2c+1
+  float sl2 = 0.f, vscale = 1.f;
+  int lim0 = 0, lim1 = 0, h = 0, mb = 0;
+  bool fresh = true;
+  long long piece_start = r0;
+
+  for (int it = 0; it < my_tiles; ++it) {
+    const long long g = r0 + it;
+    if (fresh) {
+      fresh = false;
+      piece_start = g;
+      mb = cc.seg % cc.nmb;
+      h = cc.seg / cc.nmb;
+      const int nrows = p.group * cc.sq;
+      const bool upper = p.causal || p.window_left >= 0;
+      const int q0 = mb * kDecodeRows + 2 * c4, q1 = q0 + 1;   // rows this thread accumulates
+      lim0 = upper ? cc.L - cc.sq + q0 / p.group : cc.L - 1;
+      lim1 = upper ? cc.L - cc.sq + q1 / p.group : cc.L - 1;
+      const float ksc = p.ks_vec ? p.ks_vec[h] : p.ks;
+      vscale = p.vs_vec ? p.vs_vec[h] : p.vs;
+      sl2 = p.softmax_scale * ksc * kLog2e;
+      m0 = m1 = -INFINITY;
+      l0 = l1 = 0.f;
+#pragma unroll
+      for (int i = 0; i < NDT; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+      // B fragments of Q^T: this thread supplies row (mb*8 + g8)
+      const int qr = mb * kDecodeRows + g8;
+      const bool qvalid = qr < nrows;
+      const char* qrow = p.q + 2 * ((int64_t)cc.b * p.q_bs + (int64_t)(p.qrow0[cc.b] + qr / p.group) * p.q_rs +
+                                    (int64_t)(h * p.group + qr % p.group) * p.q_hs);
+      if constexpr (KVB == 2) {
+#pragma unroll
+        for (int ks = 0; ks < NDT; ++ks) {
+          const int d = 16 * ks + 2 * c4;
+          qb[ks][0] = qvalid ? *reinterpret_cast<const uint32_t*>(qrow + 2 * d) : 0u;
+          qb[ks][1] = qvalid ? *reinterpret_cast<const uint32_t*>(qrow + 2 * (d + 8)) : 0u;
+        }
+      } else {
+#pragma unroll
+        for (int ch = 0; ch < NDT; ++ch) {
+          const int d = 16 * ch + 4 * c4;
+          uint2 a = qvalid ? *reinterpret_cast<const uint2*>(qrow + 2 * d) : make_uint2(0u, 0u);
+          if (p.q_is_bf16) {
+            a.x = pack2<false>(bf16_bits_to_float(a.x & 0xffffu), bf16_bits_to_float(a.x >> 16));
+            a.y = pack2<false>(bf16_bits_to_float(a.y & 0xffffu), bf16_bits_to_float(a.y >> 16));
+          }
+          qb[ch][0] = a.x;
+          qb[ch][1] = a.y;
+        }
+      }
+    }
+
+    const int stage = it % NS;
+    const uint32_t parity = (uint32_t)(it / NS) & 1u;
+    if (!mbar_wait_bounded(bar0 + 8u * stage, parity)) {
+      if (lane == 0) report(KB200_STATUS_WAIT_TIMEOUT, w, KID_ATTN);
+      return;
+    }
+    const uint32_t kbase = my_stage0 + (uint32_t)stage * T::STAGE_BYTES;
+    const uint32_t vbase = kbase + T::KV_TILE_BYTES;
+    const int key0 = (cc.tile0 + cc.t) * TILE_N;
+
+    // ---- S^T = K Q^T.  Two accumulator sets (even / odd d slices) keep dependent MMAs apart.
+    float s[NMT][4], s2[NMT][4];
+#pragma unroll
+    for (int mt = 0; mt < NMT; ++mt) {
+      s[mt][0] = s[mt][1] = s[mt][2] = s[mt][3] = 0.f;
+      s2[mt][0] = s2[mt][1] = s2[mt][2] = s2[mt][3] = 0.f;
+    }
+    if constexpr (KVB == 2) {
+#pragma unroll
+      for (int ks = 0; ks < NDT; ++ks) {
+#pragma unroll
+        for (int mt = 0; mt < NMT; ++mt) {
+          const int r = mt * 16 + k_row;
+          const int ch = 2 * ks + k_chunk;
+          const uint32_t addr = kbase + (uint32_t)(ch >> 3) * (TILE_N * 128) + (uint32_t)r * 128 +
+                                ((uint32_t)((ch & 7) ^ (r & 7)) << 4);
+          uint32_t a0, a1, a2, a3;
+          ldsm_x4(a0, a1, a2, a3, addr);
+          if (ks & 1) mma16816r<BF16>(s2[mt], a0, a1, a2, a3, qb[ks][0], qb[ks][1]);
+          else mma16816r<BF16>(s[mt], a0, a1, a2, a3, qb[ks][0], qb[ks][1]);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int cp = 0; cp < NDT / 2; ++cp) {
+#pragma unroll
+        for (int mt = 0; mt < NMT; ++mt) {
+          const int r = mt * 16 + k_row;
+          const int ch = 2 * cp + k_chunk;
+          const uint32_t addr = kbase + (uint32_t)r * RB + ((uint32_t)(ch ^ swz<RB>(r)) << 4);
+          uint32_t x0, x1, x2, x3;  // (keys lo, ch) (keys hi, ch) (keys lo, ch+1) (keys hi, ch+1)
+          ldsm_x4(x0, x1, x2, x3, addr);
+          uint32_t a0, a1, a2, a3;
+          e4m3x4_to_f16x4(x0, a0, a2);
+          e4m3x4_to_f16x4(x1, a1, a3);
+          mma16816r<false>(s[mt], a0, a1, a2, a3, qb[2 * cp][0], qb[2 * cp][1]);
+          e4m3x4_to_f16x4(x2, a0, a2);
+          e4m3x4_to_f16x4(x3, a1, a3);
+          mma16816r<false>(s2[mt], a0, a1, a2, a3, qb[2 * cp + 1][0], qb[2 * cp + 1][1]);
+        }
+      }
+    }
+#pragma unroll
+    for (int mt = 0; mt < NMT; ++mt) {
+      s[mt][0] += s2[mt][0]; s[mt][1] += s2[mt][1]; s[mt][2] += s2[mt][2]; s[mt][3] += s2[mt][3];
+    }
+    // s[mt] = { (key 16mt+g, q 2c), (key 16mt+g, q 2c+1), (key 16mt+g+8, q 2c), (key 16mt+g+8, q 2c+1) }
+
+    // ---- mask (only tiles that touch a boundary)
+    const int key_last = key0 + TILE_N - 1;
+    const int min_lim = (p.causal || p.window_left >= 0) ? cc.L - cc.sq : cc.L - 1;
+    if (key_last > min_lim || (p.window_left >= 0 && key0 < cc.L - 1 - p.window_left)) {
+      const int lo0 = p.window_left >= 0 ? lim0 - p.window_left : 0;
+      const int lo1 = p.window_left >= 0 ? lim1 - p.window_left : 0;
+#pragma unroll
+      for (int mt = 0; mt < NMT; ++mt) {
+        const int ka = key0 + mt * 16 + g8, kb = ka + 8;
+        if (ka > lim0 || ka < lo0) s[mt][0] = -INFINITY;
+        if (ka > lim1 || ka < lo1) s[mt][1] = -INFINITY;
+        if (kb > lim0 || kb < lo0) s[mt][2] = -INFINITY;
+        if (kb > lim1 || kb < lo1) s[mt][3] = -INFINITY;
+      }
+    }
+
+    // ---- online softmax over keys: keys run along g8 (and the m-tiles), so the row max
+    // needs a reduction over lane bits 2..4
+    float t0 = -INFINITY, t1 = -INFINITY;
+#pragma unroll
+    for (int mt = 0; mt < NMT; ++mt) {
+      t0 = fmaxf(t0, fmaxf(s[mt][0], s[mt][2]));
+      t1 = fmaxf(t1, fmaxf(s[mt][1], s[mt][3]));
+    }
+#pragma unroll
+    for (int d = 4; d < 32; d <<= 1) {
+      t0 = fmaxf(t0, __shfl_xor_sync(0xffffffffu, t0, d));
+      t1 = fmaxf(t1, __shfl_xor_sync(0xffffffffu, t1, d));
+    }
+    const float mn0 = fmaxf(m0, t0), mn1 = fmaxf(m1, t1);
+    if (__any_sync(0xffffffffu, mn0 > m0 || mn1 > m1)) {
+      const float c0 = (m0 == -INFINITY) ? 0.f : ex2((m0 - mn0) * sl2);
+      const float c1 = (m1 == -INFINITY) ? 0.f : ex2((m1 - mn1) * sl2);
+      l0 *= c0;
+      l1 *= c1;
+#pragma unroll
+      for (int i = 0; i < NDT; ++i) {
+        o[i][0] *= c0; o[i][1] *= c1; o[i][2] *= c0; o[i][3] *= c1;
+      }
+      m0 = mn0;
+      m1 = mn1;
+    }
+    const float ms0 = (m0 == -INFINITY) ? 0.f : m0 * sl2;
+    const float ms1 = (m1 == -INFINITY) ? 0.f : m1 * sl2;
+    uint32_t pb[NMT][2];  // P^T B fragments per 16-key block
+#pragma unroll
+    for (int mt = 0; mt < NMT; ++mt) {
+      const float p0 = ex2(fmaf(s[mt][0], sl2, -ms0));
+      const float p1 = ex2(fmaf(s[mt][1], sl2, -ms1));
+      const float p2 = ex2(fmaf(s[mt][2], sl2, -ms0));
+      const float p3 = ex2(fmaf(s[mt][3], sl2, -ms1));
+      l0 += p0 + p2;
+      l1 += p1 + p3;
+      pb[mt][0] = movmatrix_trans(pack2<BF16>(p0, p1));  // (keys 16mt+2c, +1 ; q g)
+      pb[mt][1] = movmatrix_trans(pack2<BF16>(p2, p3));  // (keys 16mt+8+2c, +1 ; q g)
+    }
+
+    // ---- O^T += V^T P^T.  Rows of V past the sequence end may hold anything (NaN bit
+    // patterns included): they are zeroed in the one tile that has them.
+    auto pv = [&](auto masked_tag) {
+      constexpr bool MASKED = decltype(masked_tag)::value;
+#pragma unroll
+      for (int mt = 0; mt < NMT; ++mt) {
+        uint32_t mk_lo = 0xffffffffu, mk_hi = 0xffffffffu;
+        if constexpr (MASKED) {
+          const int kv_left = cc.L - (key0 + 16 * mt);
+          mk_lo = (2 * c4 < kv_left ? 0x0000ffffu : 0u) | (2 * c4 + 1 < kv_left ? 0xffff0000u : 0u);
+          mk_hi = (2 * c4 + 8 < kv_left ? 0x0000ffffu : 0u) | (2 * c4 + 9 < kv_left ? 0xffff0000u : 0u);
+        }
+        const int row = mt * 16 + v_row;
+        if constexpr (KVB == 2) {
+#pragma unroll
+          for (int dt = 0; dt < NDT; ++dt) {
+            const int ch = 2 * dt + v_chunk;
+            const uint32_t addr = vbase + (uint32_t)(ch >> 3) * (TILE_N * 128) + (uint32_t)row * 128 +
+                                  ((uint32_t)((ch & 7) ^ (row & 7)) << 4);
+            uint32_t a0, a1, a2, a3;  // (keys lo, d lo) (keys lo, d hi) (keys hi, d lo) (keys hi, d hi)
+            ldsm_x4_t(a0, a1, a2, a3, addr);
+            if constexpr (MASKED) { a0 &= mk_lo; a1 &= mk_lo; a2 &= mk_hi; a3 &= mk_hi; }
+            mma16816r<BF16>(o[dt], a0, a1, a2, a3, pb[mt][0], pb[mt][1]);
+          }
+        } else {
+#pragma unroll
+          for (int cp = 0; cp < NDT / 2; ++cp) {
+            const int ch = 2 * cp + v_chunk;
+            const uint32_t addr = vbase + (uint32_t)row * RB + ((uint32_t)(ch ^ swz<RB>(row)) << 4);
+            uint32_t x0, x1, x2, x3;  // (keys lo, ch) (keys hi, ch) (keys lo, ch+1) (keys hi, ch+1)
+            ldsm_x4_t(x0, x1, x2, x3, addr);
+            if constexpr (MASKED) { x0 &= mk_lo; x1 &= mk_hi; x2 &= mk_lo; x3 &= mk_hi; }
+            // word = [key 2c: d, d+1 | key 2c+1: d, d+1]  ->  [d: key 2c, 2c+1 | d+1: key 2c, 2c+1]
+            x0 = __byte_perm(x0, 0, 0x3120);
+            x1 = __byte_perm(x1, 0, 0x3120);
+            x2 = __byte_perm(x2, 0, 0x3120);
+            x3 = __byte_perm(x3, 0, 0x3120);
+            uint32_t a0, a1, a2, a3;
+            e4m3x4_to_f16x4(x0, a0, a1);  // row g: d = 16ch + 2g ; row g+8: d = 16ch + 2g + 1 (keys lo)
+            e4m3x4_to_f16x4(x1, a2, a3);  // same rows, keys hi
+            mma16816r<false>(o[2 * cp], a0, a1, a2, a3, pb[mt][0], pb[mt][1]);
+            e4m3x4_to_f16x4(x2, a0, a1);
+            e4m3x4_to_f16x4(x3, a2, a3);
+            mma16816r<false>(o[2 * cp + 1], a0, a1, a2, a3, pb[mt][0], pb[mt][1]);
+          }
+        }
+      }
+    };
+    if (key0 + TILE_N > cc.L) pv(std::true_type{});
+    else pv(std::false_type{});
+
+    // ---- this stage has been read: refill it with the tile NS ahead
+    __syncwarp();
+    if (prod.more()) {
+      fence_proxy_async();
+      prod.issue(stage);
+    }
+
+    // ---- end of this warp's piece of the segment?
+    const bool seg_end = cc.t == cc.nt - 1;
+    if (seg_end || it == my_tiles - 1) {
+#pragma unroll
+      for (int d = 4; d < 32; d <<= 1) {
+        l0 += __shfl_xor_sync(0xffffffffu, l0, d);
+        l1 += __shfl_xor_sync(0xffffffffu, l1, d);
+      }
+      const bool whole = seg_end && (g - piece_start == cc.nt - 1);
+      const int nrows = p.group * cc.sq;
+      const int q0 = mb * kDecodeRows + 2 * c4, q1 = q0 + 1;
+      const bool v0 = q0 < nrows, v1 = q1 < nrows;
+      // element (slice i, half e) of this thread is d = dbase(i) + e * dstep
+      constexpr int dstep = KVB == 2 ? 8 : 1;
+      if (whole) {
+        const float i0 = l0 > 0.f ? vscale / l0 : 0.f;
+        const float i1 = l1 > 0.f ? vscale / l1 : 0.f;
+        const int qrow_base = p.qrow0[cc.b];
+        const int hq0 = h * p.group + q0 % p.group, hq1 = h * p.group + q1 % p.group;
+        const int64_t ob = (int64_t)cc.b * p.o_bs;
+        char* out0 = p.out + 2 * (ob + (int64_t)(qrow_base + q0 / p.group) * p.o_rs + (int64_t)hq0 * p.o_hs);
+        char* out1 = p.out + 2 * (ob + (int64_t)(qrow_base + q1 / p.group) * p.o_rs + (int64_t)hq1 * p.o_hs);
+        const bool obf = KVB == 2 ? BF16 : (p.q_is_bf16 != 0);
+#pragma unroll
+        for (int i = 0; i < NDT; ++i) {
+          const int d = KVB == 2 ? 16 * i + g8 : 16 * i + 2 * g8;
+          if constexpr (KVB == 2) {
+            if (v0) {
+              *reinterpret_cast<uint16_t*>(out0 + 2 * d) = (uint16_t)(pack2<BF16>(o[i][0] * i0, 0.f) & 0xffffu);
+              *reinterpret_cast<uint16_t*>(out0 + 2 * (d + dstep)) = (uint16_t)(pack2<BF16>(o[i][2] * i0, 0.f) & 0xffffu);
+            }
+            if (v1) {
+              *reinterpret_cast<uint16_t*>(out1 + 2 * d) = (uint16_t)(pack2<BF16>(o[i][1] * i1, 0.f) & 0xffffu);
+              *reinterpret_cast<uint16_t*>(out1 + 2 * (d + dstep)) = (uint16_t)(pack2<BF16>(o[i][3] * i1, 0.f) & 0xffffu);
+            }
+          } else {
+            if (v0) *reinterpret_cast<uint32_t*>(out0 + 2 * d) =
+                obf ? pack2<true>(o[i][0] * i0, o[i][2] * i0) : pack2<false>(o[i][0] * i0, o[i][2] * i0);
+            if (v1) *reinterpret_cast<uint32_t*>(out1 + 2 * d) =
+                obf ? pack2<true>(o[i][1] * i1, o[i][3] * i1) : pack2<false>(o[i][1] * i1, o[i][3] * i1);
+          }
+        }
+        if (p.lse && g8 == 0) {
+          constexpr float kLn2 = 0.6931471805599453f;
+          if (v0) p.lse[(int64_t)cc.b * p.lse_bs + (int64_t)hq0 * p.lse_hs + qrow_base + q0 / p.group] =
+              l0 > 0.f ? m0 * sl2 * kLn2 + logf(l0) : -INFINITY;
+          if (v1) p.lse[(int64_t)cc.b * p.lse_bs + (int64_t)hq1 * p.lse_hs + qrow_base + q1 / p.group] =
+              l1 > 0.f ? m1 * sl2 * kLn2 + logf(l1) : -INFINITY;
+        }
+      } else {
+        const int64_t slot = (int64_t)(cc.segbase + cc.seg) + w;
+        float* po = p.part_o + slot * (kRowsPerSeg * HD);
+        float* pml = p.part_ml + slot * (kRowsPerSeg * 2);
+        const int rl0 = 2 * c4, rl1 = rl0 + 1;  // row inside the segment
+        if (g8 == 0) {
+          pml[rl0 * 2 + 0] = (m0 == -INFINITY) ? -INFINITY : m0 * sl2;
+          pml[rl0 * 2 + 1] = l0;
+          pml[rl1 * 2 + 0] = (m1 == -INFINITY) ? -INFINITY : m1 * sl2;
+          pml[rl1 * 2 + 1] = l1;
+        }
+#pragma unroll
+        for (int i = 0; i < NDT; ++i) {
+          const int d = KVB == 2 ? 16 * i + g8 : 16 * i + 2 * g8;
+          if constexpr (KVB == 2) {
+            po[rl0 * HD + d] = o[i][0];
+            po[rl0 * HD + d + dstep] = o[i][2];
+            po[rl1 * HD + d] = o[i][1];
+            po[rl1 * HD + d + dstep] = o[i][3];
+          } else {
+            *reinterpret_cast<float2*>(po + rl0 * HD + d) = make_float2(o[i][0], o[i][2]);
+            *reinterpret_cast<float2*>(po + rl1 * HD + d) = make_float2(o[i][1], o[i][3]);
+          }
+        }
+      }
+      fresh = true;
+    }
+    if (it + 1 < my_tiles) cursor_advance(p, cc);
+  }
+}
+
+// ---------------------------------------------------------------------------
 // Merge: one block per segment.  Segments written directly are skipped,
 // segments without keys are zero-filled, the others combine their partials.
 // ---------------------------------------------------------------------------
@@ -749,7 +1150,7 @@ __global__ void __launch_bounds__(128) attn_merge_kernel(const AttnParams p) {
   }
   const int b = lo;
   const int sq = p.sq[b];
-  const int nmb = (p.group * sq + kRowsPerSeg - 1) / kRowsPerSeg;
+  const int nmb = (p.group * sq + p.rows_per_seg - 1) / p.rows_per_seg;
   const int sib = seg - p.seg_cum[b];
   const int h = sib / nmb, mb = sib - h * nmb;
   const int nt = p.nt[b];
@@ -766,9 +1167,9 @@ __global__ void __launch_bounds__(128) attn_merge_kernel(const AttnParams p) {
   const float vscale = p.vs_vec ? p.vs_vec[h] : p.vs;
   const int qr = p.qrow0[b];
   constexpr float kLn2 = 0.6931471805599453f;
-  for (int e = threadIdx.x; e < kRowsPerSeg * HD; e += 128) {
+  for (int e = threadIdx.x; e < p.rows_per_seg * HD; e += 128) {
     const int rl = e / HD, d = e - rl * HD;
-    const int row = mb * kRowsPerSeg + rl;
+    const int row = mb * p.rows_per_seg + rl;
     if (row >= nrows) continue;
     // A worker between wf and wl whose range is empty (fewer tiles than workers) wrote nothing.
     auto has_tiles = [&](int wi) {
@@ -880,29 +1281,30 @@ inline int get_pool_tmap(const TmapKey& key, int tile_n, CUtensorMap* out) {
   return KB200_OK;
 }
 
-struct DeviceInfo { int sms = 0; bool smem_set[3][2][2] = {}; };
+struct DeviceInfo { int sms = 0; };
 inline DeviceInfo& device_info(int dev) {
   static DeviceInfo info[64];
   return info[dev & 63];
 }
 
 inline int tile_n_for(int kv_dtype, int head_dim, int nw) {
-  const int raw = kAttnRingBytes / (nw * kAttnStages) / (2 * head_dim * dtype_size(kv_dtype));
+  const int stages = nw == 12 ? 2 : 3;
+  const int raw = kAttnRingBytes / (nw * stages) / (2 * head_dim * dtype_size(kv_dtype));
   return raw > 64 ? 64 : raw;
 }
 
-// Worker warps per CTA.  8 warps (two per scheduler, 8 KB stages) beat 4 warps (16 KB stages) on
-// every measured shape: one warp per scheduler cannot hide its own MMA/ALU latencies.
+// Worker warps per CTA.  One warp per scheduler (4 warps, 16 KB stages) cannot hide its own MMA/ALU
+// latencies.  bf16/f16 K/V is HBM-bound with 8 warps x 3 stages of 8 KB; e4m3 K/V carries twice the
+// tokens per byte plus the widening to f16, and is fastest with 12 warps x 2 stages of 8 KB.
 inline int attn_warps_for(int kv_dtype, int head_dim) {
   static const int forced = [] {
     const char* e = getenv("KB200_ATTN_WARPS");
     const int v = e ? atoi(e) : 0;
-    return (v == 4 || v == 8) ? v : 0;
+    return (v == 4 || v == 8 || v == 12) ? v : 0;
   }();
   if (forced) return forced;
   (void)head_dim;
-  (void)kv_dtype;
-  return 8;
+  return kv_dtype == KB200_DTYPE_E4M3 ? 12 : 8;
 }
 
 struct AttnWorkspace {
@@ -912,7 +1314,7 @@ struct AttnWorkspace {
 inline int64_t attn_max_segments(int64_t batch, int64_t total_q, int hq, int hkv) {
   const int group = hq / hkv;
   // sum over sequences of ceil(group * sq_b / 16) <= group * total_q / 16 + batch
-  return (int64_t)hkv * ((group * total_q + kRowsPerSeg - 1) / kRowsPerSeg + batch);
+  return (int64_t)hkv * ((group * total_q + kDecodeRows - 1) / kDecodeRows + batch);  // smallest segment size
 }
 
 inline AttnWorkspace attn_workspace_layout(int64_t batch, int64_t total_q, int hq, int hkv, int hd, int n_workers) {
@@ -944,30 +1346,74 @@ inline int device_sm_count(int dev, int* sms) {
   return KB200_OK;
 }
 
-template <int KVB, int HD, bool BF16, int NW>
+template <int KVB, int HD, bool BF16, int NW, int NS>
 inline int launch_attn_variant(const CUtensorMap& tmK, const CUtensorMap& tmV, const AttnParams& p, int grid,
-                               int dev, int variant_idx, cudaStream_t stream) {
-  using T = AttnTile<KVB, HD, NW>;
-  auto kern = paged_attn_kernel<KVB, HD, BF16, NW>;
-  DeviceInfo& di = device_info(dev);
-  bool& done = di.smem_set[variant_idx][HD == 128 ? 1 : 0][NW == 8 ? 1 : 0];
-  if (!done) {
+                               int dev, cudaStream_t stream) {
+  using T = AttnTile<KVB, HD, NW, NS>;
+  auto kern = paged_attn_kernel<KVB, HD, BF16, NW, NS>;
+  static bool done[64] = {};
+  if (!done[dev & 63]) {
     KB200_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM_BYTES));
-    done = true;
+    done[dev & 63] = true;
   }
   kern<<<grid, NW * 32, T::SMEM_BYTES, stream>>>(tmK, tmV, p);
   KB200_CUDA_OK(cudaGetLastError());
   return KB200_OK;
 }
 
+template <int KVB, int HD, bool BF16, int NW, int NS>
+inline int launch_decode_variant(const CUtensorMap& tmK, const CUtensorMap& tmV, const AttnParams& p, int grid,
+                                 int dev, cudaStream_t stream) {
+  using T = AttnTile<KVB, HD, NW, NS>;
+  auto kern = paged_attn_decode_kernel<KVB, HD, BF16, NW, NS>;
+  static bool done[64] = {};
+  if (!done[dev & 63]) {
+    KB200_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM_BYTES));
+    done[dev & 63] = true;
+  }
+  kern<<<grid, NW * 32, T::SMEM_BYTES, stream>>>(tmK, tmV, p);
+  KB200_CUDA_OK(cudaGetLastError());
+  return KB200_OK;
+}
+
+template <int KVB, bool BF16, int HD>
+inline int launch_decode_hd(int nw, const CUtensorMap& tmK, const CUtensorMap& tmV, const AttnParams& p, int grid,
+                            int dev, cudaStream_t stream) {
+  if (nw == 12) return launch_decode_variant<KVB, HD, BF16, 12, 2>(tmK, tmV, p, grid, dev, stream);
+  if (nw == 4) return launch_decode_variant<KVB, HD, BF16, 4, 3>(tmK, tmV, p, grid, dev, stream);
+  return launch_decode_variant<KVB, HD, BF16, 8, 3>(tmK, tmV, p, grid, dev, stream);
+}
+
+template <int KVB, bool BF16>
+inline int launch_decode_dispatch(bool d128, int nw, const CUtensorMap& tmK, const CUtensorMap& tmV,
+                                  const AttnParams& p, int grid, int dev, cudaStream_t stream) {
+  return d128 ? launch_decode_hd<KVB, BF16, 128>(nw, tmK, tmV, p, grid, dev, stream)
+              : launch_decode_hd<KVB, BF16, 64>(nw, tmK, tmV, p, grid, dev, stream);
+}
+
+// Segments of up to 8 query rows run the transposed decode kernel; KB200_DECODE8=0 forces the
+// general 16-row kernel (for A/B checks).
+inline bool decode8_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("KB200_DECODE8");
+    return !(e && e[0] == '0');
+  }();
+  return on;
+}
+
+template <int KVB, bool BF16, int HD>
+inline int launch_attn_hd(int nw, const CUtensorMap& tmK, const CUtensorMap& tmV, const AttnParams& p, int grid,
+                          int dev, cudaStream_t stream) {
+  if (nw == 12) return launch_attn_variant<KVB, HD, BF16, 12, 2>(tmK, tmV, p, grid, dev, stream);
+  if (nw == 4) return launch_attn_variant<KVB, HD, BF16, 4, 3>(tmK, tmV, p, grid, dev, stream);
+  return launch_attn_variant<KVB, HD, BF16, 8, 3>(tmK, tmV, p, grid, dev, stream);
+}
+
 template <int KVB, bool BF16>
 inline int launch_attn_dispatch(bool d128, int nw, const CUtensorMap& tmK, const CUtensorMap& tmV,
-                                const AttnParams& p, int grid, int dev, int variant_idx, cudaStream_t stream) {
-  if (d128)
-    return nw == 8 ? launch_attn_variant<KVB, 128, BF16, 8>(tmK, tmV, p, grid, dev, variant_idx, stream)
-                   : launch_attn_variant<KVB, 128, BF16, 4>(tmK, tmV, p, grid, dev, variant_idx, stream);
-  return nw == 8 ? launch_attn_variant<KVB, 64, BF16, 8>(tmK, tmV, p, grid, dev, variant_idx, stream)
-                 : launch_attn_variant<KVB, 64, BF16, 4>(tmK, tmV, p, grid, dev, variant_idx, stream);
+                                const AttnParams& p, int grid, int dev, cudaStream_t stream) {
+  return d128 ? launch_attn_hd<KVB, BF16, 128>(nw, tmK, tmV, p, grid, dev, stream)
+              : launch_attn_hd<KVB, BF16, 64>(nw, tmK, tmV, p, grid, dev, stream);
 }
 
 inline int launch_paged_attention(const kb200_attn_args* a) {
@@ -1014,6 +1460,10 @@ inline int launch_paged_attention(const kb200_attn_args* a) {
   KB200_REQUIRE((reinterpret_cast<uintptr_t>(a->workspace) & 255) == 0, "workspace must be 256-byte aligned");
 
   const int tile_n = tile_n_for(a->kv_dtype, a->head_dim, nw);
+  // The transposed decode kernel pays off where the math is the limiter (e4m3 K/V); 16-bit K/V
+  // is within a few percent of the HBM roofline with the general kernel already.
+  const bool decode8 = decode8_enabled() && a->kv_dtype == KB200_DTYPE_E4M3 &&
+                       (int64_t)group * a->seqlen_q <= kDecodeRows;
   {
     // every copy lands on a 128-byte boundary of shared memory
     const int row_bytes = a->head_dim * es;
@@ -1074,6 +1524,7 @@ inline int launch_paged_attention(const kb200_attn_args* a) {
   p.q_is_bf16 = a->q_dtype == KB200_DTYPE_BF16;
   p.n_workers = n_workers;
   p.tile_n = tile_n;
+  p.rows_per_seg = decode8 ? kDecodeRows : kRowsPerSeg;
 
   cudaStream_t stream = static_cast<cudaStream_t>(a->stream);
   attn_plan_kernel<<<1, 256, 0, stream>>>(p);
@@ -1081,16 +1532,23 @@ inline int launch_paged_attention(const kb200_attn_args* a) {
 
   int rc;
   const bool d128 = a->head_dim == 128;
-  if (a->kv_dtype == KB200_DTYPE_E4M3)
-    rc = launch_attn_dispatch<1, false>(d128, nw, tmK, tmV, p, grid, a->device, 0, stream);
+  if (decode8) {
+    if (a->kv_dtype == KB200_DTYPE_E4M3)
+      rc = launch_decode_dispatch<1, false>(d128, nw, tmK, tmV, p, grid, a->device, stream);
+    else if (a->kv_dtype == KB200_DTYPE_BF16)
+      rc = launch_decode_dispatch<2, true>(d128, nw, tmK, tmV, p, grid, a->device, stream);
+    else
+      rc = launch_decode_dispatch<2, false>(d128, nw, tmK, tmV, p, grid, a->device, stream);
+  } else if (a->kv_dtype == KB200_DTYPE_E4M3)
+    rc = launch_attn_dispatch<1, false>(d128, nw, tmK, tmV, p, grid, a->device, stream);
   else if (a->kv_dtype == KB200_DTYPE_BF16)
-    rc = launch_attn_dispatch<2, true>(d128, nw, tmK, tmV, p, grid, a->device, 1, stream);
+    rc = launch_attn_dispatch<2, true>(d128, nw, tmK, tmV, p, grid, a->device, stream);
   else
-    rc = launch_attn_dispatch<2, false>(d128, nw, tmK, tmV, p, grid, a->device, 2, stream);
+    rc = launch_attn_dispatch<2, false>(d128, nw, tmK, tmV, p, grid, a->device, stream);
   if (rc) return rc;
 
   const int64_t max_seg = packed ? attn_max_segments(a->batch, a->total_q, a->n_q_heads, a->n_kv_heads)
-                                 : a->batch * a->n_kv_heads * ((group * (int64_t)a->seqlen_q + kRowsPerSeg - 1) / kRowsPerSeg);
+                                 : a->batch * a->n_kv_heads * ((group * (int64_t)a->seqlen_q + p.rows_per_seg - 1) / p.rows_per_seg);
   KB200_REQUIRE(max_seg <= 0x7fffffff, "too many segments");
   if (d128) attn_merge_kernel<128><<<(int)max_seg, 128, 0, stream>>>(p);
   else attn_merge_kernel<64><<<(int)max_seg, 128, 0, stream>>>(p);
