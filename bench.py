@@ -492,7 +492,16 @@ def main() -> None:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--batch", type=int, default=0, help="override the workload's batch (profiling on a small case)")
+    ap.add_argument("--layers", type=int, default=0, help="override the workload's layer count (profiling)")
     args = ap.parse_args()
+    if args.batch or args.layers:
+        WORKLOADS[args.workload] = dict(WORKLOADS[args.workload])
+        if args.batch:
+            WORKLOADS[args.workload]["batch"] = args.batch
+        if args.layers:
+            WORKLOADS[args.workload]["layers"] = args.layers
+        WORKLOADS[args.workload]["desc"] += f" [reduced for profiling: batch={WORKLOADS[args.workload]['batch']}, layers={WORKLOADS[args.workload]['layers']}]"
     if args.impl == "reference":
         run_reference_arm(args)
         return
