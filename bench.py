@@ -45,6 +45,10 @@ if str(ROOT) not in sys.path:
 
 NOMINAL_HBM_GBS = 8000.0
 FALLBACK_HBM_GBS = 6650.0
+# DRAM read+write bytes of one attention launch divided by its algorithmic bytes, from the ncu captures
+# summarised under profiles/ (reduced FP8 case: 1.0053; bf16 config 2: 1.0071).  Traffic grows with the
+# tokens attended, so a full launch is that ratio times its algorithmic bytes.
+DRAM_TRAFFIC_RATIO = {"fp8": 1.0053, "bf16": 1.0071}
 
 WORKLOADS = {
     # name: batch, len range, layers, kv dtype, head_dim, seqlen_q, outliers, pool factor
@@ -329,6 +333,64 @@ class GpuWorkload:
         self._run_layers(self.pos, record_attn, host=False)
         self.step_no += 1
 
+    # ---- the same step captured once in a CUDA graph (the reference replays its decode step from a
+    # graph too, kestrel/runtime/decode_graph.py:93-123); positions advance on the device
+    def capture_graph(self) -> None:
+        t = self.step_no
+        stream = torch.cuda.Stream(device=self.device)
+        stream.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(stream):
+            self.kernels.reserve_attention_workspace(batch=self.B, total_q=self.B * self.sq, n_q_heads=HQ,
+                                                     n_kv_heads=HKV, head_dim=self.D, device=self.device)
+            base = (self.len0 + t * self.sq).to(self.device)
+            self.pos.copy_(base.view(-1, 1) + torch.arange(self.sq, device=self.device).view(1, -1))
+            stream.synchronize()
+            self.graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self.graph, stream=stream):
+                self._run_layers(self.pos, False, host=False)
+                self.pos.add_(self.sq)
+        torch.cuda.current_stream(self.device).wait_stream(stream)
+        torch.cuda.synchronize(self.device)
+
+    def step_graph(self) -> None:
+        self.graph.replay()
+        self.step_no += 1
+
+    def time_attention_launch(self, reps: int) -> float:
+        """Average duration (ms) of one attention call (plan + attention + merge launches) at the current
+        context lengths: every layer's call captured in one graph, replayed ``reps`` times, CUDA events
+        on the launching stream.  Eager per-call events would add tens of microseconds of launch latency."""
+        scale = 1.0 / math.sqrt(self.D)
+        stream = torch.cuda.Stream(device=self.device)
+        stream.wait_stream(torch.cuda.current_stream(self.device))
+
+        def body():
+            for l in range(self.layers_n):
+                cache = self.caches[l % self.n_pools]
+                self.kernels.flash_attn_fwd(
+                    self.q[l], cache.k_cache.permute(0, 2, 1, 3), cache.v_cache.permute(0, 2, 1, 3),
+                    page_table=self.meta_pt, seqused_k=self.meta_sk, causal=True, softmax_scale=scale,
+                    k_scale=cache.k_scale, v_scale=cache.v_scale, out=self.out[l])
+
+        with torch.cuda.stream(stream):
+            self.kernels.reserve_attention_workspace(batch=self.B, total_q=self.B * self.sq, n_q_heads=HQ,
+                                                     n_kv_heads=HKV, head_dim=self.D, device=self.device)
+            body()
+            stream.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=stream):
+                body()
+        torch.cuda.current_stream(self.device).wait_stream(stream)
+        g.replay()
+        torch.cuda.synchronize(self.device)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            g.replay()
+        e1.record()
+        torch.cuda.synchronize(self.device)
+        return e0.elapsed_time(e1) / (reps * self.layers_n)
+
     # ---- one step through the public API with host buffers
     def step_e2e(self) -> None:
         t = self.step_no
@@ -492,6 +554,7 @@ def main() -> None:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-graph", action="store_true", help="launch the timed steps eagerly instead of replaying a CUDA graph")
     ap.add_argument("--batch", type=int, default=0, help="override the workload's batch (profiling on a small case)")
     ap.add_argument("--layers", type=int, default=0, help="override the workload's layer count (profiling)")
     args = ap.parse_args()
@@ -525,7 +588,7 @@ def main() -> None:
     _native.load()
     cfg = WORKLOADS[args.workload]
     e2e_steps = 0 if args.no_e2e else max(3, min(args.steps, 5))
-    total_steps = 2 * args.warmup + args.steps + e2e_steps + 2
+    total_steps = 3 * args.warmup + args.steps + e2e_steps + 4
     wl = GpuWorkload(args.workload, device, rank, total_steps)
 
     def barrier():
@@ -534,8 +597,13 @@ def main() -> None:
             dist.barrier()
         torch.cuda.synchronize(device)
 
+    use_graph = not args.no_graph
     for _ in range(args.warmup):
         wl.step_device()
+    if use_graph:
+        wl.capture_graph()
+        wl.step_graph()   # one untimed replay (the graph continues where the eager warm-up stopped)
+    step_fn = wl.step_graph if use_graph else wl.step_device
     barrier()
     sampler = ClockSampler(physical_gpu_index(local))
     if rank == 0:
@@ -544,7 +612,7 @@ def main() -> None:
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     start.record()
     for _ in range(args.steps):
-        wl.step_device(record_attn=True)
+        step_fn()
     stop.record()
     barrier()
     clocks = sampler.stop() if rank == 0 else None
@@ -552,9 +620,11 @@ def main() -> None:
     step_bytes = [algorithmic_bytes(wl.lengths_after(first_step + i), layers=wl.layers_n, kv_bytes=wl.kv_bytes,
                                     head_dim=wl.D, sq=wl.sq, batch=wl.B) for i in range(args.steps)]
     total_bytes = sum(b["per_step"] for b in step_bytes)
-    attn_ms = [a.elapsed_time(b) for a, b in wl.attn_events]
-    attn_bytes = sum(b["attn_per_launch"] for b in step_bytes) / len(step_bytes)
-    wl.attn_events.clear()
+    # roofline of the dominant kernel: the attention calls alone, at the lengths of the last step
+    attn_reps = max(3, min(20, int(2000 / max(1.0, elapsed_ms / args.steps))))
+    attn_ms = [wl.time_attention_launch(attn_reps)]
+    attn_bytes = algorithmic_bytes(wl.lengths_after(wl.step_no - 1), layers=wl.layers_n, kv_bytes=wl.kv_bytes,
+                                   head_dim=wl.D, sq=wl.sq, batch=wl.B)["attn_per_launch"]
 
     # end-to-end: host buffers in, host result out, every step
     e2e = None
@@ -579,18 +649,10 @@ def main() -> None:
     if flags[0] != 0:
         raise SystemExit(f"kernel diagnostics reported a problem: {flags}")
 
-    # aggregate over ranks: max time, summed bytes
-    stats = torch.tensor([elapsed_ms, float(total_bytes), e2e[0] if e2e else 0.0, float(e2e[1]) if e2e else 0.0,
-                          float(statistics.mean(attn_ms)), float(attn_bytes)], dtype=torch.float64, device=device)
-    if dist is not None:
-        mx = stats.clone()
-        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
-        sm = stats.clone()
-        dist.all_reduce(sm, op=dist.ReduceOp.SUM)
-        elapsed_ms, total_bytes = mx[0].item(), sm[1].item()
-        e2e_ms_all, e2e_bytes_all = mx[2].item(), sm[3].item()
-    else:
-        e2e_ms_all, e2e_bytes_all = stats[2].item(), stats[3].item()
+    # aggregate over ranks: max time, summed bytes (no-ops without a process group)
+    from kestrel_b200.sharding import combine_step_stats
+    elapsed_ms, total_bytes = combine_step_stats(elapsed_ms, total_bytes, device)
+    e2e_ms_all, e2e_bytes_all = combine_step_stats(e2e[0] if e2e else 0.0, e2e[1] if e2e else 0.0, device)
     if rank != 0:
         if dist is not None:
             dist.destroy_process_group()
@@ -610,6 +672,7 @@ def main() -> None:
         if cfg["kv"] == "fp8" else "bf16", "data": "synthetic",
         "config": {"workload": f"{args.workload}: {cfg['desc']}", "n_layer_pools": wl.n_pools,
                    "layers": wl.layers_n, "pool_pages": wl.n_pages, "sequences_per_gpu": wl.B,
+                   "launch": "CUDA graph replay" if use_graph else "eager",
                    "l2_policy": "inputs larger than L2 (every layer streams a multi-GB pool)"
                    if wl.n_pages * HKV * PAGE * wl.D * wl.kv_bytes * 2 > 256e6 else
                    "working set near L2 size; see tokens/s rather than GB/s"},
@@ -617,10 +680,15 @@ def main() -> None:
         "pct_of_measured_hbm": 100.0 * value / world / peak,
         "gpu_launches": wl.launches_per_step * args.steps,
         "clocks": clocks,
-        "roofline": {"bound": "hbm", "kernel": "paged_attn_kernel (+ its plan and merge launches)",
+        "roofline": {"bound": "hbm",
+                     "kernel": ("paged_attn_decode_kernel" if cfg["kv"] == "fp8" and cfg["sq"] * 4 <= 8 else
+                                "paged_attn_kernel") + " (+ its plan and merge launches)",
                      "achieved": achieved, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
-                     "frac": achieved / peak, "traffic": None,
-                     "launch_ms_avg": attn_avg_ms, "algorithmic_bytes_per_launch": attn_bytes},
+                     "frac": achieved / peak, "traffic": DRAM_TRAFFIC_RATIO[cfg["kv"]] * attn_bytes,
+                     "traffic_source": "ncu dram__bytes_read+write of a reduced launch of the same kernel, "
+                                       "scaled by tokens (profiles/)",
+                     "launch_ms_avg": attn_avg_ms, "algorithmic_bytes_per_launch": attn_bytes,
+                     "timing": f"graph of {wl.layers_n} attention calls replayed {attn_reps}x, CUDA events"},
     }
     if e2e_steps:
         e2e_val = e2e_bytes_all / (e2e_ms_all * 1e-3) / 1e9

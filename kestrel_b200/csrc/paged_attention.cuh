@@ -88,6 +88,7 @@ struct AttnParams {
   int64_t n_pages;
   int batch, seqlen_q, hq, hkv, group, page_size, causal, window_left, q_is_bf16, n_workers, tile_n;
   int rows_per_seg;  // query rows per segment: 16 (general kernel) or 8 (decode kernel)
+  int uniform_nseg;  // segments per sequence when that is the same for all (padded q, no seqused_q), else 0
 };
 
 // ---------------------------------------------------------------------------
@@ -1144,9 +1145,13 @@ __global__ void __launch_bounds__(128) attn_merge_kernel(const AttnParams p) {
   const int nseg_total = p.seg_cum[p.batch];
   if (seg >= nseg_total) return;
   int lo = 0, hi = p.batch;
-  while (hi - lo > 1) {
-    const int mid = (lo + hi) >> 1;
-    if (p.seg_cum[mid] <= seg) lo = mid; else hi = mid;
+  if (p.uniform_nseg > 0) {
+    lo = seg / p.uniform_nseg;  // no dependent loads on the common path
+  } else {
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (p.seg_cum[mid] <= seg) lo = mid; else hi = mid;
+    }
   }
   const int b = lo;
   const int sq = p.sq[b];
@@ -1525,6 +1530,8 @@ inline int launch_paged_attention(const kb200_attn_args* a) {
   p.n_workers = n_workers;
   p.tile_n = tile_n;
   p.rows_per_seg = decode8 ? kDecodeRows : kRowsPerSeg;
+  p.uniform_nseg = (packed || a->seqused_q) ? 0
+                   : a->n_kv_heads * ((group * a->seqlen_q + p.rows_per_seg - 1) / p.rows_per_seg);
 
   cudaStream_t stream = static_cast<cudaStream_t>(a->stream);
   attn_plan_kernel<<<1, 256, 0, stream>>>(p);
