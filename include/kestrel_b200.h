@@ -200,6 +200,43 @@ KB200_API uint64_t kb200_attn_workspace_bytes(int64_t batch, int64_t total_q, in
 
 KB200_API int kb200_paged_attention(const kb200_attn_args* args);
 
+/* ---------------------------------------------------------------------------
+ * kb200_paged_attention without a caller-provided scratch buffer.  This entry
+ * point has no counterpart in the reference.
+ *
+ * Who needs it: hosts that may not (or cannot) create device allocations once
+ * they are running -- an engine whose HBM is handed out completely at start-up
+ * (Kestrel gives everything left after the weights to the KV pool), a plain C
+ * or embedded host with no device allocator at hand, code that runs between
+ * the begin and end of a stream capture.  kb200_paged_attention makes such a
+ * caller find kb200_attn_workspace_bytes() of device memory first; this
+ * variant brings its own.
+ *
+ * How: the scratch (per-sequence plan arrays and the split-KV partials) lives
+ * in a fixed array inside the library's device image,
+ * KB200_STATIC_SCRATCH_BYTES (32 MiB) per GPU that loads the library, held
+ * until the process exits.  `args->workspace` and `args->workspace_bytes` are
+ * ignored; every other field means what it means for kb200_paged_attention and
+ * the results are the same.  The call allocates and frees nothing, on the host
+ * API or through any library.
+ *
+ * Limits and rules:
+ *   - the problem must fit: kb200_attn_workspace_bytes(batch, total_q, ...) <=
+ *     KB200_STATIC_SCRATCH_BYTES (decode batches of up to 188 sequences at
+ *     32 query / 8 KV heads, head_dim 128), otherwise KB200_ERR_WORKSPACE with a message saying how
+ *     much was needed;
+ *   - the first call on each device looks up the array's device address (one
+ *     cudaGetSymbolAddress, no allocation): make that first call outside any
+ *     stream capture;
+ *   - all calls on one GPU share the one array, whatever their stream.  Nothing in
+ *     it has to be zero on entry and nothing is carried from call to call (each
+ *     call rewrites what it reads), but two calls that overlap in time on the
+ *     same GPU would overwrite each other's partial results: run them one after
+ *     another (same stream, or ordered by events).
+ */
+#define KB200_STATIC_SCRATCH_BYTES (32u * 1024u * 1024u)
+KB200_API int kb200_paged_attention_static(const kb200_attn_args* args);
+
 #ifdef __cplusplus
 }
 #endif

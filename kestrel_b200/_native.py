@@ -14,6 +14,7 @@ LIB_PATH = Path(__file__).resolve().parent / "libkestrel_b200.so"
 ABI_VERSION = 1
 
 DTYPE_F32, DTYPE_F16, DTYPE_BF16, DTYPE_E4M3 = 0, 1, 2, 3
+STATIC_SCRATCH_BYTES = 32 * 1024 * 1024  # KB200_STATIC_SCRATCH_BYTES
 
 STATUS_BAD_SLOT, STATUS_BAD_PAGE, STATUS_BAD_ROW, STATUS_WAIT_TIMEOUT = 1, 2, 4, 8
 
@@ -28,6 +29,7 @@ EXPORTS = (
     "kb200_copy_pages",
     "kb200_attn_workspace_bytes",
     "kb200_paged_attention",
+    "kb200_paged_attention_static",
 )
 
 
@@ -114,6 +116,8 @@ def _declare(lib: C.CDLL) -> None:
     lib.kb200_attn_workspace_bytes.argtypes = [i64, i64, i32, i32, i32, i32]
     lib.kb200_paged_attention.restype = C.c_int
     lib.kb200_paged_attention.argtypes = [C.POINTER(AttnArgs)]
+    lib.kb200_paged_attention_static.restype = C.c_int
+    lib.kb200_paged_attention_static.argtypes = [C.POINTER(AttnArgs)]
 
 
 def load() -> C.CDLL:

@@ -90,3 +90,61 @@ int kb200_paged_attention(const kb200_attn_args* args) {
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------
+// Allocation-free variant: the scratch is a fixed array in the device image.
+// In host code `g_static_scratch` is only a handle for the symbol, not an
+// address a kernel could use; the device address is looked up once per GPU,
+// with that GPU current, and cached.
+// ---------------------------------------------------------------------------
+
+static __device__ __align__(256) unsigned char g_static_scratch[KB200_STATIC_SCRATCH_BYTES];
+
+namespace {
+std::mutex g_static_mu;
+void* g_static_ptr[64] = {nullptr};
+
+// Device address of g_static_scratch on `device` (which must be the current device).
+int static_scratch_address(int device, void** out) {
+  if (device < 0 || device >= 64) return fail(KB200_ERR_INVALID, "device index %d out of range", device);
+  std::lock_guard<std::mutex> lk(g_static_mu);
+  if (!g_static_ptr[device]) {
+    void* ptr = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+    if (e != cudaSuccess || !ptr)
+      return fail(KB200_ERR_CUDA, "cudaGetSymbolAddress(static scratch) failed on device %d: %s", device,
+                  cudaGetErrorString(e));
+    g_static_ptr[device] = ptr;
+  }
+  *out = g_static_ptr[device];
+  return KB200_OK;
+}
+}  // namespace
+
+extern "C" {
+
+int kb200_paged_attention_static(const kb200_attn_args* args) {
+  if (!args) return fail(KB200_ERR_INVALID, "args is null");
+  if (args->struct_bytes != sizeof(kb200_attn_args))
+    return fail(KB200_ERR_INVALID, "kb200_attn_args size mismatch: got %u, built with %zu", args->struct_bytes,
+                sizeof(kb200_attn_args));
+  KB200_ENTER(args->device);
+  if (args->batch > 0 && args->total_q > 0) {
+    const uint64_t need = kb200_attn_workspace_bytes(args->batch, args->total_q, args->n_q_heads, args->n_kv_heads,
+                                                     args->head_dim, args->device);
+    if (need == 0) return fail(KB200_ERR_INVALID, "cannot size the scratch for these arguments");
+    if (need > KB200_STATIC_SCRATCH_BYTES)
+      return fail(KB200_ERR_WORKSPACE,
+                  "problem needs %llu bytes of scratch, the built-in buffer holds %u: use kb200_paged_attention "
+                  "with a caller-provided workspace",
+                  (unsigned long long)need, (unsigned)KB200_STATIC_SCRATCH_BYTES);
+  }
+  void* scratch = nullptr;
+  if (int rc = static_scratch_address(args->device, &scratch)) return rc;
+  kb200_attn_args local = *args;
+  local.workspace = scratch;
+  local.workspace_bytes = KB200_STATIC_SCRATCH_BYTES;
+  return launch_paged_attention(&local);
+}
+
+}  // extern "C"
