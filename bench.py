@@ -199,13 +199,8 @@ class GpuWorkload:
         self.pool = KVMemoryPool(device=device)
         shared_cache = None
         if prefix:
-            class _Owner:  # stands in for the radix tree: owns the shared prefix pages
-                page_granular = True
-                _free_pages_sink = None
-                def evict(self, n): return 0
-                def evictable_page_count(self): return 0
-                def reclaimable_page_count(self): return 0
-            shared_cache = _Owner()
+            from kestrel_b200.prefix_cache import ImageToken, PagedRadixCache, attach_cached_prefix
+            shared_cache = PagedRadixCache(page_size=PAGE)
         self.pt = PageTable(n_pages=self.n_pages, page_size=PAGE, max_batch_size=self.B + 2, device=device,
                             prefix_cache=shared_cache)
         # pages scattered by a seeded permutation of the free list
@@ -225,17 +220,28 @@ class GpuWorkload:
         # rows and pages
         self.rows = []
         if prefix:
+            # the shared prefix lives in the radix cache; every request matches it, maps the 45 full pages
+            # and gets a copy-on-write page for the partly filled 46th
             owner = self.pt.allocate()
             self.pt.reserve(owner, prefix)
-            shared = list(self.pt.page_table_cpu[owner])
             self.owner_row = owner
+            image = [ImageToken(content_hash=1000 + rank, kv_length_=prefix)]
+            assert shared_cache.insert(image, list(self.pt.page_table_cpu[owner])).inserted_pages == -(-prefix // PAGE)
+
+            class _Text:
+                def __init__(self, req, k): self.key = (0, req, k)
+                def cache_key(self): return self.key
+                def kv_length(self): return 1
+
             for b in range(self.B):
-                r = self.pt.allocate() if self.pt.free_batch_idx else None
-                if r is None:
+                if not self.pt.free_batch_idx:
                     raise RuntimeError("page table has too few rows")
-                self.pt.map_pages(r, 0, shared)
-                if prefix % PAGE:
-                    self.pt.cow_page(r, len(shared) - 1)
+                r = self.pt.allocate()
+                n_suffix = int(suffix[b])
+                prompt = image + [_Text(b, k) for k in range(n_suffix)]
+                skip, n_shared, match = attach_cached_prefix(self.pt, shared_cache, r, prompt, prefix + n_suffix)
+                assert skip == prefix and n_shared == prefix // PAGE
+                shared_cache.unlock_prefill(match.last_node)
                 self.pt.reserve(r, int(final[b]))
                 self.rows.append(r)
         else:

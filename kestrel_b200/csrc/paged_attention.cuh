@@ -1172,34 +1172,41 @@ __global__ void __launch_bounds__(128) attn_merge_kernel(const AttnParams p) {
   const float vscale = p.vs_vec ? p.vs_vec[h] : p.vs;
   const int qr = p.qrow0[b];
   constexpr float kLn2 = 0.6931471805599453f;
-  for (int e = threadIdx.x; e < p.rows_per_seg * HD; e += 128) {
-    const int rl = e / HD, d = e - rl * HD;
+  // A worker between wf and wl whose range is empty (fewer tiles than workers) wrote nothing.
+  const bool all_have = total >= p.n_workers;
+  auto has_tiles = [&](int wi) {
+    return all_have || (long long)wi * total / p.n_workers < (long long)(wi + 1) * total / p.n_workers;
+  };
+  // one work item = 4 consecutive d of one query row; the partial loads of an item are independent
+  constexpr int kQuads = HD / 4;
+  for (int item = threadIdx.x; item < p.rows_per_seg * kQuads; item += 128) {
+    const int rl = item / kQuads, d = (item - rl * kQuads) * 4;
     const int row = mb * p.rows_per_seg + rl;
     if (row >= nrows) continue;
-    // A worker between wf and wl whose range is empty (fewer tiles than workers) wrote nothing.
-    auto has_tiles = [&](int wi) {
-      return (long long)wi * total / p.n_workers < (long long)(wi + 1) * total / p.n_workers;
-    };
     float M = -INFINITY;
     for (int wi = wf; wi <= wl; ++wi)
       if (has_tiles(wi)) M = fmaxf(M, p.part_ml[((int64_t)seg + wi) * (kRowsPerSeg * 2) + rl * 2]);
-    float L = 0.f, acc = 0.f;
+    float L = 0.f;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     if (M != -INFINITY) {
       for (int wi = wf; wi <= wl; ++wi) {
         if (!has_tiles(wi)) continue;
         const int64_t slot = (int64_t)seg + wi;
-        const float mi = p.part_ml[slot * (kRowsPerSeg * 2) + rl * 2];
-        if (mi == -INFINITY) continue;
-        const float wgt = ex2(mi - M);
-        L += wgt * p.part_ml[slot * (kRowsPerSeg * 2) + rl * 2 + 1];
-        acc += wgt * p.part_o[slot * (kRowsPerSeg * HD) + rl * HD + d];
+        const float2 ml = *reinterpret_cast<const float2*>(p.part_ml + slot * (kRowsPerSeg * 2) + rl * 2);
+        if (ml.x == -INFINITY) continue;
+        const float wgt = ex2(ml.x - M);
+        const float4 o = *reinterpret_cast<const float4*>(p.part_o + slot * (kRowsPerSeg * HD) + rl * HD + d);
+        L += wgt * ml.y;
+        acc.x += wgt * o.x; acc.y += wgt * o.y; acc.z += wgt * o.z; acc.w += wgt * o.w;
       }
     }
-    const float val = L > 0.f ? acc * vscale / L : 0.f;
+    const float inv = L > 0.f ? vscale / L : 0.f;
     const int j = row / p.group, hq = h * p.group + row % p.group;
     const int64_t oi = (int64_t)b * p.o_bs + (int64_t)(qr + j) * p.o_rs + (int64_t)hq * p.o_hs + d;
-    if (p.q_is_bf16) reinterpret_cast<__nv_bfloat16*>(p.out)[oi] = __float2bfloat16_rn(val);
-    else reinterpret_cast<__half*>(p.out)[oi] = __float2half_rn(val);
+    uint2 packed;
+    if (p.q_is_bf16) packed = make_uint2(pack2<true>(acc.x * inv, acc.y * inv), pack2<true>(acc.z * inv, acc.w * inv));
+    else packed = make_uint2(pack2<false>(acc.x * inv, acc.y * inv), pack2<false>(acc.z * inv, acc.w * inv));
+    *reinterpret_cast<uint2*>(p.out + 2 * oi) = packed;
     if (p.lse && d == 0)
       p.lse[(int64_t)b * p.lse_bs + (int64_t)hq * p.lse_hs + qr + j] = L > 0.f ? M * kLn2 + logf(L) : -INFINITY;
   }

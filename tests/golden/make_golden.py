@@ -242,6 +242,103 @@ def page_table_traces(kc):
     return traces
 
 
+class Tok:
+    """Token double with the interface the caches key on."""
+
+    def __init__(self, ident: int, kv: int = 1):
+        self.ident, self.kv = ident, kv
+
+    def cache_key(self):
+        return (0, self.ident, self.kv)
+
+    def kv_length(self):
+        return self.kv
+
+
+def radix_traces(root: str):
+    """Random op sequences on the reference RadixPrefixCache (one KV position per page)."""
+    from kestrel.prefix_cache import CacheNamespace, RadixPrefixCache
+
+    traces = []
+    for seed in (21, 22, 23, 24, 25):
+        rng = random.Random(seed)
+        freed: list[int] = []
+        cache = RadixPrefixCache(free_pages_sink=lambda pages: freed.extend(pages))
+        namespaces = [None, CacheNamespace(lora_id="a"), CacheNamespace(image_hash=7)]
+        next_page = [100]
+        handles = []      # nodes returned so far
+        locks = []        # (kind, handle index) currently held
+        ops = []
+
+        def seq():
+            n = rng.randrange(1, 7)
+            base = rng.choice([[1, 2, 3, 4, 5, 6, 7], [1, 2, 9, 9, 9, 9, 9], [5, 5, 5, 5, 5, 5, 5]])
+            ids = base[:n] if rng.random() < 0.7 else [rng.randrange(1, 6) for _ in range(n)]
+            return [(i, 3 if i == 9 else 1) for i in ids]
+
+        for _ in range(260):
+            kind = rng.choice(["insert", "insert", "match", "match", "lock", "unlock", "evict", "lock_prefill"])
+            rec = {"op": kind}
+            if kind in ("insert", "match"):
+                toks = seq()
+                ns_i = rng.randrange(len(namespaces))
+                objs = [Tok(i, k) for i, k in toks]
+                rec.update(tokens=toks, ns=ns_i)
+                if kind == "match":
+                    m = cache.match_prefix(objs, namespaces[ns_i])
+                    handles.append(m.last_node)
+                    rec["ret"] = [list(m.matched_pages), m.matched_kv_length, m.matched_token_count,
+                                  len(m.unmatched_tokens), m.last_node is not None]
+                else:
+                    m = cache.match_prefix(objs, namespaces[ns_i])
+                    handles.append(m.last_node)
+                    total = sum(k for _, k in toks)
+                    reuse = rng.random() < 0.85
+                    pages = list(m.matched_pages) if reuse else []
+                    while len(pages) < total:
+                        pages.append(next_page[0])
+                        next_page[0] += 1
+                    rec.update(pages=pages, reuse=reuse)
+                    r = cache.insert(objs, pages, namespaces[ns_i])
+                    handles.append(r.node)
+                    rec["ret"] = [r.inserted_pages]
+            elif kind in ("lock", "lock_prefill"):
+                live = [i for i, h in enumerate(handles) if h is not None]
+                if not live:
+                    continue
+                i = rng.choice(live)
+                # only lock nodes that are still attached to a tree
+                node = handles[i]
+                if node.parent is None:   # a namespace root: callers never lock it
+                    continue
+                top = node
+                while top.parent is not None:
+                    top = top.parent
+                if top.namespace is None or cache._trees.get(top.namespace) is not top:
+                    continue
+                p = node.parent
+                if p is not None and node.tokens and p.children.get(node.tokens[0].cache_key()) is not node:
+                    continue
+                (cache.lock if kind == "lock" else cache.lock_prefill)(node)
+                locks.append((kind, i))
+                rec.update(h=i)
+            elif kind == "unlock":
+                if not locks:
+                    continue
+                k, i = locks.pop(rng.randrange(len(locks)))
+                (cache.unlock if k == "lock" else cache.unlock_prefill)(handles[i])
+                rec.update(h=i, kind=k)
+            elif kind == "evict":
+                n = rng.randrange(1, 6)
+                del freed[:]
+                got = cache.evict(n)
+                rec.update(n=n, ret=[got, sorted(freed)])
+            rec["counts"] = [cache.total_cached_pages, cache.evictable_page_count(), cache.reclaimable_page_count()]
+            ops.append(rec)
+        traces.append({"seed": seed, "ops": ops})
+    return traces
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", default="/root/reference")
@@ -263,6 +360,7 @@ def main() -> None:
     np.savez_compressed(HERE / "reference_vectors.npz", **out)
     (HERE / "reference_vectors.json").write_text(json.dumps(metas, indent=1))
     (HERE / "page_table_traces.json").write_text(json.dumps(page_table_traces(kc)))
+    (HERE / "radix_traces.json").write_text(json.dumps(radix_traces(args.reference)))
     print("wrote", sorted(p.name for p in HERE.iterdir()))
 
 

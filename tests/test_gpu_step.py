@@ -157,34 +157,38 @@ def test_config5_shape_four_token_verify():
     st.check_pools_bit_exact()
 
 
-class _SharedPrefix:
-    page_granular = True
-    _free_pages_sink = None
-
-    def evict(self, n): return 0
-    def evictable_page_count(self): return 0
-    def reclaimable_page_count(self): return 0
-
-
 def test_config4_shape_shared_prefix_with_cow():
-    """One 729-token prefix (45 full pages + 9 tokens) shared by every request; the partly filled
-    46th page is copied on write before each request's first private token; then decode steps.
-    The oracle runs every request on private pages holding the same tokens."""
+    """One 729-token image prefix (45 full pages + 9 tokens) cached in the radix tree and reused by
+    every request: the full pages are shared, the partly filled 46th page is copied on write before
+    each request's first private token; then decode steps.  The oracle sees the same page table and
+    the same appends, so pool contents must match bit for bit and attention within tolerance."""
+    from kestrel_b200.prefix_cache import ImageToken, PagedRadixCache, attach_cached_prefix
+
     n_req, P, hq, hkv, D = 12, 16, 32, 8, 64
     prefix = 729
+    cache = PagedRadixCache(page_size=P)
     st = Stack(n_layers=2, n_pages=900, page_size=P, max_batch=n_req + 2, hq=hq, hkv=hkv, dim=D, dtype=torch.bfloat16,
-               seed=1004, prefix_cache=_SharedPrefix())
+               seed=1004, prefix_cache=cache)
     suffix = torch.randint(32, 257, (n_req,), generator=st.g).tolist()
+    image = [ImageToken(content_hash=42, kv_length_=prefix)]
     owner = st.pt.allocate()
     _prefill(st, [owner], [prefix], chunk=128, slack=0)
     shared = list(st.pt.page_table_cpu[owner])
     assert len(shared) == 46
+    assert cache.insert(image, shared).inserted_pages == 46
     rows = []
-    for s in suffix:
+    for i, s in enumerate(suffix):
         r = st.pt.allocate()
-        st.pt.map_pages(r, 0, shared)
-        src, dst = st.pt.cow_page(r, 45)
-        assert src == shared[45]
+
+        class Text:  # request-specific suffix tokens
+            def __init__(self, k): self.k = k
+            def cache_key(self): return (0, i, self.k)
+            def kv_length(self): return 1
+
+        prompt = image + [Text(k) for k in range(s)]
+        skip, n_shared, match = attach_cached_prefix(st.pt, cache, r, prompt, prefix + s)
+        assert (skip, n_shared, match.partial_page_tokens) == (prefix, 45, 9)
+        cache.unlock_prefill(match.last_node)
         rows.append(r)
     src_pages, dst_pages = st.pt.take_pending_page_copies()
     assert len(dst_pages) == n_req

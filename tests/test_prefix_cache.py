@@ -1,0 +1,201 @@
+"""The page-granular radix prefix cache: traces recorded from the reference cache (one position per
+page) replay identically; page sizes above one add partial-page matches, copy-on-write and
+page ownership across node boundaries."""
+
+import json
+
+import pytest
+
+from kestrel_b200.kv_cache import PageTable
+from kestrel_b200.prefix_cache import (CacheNamespace, ImageToken, PagedRadixCache, attach_cached_prefix)
+
+
+class Tok:
+    def __init__(self, ident, kv=1):
+        self.ident, self.kv = ident, kv
+
+    def cache_key(self):
+        return (0, self.ident, self.kv)
+
+    def kv_length(self):
+        return self.kv
+
+
+def toks(*ids):
+    return [Tok(i) for i in ids]
+
+
+def test_reference_traces_replay_identically_at_page_size_one(golden_dir):
+    traces = json.loads((golden_dir / "radix_traces.json").read_text())
+    namespaces = [None, CacheNamespace(lora_id="a"), CacheNamespace(image_hash=7)]
+    checked = 0
+    for tr in traces:
+        freed = []
+        cache = PagedRadixCache(page_size=1, free_pages_sink=lambda pages: freed.extend(pages))
+        handles = []
+        for i, rec in enumerate(tr["ops"]):
+            op = rec["op"]
+            where = (tr["seed"], i, op)
+            if op in ("match", "insert"):
+                objs = [Tok(a, k) for a, k in rec["tokens"]]
+                ns = namespaces[rec["ns"]]
+                m = cache.match_prefix(objs, ns)
+                handles.append(m.last_node)
+                if op == "match":
+                    got = [list(m.matched_pages), m.matched_kv_length, m.matched_token_count, len(m.unmatched_tokens),
+                           m.last_node is not None]
+                    assert got == rec["ret"], where
+                    assert m.partial_page_tokens == 0
+                else:
+                    if rec["reuse"]:
+                        assert rec["pages"][: len(m.matched_pages)] == m.matched_pages, where
+                    r = cache.insert(objs, rec["pages"], ns)
+                    handles.append(r.node)
+                    assert [r.inserted_pages] == rec["ret"], where
+            elif op == "lock":
+                cache.lock(handles[rec["h"]])
+            elif op == "lock_prefill":
+                cache.lock_prefill(handles[rec["h"]])
+            elif op == "unlock":
+                (cache.unlock if rec["kind"] == "lock" else cache.unlock_prefill)(handles[rec["h"]])
+            elif op == "evict":
+                del freed[:]
+                got = cache.evict(rec["n"])
+                assert [got, sorted(freed)] == rec["ret"], where
+            assert [cache.total_cached_pages, cache.evictable_page_count(), cache.reclaimable_page_count()] == rec["counts"], where
+            checked += 1
+    assert checked > 1000
+
+
+def test_match_insert_split_basics():
+    c = PagedRadixCache(page_size=1)
+    assert c.match_prefix(toks(1, 2)).matched_kv_length == 0
+    r = c.insert(toks(1, 2, 3), [10, 11, 12])
+    assert r.inserted_pages == 3 and c.total_cached_pages == 3
+    m = c.match_prefix(toks(1, 2, 99))
+    assert (m.matched_pages, m.matched_token_count, len(m.unmatched_tokens)) == ([10, 11], 2, 1)
+    assert m.last_node.tokens[-1].ident == 2 and len(m.last_node.children) == 1   # the node was split
+    assert c.insert(toks(1, 2, 3), [10, 11, 12]).inserted_pages == 0             # already there
+    assert c.insert(toks(1, 2, 4), [70, 71, 72]).inserted_pages == 0             # foreign pages for a cached prefix
+    assert c.insert(toks(1, 2, 4), [10, 11, 72]).inserted_pages == 1
+    with pytest.raises(AssertionError, match="Page count mismatch"):
+        c.insert(toks(5), [1, 2])
+    ns = CacheNamespace(lora_id="x")
+    assert c.match_prefix(toks(1, 2), ns).matched_kv_length == 0
+    c.insert(toks(1, 2), [40, 41], ns)
+    assert c.match_prefix(toks(1, 2), ns).matched_pages == [40, 41]
+
+
+def test_locks_eviction_order_and_counts():
+    freed = []
+    c = PagedRadixCache(page_size=1, free_pages_sink=freed.extend)
+    a = c.insert(toks(1, 2), [1, 2]).node
+    b = c.insert(toks(1, 2, 3), [1, 2, 3]).node
+    d = c.insert(toks(7), [9]).node
+    assert (c.total_cached_pages, c.evictable_page_count(), c.reclaimable_page_count()) == (4, 2, 4)
+    c.lock(b)
+    assert (c.evictable_page_count(), c.reclaimable_page_count()) == (1, 1)
+    assert c.evict(10) == 1 and freed == [9]         # only the unlocked leaf goes
+    c.unlock(b)
+    c.match_prefix(toks(1, 2, 3))                    # touch
+    assert c.evict(1) == 1 and freed[-1] == 3        # leaf first, then its parent becomes a leaf
+    assert c.evict(5) == 2 and sorted(freed[-2:]) == [1, 2]
+    assert c.total_cached_pages == 0 and c.match_prefix(toks(1)).matched_kv_length == 0
+    with pytest.raises(AssertionError, match="underflow"):
+        c.unlock(a)
+    _ = d
+
+
+def test_prefill_lock_blocks_split():
+    c = PagedRadixCache(page_size=1)
+    n = c.insert(toks(1, 2, 3, 4), [1, 2, 3, 4]).node
+    c.lock_prefill(n)
+    m = c.match_prefix(toks(1, 2, 9))
+    assert m.matched_kv_length == 0 and m.last_node is None     # cannot split a node a prefill is reading
+    assert c.insert(toks(1, 2, 9), [1, 2, 50]).inserted_pages == 0
+    c.unlock_prefill(n)
+    assert c.match_prefix(toks(1, 2, 9)).matched_pages == [1, 2]
+
+
+def test_partial_page_match_and_ownership_at_page_size_16():
+    P = 16
+    freed = []
+    c = PagedRadixCache(page_size=P, free_pages_sink=freed.extend)
+    prefix = [ImageToken(content_hash=1, kv_length_=729)]
+    # first request: image + 20 text tokens = 749 positions = 47 pages (the last holds 13 tokens)
+    seq_a = prefix + toks(*range(100, 120))
+    pages_a = list(range(200, 247))
+    ra = c.insert(seq_a, pages_a)
+    assert ra.inserted_pages == 47 and c.total_cached_pages == 47
+    # second request shares only the image: 45 full pages + 9 tokens of page 46
+    m = c.match_prefix(prefix + toks(500, 501))
+    assert m.matched_kv_length == 729 and m.partial_page_tokens == 9
+    assert m.matched_pages == pages_a[:46]
+    upper = m.last_node
+    assert upper.kv_len == 729 and len(upper.physical_pages) == 46
+    lower = next(iter(upper.children.values()))
+    assert lower.start == 729 and lower.physical_pages == tuple(pages_a[45:])   # page 245 straddles the cut
+    assert c.total_cached_pages == 47                                              # nothing gained or lost by the split
+    # the second request copied page 245 to 300 and continues on its own pages
+    seq_b = prefix + toks(500, 501, 502)
+    pages_b = pages_a[:45] + [300]
+    rb = c.insert(seq_b, pages_b)
+    assert rb.inserted_pages == 1 and c.total_cached_pages == 48
+    assert rb.node.start == 729 and rb.node.physical_pages == (300,)
+    m2 = c.match_prefix(seq_b)
+    assert m2.matched_kv_length == 732 and m2.matched_pages == pages_b and m2.partial_page_tokens == 12
+    # a request that did not map the shared pages cannot insert over them
+    assert c.insert(prefix + toks(7), list(range(900, 946))).inserted_pages == 0
+    # eviction: leaves first; the straddling page stays with the image node until that goes too
+    c.lock(rb.node)
+    assert c.evict(100) == 1 and freed == [246]      # request A's tail owns only its last page
+    c.unlock(rb.node)
+    assert c.evict(1) == 1 and freed[-1] == 300
+    assert c.evict(100) == 46 and sorted(freed[-46:]) == pages_a[:46]
+    assert c.total_cached_pages == 0 and c.evictable_page_count() == 0 and c.reclaimable_page_count() == 0
+
+
+def test_attach_cached_prefix_maps_shared_pages_and_queues_cow():
+    P = 16
+    cache = PagedRadixCache(page_size=P)
+    pt = PageTable(n_pages=200, page_size=P, max_batch_size=6, device="cpu", prefix_cache=cache)
+    assert cache._free_pages_sink == pt.free_pages_to_pool
+    image = [ImageToken(content_hash=5, kv_length_=729)]
+    # request 1: miss, prefill, insert, keep its node locked while it decodes
+    r1 = pt.allocate()
+    prompt1 = image + toks(*range(10, 40))
+    skip, shared, match = attach_cached_prefix(pt, cache, r1, prompt1, 759)
+    assert (skip, shared) == (0, 0) and match.last_node is None
+    pt.reserve(r1, 759)
+    ins = cache.insert(prompt1, pt.get_pages(r1, 0, 48))
+    assert ins.inserted_pages == 48
+    cache.lock(ins.node)
+    # request 2: same image, other text
+    r2 = pt.allocate()
+    prompt2 = image + toks(*range(50, 60))
+    skip, shared, match = attach_cached_prefix(pt, cache, r2, prompt2, 739)
+    assert skip == 729 and shared == 45 and match.partial_page_tokens == 9
+    row1, row2 = pt.page_table_cpu[r1], pt.page_table_cpu[r2]
+    assert row2[:45] == row1[:45] and row2[45] != row1[45] and len(row2) == 46
+    assert pt.take_pending_page_copies() == ([row1[45]], [row2[45]])
+    pt.reserve(r2, 739)
+    cache.unlock_prefill(match.last_node)
+    ins2 = cache.insert(prompt2, pt.get_pages(r2, 0, 47))
+    assert ins2.inserted_pages == 2          # its copy of the straddling page + one more
+    # a full match is capped so that one position is still computed
+    r3 = pt.allocate()
+    skip, shared, match3 = attach_cached_prefix(pt, cache, r3, prompt2, 739)
+    assert skip == 738 and shared == 46 and len(pt.page_table_cpu[r3]) == 47
+    cache.unlock_prefill(match3.last_node)
+    # releasing: cache-owned leading pages stay, private ones return
+    free_before = pt.pages_available
+    pt.erase(r3, cached_page_count=shared)
+    assert pt.pages_available == free_before + 1          # only the copied page was private
+    pt.erase(r2, cached_page_count=47)
+    cache.unlock(ins.node)
+    pt.erase(r1, cached_page_count=48)
+    # pressure: a big reservation evicts cached prefixes through the page table
+    big = pt.allocate()
+    assert pt.can_reserve_with_eviction(190 * P, big)
+    assert pt.reserve(big, 190 * P)
+    assert cache.total_cached_pages < 50
