@@ -41,6 +41,8 @@ __device__ __forceinline__ uint32_t quant2(float a, float b, float s) {
 // size when pointers/strides are not 16-byte aligned).
 template <int CHUNK>
 __global__ void __launch_bounds__(256) append_copy_kernel(const AppendParams p, int row_bytes) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int chunks_per_row = row_bytes / CHUNK;
   const int64_t per_tensor = p.num_tokens * p.n_kv_heads * chunks_per_row;
   const int64_t total = 2 * per_tensor;
@@ -80,6 +82,8 @@ __global__ void __launch_bounds__(256) append_copy_kernel(const AppendParams p, 
 // thread: 16 (one 16-byte store) when aligned, else 2.
 template <typename In, int EPT>
 __global__ void __launch_bounds__(256) append_quant_kernel(const AppendParams p) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int chunks_per_row = p.head_dim / EPT;
   const int64_t per_tensor = p.num_tokens * p.n_kv_heads * chunks_per_row;
   const int64_t total = 2 * per_tensor;
@@ -191,33 +195,33 @@ inline int launch_append(const void* key, const void* value, int64_t key_token_s
   if (!quant) {
     if (vec_ok) {
       int64_t items = 2 * num_tokens * n_kv_heads * (row_out_bytes / 16);
-      append_copy_kernel<16><<<blocks_for(items), threads, 0, stream>>>(p, row_out_bytes);
+      KB200_CUDA_OK(launch_kernel(append_copy_kernel<16>, dim3(blocks_for(items)), dim3(threads), 0, stream, p, row_out_bytes));
     } else {
       int64_t items = 2 * num_tokens * n_kv_heads * head_dim;
       if (c_sz == 4)
-        append_copy_kernel<4><<<blocks_for(items), threads, 0, stream>>>(p, row_out_bytes);
+        KB200_CUDA_OK(launch_kernel(append_copy_kernel<4>, dim3(blocks_for(items)), dim3(threads), 0, stream, p, row_out_bytes));
       else if (c_sz == 2)
-        append_copy_kernel<2><<<blocks_for(items), threads, 0, stream>>>(p, row_out_bytes);
+        KB200_CUDA_OK(launch_kernel(append_copy_kernel<2>, dim3(blocks_for(items)), dim3(threads), 0, stream, p, row_out_bytes));
       else
-        append_copy_kernel<1><<<blocks_for(items), threads, 0, stream>>>(p, row_out_bytes);
+        KB200_CUDA_OK(launch_kernel(append_copy_kernel<1>, dim3(blocks_for(items)), dim3(threads), 0, stream, p, row_out_bytes));
     }
   } else {
     if (vec_ok) {
       int64_t items = 2 * num_tokens * n_kv_heads * (head_dim / 16);
       if (in_dtype == KB200_DTYPE_BF16)
-        append_quant_kernel<__nv_bfloat16, 16><<<blocks_for(items), threads, 0, stream>>>(p);
+        KB200_CUDA_OK(launch_kernel(append_quant_kernel<__nv_bfloat16, 16>, dim3(blocks_for(items)), dim3(threads), 0, stream, p));
       else if (in_dtype == KB200_DTYPE_F16)
-        append_quant_kernel<__half, 16><<<blocks_for(items), threads, 0, stream>>>(p);
+        KB200_CUDA_OK(launch_kernel(append_quant_kernel<__half, 16>, dim3(blocks_for(items)), dim3(threads), 0, stream, p));
       else
-        append_quant_kernel<float, 16><<<blocks_for(items), threads, 0, stream>>>(p);
+        KB200_CUDA_OK(launch_kernel(append_quant_kernel<float, 16>, dim3(blocks_for(items)), dim3(threads), 0, stream, p));
     } else {
       int64_t items = 2 * num_tokens * n_kv_heads * (head_dim / 2);
       if (in_dtype == KB200_DTYPE_BF16)
-        append_quant_kernel<__nv_bfloat16, 2><<<blocks_for(items), threads, 0, stream>>>(p);
+        KB200_CUDA_OK(launch_kernel(append_quant_kernel<__nv_bfloat16, 2>, dim3(blocks_for(items)), dim3(threads), 0, stream, p));
       else if (in_dtype == KB200_DTYPE_F16)
-        append_quant_kernel<__half, 2><<<blocks_for(items), threads, 0, stream>>>(p);
+        KB200_CUDA_OK(launch_kernel(append_quant_kernel<__half, 2>, dim3(blocks_for(items)), dim3(threads), 0, stream, p));
       else
-        append_quant_kernel<float, 2><<<blocks_for(items), threads, 0, stream>>>(p);
+        KB200_CUDA_OK(launch_kernel(append_quant_kernel<float, 2>, dim3(blocks_for(items)), dim3(threads), 0, stream, p));
     }
   }
   KB200_CUDA_OK(cudaGetLastError());

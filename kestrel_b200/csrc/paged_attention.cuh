@@ -207,6 +207,8 @@ __global__ void __launch_bounds__(256) attn_plan_kernel(const AttnParams p) {
   __shared__ long long carry_t;
   __shared__ int carry_s;
   const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+  pdl_wait();   // the plan arrays may still be read by the merge kernel of the previous call
+  pdl_launch_dependents();
   if (tid == 0) { carry_t = 0; carry_s = 0; }
   __syncthreads();
   for (int base = 0; base < p.batch; base += 256) {
@@ -415,6 +417,8 @@ paged_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
   }
   __syncthreads();
   // No block-wide barrier below this line: warps are independent workers.
+  pdl_launch_dependents();
+  pdl_wait();   // the plan (and, before it, the append) must have completed
 
   const long long total = p.tile_cum[p.batch];
   const int w = blockIdx.x * kAttnWarps + warp;
@@ -807,6 +811,8 @@ paged_attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
   }
   __syncthreads();
   // No block-wide barrier below this line: warps are independent workers.
+  pdl_launch_dependents();
+  pdl_wait();   // the plan (and, before it, the append) must have completed
 
   const long long total = p.tile_cum[p.batch];
   const int w = blockIdx.x * NW + warp;
@@ -1142,6 +1148,8 @@ paged_attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
 template <int HD>
 __global__ void __launch_bounds__(128) attn_merge_kernel(const AttnParams p) {
   const int seg = blockIdx.x;
+  pdl_wait();
+  pdl_launch_dependents();
   const int nseg_total = p.seg_cum[p.batch];
   if (seg >= nseg_total) return;
   int lo = 0, hi = p.batch;
@@ -1368,8 +1376,7 @@ inline int launch_attn_variant(const CUtensorMap& tmK, const CUtensorMap& tmV, c
     KB200_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM_BYTES));
     done[dev & 63] = true;
   }
-  kern<<<grid, NW * 32, T::SMEM_BYTES, stream>>>(tmK, tmV, p);
-  KB200_CUDA_OK(cudaGetLastError());
+  KB200_CUDA_OK(launch_kernel(kern, dim3(grid), dim3(NW * 32), T::SMEM_BYTES, stream, tmK, tmV, p));
   return KB200_OK;
 }
 
@@ -1383,8 +1390,7 @@ inline int launch_decode_variant(const CUtensorMap& tmK, const CUtensorMap& tmV,
     KB200_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM_BYTES));
     done[dev & 63] = true;
   }
-  kern<<<grid, NW * 32, T::SMEM_BYTES, stream>>>(tmK, tmV, p);
-  KB200_CUDA_OK(cudaGetLastError());
+  KB200_CUDA_OK(launch_kernel(kern, dim3(grid), dim3(NW * 32), T::SMEM_BYTES, stream, tmK, tmV, p));
   return KB200_OK;
 }
 
@@ -1541,8 +1547,7 @@ inline int launch_paged_attention(const kb200_attn_args* a) {
                    : a->n_kv_heads * ((group * a->seqlen_q + p.rows_per_seg - 1) / p.rows_per_seg);
 
   cudaStream_t stream = static_cast<cudaStream_t>(a->stream);
-  attn_plan_kernel<<<1, 256, 0, stream>>>(p);
-  KB200_CUDA_OK(cudaGetLastError());
+  KB200_CUDA_OK(launch_kernel(attn_plan_kernel, dim3(1), dim3(256), 0, stream, p));
 
   int rc;
   const bool d128 = a->head_dim == 128;
@@ -1559,9 +1564,8 @@ inline int launch_paged_attention(const kb200_attn_args* a) {
   const int64_t max_seg = packed ? attn_max_segments(a->batch, a->total_q, a->n_q_heads, a->n_kv_heads)
                                  : a->batch * a->n_kv_heads * ((group * (int64_t)a->seqlen_q + p.rows_per_seg - 1) / p.rows_per_seg);
   KB200_REQUIRE(max_seg <= 0x7fffffff, "too many segments");
-  if (d128) attn_merge_kernel<128><<<(int)max_seg, 128, 0, stream>>>(p);
-  else attn_merge_kernel<64><<<(int)max_seg, 128, 0, stream>>>(p);
-  KB200_CUDA_OK(cudaGetLastError());
+  if (d128) KB200_CUDA_OK(launch_kernel(attn_merge_kernel<128>, dim3((unsigned)max_seg), dim3(128), 0, stream, p));
+  else KB200_CUDA_OK(launch_kernel(attn_merge_kernel<64>, dim3((unsigned)max_seg), dim3(128), 0, stream, p));
   return KB200_OK;
 }
 
