@@ -272,6 +272,13 @@ class GpuWorkload:
                      for _ in range(2)]
         self.h_out = torch.empty(self.layers_n, self.B, self.sq, HQ, self.D, dtype=torch.bfloat16).pin_memory()
         self.h_pos = torch.zeros(self.B, self.sq, dtype=torch.int64).pin_memory()
+        self.h2d_stream = torch.cuda.Stream(device=device)
+        self.d2h_stream = torch.cuda.Stream(device=device)
+        self.in_ready = [torch.cuda.Event(), torch.cuda.Event()]
+        self.in_free = [torch.cuda.Event(), torch.cuda.Event()]
+        self.out_done = [torch.cuda.Event(), torch.cuda.Event()]
+        for ev in self.in_free:
+            ev.record(torch.cuda.current_stream(device))
         self.attn_events: list[tuple[torch.cuda.Event, torch.cuda.Event]] = []
         self.launches_per_step = 2 + self.layers_n * 4
 
@@ -415,11 +422,17 @@ class GpuWorkload:
         self.pt.populate_paged_kv_metadata(batch_idx=self.batch_idx, input_pos=pos[:, -1].to(torch.int32),
                                            out_page_table=self.meta_pt, out_seqused_k=self.meta_sk)
         scale = 1.0 / math.sqrt(self.D)
+        compute = torch.cuda.current_stream(self.device)
         for l in range(self.layers_n):
             cache = self.caches[l % self.n_pools]
             if host:
+                # inputs of layer l+1 cross PCIe on a copy stream while layer l computes
+                if l == 0:
+                    self._stage_in(0)
+                if l + 1 < self.layers_n:
+                    self._stage_in(l + 1)
+                compute.wait_event(self.in_ready[l & 1])
                 d = self.d_in[l & 1]
-                d.copy_(self.h_in[l], non_blocking=True)
                 q, k, v = d.split([HQ * self.D, HKV * self.D, HKV * self.D], dim=-1)
                 q = q.view(self.B, self.sq, HQ, self.D)
                 k = k.view(self.B, self.sq, HKV, self.D)
@@ -438,7 +451,21 @@ class GpuWorkload:
                 e1.record()
                 self.attn_events.append((e0, e1))
             if host:
-                self.h_out[l].copy_(out, non_blocking=True)
+                self.in_free[l & 1].record(compute)          # the staging buffer may be refilled
+                self.out_done[l & 1].record(compute)
+                with torch.cuda.stream(self.d2h_stream):
+                    self.d2h_stream.wait_event(self.out_done[l & 1])
+                    self.h_out[l].copy_(out, non_blocking=True)
+        if host:
+            compute.wait_stream(self.d2h_stream)
+
+    def _stage_in(self, l: int) -> None:
+        """Host -> device copy of layer ``l``'s fused q/k/v rows into staging buffer ``l & 1`` on the copy
+        stream, after the layer that used that buffer last has consumed it."""
+        with torch.cuda.stream(self.h2d_stream):
+            self.h2d_stream.wait_event(self.in_free[l & 1])
+            self.d_in[l & 1].copy_(self.h_in[l], non_blocking=True)
+            self.in_ready[l & 1].record(self.h2d_stream)
 
     def e2e_bytes(self) -> tuple[int, int]:
         h2d = self.layers_n * self.h_in[0].numel() * 2 + self.h_pos.numel() * 8
