@@ -58,7 +58,8 @@ enum {
   KB200_STATUS_BAD_SLOT = 1,    /* append: slot >= n_pages * page_size (row skipped) */
   KB200_STATUS_BAD_PAGE = 2,    /* a page index outside [0, n_pages) (access skipped / zero filled) */
   KB200_STATUS_BAD_ROW = 4,     /* a page-table row index outside the table (row skipped) */
-  KB200_STATUS_WAIT_TIMEOUT = 8 /* a bounded wait on a shared-memory barrier ran out */
+  KB200_STATUS_WAIT_TIMEOUT = 8, /* a bounded wait on a shared-memory barrier ran out */
+  KB200_STATUS_BAD_POSITION = 16 /* rotary: a position outside the cos/sin table (clamped) */
 };
 
 KB200_API int kb200_abi_version(void);
@@ -125,6 +126,58 @@ KB200_API int kb200_build_paged_kv_metadata(
     const void* batch_idx, int32_t batch_idx_is_i64, const int32_t* input_pos,
     int32_t* out_page_table, int64_t out_row_stride, int64_t out_cols, int32_t* out_seqused_k,
     int64_t batch, int32_t page_size, int32_t device, void* stream);
+
+/* ---------------------------------------------------------------------------
+ * Per-step decode metadata in one launch: kb200_build_paged_kv_metadata followed
+ * by kb200_build_slot_mapping for the `n_new` tokens each active row appends this
+ * step (positions input_pos[r] - n_new + 1 .. input_pos[r]).  Fuses the two calls
+ * the reference makes at the top of every decode step
+ * (kestrel/models/moondream/runtime.py:2554-2564).
+ *
+ *   out_slots      device int64 [batch, n_new]
+ *   out_positions  device int64 [batch, n_new] or NULL (the position_ids the
+ *                  reference derives with input_pos.to(long).view(-1, 1))
+ * Other arguments as kb200_build_paged_kv_metadata.
+ */
+KB200_API int kb200_build_decode_step_metadata(
+    const int32_t* page_table, int64_t pt_row_stride, int64_t pt_rows, int64_t pt_cols,
+    const void* batch_idx, int32_t batch_idx_is_i64, const int32_t* input_pos,
+    int32_t* out_page_table, int64_t out_row_stride, int64_t out_cols, int32_t* out_seqused_k,
+    int64_t* out_slots, int64_t* out_positions, int64_t batch, int32_t n_new, int32_t page_size,
+    int32_t device, void* stream);
+
+/* ---------------------------------------------------------------------------
+ * Rotary embedding, optionally fused with the append that follows it.
+ * Replaces rotary.rotary_embedding(position_ids, q, k, head_dim, cos_sin_cache)
+ * (kestrel/models/moondream/text.py:125) and, when key_cache is non-NULL, also
+ * the PagedKVCache.update that comes right after it on the same K
+ * (kestrel/models/moondream/text.py:132 -> kestrel/kv_cache.py:222-231) in one
+ * launch: Q is rotated in place, K is rotated (written back when `write_k` != 0)
+ * and rotated K plus V are scattered into the pool pages by slot, quantised to
+ * e4m3 when cache_dtype is E4M3.
+ *
+ *   q, k, v        device rows [num_tokens, heads, head_dim] of `in_dtype`
+ *                  (F32/F16/BF16), head stride == head_dim, token strides given;
+ *                  q may be NULL with n_q_heads == 0
+ *   positions      device int32/int64 [num_tokens]
+ *   cos_sin_cache  device fp32 [max_pos, rot_dim]: cos of rot_dim/2 frequencies, then
+ *                  sin (kestrel/models/moondream/rope.py:6-32); rot_dim <= head_dim,
+ *                  NeoX pairing (i, i + rot_dim/2), elements past rot_dim pass through
+ *   key_cache ...  as kb200_reshape_and_cache_flash; key_cache == NULL: rotate only
+ * Rounding: y1 = x1*cos - x2*sin, y2 = x2*cos + x1*sin in fp32 with separately
+ * rounded products, rounded once to `in_dtype`; the pool receives the bytes an
+ * append of the rotated row would write.  Positions outside [0, max_pos) are
+ * clamped and flagged in the device status.
+ */
+KB200_API int kb200_rope_append(
+    void* q, void* k, const void* v, int64_t q_token_stride, int64_t k_token_stride,
+    int64_t v_token_stride, int64_t num_tokens, int32_t n_q_heads, int32_t n_kv_heads,
+    int32_t head_dim, int32_t rot_dim, const void* positions, int32_t positions_is_i64,
+    const float* cos_sin_cache, int64_t max_pos, int64_t cos_sin_row_stride, void* key_cache,
+    void* value_cache, int64_t cache_page_stride, int64_t cache_token_stride,
+    int64_t cache_head_stride, const int64_t* slot_mapping, int64_t n_pages, int32_t page_size,
+    int32_t in_dtype, int32_t cache_dtype, const float* k_scale, const float* v_scale,
+    int32_t n_scales, int32_t write_k, int32_t device, void* stream);
 
 /* ---------------------------------------------------------------------------
  * Copy-on-write page copy: for every pool in `caches` (HOST array of `n_caches`

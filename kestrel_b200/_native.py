@@ -18,7 +18,7 @@ ABI_VERSION = 1
 DTYPE_F32, DTYPE_F16, DTYPE_BF16, DTYPE_E4M3 = 0, 1, 2, 3
 STATIC_SCRATCH_BYTES = 32 * 1024 * 1024  # KB200_STATIC_SCRATCH_BYTES
 
-STATUS_BAD_SLOT, STATUS_BAD_PAGE, STATUS_BAD_ROW, STATUS_WAIT_TIMEOUT = 1, 2, 4, 8
+STATUS_BAD_SLOT, STATUS_BAD_PAGE, STATUS_BAD_ROW, STATUS_WAIT_TIMEOUT, STATUS_BAD_POSITION = 1, 2, 4, 8, 16
 
 # Every symbol include/kestrel_b200.h declares.
 EXPORTS = (
@@ -28,6 +28,8 @@ EXPORTS = (
     "kb200_reshape_and_cache_flash",
     "kb200_build_slot_mapping",
     "kb200_build_paged_kv_metadata",
+    "kb200_build_decode_step_metadata",
+    "kb200_rope_append",
     "kb200_copy_pages",
     "kb200_attn_workspace_bytes",
     "kb200_paged_attention",
@@ -111,6 +113,15 @@ def _declare(lib: C.CDLL) -> None:
     lib.kb200_build_paged_kv_metadata.restype = C.c_int
     lib.kb200_build_paged_kv_metadata.argtypes = [
         vp, i64, i64, i64, vp, i32, vp, vp, i64, i64, vp, i64, i32, i32, vp,
+    ]
+    lib.kb200_build_decode_step_metadata.restype = C.c_int
+    lib.kb200_build_decode_step_metadata.argtypes = [
+        vp, i64, i64, i64, vp, i32, vp, vp, i64, i64, vp, vp, vp, i64, i32, i32, i32, vp,
+    ]
+    lib.kb200_rope_append.restype = C.c_int
+    lib.kb200_rope_append.argtypes = [
+        vp, vp, vp, i64, i64, i64, i64, i32, i32, i32, i32, vp, i32, vp, i64, i64,
+        vp, vp, i64, i64, i64, vp, i64, i32, i32, i32, vp, vp, i32, i32, i32, vp,
     ]
     lib.kb200_copy_pages.restype = C.c_int
     lib.kb200_copy_pages.argtypes = [C.POINTER(vp), i32, i64, i64, i64, vp, vp, i64, i32, vp]

@@ -129,6 +129,7 @@ enum KernelId : int {
   KID_ATTN_PLAN = 5,
   KID_ATTN = 6,
   KID_ATTN_MERGE = 7,
+  KID_ROPE_APPEND = 8,
 };
 
 }  // namespace kb200

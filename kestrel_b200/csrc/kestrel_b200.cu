@@ -2,6 +2,7 @@
 // One translation unit: the kernels live in the .cuh files next to this one.
 #include "common.cuh"
 #include "cache_ops.cuh"
+#include "rope_append.cuh"
 #include "paged_attention.cuh"
 
 using namespace kb200;
@@ -65,6 +66,43 @@ int kb200_build_paged_kv_metadata(const int32_t* page_table, int64_t pt_row_stri
   return launch_metadata(page_table, pt_row_stride, pt_rows, pt_cols, batch_idx, batch_idx_is_i64, input_pos,
                          out_page_table, out_row_stride, out_cols, out_seqused_k, batch, page_size,
                          static_cast<cudaStream_t>(stream));
+}
+
+int kb200_build_decode_step_metadata(const int32_t* page_table, int64_t pt_row_stride, int64_t pt_rows,
+                                     int64_t pt_cols, const void* batch_idx, int32_t batch_idx_is_i64,
+                                     const int32_t* input_pos, int32_t* out_page_table, int64_t out_row_stride,
+                                     int64_t out_cols, int32_t* out_seqused_k, int64_t* out_slots,
+                                     int64_t* out_positions, int64_t batch, int32_t n_new, int32_t page_size,
+                                     int32_t device, void* stream) {
+  KB200_ENTER(device);
+  return launch_decode_step_metadata(page_table, pt_row_stride, pt_rows, pt_cols, batch_idx, batch_idx_is_i64,
+                                     input_pos, out_page_table, out_row_stride, out_cols, out_seqused_k, out_slots,
+                                     out_positions, batch, n_new, page_size, static_cast<cudaStream_t>(stream));
+}
+
+int kb200_rope_append(void* q, void* k, const void* v, int64_t q_token_stride, int64_t k_token_stride,
+                      int64_t v_token_stride, int64_t num_tokens, int32_t n_q_heads, int32_t n_kv_heads,
+                      int32_t head_dim, int32_t rot_dim, const void* positions, int32_t positions_is_i64,
+                      const float* cos_sin_cache, int64_t max_pos, int64_t cos_sin_row_stride, void* key_cache,
+                      void* value_cache, int64_t cache_page_stride, int64_t cache_token_stride,
+                      int64_t cache_head_stride, const int64_t* slot_mapping, int64_t n_pages, int32_t page_size,
+                      int32_t in_dtype, int32_t cache_dtype, const float* k_scale, const float* v_scale,
+                      int32_t n_scales, int32_t write_k, int32_t device, void* stream) {
+  KB200_ENTER(device);
+  RopeAppendArgs a;
+  a.q = q; a.k = k; a.v = v;
+  a.q_token_stride = q_token_stride; a.k_token_stride = k_token_stride; a.v_token_stride = v_token_stride;
+  a.num_tokens = num_tokens;
+  a.n_q_heads = n_q_heads; a.n_kv_heads = n_kv_heads; a.head_dim = head_dim; a.rot_dim = rot_dim;
+  a.positions = positions; a.positions_is_i64 = positions_is_i64;
+  a.cos_sin_cache = cos_sin_cache; a.max_pos = max_pos; a.cos_sin_row_stride = cos_sin_row_stride;
+  a.key_cache = key_cache; a.value_cache = value_cache;
+  a.cache_page_stride = cache_page_stride; a.cache_token_stride = cache_token_stride;
+  a.cache_head_stride = cache_head_stride;
+  a.slot_mapping = slot_mapping; a.n_pages = n_pages; a.page_size = page_size;
+  a.in_dtype = in_dtype; a.cache_dtype = cache_dtype;
+  a.k_scale = k_scale; a.v_scale = v_scale; a.n_scales = n_scales; a.write_k = write_k;
+  return launch_rope_append(a, static_cast<cudaStream_t>(stream));
 }
 
 int kb200_copy_pages(void* const* caches, int32_t n_caches, int64_t page_bytes, int64_t page_stride_bytes,

@@ -203,6 +203,185 @@ def build_paged_kv_metadata(page_table: torch.Tensor, batch_idx: torch.Tensor, i
         out_seqused_k.data_ptr(), B, int(page_size), dev, _stream(dev)))
 
 
+def build_decode_step_metadata(page_table: torch.Tensor, batch_idx: torch.Tensor, input_pos: torch.Tensor,
+                               out_page_table: torch.Tensor, out_seqused_k: torch.Tensor, page_size: int, *,
+                               n_new: int = 1, out_slot_mapping: Optional[torch.Tensor] = None,
+                               out_positions: Optional[torch.Tensor] = None) -> tuple[torch.Tensor, torch.Tensor]:
+    """One launch for the head of a decode step (``kestrel/models/moondream/runtime.py:2554-2564``):
+    :func:`build_paged_kv_metadata`, the int64 ``position_ids`` and the slot mapping of the ``n_new``
+    tokens per row that end at ``input_pos``.  Returns ``(slot_mapping, position_ids)``, both int64
+    ``[B, n_new]`` (written into ``out_slot_mapping`` / ``out_positions`` when given)."""
+    dev = _require_cuda("page_table", page_table)
+    for nm, t in (("batch_idx", batch_idx), ("input_pos", input_pos), ("out_page_table", out_page_table),
+                  ("out_seqused_k", out_seqused_k)):
+        if _require_cuda(nm, t) != dev:
+            raise ValueError(f"{nm} must live on the page table's device")
+    if page_table.dtype != torch.int32 or out_page_table.dtype != torch.int32:
+        raise ValueError("page tables must be int32")
+    if input_pos.dtype != torch.int32 or out_seqused_k.dtype != torch.int32:
+        raise ValueError("input_pos and out_seqused_k must be int32")
+    if batch_idx.dtype not in (torch.int32, torch.int64) or batch_idx.ndim != 1 or input_pos.ndim != 1:
+        raise ValueError("batch_idx must be 1-D int32/int64 and input_pos 1-D")
+    if page_table.ndim != 2 or out_page_table.ndim != 2 or page_table.stride(1) != 1 or out_page_table.stride(1) != 1:
+        raise ValueError("page tables must be 2-D and contiguous in the last dimension")
+    B = batch_idx.shape[0]
+    n_new = int(n_new)
+    if n_new < 1:
+        raise ValueError("n_new must be at least 1")
+    if input_pos.shape[0] != B or out_page_table.shape[0] < B or out_seqused_k.shape[0] < B:
+        raise ValueError("metadata buffers are smaller than the batch")
+    if not out_seqused_k.is_contiguous():
+        raise ValueError("out_seqused_k must be contiguous")
+    outs = []
+    for nm, t in (("out_slot_mapping", out_slot_mapping), ("out_positions", out_positions)):
+        if t is None:
+            t = torch.empty((B, n_new), dtype=torch.int64, device=page_table.device)
+        elif (t.dtype != torch.int64 or t.shape != (B, n_new) or not t.is_contiguous()
+              or _require_cuda(nm, t) != dev):
+            raise ValueError(f"{nm} must be a contiguous int64 [batch, n_new] tensor on the page table's device")
+        outs.append(t)
+    slots, positions = outs
+    if B == 0:
+        return slots, positions
+    batch_idx = batch_idx.contiguous()
+    input_pos = input_pos.contiguous()
+    lib = _native.load()
+    _native.check(lib.kb200_build_decode_step_metadata(
+        page_table.data_ptr(), page_table.stride(0), page_table.shape[0], page_table.shape[1],
+        batch_idx.data_ptr(), int(batch_idx.dtype == torch.int64), input_pos.data_ptr(),
+        out_page_table.data_ptr(), out_page_table.stride(0), out_page_table.shape[1],
+        out_seqused_k.data_ptr(), slots.data_ptr(), positions.data_ptr(), B, n_new, int(page_size),
+        dev, _stream(dev)))
+    return slots, positions
+
+
+def _token_rows(name: str, t: torch.Tensor) -> tuple[torch.Tensor, int, int, int]:
+    """``[T, H, D]`` view of ``t`` (``[T, H, D]`` or ``[B, S, H, D]``) without copying; heads and
+    head_dim must be compact, the token stride is free (slices of a fused projection)."""
+    if t.ndim == 4:
+        B, S, H, D = t.shape
+        sb, ss, sh, sd = t.stride()
+        if sd != 1 or sh != D:
+            raise ValueError(f"{name} must be compact across heads/head_dim; got stride={t.stride()}")
+        if B == 1:
+            t = t[0]
+        elif S == 1:
+            t = t[:, 0]
+        elif sb == S * ss:
+            t = t.as_strided((B * S, H, D), (ss, sh, sd), t.storage_offset())
+        else:
+            raise ValueError(f"{name} cannot be viewed as token rows; got shape={tuple(t.shape)} stride={t.stride()}")
+    if t.ndim != 3:
+        raise ValueError(f"{name} must have shape [tokens, heads, head_dim] or [batch, seq, heads, head_dim]")
+    T, H, D = t.shape
+    if t.stride(2) != 1 or t.stride(1) != D:
+        raise ValueError(f"{name} must be compact across heads/head_dim; got stride={t.stride()}")
+    return t, T, H, D
+
+
+def rope_reshape_and_cache(positions: torch.Tensor, q: Optional[torch.Tensor], k: torch.Tensor,
+                           v: Optional[torch.Tensor], cos_sin_cache: torch.Tensor,
+                           key_cache: Optional[torch.Tensor] = None, value_cache: Optional[torch.Tensor] = None,
+                           slot_mapping: Optional[torch.Tensor] = None, kv_cache_dtype: str = "auto",
+                           k_scale: Optional[torch.Tensor] = None, v_scale: Optional[torch.Tensor] = None, *,
+                           write_k: bool = True) -> None:
+    """Rotary embedding of ``q`` and ``k`` in place and, when the pools are given, the append of
+    rotated ``k`` plus ``v`` in the same launch -- ``rotary_embedding`` followed by
+    ``PagedKVCache.update`` (``kestrel/models/moondream/text.py:125`` and ``:132``).
+
+    ``positions`` int32/int64 with one entry per token row; ``q``/``k``/``v`` ``[T, H, D]`` or
+    ``[B, S, H, D]`` views (``q`` may be ``None``); ``cos_sin_cache`` fp32 ``[max_pos, rot_dim]`` in the
+    layout of ``kestrel/models/moondream/rope.py:6-32``.  Pool arguments as
+    :func:`reshape_and_cache_flash`; with ``write_k=False`` the rotated K only goes to the pool.
+    The pool contents are bit-identical to the two separate calls.
+    """
+    dev = _require_cuda("k", k)
+    k_rows, T, Hkv, D = _token_rows("k", k)
+    Hq = 0
+    q_rows = None
+    if q is not None:
+        if _require_cuda("q", q) != dev or q.dtype != k.dtype:
+            raise ValueError("q must live on k's device and share its dtype")
+        q_rows, Tq, Hq, Dq = _token_rows("q", q)
+        if (Tq, Dq) != (T, D):
+            raise ValueError("q and k disagree on token count or head_dim")
+    in_dt = _TORCH_TO_DTYPE.get(k.dtype)
+    if in_dt is None or k.dtype in (torch.uint8, torch.float8_e4m3fn):
+        raise ValueError(f"unsupported row dtype {k.dtype}")
+    if _require_cuda("positions", positions) != dev or positions.dtype not in (torch.int32, torch.int64):
+        raise ValueError("positions must be an int32/int64 tensor on k's device")
+    if positions.numel() != T:
+        raise ValueError("positions must hold one entry per token row")
+    positions = positions.contiguous()
+    if (_require_cuda("cos_sin_cache", cos_sin_cache) != dev or cos_sin_cache.dtype != torch.float32
+            or cos_sin_cache.ndim != 2 or cos_sin_cache.stride(1) != 1):
+        raise ValueError("cos_sin_cache must be an fp32 [max_pos, rot_dim] tensor on k's device")
+    max_pos, rot = cos_sin_cache.shape
+    if rot % 2 or rot > D or rot <= 0:
+        raise ValueError(f"rot_dim {rot} must be even and at most head_dim {D}")
+    append = key_cache is not None
+    ptrs = dict(kc=None, vc=None, slots=None, ks=None, vs=None)
+    ps = ts = hs = 0
+    n_pages, P, n_scales = 0, 1, 1
+    cache_dt = in_dt
+    v_rows = None
+    if append:
+        if v is None or value_cache is None or slot_mapping is None:
+            raise ValueError("the fused append needs v, value_cache and slot_mapping")
+        if _require_cuda("v", v) != dev or v.dtype != k.dtype:
+            raise ValueError("v must live on k's device and share its dtype")
+        v_rows, Tv, Hv, Dv = _token_rows("v", v)
+        if (Tv, Hv, Dv) != (T, Hkv, D):
+            raise ValueError("k and v must have the same shape")
+        n_pages, P, Hc, Dc, ps, ts, hs = _cache_view_geometry("key_cache", key_cache)
+        if _cache_view_geometry("value_cache", value_cache) != (n_pages, P, Hc, Dc, ps, ts, hs):
+            raise ValueError("key_cache and value_cache must have the same shape and strides")
+        if (Hc, Dc) != (Hkv, D):
+            raise ValueError(f"cache heads/head_dim {(Hc, Dc)} do not match the rows {(Hkv, D)}")
+        for nm, t in (("key_cache", key_cache), ("value_cache", value_cache), ("slot_mapping", slot_mapping)):
+            if _require_cuda(nm, t) != dev:
+                raise ValueError(f"{nm} lives on a different device than k")
+        if slot_mapping.dtype != torch.int64 or not slot_mapping.is_contiguous() or slot_mapping.numel() != T:
+            raise ValueError("slot_mapping must be a contiguous int64 tensor with one entry per token row")
+        if str(kv_cache_dtype).startswith("fp8"):
+            if key_cache.dtype not in (torch.uint8, torch.float8_e4m3fn):
+                raise ValueError("fp8 kv_cache_dtype needs uint8 or float8_e4m3fn caches")
+            cache_dt = _native.DTYPE_E4M3
+            for nm, s in (("k_scale", k_scale), ("v_scale", v_scale)):
+                if s is None or s.dtype != torch.float32 or _require_cuda(nm, s) != dev:
+                    raise ValueError(f"{nm} must be an fp32 tensor on the cache device")
+                if s.numel() not in (1, Hkv) or not s.is_contiguous():
+                    raise ValueError(f"{nm} must hold 1 or n_kv_heads contiguous values")
+            if k_scale.numel() != v_scale.numel():
+                raise ValueError("k_scale and v_scale must have the same number of elements")
+            n_scales = k_scale.numel()
+            ptrs["ks"], ptrs["vs"] = k_scale.data_ptr(), v_scale.data_ptr()
+        elif key_cache.dtype != k.dtype:
+            raise ValueError(f"cache dtype {key_cache.dtype} does not match row dtype {k.dtype}")
+        ptrs["kc"], ptrs["vc"], ptrs["slots"] = key_cache.data_ptr(), value_cache.data_ptr(), slot_mapping.data_ptr()
+    if T == 0:
+        return
+    lib = _native.load()
+    _native.check(lib.kb200_rope_append(
+        q_rows.data_ptr() if q_rows is not None else None, k_rows.data_ptr(),
+        v_rows.data_ptr() if v_rows is not None else None,
+        q_rows.stride(0) if q_rows is not None else 0, k_rows.stride(0),
+        v_rows.stride(0) if v_rows is not None else 0, T, Hq, Hkv, D, rot,
+        positions.data_ptr(), int(positions.dtype == torch.int64),
+        cos_sin_cache.data_ptr(), max_pos, cos_sin_cache.stride(0),
+        ptrs["kc"], ptrs["vc"], ps, ts, hs, ptrs["slots"], n_pages, P, in_dt, cache_dt,
+        ptrs["ks"], ptrs["vs"], n_scales, 1 if write_k else 0, dev, _stream(dev)))
+
+
+def rotary_embedding(position_ids: torch.Tensor, q: torch.Tensor, k: torch.Tensor, head_dim: int,
+                     cos_sin_cache: torch.Tensor) -> None:
+    """In-place rotary embedding of ``q`` and ``k`` (``[B, S, H, D]``) with the call shape of
+    ``kestrel_kernels``' ``rotary.rotary_embedding`` (``kestrel/models/moondream/text.py:34,125``)."""
+    if q.shape[-1] != head_dim or k.shape[-1] != head_dim:
+        raise ValueError("head_dim does not match q/k")
+    rope_reshape_and_cache(position_ids, q, k, None, cos_sin_cache)
+
+
 def copy_pages(caches: Sequence[torch.Tensor], src_pages, dst_pages) -> None:
     """Copy-on-write: copy physical page ``src_pages[i]`` onto ``dst_pages[i]`` in every pool of
     ``caches`` (each ``[n_pages, ...]`` with contiguous pages; all the same geometry) in one launch.
@@ -461,7 +640,16 @@ class _CacheOps:
     reshape_and_cache_flash = staticmethod(reshape_and_cache_flash)
     build_paged_kv_metadata = staticmethod(build_paged_kv_metadata)
     build_slot_mapping = staticmethod(build_slot_mapping)
+    build_decode_step_metadata = staticmethod(build_decode_step_metadata)
+    rope_reshape_and_cache = staticmethod(rope_reshape_and_cache)
     copy_pages = staticmethod(copy_pages)
+
+
+class _RotaryOps:
+    rotary_embedding = staticmethod(rotary_embedding)
+
+    def __getattr__(self, item: str):
+        raise NotImplementedError(f"kestrel_kernels.rotary.{item} is outside the paged-KV path")
 
 
 class _AttentionOps:
@@ -477,7 +665,8 @@ class Runtime:
     def __init__(self) -> None:
         self.cache = _CacheOps()
         self.attention = _AttentionOps()
-        for name in ("rotary", "linear", "vision", "dense", "tau", "moe", "gated_delta", "sampling",
+        self.rotary = _RotaryOps()
+        for name in ("linear", "vision", "dense", "tau", "moe", "gated_delta", "sampling",
                      "megakernel", "generated_decode", "linear_ops"):
             setattr(self, name, _Unavailable(name))
 

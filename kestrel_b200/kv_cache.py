@@ -176,6 +176,22 @@ class PagedKVCache(torch.nn.Module):
             slots, self._kv_cache_dtype, self.k_scale_tensor.view(-1), self.v_scale_tensor.view(-1))
         return k_val, v_val
 
+    def rope_update(self, input_pos, q, k_val, v_val, cos_sin_cache: torch.Tensor, *,
+                    slot_mapping: torch.Tensor, write_k: bool = True):
+        """Rotary embedding of ``q`` and ``k_val`` at ``input_pos`` followed by :meth:`update`, as
+        one kernel launch (``kestrel/models/moondream/text.py:125`` then ``:132``).  ``q`` and
+        ``k_val`` are rotated in place; the pools end up bit-identical to the two separate calls.
+        Not in the reference."""
+        if slot_mapping.shape != input_pos.shape:
+            raise ValueError("slot_mapping must match input_pos shape")
+        slots = slot_mapping.to(device=k_val.device, dtype=torch.int64).contiguous().view(-1)
+        _k.rope_reshape_and_cache(
+            input_pos.reshape(-1), q, k_val, v_val, cos_sin_cache,
+            self.k_cache.permute(0, 2, 1, 3), self.v_cache.permute(0, 2, 1, 3),
+            slots, self._kv_cache_dtype, self.k_scale_tensor.view(-1), self.v_scale_tensor.view(-1),
+            write_k=write_k)
+        return k_val, v_val
+
 
 @dataclass(frozen=True, slots=True)
 class PagedKVLayerSpec:
@@ -480,3 +496,17 @@ class PageTable:
             return
         _k.build_paged_kv_metadata(self.page_table, batch_idx, input_pos, out_page_table, out_seqused_k,
                                    self.page_size)
+
+    def populate_decode_step(self, *, batch_idx: torch.Tensor, input_pos: torch.Tensor,
+                             out_page_table: torch.Tensor, out_seqused_k: torch.Tensor, n_new: int = 1,
+                             out_slot_mapping: Optional[torch.Tensor] = None,
+                             out_positions: Optional[torch.Tensor] = None) -> tuple[torch.Tensor, torch.Tensor]:
+        """:meth:`populate_paged_kv_metadata`, ``position_ids`` and :meth:`build_slot_mapping` for
+        the ``n_new`` tokens per row ending at ``input_pos`` in one launch (the three steps at
+        ``kestrel/models/moondream/runtime.py:2554-2564``).  Returns ``(slot_mapping, position_ids)``,
+        int64 ``[B, n_new]``.  Not in the reference."""
+        if out_page_table.ndim != 2 or out_page_table.shape[1] < self.n_pages:
+            raise ValueError("out_page_table has insufficient page capacity")
+        return _k.build_decode_step_metadata(self.page_table, batch_idx, input_pos, out_page_table, out_seqused_k,
+                                             self.page_size, n_new=n_new, out_slot_mapping=out_slot_mapping,
+                                             out_positions=out_positions)

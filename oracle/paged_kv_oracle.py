@@ -17,6 +17,12 @@ What it restates (paths are relative to the m87-labs/kestrel v0.5.0 tree):
                              ``kestrel/models/moondream/text.py:132-185``
 * FP8 e4m3 quantise       -- ``reshape_and_cache_flash(..., "fp8_e4m3", k_scale, v_scale)`` as called
                              at ``kestrel/kv_cache.py:222-231``
+* rotary embedding        -- ``rotary_embedding(position_ids, q, k, head_dim, cos_sin_cache)`` as called at
+                             ``kestrel/models/moondream/text.py:125`` on the table of
+                             ``kestrel/models/moondream/rope.py:6-32``; rotate-half formula of
+                             ``kestrel/ops/rotary.py:58-72``
+* per-step metadata       -- ``kestrel/models/moondream/runtime.py:2554-2564`` (metadata builder, then
+                             ``input_pos.to(long).view(-1, 1)`` and the slot mapping of those positions)
 * copy-on-write page copy -- no counterpart in the reference (it forbids prefix caching
                              with page_size > 1, ``kestrel/kv_cache.py:331-335``)
 
@@ -30,7 +36,11 @@ for those two this oracle *defines* the semantics from the call sites
 bottom-right aligned causal mask, fp32 softmax; FP8 code =
 round-to-nearest-even, saturate-to-finite of ``x / scale``): **parity
 unpinned** for attention outputs and FP8 codes; the FP8 encoder is
-cross-checked against ``torch.float8_e4m3fn``.
+cross-checked against ``torch.float8_e4m3fn``.  The rotary kernel is in the same
+wheel: its cos/sin table and the rotate-half formula are pinned (fixtures made
+from ``rope.py`` and ``ops/rotary.py``), the rounding of 16-bit rows is defined
+here as "fp32 arithmetic with separately rounded products, one rounding to the
+row dtype" -- **parity unpinned** for that rounding.
 """
 
 from __future__ import annotations
@@ -297,3 +307,49 @@ def decode_step(q, k_new, v_new, k_cache, v_cache, page_table_rows, batch_idx, i
     out = paged_attention(q, k_cache, v_cache, compact, seqused, softmax_scale=softmax_scale,
                           k_scale=k_scale, v_scale=v_scale)
     return out, seqused
+
+
+# ----------------------------------------------------------------------------
+# Rotary embedding (NeoX pairing, partial rotary) and the per-step metadata
+# ----------------------------------------------------------------------------
+
+def precompute_freqs_cis(dim: int, end: int, theta: float) -> torch.Tensor:
+    """fp32 ``[end, dim]`` table: cos of ``dim/2`` frequencies then their sin
+    (``kestrel/models/moondream/rope.py:6-32``); ``dim`` is the rotated width."""
+    inv_freq = 1.0 / (theta ** (torch.arange(0, dim, 2, dtype=torch.float32) / float(dim)))
+    freqs = torch.arange(end, dtype=torch.float32).unsqueeze(1) * inv_freq.unsqueeze(0)
+    return torch.cat([torch.cos(freqs), torch.sin(freqs)], dim=-1)
+
+
+def rotary_embedding(positions: torch.Tensor, x: torch.Tensor, cos_sin_cache: torch.Tensor) -> torch.Tensor:
+    """Rotated copy of ``x [T, H, D]`` (any float dtype) for ``positions [T]``.
+
+    Elements ``i`` and ``i + rot/2`` (``rot = cos_sin_cache.shape[1]``) form a pair,
+    ``y1 = x1*cos - x2*sin``, ``y2 = x2*cos + x1*sin`` in fp32 (two rounded products,
+    one rounded sum: what ``tensor*cos + rotate_half(tensor)*sin`` of
+    ``kestrel/ops/rotary.py:58-72`` evaluates to in fp32), result rounded to ``x.dtype``;
+    elements past ``rot`` are unchanged (call site ``kestrel/models/moondream/text.py:125``)."""
+    rot = cos_sin_cache.shape[1]
+    half = rot // 2
+    cs = cos_sin_cache[positions.reshape(-1).long()].float()
+    cos, sin = cs[:, None, :half], cs[:, None, half:]
+    xf = x.float()
+    x1, x2 = xf[..., :half], xf[..., half:rot]
+    y1 = x1 * cos - x2 * sin
+    y2 = x2 * cos + x1 * sin
+    out = xf.clone()
+    out[..., :half] = y1
+    out[..., half:rot] = y2
+    return out.to(x.dtype)
+
+
+def build_decode_step_metadata(page_table: torch.Tensor, batch_idx: torch.Tensor, input_pos: torch.Tensor,
+                               out_page_table: torch.Tensor, out_seqused_k: torch.Tensor, page_size: int,
+                               n_new: int = 1) -> tuple[torch.Tensor, torch.Tensor]:
+    """The metadata builder followed by the slot mapping of the ``n_new`` positions that end at
+    ``input_pos`` (``kestrel/models/moondream/runtime.py:2554-2564``); returns ``(slots, positions)``,
+    both int64 ``[B, n_new]``."""
+    build_paged_kv_metadata(page_table, batch_idx, input_pos, out_page_table, out_seqused_k, page_size)
+    positions = input_pos.to(torch.int64).view(-1, 1) - (n_new - 1) + torch.arange(n_new, dtype=torch.int64).view(1, -1)
+    slots = build_slot_mapping(page_table, batch_idx.view(-1), positions, page_size)
+    return slots, positions

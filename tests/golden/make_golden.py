@@ -15,6 +15,9 @@ take its torch path (``kestrel/kv_cache.py:216-220``) -- and records:
 * ``meta_*``          the vector of ``tests/test_page_table.py:48-79`` with the outputs its
                       assertions require (checked here against the torch restatement in
                       ``kestrel/models/qwen35/runtime.py:1161-1166``);
+* ``rope_vectors.npz``  the cos/sin table of ``kestrel/models/moondream/rope.py`` (Moondream's
+                      geometry: 32 rotated of 64 head dims, theta 1.5e6) and fp32 rows rotated with
+                      ``kestrel/ops/rotary.py:apply_rotary`` (both files loaded by path, unmodified);
 * ``page_table_traces.json``   random op sequences on the reference ``PageTable`` with every
                       return value and the resulting host state.
 
@@ -339,6 +342,37 @@ def radix_traces(root: str):
     return traces
 
 
+def rope_vectors(root: str) -> dict[str, np.ndarray]:
+    import importlib.util
+
+    def load(name, rel):
+        spec = importlib.util.spec_from_file_location(name, str(Path(root) / rel))
+        mod = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(mod)
+        return mod
+
+    rope = load("_ref_rope", "kestrel/models/moondream/rope.py")
+    rotary = load("_ref_rotary", "kestrel/ops/rotary.py")
+    out: dict[str, np.ndarray] = {}
+    rot, end, theta = 32, 96, 1_500_000.0
+    table = rope.precompute_freqs_cis(rot, end, theta)
+    out["table"] = table.numpy()
+    out["table_args"] = np.array([rot, end, theta], dtype=np.float64)
+    g = torch.Generator().manual_seed(301)
+    T, H, D = 7, 3, 64
+    x = torch.randn(T, H, D, generator=g)
+    pos = torch.randint(0, end, (T,), generator=g)
+    half = rot // 2
+    cos = torch.cat([table[pos, :half], table[pos, :half]], dim=-1)   # [T, rot], the cat(freqs, freqs) layout
+    sin = torch.cat([table[pos, half:], table[pos, half:]], dim=-1)
+    y = x.clone()
+    y[..., :rot] = rotary.apply_rotary(x[..., :rot], cos, sin, unsqueeze_dim=1)
+    out["x"] = x.numpy()
+    out["pos"] = pos.numpy()
+    out["y"] = y.numpy()
+    return out
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", default="/root/reference")
@@ -361,6 +395,7 @@ def main() -> None:
     (HERE / "reference_vectors.json").write_text(json.dumps(metas, indent=1))
     (HERE / "page_table_traces.json").write_text(json.dumps(page_table_traces(kc)))
     (HERE / "radix_traces.json").write_text(json.dumps(radix_traces(args.reference)))
+    np.savez_compressed(HERE / "rope_vectors.npz", **rope_vectors(args.reference))
     print("wrote", sorted(p.name for p in HERE.iterdir()))
 
 

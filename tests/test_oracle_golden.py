@@ -179,3 +179,51 @@ def test_copy_pages_and_decode_step():
         got = O.gather_kv(kc, p["page_table"][b], p["lengths"][b])[-1]
         assert torch.equal(got, k_new[b, 0])
     assert out.shape == (2, 1, 4, 8) and torch.isfinite(out).all()
+
+
+# ---------------------------------------------------------------------------
+# rotary embedding and the per-step metadata
+# ---------------------------------------------------------------------------
+
+def test_rope_table_matches_reference(golden_dir):
+    vec = np.load(golden_dir / "rope_vectors.npz")
+    rot, end, theta = vec["table_args"].tolist()
+    got = O.precompute_freqs_cis(int(rot), int(end), float(theta))
+    want = torch.from_numpy(vec["table"])
+    assert got.shape == want.shape and got.dtype == torch.float32
+    # cos/sin come from the host's libm: allow the last bit
+    assert (got - want).abs().max().item() <= 2.0 ** -23
+
+
+def test_rope_matches_reference_rotate_half_in_fp32(golden_dir):
+    vec = np.load(golden_dir / "rope_vectors.npz")
+    x, pos, want = (torch.from_numpy(vec[k]) for k in ("x", "pos", "y"))
+    got = O.rotary_embedding(pos, x, torch.from_numpy(vec["table"]))
+    assert torch.equal(got.view(torch.int32), want.view(torch.int32))
+    # elements past the rotated width pass through
+    rot = vec["table"].shape[1]
+    assert torch.equal(got[..., rot:], x[..., rot:])
+
+
+def test_rope_rounds_once_to_the_row_dtype():
+    g = torch.Generator().manual_seed(5)
+    table = O.precompute_freqs_cis(32, 128, 1.5e6)
+    x = torch.randn(9, 2, 64, generator=g).to(torch.bfloat16)
+    pos = torch.randint(0, 128, (9,), generator=g)
+    got = O.rotary_embedding(pos, x, table)
+    assert got.dtype == torch.bfloat16
+    assert torch.equal(got, O.rotary_embedding(pos, x.float(), table).to(torch.bfloat16))
+    assert torch.equal(O.rotary_embedding(torch.zeros(9, dtype=torch.long), x, table), x)  # angle 0
+
+
+def test_decode_step_metadata_is_metadata_then_slot_mapping(vec):
+    table = torch.from_numpy(vec["meta_table"])
+    batch = torch.from_numpy(vec["meta_batch"])
+    pos = torch.from_numpy(vec["meta_pos"])
+    out_pt = torch.full((2, 16), -99, dtype=torch.int32)
+    out_sk = torch.zeros(2, dtype=torch.int32)
+    slots, positions = O.build_decode_step_metadata(table, batch, pos, out_pt, out_sk, 4, n_new=3)
+    assert torch.equal(out_pt, torch.from_numpy(vec["meta_out_table"]))
+    assert torch.equal(out_sk, torch.from_numpy(vec["meta_out_seqused"]))
+    assert positions.tolist() == [[5, 6, 7], [6, 7, 8]]
+    assert torch.equal(slots, O.build_slot_mapping(table, batch, positions, 4))
