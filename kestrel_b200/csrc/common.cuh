@@ -130,6 +130,7 @@ enum KernelId : int {
   KID_ATTN = 6,
   KID_ATTN_MERGE = 7,
   KID_ROPE_APPEND = 8,
+  KID_PREFILL = 9,
 };
 
 }  // namespace kb200

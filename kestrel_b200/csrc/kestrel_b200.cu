@@ -4,6 +4,7 @@
 #include "cache_ops.cuh"
 #include "rope_append.cuh"
 #include "paged_attention.cuh"
+#include "paged_prefill.cuh"
 
 using namespace kb200;
 

@@ -1244,8 +1244,9 @@ struct TmapKey {
   const void* base;
   int64_t page_stride, token_stride, head_stride, n_pages;
   int32_t page_size, hkv, hd, dtype, device;
+  int32_t box_rows = 0;   // filled in by get_pool_tmap
   bool operator==(const TmapKey& o) const {
-    return base == o.base && page_stride == o.page_stride && token_stride == o.token_stride &&
+    return box_rows == o.box_rows && base == o.base && page_stride == o.page_stride && token_stride == o.token_stride &&
            head_stride == o.head_stride && n_pages == o.n_pages && page_size == o.page_size &&
            hkv == o.hkv && hd == o.hd && dtype == o.dtype && device == o.device;
   }
@@ -1256,14 +1257,16 @@ struct TmapKeyHash {
     auto mix = [&](uint64_t v) { h ^= v + 0x9e3779b97f4a7c15ull + (h << 6) + (h >> 2); };
     mix((uint64_t)k.page_stride); mix((uint64_t)k.token_stride); mix((uint64_t)k.head_stride);
     mix((uint64_t)k.n_pages); mix((uint64_t)k.page_size); mix((uint64_t)k.hkv); mix((uint64_t)k.hd);
-    mix((uint64_t)k.dtype); mix((uint64_t)k.device);
+    mix((uint64_t)k.dtype); mix((uint64_t)k.device); mix((uint64_t)k.box_rows);
     return h;
   }
 };
 
 // One tensor map per pool view: dims (innermost first) D, P, H_kv, n_pages;
 // box = (128 bytes of D, min(P, TILE_N) tokens, 1 head, 1 page), 128-byte swizzle.
-inline int get_pool_tmap(const TmapKey& key, int tile_n, CUtensorMap* out) {
+inline int get_pool_tmap(const TmapKey& key_in, int tile_n, CUtensorMap* out) {
+  TmapKey key = key_in;
+  key.box_rows = key.page_size < tile_n ? key.page_size : tile_n;
   static std::mutex mu;
   static std::unordered_map<TmapKey, CUtensorMap, TmapKeyHash> cache;
   {
@@ -1276,7 +1279,7 @@ inline int get_pool_tmap(const TmapKey& key, int tile_n, CUtensorMap* out) {
   const int es = dtype_size(key.dtype);
   const int row_bytes = key.hd * es;
   const int rb = row_bytes > 128 ? 128 : row_bytes;
-  const int box_rows = key.page_size < tile_n ? key.page_size : tile_n;
+  const int box_rows = key.box_rows;
   cuuint64_t dims[4] = {(cuuint64_t)key.hd, (cuuint64_t)key.page_size, (cuuint64_t)key.hkv, (cuuint64_t)key.n_pages};
   cuuint64_t strides[3] = {(cuuint64_t)(key.token_stride * es), (cuuint64_t)(key.head_stride * es),
                            (cuuint64_t)(key.page_stride * es)};
@@ -1434,6 +1437,13 @@ inline int launch_attn_dispatch(bool d128, int nw, const CUtensorMap& tmK, const
               : launch_attn_hd<KVB, BF16, 64>(nw, tmK, tmV, p, grid, dev, stream);
 }
 
+// paged_prefill.cuh
+bool prefill_enabled();
+template <int HD, bool BF16>
+int launch_prefill_variant(const CUtensorMap& tmK, const CUtensorMap& tmV, const AttnParams& p, int grid, int dev,
+                           cudaStream_t stream);
+constexpr int kPrefillRowsPerSeg = 128, kPrefillTileKeys = 128, kPrefillMinPackedRows = 64;
+
 inline int launch_paged_attention(const kb200_attn_args* a) {
   KB200_REQUIRE(a != nullptr, "args is null");
   KB200_REQUIRE(a->struct_bytes == sizeof(kb200_attn_args), "kb200_attn_args size mismatch: got %u, built with %zu",
@@ -1477,10 +1487,14 @@ inline int launch_paged_attention(const kb200_attn_args* a) {
                 (unsigned long long)a->workspace_bytes);
   KB200_REQUIRE((reinterpret_cast<uintptr_t>(a->workspace) & 255) == 0, "workspace must be 256-byte aligned");
 
-  const int tile_n = tile_n_for(a->kv_dtype, a->head_dim, nw);
+  // Many query rows per sequence (prompt chunks) with 16-bit K/V: the tensor-memory kernel, one
+  // CTA per 128 packed rows, no split over keys and no merge.
+  const bool prefill = prefill_enabled() && a->kv_dtype != KB200_DTYPE_E4M3 &&
+                       (int64_t)group * a->seqlen_q >= kPrefillMinPackedRows;
+  const int tile_n = prefill ? kPrefillTileKeys : tile_n_for(a->kv_dtype, a->head_dim, nw);
   // The transposed decode kernel pays off where the math is the limiter (e4m3 K/V); 16-bit K/V
   // is within a few percent of the HBM roofline with the general kernel already.
-  const bool decode8 = decode8_enabled() && a->kv_dtype == KB200_DTYPE_E4M3 &&
+  const bool decode8 = !prefill && decode8_enabled() && a->kv_dtype == KB200_DTYPE_E4M3 &&
                        (int64_t)group * a->seqlen_q <= kDecodeRows;
   {
     // every copy lands on a 128-byte boundary of shared memory
@@ -1542,7 +1556,7 @@ inline int launch_paged_attention(const kb200_attn_args* a) {
   p.q_is_bf16 = a->q_dtype == KB200_DTYPE_BF16;
   p.n_workers = n_workers;
   p.tile_n = tile_n;
-  p.rows_per_seg = decode8 ? kDecodeRows : kRowsPerSeg;
+  p.rows_per_seg = prefill ? kPrefillRowsPerSeg : decode8 ? kDecodeRows : kRowsPerSeg;
   p.uniform_nseg = (packed || a->seqused_q) ? 0
                    : a->n_kv_heads * ((group * a->seqlen_q + p.rows_per_seg - 1) / p.rows_per_seg);
 
@@ -1551,6 +1565,17 @@ inline int launch_paged_attention(const kb200_attn_args* a) {
 
   int rc;
   const bool d128 = a->head_dim == 128;
+  if (prefill) {
+    const int64_t nseg = packed ? (int64_t)a->n_kv_heads * ((group * a->total_q + kPrefillRowsPerSeg - 1) / kPrefillRowsPerSeg + a->batch)
+                                : a->batch * (int64_t)a->n_kv_heads * ((group * (int64_t)a->seqlen_q + kPrefillRowsPerSeg - 1) / kPrefillRowsPerSeg);
+    KB200_REQUIRE(nseg <= 0x7fffffff, "too many segments");
+    const bool bf = a->kv_dtype == KB200_DTYPE_BF16;
+    if (d128) rc = bf ? launch_prefill_variant<128, true>(tmK, tmV, p, (int)nseg, a->device, stream)
+                      : launch_prefill_variant<128, false>(tmK, tmV, p, (int)nseg, a->device, stream);
+    else rc = bf ? launch_prefill_variant<64, true>(tmK, tmV, p, (int)nseg, a->device, stream)
+                 : launch_prefill_variant<64, false>(tmK, tmV, p, (int)nseg, a->device, stream);
+    return rc;   // every segment is written by its own CTA: nothing to merge
+  }
   if (decode8)  // e4m3 only (the kernel template also covers 16-bit K/V; measured no faster there)
     rc = launch_decode_dispatch<1, false>(d128, nw, tmK, tmV, p, grid, a->device, stream);
   else if (a->kv_dtype == KB200_DTYPE_E4M3)

@@ -1,0 +1,120 @@
+"""GPU parity of the paged prefill attention (many query rows per sequence, the tensor-memory
+kernel) against the fp32 CPU oracle, through the same ``flash_attn_fwd`` surface and with the same
+tolerance as the decode tests: ``|got - want| <= 2e-2 + 1e-2 * |want|`` per element and a relative
+L2 error per output row of at most 1e-2."""
+
+import pytest
+import torch
+
+from helpers import make_paged_problem
+from kestrel_b200 import _native, kernels
+from oracle import paged_kv_oracle as O
+from test_gpu_attention import assert_close, run_case
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+@pytest.fixture(autouse=True)
+def _clean_status():
+    _native.device_status(torch.cuda.current_device(), clear=True)
+    yield
+    flags = _native.device_status(torch.cuda.current_device(), clear=True)
+    assert flags[0] == 0, f"kernel diagnostics: {flags}"
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("head_dim", [128, 64])
+def test_prefill_chunk_on_a_cached_prefix(dtype, head_dim):
+    # a 128-token prompt chunk per sequence on top of contexts of assorted lengths (bottom-right causal)
+    lengths = [128, 129, 200, 729 + 128, 1000, 143, 257, 2048]
+    p = make_paged_problem(seed=11, batch=len(lengths), len_lo=0, len_hi=0, n_q_heads=32, n_kv_heads=8,
+                           head_dim=head_dim, page_size=16, seqlen_q=128, dtype=dtype, lengths=lengths)
+    out, want = run_case(p, dtype)
+    assert_close(out, want, f"prefill chunk {dtype} D={head_dim}")
+
+
+@pytest.mark.parametrize("seqlen_q,group,heads_kv,head_dim", [(16, 4, 8, 128), (37, 4, 2, 128), (64, 1, 4, 64),
+                                                               (100, 8, 1, 128), (33, 2, 3, 64), (130, 1, 2, 128),
+                                                               (21, 6, 2, 128)])
+def test_prefill_shapes_and_gqa(seqlen_q, group, heads_kv, head_dim):
+    lengths = [seqlen_q, seqlen_q + 1, seqlen_q + 15, seqlen_q + 113, 3 * seqlen_q + 500, max(1, seqlen_q - 5), 7]
+    p = make_paged_problem(seed=12 + seqlen_q, batch=len(lengths), len_lo=0, len_hi=0, n_q_heads=group * heads_kv,
+                           n_kv_heads=heads_kv, head_dim=head_dim, page_size=16, seqlen_q=seqlen_q,
+                           dtype=torch.bfloat16, lengths=lengths)
+    out, want = run_case(p, torch.bfloat16)
+    assert_close(out, want, f"Sq={seqlen_q} G={group} Hkv={heads_kv} D={head_dim}")
+
+
+@pytest.mark.parametrize("page_size", [1, 2, 8, 16, 64, 256])
+def test_prefill_page_sizes(page_size):
+    lengths = [300, 64, 65, 1, 513]
+    p = make_paged_problem(seed=13, batch=len(lengths), len_lo=0, len_hi=0, n_q_heads=8, n_kv_heads=2, head_dim=128,
+                           page_size=page_size, seqlen_q=32, dtype=torch.bfloat16, lengths=lengths)
+    out, want = run_case(p, torch.bfloat16)
+    assert_close(out, want, f"page_size={page_size}")
+
+
+@pytest.mark.parametrize("causal,window", [(False, None), (True, 63), (True, 200), (True, 0)])
+def test_prefill_non_causal_and_sliding_window(causal, window):
+    lengths = [64, 100, 400, 1500]
+    p = make_paged_problem(seed=14, batch=len(lengths), len_lo=0, len_hi=0, n_q_heads=16, n_kv_heads=4, head_dim=128,
+                           page_size=16, seqlen_q=48, dtype=torch.bfloat16, lengths=lengths)
+    out, want = run_case(p, torch.bfloat16, causal=causal, window=window)
+    assert_close(out, want, f"causal={causal} window={window}")
+
+
+def test_prefill_seqused_q_lse_and_empty_sequences():
+    lengths = [500, 0, 77, 1024, 300]
+    p = make_paged_problem(seed=15, batch=len(lengths), len_lo=0, len_hi=0, n_q_heads=32, n_kv_heads=8, head_dim=64,
+                           page_size=16, seqlen_q=40, dtype=torch.bfloat16, lengths=lengths)
+    sq = torch.tensor([40, 40, 13, 0, 33], dtype=torch.int32)
+    out, want, lse, want_lse = run_case(p, torch.bfloat16, seqused_q=sq, return_lse=True)
+    for b, n in enumerate(sq.tolist()):  # rows past seqused_q are not written: compare the valid ones
+        if n == 0:
+            continue
+        assert_close(out[b, :n], want[b, :n], f"seqused_q row {b}")
+        got, ref = lse[b, :, :n].cpu(), want_lse[b, :, :n]
+        fin = torch.isfinite(ref)
+        assert torch.equal(torch.isfinite(got), fin)
+        assert (got[fin] - ref[fin]).abs().max().item() <= 2e-2 if fin.any() else True
+
+
+def test_prefill_packed_rows_with_cu_seqlens():
+    lengths = [200, 64, 1000, 129]
+    qlens = [64, 17, 128, 129]
+    Sq = max(qlens)
+    p = make_paged_problem(seed=16, batch=len(lengths), len_lo=0, len_hi=0, n_q_heads=8, n_kv_heads=2, head_dim=128,
+                           page_size=16, seqlen_q=Sq, dtype=torch.bfloat16, lengths=lengths)
+    want = O.paged_attention(p["q"].to(torch.bfloat16).float(), p["k_pool"], p["v_pool"], p["page_table"],
+                             p["seqused_k"], seqused_q=torch.tensor(qlens))
+    q_packed = torch.cat([p["q"][b, :n] for b, n in enumerate(qlens)]).to(torch.bfloat16).to(DEV)
+    cu = torch.tensor([0] + list(torch.tensor(qlens).cumsum(0)), dtype=torch.int32, device=DEV)
+    out, _ = kernels.flash_attn_fwd(
+        q_packed, p["k_pool"].to(torch.bfloat16).to(DEV).permute(0, 2, 1, 3),
+        p["v_pool"].to(torch.bfloat16).to(DEV).permute(0, 2, 1, 3), page_table=p["page_table"].to(DEV),
+        seqused_k=p["seqused_k"].to(DEV), cu_seqlens_q=cu, max_seqlen_q=Sq, causal=True)
+    start = 0
+    for b, n in enumerate(qlens):
+        assert_close(out[start:start + n], want[b, :n], f"packed sequence {b}")
+        start += n
+
+
+def test_prefill_ignores_garbage_past_the_sequence_end():
+    # rows of the last page beyond seqused_k hold NaN patterns; they must not reach the output
+    lengths = [77, 130, 5]
+    p = make_paged_problem(seed=17, batch=len(lengths), len_lo=0, len_hi=0, n_q_heads=8, n_kv_heads=2, head_dim=128,
+                           page_size=16, seqlen_q=64, dtype=torch.bfloat16, lengths=lengths)
+    k = p["k_pool"].to(torch.bfloat16).to(DEV)
+    v = p["v_pool"].to(torch.bfloat16).to(DEV)
+    for b, L in enumerate(lengths):
+        page = int(p["page_table"][b, (L - 1) // 16])
+        off = L % 16
+        if off:
+            k[page, :, off:, :] = float("nan")
+            v[page, :, off:, :] = float("nan")
+    q = p["q"].to(torch.bfloat16).to(DEV)
+    out, _ = kernels.flash_attn_fwd(q, k.permute(0, 2, 1, 3), v.permute(0, 2, 1, 3), page_table=p["page_table"].to(DEV),
+                                    seqused_k=p["seqused_k"].to(DEV), causal=True)
+    want = O.paged_attention(p["q"].to(torch.bfloat16).float(), p["k_pool"], p["v_pool"], p["page_table"], p["seqused_k"])
+    assert_close(out, want, "garbage past the end")
