@@ -1442,7 +1442,7 @@ bool prefill_enabled();
 template <int HD, bool BF16>
 int launch_prefill_variant(const CUtensorMap& tmK, const CUtensorMap& tmV, const AttnParams& p, int grid, int dev,
                            cudaStream_t stream);
-constexpr int kPrefillRowsPerSeg = 128, kPrefillTileKeys = 128, kPrefillMinPackedRows = 64;
+constexpr int kPrefillRowsPerSeg = 256, kPrefillTileKeys = 128, kPrefillMinPackedRows = 64;
 
 inline int launch_paged_attention(const kb200_attn_args* a) {
   KB200_REQUIRE(a != nullptr, "args is null");
@@ -1488,7 +1488,7 @@ inline int launch_paged_attention(const kb200_attn_args* a) {
   KB200_REQUIRE((reinterpret_cast<uintptr_t>(a->workspace) & 255) == 0, "workspace must be 256-byte aligned");
 
   // Many query rows per sequence (prompt chunks) with 16-bit K/V: the tensor-memory kernel, one
-  // CTA per 128 packed rows, no split over keys and no merge.
+  // CTA per 256 packed rows, no split over keys and no merge.
   const bool prefill = prefill_enabled() && a->kv_dtype != KB200_DTYPE_E4M3 &&
                        (int64_t)group * a->seqlen_q >= kPrefillMinPackedRows;
   const int tile_n = prefill ? kPrefillTileKeys : tile_n_for(a->kv_dtype, a->head_dim, nw);
