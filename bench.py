@@ -22,6 +22,12 @@ The one JSON line printed by rank 0 carries the whole-job HBM GB/s (``value``), 
 end-to-end number with host buffers (``e2e``), the roofline of the attention kernel, the clocks
 seen during the timed region and a CPU baseline (the oracle timed on the host cores).
 ``--impl reference`` times the CPU restatement of the reference's torch path instead.
+
+``--workload pf4|pf_long`` measure the prefill mode of the same op (rotary + append of a prompt chunk,
+then paged attention of the chunk's queries over prefix + chunk): compute-bound, reported in TFLOP/s
+against the measured bf16 tensor peak.  ``pf4`` is the prefill phase of configuration 4 (512 requests
+on a shared 729-token prefix, suffixes U[32,256] appended in chunks of up to 128 tokens, D=64);
+``pf_long`` is 32 sequences appending a 512-token chunk on 4096 cached tokens, D=128.
 """
 
 from __future__ import annotations
@@ -65,6 +71,16 @@ WORKLOADS = {
                       "32/8 heads, D=128, page 16"),
 }
 HQ, HKV, PAGE = 32, 8, 16
+
+PREFILL_WORKLOADS = {
+    "pf4": dict(batch=512, prefix=729, lo=32, hi=256, chunk=128, head_dim=64, rot=32,
+                desc="prefill phase of cfg4: 512 requests on a shared, cached 729-token prefix, suffix U[32,256] in "
+                     "chunks of <=128 tokens; rotary + append + paged attention per chunk, bf16, 32/8 heads, D=64, page 16"),
+    "pf_long": dict(batch=32, prefix=4096, lo=512, hi=512, chunk=512, head_dim=128, rot=128,
+                    desc="32 sequences append a 512-token chunk on 4096 cached tokens; rotary + append + paged "
+                         "attention, bf16, 32/8 heads, D=128, page 16"),
+}
+FALLBACK_BF16_TFLOPS = 1590.0
 
 
 # ----------------------------------------------------------------------------------------------
@@ -300,8 +316,7 @@ class GpuWorkload:
             seqs = [(r, 0, int(L)) for r, L in zip(self.rows, self.len0.tolist())]
         rows = torch.cat([torch.full((e - s,), r, dtype=torch.int32) for r, s, e in seqs]).to(dev)
         pos = torch.cat([torch.arange(s, e, dtype=torch.int32) for r, s, e in seqs]).to(dev)
-        slots = self.kernels.build_slot_mapping(self.pt.page_table, rows, pos.view(-1, 1).contiguous().view(-1), PAGE) \
-            if False else self.kernels.build_slot_mapping(self.pt.page_table, rows.view(-1, 1), pos.view(-1, 1), PAGE).view(-1)
+        slots = self.kernels.build_slot_mapping(self.pt.page_table, rows.view(-1, 1), pos.view(-1, 1), PAGE).view(-1)
         T = slots.numel()
         for l, cache in enumerate(self.caches):
             seeds = [(l * 1000003 + c) for c in range((T + chunk_tokens - 1) // chunk_tokens)]
@@ -474,6 +489,265 @@ class GpuWorkload:
 
 
 # ----------------------------------------------------------------------------------------------
+# Prefill workload (compute-bound mode of the same op)
+# ----------------------------------------------------------------------------------------------
+
+def measured_bf16_peak() -> tuple[float, str]:
+    f = ROOT / "MEASURED_PEAKS.json"
+    if f.exists():
+        try:
+            return float(json.loads(f.read_text())["bf16_tflops"]), "measured (burst)"
+        except Exception:
+            pass
+    return FALLBACK_BF16_TFLOPS, "fallback"
+
+
+class PrefillWorkload:
+    """One *step* = one prefill pass: every chunk of every request is rotated, appended and attended.
+    Chunks of one pass that belong to different requests run as one packed (``cu_seqlens_q``) call."""
+
+    def __init__(self, name: str, device: torch.device, rank: int):
+        from kestrel_b200.kv_cache import KVMemoryPool, PagedKVCache, PageTable
+        from kestrel_b200 import kernels
+        from oracle import paged_kv_oracle as O   # only for the cos/sin table constructor
+
+        self.kernels, self.cfg, self.device = kernels, PREFILL_WORKLOADS[name], device
+        cfg = self.cfg
+        self.B, self.D, self.prefix, self.chunk = cfg["batch"], cfg["head_dim"], cfg["prefix"], cfg["chunk"]
+        g = torch.Generator().manual_seed(2000 + rank)
+        self.suffix = torch.randint(cfg["lo"], cfg["hi"] + 1, (self.B,), generator=g)
+        own_pages = (self.prefix % PAGE + self.suffix + PAGE - 1) // PAGE        # pages a request writes
+        shared_full = self.prefix // PAGE
+        n_pages = int(own_pages.sum()) + (shared_full + 1) * (1 if name == "pf4" else self.B) + 16
+        self.n_pages = int(n_pages * 1.25)
+        self.pool = KVMemoryPool(device=device)
+        self.pt = PageTable(n_pages=self.n_pages, page_size=PAGE, max_batch_size=self.B + 2, device=device)
+        order = torch.randperm(len(self.pt.free_pages), generator=g).tolist()
+        self.pt.free_pages = [self.pt.free_pages[i] for i in order]
+        self.cache = PagedKVCache(self.pt, n_heads=HKV, head_dim=self.D, dtype=torch.bfloat16, pool=self.pool)
+        self.rows = []
+        share = name == "pf4"
+        owner = None
+        if share:
+            owner = self.pt.allocate()
+            self.pt.reserve(owner, self.prefix)
+            shared = list(self.pt.page_table_cpu[owner])[:shared_full]
+        for b in range(self.B):
+            r = self.pt.allocate()
+            if share and shared_full:
+                self.pt.map_pages(r, 0, shared)                 # the cached prefix pages, referenced by all
+            self.pt.reserve(r, self.prefix + int(self.suffix[b]))
+            self.rows.append(r)
+        self.pt.commit_block_table()
+        dg = torch.Generator(device=device).manual_seed(77 + rank)
+        # the cached prefix (random K/V written straight into the pool pages)
+        self.cache.k_cache.copy_(torch.randn(self.cache.k_cache.shape, generator=dg, device=device, dtype=torch.bfloat16))
+        self.cache.v_cache.copy_(torch.randn(self.cache.v_cache.shape, generator=dg, device=device, dtype=torch.bfloat16))
+        self.table = O.precompute_freqs_cis(cfg["rot"], self.prefix + cfg["hi"] + 1, 1.5e6).to(device)
+        # passes: chunk c of every request that still has tokens
+        self.passes = []
+        W = (HQ + 2 * HKV) * self.D
+        n_chunks = int((int(self.suffix.max()) + self.chunk - 1) // self.chunk)
+        for c in range(n_chunks):
+            qlens = (self.suffix - c * self.chunk).clamp(min=0, max=self.chunk)
+            live = (qlens > 0).nonzero().view(-1)
+            ql = qlens[live]
+            total = int(ql.sum())
+            cu = torch.zeros(live.numel() + 1, dtype=torch.int32)
+            cu[1:] = ql.cumsum(0)
+            start = self.prefix + c * self.chunk
+            pos = torch.cat([torch.arange(start, start + int(n)) for n in ql.tolist()])
+            rows = torch.tensor([self.rows[i] for i in live.tolist()], dtype=torch.int64)
+            row_of_tok = torch.repeat_interleave(rows, ql)
+            seq_k = (start + ql).to(torch.int32)
+            pairs = int((ql * start + ql * (ql + 1) // 2).sum())          # visible (query, key) pairs per head
+            rows_dev = rows.to(device)
+            ps = dict(
+                total=total, cu=cu.to(device), max_q=int(ql.max()), pos=pos.to(device),
+                slots=kernels.build_slot_mapping(self.pt.page_table, row_of_tok.to(device).view(-1, 1),
+                                                 pos.to(device).view(-1, 1), PAGE).view(-1),
+                page_table=self.pt.page_table[rows_dev].contiguous(), seqused_k=seq_k.to(device), pairs=pairs,
+                qkv=torch.randn(total, W, generator=dg, device=device, dtype=torch.bfloat16),
+                out=torch.empty(total, HQ, self.D, device=device, dtype=torch.bfloat16),
+                h_qkv=torch.randn(total, W, dtype=torch.bfloat16).pin_memory(),
+                h_out=torch.empty(total, HQ, self.D, dtype=torch.bfloat16).pin_memory())
+            self.passes.append(ps)
+        self.flops = sum(4 * self.D * HQ * ps["pairs"] for ps in self.passes)
+        self.tokens = sum(ps["total"] for ps in self.passes)
+        self.launches_per_step = 3 * len(self.passes)   # rope+append, plan, attention
+        self.attn_bytes = sum(2 * ps["total"] * HQ * self.D * 2 for ps in self.passes)
+
+    def _pass(self, ps, qkv, out, attn_only=False):
+        q, k, v = qkv.split([HQ * self.D, HKV * self.D, HKV * self.D], dim=-1)
+        q, k, v = q.unflatten(-1, (HQ, self.D)), k.unflatten(-1, (HKV, self.D)), v.unflatten(-1, (HKV, self.D))
+        if not attn_only:
+            self.kernels.rope_reshape_and_cache(ps["pos"], q, k, v, self.table, self.cache.k_cache.permute(0, 2, 1, 3),
+                                                self.cache.v_cache.permute(0, 2, 1, 3), ps["slots"], "auto",
+                                                write_k=False)
+        self.kernels.flash_attn_fwd(q, self.cache.k_cache.permute(0, 2, 1, 3), self.cache.v_cache.permute(0, 2, 1, 3),
+                                    page_table=ps["page_table"], seqused_k=ps["seqused_k"], cu_seqlens_q=ps["cu"],
+                                    max_seqlen_q=ps["max_q"], causal=True, out=out)
+
+    def step_device(self, attn_only=False):
+        for ps in self.passes:
+            self._pass(ps, ps["qkv"], ps["out"], attn_only)
+
+    def step_e2e(self):
+        for ps in self.passes:
+            ps["qkv"].copy_(ps["h_qkv"], non_blocking=True)
+            self._pass(ps, ps["qkv"], ps["out"])
+            ps["h_out"].copy_(ps["out"], non_blocking=True)
+        torch.cuda.current_stream(self.device).synchronize()
+
+    def e2e_bytes(self):
+        return (sum(ps["h_qkv"].numel() * 2 for ps in self.passes), sum(ps["h_out"].numel() * 2 for ps in self.passes))
+
+
+def time_cpu_prefill(name: str, target_seconds: float = 12.0) -> dict:
+    """The oracle (rotary, append, gather + attention in fp32 torch) on a few requests of the workload."""
+    from oracle import paged_kv_oracle as O
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    cfg = PREFILL_WORKLOADS[name]
+    D, prefix, chunk = cfg["head_dim"], cfg["prefix"], min(cfg["chunk"], cfg["hi"])
+    nreq = 2
+    g = torch.Generator().manual_seed(5)
+    L = prefix + chunk
+    pages = -(-L // PAGE)
+    table = (torch.randperm(nreq * pages, generator=g) + 1).view(nreq, pages).to(torch.int32)
+    kc = torch.randn(nreq * pages + 1, HKV, PAGE, D, generator=g)
+    vc = torch.randn(nreq * pages + 1, HKV, PAGE, D, generator=g)
+    cs = O.precompute_freqs_cis(cfg["rot"], L + 1, 1.5e6)
+    q = torch.randn(nreq, chunk, HQ, D, generator=g).to(torch.bfloat16)
+    k = torch.randn(nreq, chunk, HKV, D, generator=g).to(torch.bfloat16)
+    v = torch.randn(nreq, chunk, HKV, D, generator=g).to(torch.bfloat16)
+    pos = torch.arange(prefix, L).repeat(nreq)
+    slots = O.build_slot_mapping(table, torch.arange(nreq), pos.view(nreq, chunk), PAGE).view(-1)
+
+    def one():
+        qr = O.rotary_embedding(pos, q.view(-1, HQ, D), cs).view(nreq, chunk, HQ, D)
+        kr = O.rotary_embedding(pos, k.view(-1, HKV, D), cs)
+        O.append(kc, vc, kr, v.view(-1, HKV, D), slots)
+        return O.paged_attention(qr.float(), kc, vc, table, torch.full((nreq,), L, dtype=torch.int32))
+
+    one()
+    t0 = time.perf_counter()
+    one()
+    dt = time.perf_counter() - t0
+    reps = max(1, min(20, int(target_seconds / max(dt, 1e-3))))
+    times = []
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        one()
+        times.append(time.perf_counter() - t0)
+    med = statistics.median(times)
+    flops = 4 * D * HQ * nreq * (chunk * prefix + chunk * (chunk + 1) // 2)
+    return {"value": flops / med / 1e12, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+            "sample": f"{nreq} requests x one {chunk}-token chunk on a {prefix}-token prefix, {reps} repetitions "
+                      f"(oracle: torch CPU restatement, {cores} threads)", "tokens_per_s": nreq * chunk / med,
+            "steps": reps, "ms_per_sample_step": med * 1e3}
+
+
+def run_prefill(args) -> None:
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    cfg = PREFILL_WORKLOADS[args.workload]
+    if args.impl == "reference":
+        if rank == 0:
+            res = time_cpu_prefill(args.workload, 25.0)
+            print(json.dumps({
+                "impl": "reference", "metric": "paged append+prefill-attn TFLOP/s", "value": res["value"],
+                "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": res["steps"], "warmup": args.warmup,
+                "ms_per_step": res["ms_per_sample_step"], "higher_is_better": True, "scaling": "weak",
+                "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+                "config": {"workload": f"{args.workload}: {cfg['desc']}", "timing": "host wall clock on a bounded sample"},
+                "tokens_per_s": res["tokens_per_s"],
+                "cpu_baseline": {k: res[k] for k in ("value", "unit", "cores", "kind", "sample")},
+                "e2e": {"value": res["value"], "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+                "gpu_launches": 0}), flush=True)
+        return
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (the kernels have no CPU fallback)")
+    device = torch.device("cuda", local)
+    torch.cuda.set_device(device)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=device)
+    from kestrel_b200 import _native
+    from kestrel_b200.sharding import combine_step_stats
+    _native.load()
+    wl = PrefillWorkload(args.workload, device, rank)
+    warm = max(3, args.warmup)
+
+    def barrier():
+        torch.cuda.synchronize(device)
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize(device)
+
+    def timed(fn, n):
+        for _ in range(warm):
+            fn()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        barrier()
+        return e0.elapsed_time(e1)
+
+    sampler = ClockSampler(physical_gpu_index(local))
+    if rank == 0:
+        sampler.start()
+    ms = timed(wl.step_device, args.steps)
+    clocks = sampler.stop() if rank == 0 else None
+    attn_ms = timed(lambda: wl.step_device(attn_only=True), args.steps) / args.steps
+    e2e_ms = None if args.no_e2e else timed(wl.step_e2e, max(3, min(args.steps, 5)))
+    flags = _native.device_status(local, clear=True)
+    if flags[0] != 0:
+        raise SystemExit(f"kernel diagnostics reported a problem: {flags}")
+    ms_all, flops_all = combine_step_stats(ms, float(wl.flops) * args.steps, device)
+    e2e_all = combine_step_stats(e2e_ms or 0.0, float(wl.flops) * max(3, min(args.steps, 5)), device)
+    if rank != 0:
+        if dist is not None:
+            dist.destroy_process_group()
+        return
+    peak, peak_kind = measured_bf16_peak()
+    value = flops_all / (ms_all * 1e-3) / 1e12
+    achieved = wl.flops / (attn_ms * 1e-3) / 1e12
+    h2d, d2h = wl.e2e_bytes()
+    line = {
+        "metric": "paged append+prefill-attn TFLOP/s", "value": value, "unit": "TFLOP/s", "n_gpus": world,
+        "steps": args.steps, "warmup": warm, "ms_per_step": ms_all / args.steps, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16 operands, fp32 accumulate and softmax", "data": "synthetic",
+        "config": {"workload": f"{args.workload}: {cfg['desc']}", "passes_per_step": len(wl.passes),
+                   "tokens_per_step": wl.tokens, "pool_pages": wl.n_pages, "launch": "eager",
+                   "flops": "4 * head_dim * n_q_heads * visible (query, key) pairs (causal): useful work only",
+                   "l2_policy": "K/V of a pass exceed L2 except the shared prefix of pf4, which is L2-resident by design"},
+        "tokens_per_s": world * wl.tokens / (ms_all / args.steps * 1e-3),
+        "gpu_launches": wl.launches_per_step * args.steps, "clocks": clocks,
+        "roofline": {"bound": "tensor", "kernel": "paged_prefill_kernel (+ its plan launch)", "achieved": achieved,
+                     "peak": peak, "peak_kind": peak_kind, "unit": "TFLOP/s", "frac": achieved / peak, "traffic": None,
+                     "launch_ms_avg": attn_ms / len(wl.passes), "algorithmic_flops_per_step": wl.flops,
+                     "timing": "attention calls of a step alone, CUDA events"},
+    }
+    if e2e_ms is not None:
+        n = max(3, min(args.steps, 5))
+        line["e2e"] = {"value": e2e_all[1] / (e2e_all[0] * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
+                       "d2h_bytes_per_step": d2h, "ms_per_step": e2e_all[0] / n, "steps": n}
+    if world == 1 and not args.no_cpu_baseline:
+        cb = time_cpu_prefill(args.workload)
+        line["cpu_baseline"] = {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")}
+    print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+# ----------------------------------------------------------------------------------------------
 # CPU arm: the oracle (a port of the reference's torch path) on a bounded sample of the workload
 # ----------------------------------------------------------------------------------------------
 
@@ -583,7 +857,7 @@ def main() -> None:
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--workload", default="cfg3", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="cfg3", choices=sorted(WORKLOADS) + sorted(PREFILL_WORKLOADS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
@@ -591,6 +865,9 @@ def main() -> None:
     ap.add_argument("--batch", type=int, default=0, help="override the workload's batch (profiling on a small case)")
     ap.add_argument("--layers", type=int, default=0, help="override the workload's layer count (profiling)")
     args = ap.parse_args()
+    if args.workload in PREFILL_WORKLOADS:
+        run_prefill(args)
+        return
     if args.batch or args.layers:
         WORKLOADS[args.workload] = dict(WORKLOADS[args.workload])
         if args.batch:

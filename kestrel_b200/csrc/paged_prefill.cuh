@@ -12,12 +12,13 @@
 //                   K_0 V_0 K_1 V_1 ... tiles shared by both Q tiles)
 //   MMA warp        S_x = Q_x K^T (tcgen05.mma, M=128 N=128, operands from shared-memory
 //                   descriptors, accumulator in tensor memory) and O_x += P_x V with
-//                   P_x read back from shared memory; the two Q tiles alternate
+//                   P_x read from tensor memory (it overlays S_x), which halves the
+//                   shared-memory operand traffic of that product; the two Q tiles alternate
 //                   (PV_A QK_A PV_B QK_B) so one tile's products run under the other's
 //                   softmax
 //   2 x 4 softmax   one row per thread: tcgen05.ld of S, mask, online softmax (fp32,
-//   warps           base 2), P written to shared memory as the A operand of the second
-//                   product.  O stays in tensor memory across tiles; the running
+//   warps           base 2), P written back over S as packed 16-bit pairs (tcgen05.st), the
+//                   A operand of the second product.  O stays in tensor memory; the running
 //                   maximum is raised (and O rescaled through tcgen05.ld/st) only when
 //                   it grew by more than 2^8, so weights stay bounded and the rescale
 //                   is rare
@@ -42,11 +43,9 @@ struct PrefillSmem {
   static constexpr int SLAB = kPfTileRows * 128;                // bytes of one 128-row slab
   static constexpr int Q_TILE = NH * SLAB;
   static constexpr int KV_TILE = NH * kPrefillKeys * 128;       // one K or V tile
-  static constexpr int RING = HD == 128 ? 3 : 6;                // K/V tiles in flight (K0 V0 K1 V1 ...)
-  static constexpr int P_TILE = 2 * SLAB;                       // 128 rows x 128 keys, 16-bit
+  static constexpr int RING = HD == 128 ? 5 : 8;                // K/V tiles in flight (K0 V0 K1 V1 ...)
   static constexpr int OFF_Q = 0;
-  static constexpr int OFF_P = 2 * Q_TILE;
-  static constexpr int OFF_KV = OFF_P + 2 * P_TILE;
+  static constexpr int OFF_KV = 2 * Q_TILE;
   static constexpr int OFF_BAR = OFF_KV + RING * KV_TILE;
   static constexpr int N_BARS = 2 * RING + 6;
   static constexpr int OFF_TMEM = OFF_BAR + 8 * N_BARS;
@@ -82,6 +81,16 @@ __device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t desc_a, uint6
       ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// D[tmem] (+)= A[tmem] * B[smem desc]: A is M x 16 with lane = row and two 16-bit elements per column
+__device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc,
+                                            uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 // 32 lanes x 32 consecutive fp32 columns: thread i of the warp gets lane (lane base + i)
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
   uint32_t r[32];
@@ -98,6 +107,20 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
   tc_wait_ld();
 #pragma unroll
   for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// the same load without the wait: the caller issues tc_wait_ld() before it reads v
+__device__ __forceinline__ void tmem_ld32_nowait(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
 }
 
 // four tcgen05.ld of 32 columns each, one wait: a whole 128-column row
@@ -132,6 +155,25 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) 
         "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])), "r"(__float_as_uint(v[23])),
         "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])), "r"(__float_as_uint(v[27])),
         "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st32u(uint32_t taddr, const uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
+        "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]),
+        "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]),
+        "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st16u(uint32_t taddr, const uint32_t (&v)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
+        "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
       : "memory");
 }
 __device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
@@ -285,6 +327,11 @@ paged_prefill_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
       int nvalid = L - key0;
       if (nvalid > BN) nvalid = BN;
       const int nvb = (nvalid + box_rows - 1) >> box_shift;
+#ifdef KB200_PF_DEBUG_NOTMA
+      if (lane == 0) mbar_arrive(B_FULL(s));
+      __syncwarp();
+      continue;
+#endif
       if (lane == 0) mbar_expect_tx(B_FULL(s), (uint32_t)((nvb << box_shift) * HD * 2));
       __syncwarp();
       const uint32_t dst0 = sbase + SM::OFF_KV + (uint32_t)s * SM::KV_TILE;
@@ -309,17 +356,23 @@ paged_prefill_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
     auto kv_wait = [&](int idx) {
       ok = ok && mbar_wait_bounded(B_FULL(idx % RING), (uint32_t)(idx / RING) & 1u);
     };
+    // Descriptors differ only in their start-address field (low 14 bits, units of 16 bytes): the
+    // high word and the layout bits are built once, the per-step offsets are compile-time constants.
+    constexpr uint32_t kDescHi = (uint32_t)((1024u >> 4) | (1u << 14) | (2u << 29));   // sbo = 1024, version, 128-byte swizzle
+    constexpr uint32_t kLboK = (16u >> 4) << 16;                 // K-major operands: unused leading offset
+    constexpr uint32_t kLboV = ((uint32_t)(BN * 128) >> 4) << 16;  // V (MN-major): distance between 64-column slabs
+    auto mk = [](uint32_t lo) { return ((uint64_t)kDescHi << 32) | lo; };
     auto qk = [&](int x, int i) {   // S_x = Q_x K_i^T
       tc_fence_after();
       if (lane == 0) {
-        const uint32_t q_addr = sbase + SM::OFF_Q + (uint32_t)x * SM::Q_TILE;
-        const uint32_t k_addr = kv_addr(2 * i);
+        const uint32_t q_lo = ((sbase + SM::OFF_Q + (uint32_t)x * SM::Q_TILE) >> 4) | kLboK;
+        const uint32_t k_lo = (kv_addr(2 * i) >> 4) | kLboK;
         const uint32_t s_tmem = tmem_base + S_COL + (uint32_t)x * BN;
 #pragma unroll
         for (int k = 0; k < HD / 16; ++k) {
-          const uint64_t da = umma_desc(q_addr + (uint32_t)(k >> 2) * SM::SLAB + (uint32_t)(k & 3) * 32, 16, 1024);
-          const uint64_t db = umma_desc(k_addr + (uint32_t)(k >> 2) * (BN * 128) + (uint32_t)(k & 3) * 32, 16, 1024);
-          umma_f16(s_tmem, da, db, IDESC_QK, k > 0 ? 1u : 0u);
+          const uint32_t oq = ((uint32_t)(k >> 2) * SM::SLAB + (uint32_t)(k & 3) * 32) >> 4;
+          const uint32_t ok_ = ((uint32_t)(k >> 2) * (BN * 128) + (uint32_t)(k & 3) * 32) >> 4;
+          umma_f16(s_tmem, mk(q_lo + oq), mk(k_lo + ok_), IDESC_QK, k > 0 ? 1u : 0u);
         }
         tc_commit(B_SREADY(x));
       }
@@ -330,13 +383,18 @@ paged_prefill_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
       if (!ok) return;
       tc_fence_after();
       if (lane == 0) {
-        const uint32_t p_addr = sbase + SM::OFF_P + (uint32_t)x * SM::P_TILE;
-        const uint32_t v_addr = kv_addr(2 * i + 1);
+        const uint32_t p_tmem = tmem_base + S_COL + (uint32_t)x * BN;   // P overlays the first 64 columns of S_x
+        const uint32_t v_lo = (kv_addr(2 * i + 1) >> 4) | kLboV;
         const uint32_t o_tmem = tmem_base + O_COL + (uint32_t)x * 128;
-        for (int k = 0; k < ksteps; ++k) {
-          const uint64_t da = umma_desc(p_addr + (uint32_t)(k >> 2) * SM::SLAB + (uint32_t)(k & 3) * 32, 16, 1024);
-          const uint64_t db = umma_desc(v_addr + (uint32_t)k * 2048, BN * 128, 1024);
-          umma_f16(o_tmem, da, db, IDESC_PV, (i > 0 || k > 0) ? 1u : 0u);
+        if (ksteps == BN / 16) {
+#pragma unroll
+          for (int k = 0; k < BN / 16; ++k)
+            umma_f16_ts(o_tmem, p_tmem + (uint32_t)k * 8, mk(v_lo + (uint32_t)k * (2048 >> 4)), IDESC_PV,
+                        (i > 0 || k > 0) ? 1u : 0u);
+        } else {
+          for (int k = 0; k < ksteps; ++k)
+            umma_f16_ts(o_tmem, p_tmem + (uint32_t)k * 8, mk(v_lo + (uint32_t)k * (2048 >> 4)), IDESC_PV,
+                        (i > 0 || k > 0) ? 1u : 0u);
         }
         tc_commit(B_PVDONE(x));
       }
@@ -421,9 +479,14 @@ paged_prefill_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
           if (kk > lim || kk < lo) s[i] = -INFINITY;
         }
       }
-      float mx = -INFINITY;
+      // eight independent running maxima: a single chain of 128 dependent fmax would cost ~500 cycles
+      float mx8[8];
 #pragma unroll
-      for (int i = 0; i < BN; ++i) mx = fmaxf(mx, s[i]);
+      for (int i = 0; i < 8; ++i) mx8[i] = s[i];
+#pragma unroll
+      for (int i = 8; i < BN; ++i) mx8[i & 7] = fmaxf(mx8[i & 7], s[i]);
+      const float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])),
+                             fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
       if (it == 0) {
         m = mx;   // the first product overwrites O: nothing to rescale
       } else {
@@ -450,25 +513,46 @@ paged_prefill_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
         }
       }
       const float ms = (m == -INFINITY) ? 0.f : m * sl2;
-      float lsum = 0.f;
+      float ls4[4] = {0.f, 0.f, 0.f, 0.f};   // independent partial row sums
+#ifndef KB200_PF_DEBUG_NOSOFTMAX
+      // weights as packed 16-bit pairs over the first 64 columns of S_x: the A operand of P V.
+      // S is read a second time, 32 columns at a time (keeping all 128 scores live across the
+      // exponentials costs more in registers than the second read costs in time); chunk c of P
+      // lands on columns [16c, 16c+16), inside S columns that are already in registers.
+      const bool masked = key0 + BN - 1 > lim || key0 < lo;
+      uint32_t raw[2][32];   // the load of chunk c + 1 is in flight while chunk c is turned into weights
+      tmem_ld32_nowait(s_tmem, raw[0]);
 #pragma unroll
-      for (int c = 0; c < BN / 8; ++c) {   // 16-byte chunk c of this row's weights
-        uint32_t w[4];
+      for (int c = 0; c < BN / 32; ++c) {
+        tc_wait_ld();
+        if (c + 1 < BN / 32) tmem_ld32_nowait(s_tmem + 32u * (c + 1), raw[(c + 1) & 1]);
+        float v[32];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const float p0 = ex2(fmaf(s[8 * c + 2 * i], sl2, -ms));       // exp2(-inf) = 0 for masked keys
-          const float p1 = ex2(fmaf(s[8 * c + 2 * i + 1], sl2, -ms));
-          lsum += p0 + p1;
+        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(raw[c & 1][i]);
+        if (masked) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int kk = key0 + 32 * c + i;
+            if (kk > lim || kk < lo) v[i] = -INFINITY;
+          }
+        }
+        uint32_t w[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const float p0 = ex2(fmaf(v[2 * i], sl2, -ms));       // exp2(-inf) = 0 for masked keys
+          const float p1 = ex2(fmaf(v[2 * i + 1], sl2, -ms));
+          ls4[i & 3] += p0 + p1;
           w[i] = pack2<BF16>(p0, p1);
         }
-        const uint32_t off = SM::OFF_P + (uint32_t)x * SM::P_TILE + (uint32_t)(c >> 3) * SM::SLAB + (uint32_t)r * 128 +
-                             (uint32_t)(((c & 7) ^ (r & 7)) << 4);
-        *reinterpret_cast<uint4*>(sgen + off) = make_uint4(w[0], w[1], w[2], w[3]);
+        tmem_st16u(s_tmem + 16u * c, w);
       }
-      l += lsum;
-      // S has been read and P written: the tensor core may overwrite S and read P
+      tc_wait_st();
+#else
+      ls4[0] = mx + ms;
+#endif
+      l += (ls4[0] + ls4[1]) + (ls4[2] + ls4[3]);
+      // S has been read and P written: the tensor core may read P and then overwrite S
       tc_fence_before();
-      fence_proxy_async();
       mbar_arrive(B_PREADY(x));
     }
     if (ok && n_mine > 0) {
