@@ -178,6 +178,32 @@ __device__ __forceinline__ void tmem_st16u(uint32_t taddr, const uint32_t (&v)[1
 }
 __device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
+// Packed fp32 pairs (one instruction, two lanes) and the three-input maximum: the softmax warps
+// are bound by instruction issue, and these halve the count of their arithmetic instructions.
+__device__ __forceinline__ uint64_t pack_f32x2(float a, float b) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+  return r;
+}
+__device__ __forceinline__ void unpack_f32x2(uint64_t v, float& a, float& b) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma_f32x2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t add_f32x2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
 // Shared-memory matrix descriptor, 128-byte swizzle; offsets in bytes.
 //   K-major operand  (rows of 128 bytes along K, 8-row groups 1024 bytes apart): lbo unused (1), sbo = 1024
 //   MN-major operand (rows of 128 bytes along MN, one row per K index):          lbo = distance between
@@ -484,7 +510,12 @@ paged_prefill_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
 #pragma unroll
       for (int i = 0; i < 8; ++i) mx8[i] = s[i];
 #pragma unroll
-      for (int i = 8; i < BN; ++i) mx8[i & 7] = fmaxf(mx8[i & 7], s[i]);
+      for (int i = 8; i + 16 <= BN; i += 16) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) mx8[k] = max3(mx8[k], s[i + k], s[i + 8 + k]);
+      }
+#pragma unroll
+      for (int k = 0; k < 8; ++k) mx8[k] = fmaxf(mx8[k], s[BN - 8 + k]);
       const float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])),
                              fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
       if (it == 0) {
@@ -514,6 +545,8 @@ paged_prefill_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
       }
       const float ms = (m == -INFINITY) ? 0.f : m * sl2;
       float ls4[4] = {0.f, 0.f, 0.f, 0.f};   // independent partial row sums
+      uint64_t ls2[4] = {0ull, 0ull, 0ull, 0ull};   // the same as packed pairs (bit pattern of 0.f, 0.f)
+      const uint64_t sl2x2 = pack_f32x2(sl2, sl2), nmsx2 = pack_f32x2(-ms, -ms);
 #ifndef KB200_PF_DEBUG_NOSOFTMAX
       // weights as packed 16-bit pairs over the first 64 columns of S_x: the A operand of P V.
       // S is read a second time, 32 columns at a time (keeping all 128 scores live across the
@@ -539,9 +572,10 @@ paged_prefill_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
         uint32_t w[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-          const float p0 = ex2(fmaf(v[2 * i], sl2, -ms));       // exp2(-inf) = 0 for masked keys
-          const float p1 = ex2(fmaf(v[2 * i + 1], sl2, -ms));
-          ls4[i & 3] += p0 + p1;
+          float x0, x1;
+          unpack_f32x2(fma_f32x2(pack_f32x2(v[2 * i], v[2 * i + 1]), sl2x2, nmsx2), x0, x1);
+          const float p0 = ex2(x0), p1 = ex2(x1);                  // exp2(-inf) = 0 for masked keys
+          ls2[i & 3] = add_f32x2(ls2[i & 3], pack_f32x2(p0, p1));
           w[i] = pack2<BF16>(p0, p1);
         }
         tmem_st16u(s_tmem + 16u * c, w);
@@ -550,6 +584,12 @@ paged_prefill_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
 #else
       ls4[0] = mx + ms;
 #endif
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        float a, b;
+        unpack_f32x2(ls2[k], a, b);
+        ls4[k] += a + b;
+      }
       l += (ls4[0] + ls4[1]) + (ls4[2] + ls4[3]);
       // S has been read and P written: the tensor core may read P and then overwrite S
       tc_fence_before();
