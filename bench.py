@@ -509,7 +509,6 @@ class PrefillWorkload:
     def __init__(self, name: str, device: torch.device, rank: int):
         from kestrel_b200.kv_cache import KVMemoryPool, PagedKVCache, PageTable
         from kestrel_b200 import kernels
-        from oracle import paged_kv_oracle as O   # only for the cos/sin table constructor
 
         self.kernels, self.cfg, self.device = kernels, PREFILL_WORKLOADS[name], device
         cfg = self.cfg
@@ -543,7 +542,10 @@ class PrefillWorkload:
         # the cached prefix (random K/V written straight into the pool pages)
         self.cache.k_cache.copy_(torch.randn(self.cache.k_cache.shape, generator=dg, device=device, dtype=torch.bfloat16))
         self.cache.v_cache.copy_(torch.randn(self.cache.v_cache.shape, generator=dg, device=device, dtype=torch.bfloat16))
-        self.table = O.precompute_freqs_cis(cfg["rot"], self.prefix + cfg["hi"] + 1, 1.5e6).to(device)
+        # cos/sin table in the layout of kestrel/models/moondream/rope.py: cos of rot/2 frequencies, then sin
+        inv_freq = 1.0 / (1.5e6 ** (torch.arange(0, cfg["rot"], 2, dtype=torch.float32) / cfg["rot"]))
+        freqs = torch.arange(self.prefix + cfg["hi"] + 1, dtype=torch.float32).unsqueeze(1) * inv_freq
+        self.table = torch.cat([freqs.cos(), freqs.sin()], dim=-1).to(device)
         # passes: chunk c of every request that still has tokens
         self.passes = []
         W = (HQ + 2 * HKV) * self.D
