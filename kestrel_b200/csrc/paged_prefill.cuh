@@ -157,17 +157,6 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) 
         "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
       : "memory");
 }
-__device__ __forceinline__ void tmem_st32u(uint32_t taddr, const uint32_t (&v)[32]) {
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
-      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
-      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
-      ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
-        "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]),
-        "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]),
-        "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
-      : "memory");
-}
 __device__ __forceinline__ void tmem_st16u(uint32_t taddr, const uint32_t (&v)[16]) {
   asm volatile(
       "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
@@ -204,19 +193,12 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
   return d;
 }
 
-// Shared-memory matrix descriptor, 128-byte swizzle; offsets in bytes.
-//   K-major operand  (rows of 128 bytes along K, 8-row groups 1024 bytes apart): lbo unused (1), sbo = 1024
-//   MN-major operand (rows of 128 bytes along MN, one row per K index):          lbo = distance between
-//                     64-element column slabs, sbo = 1024 (8 K indices)
-__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
-  uint64_t d = 0;
-  d |= (uint64_t)((smem_addr >> 4) & 0x3FFFu);
-  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;
-  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32;
-  d |= 1ull << 46;   // descriptor version of this architecture
-  d |= 2ull << 61;   // 128-byte swizzle
-  return d;
-}
+// Shared-memory matrix descriptors (64 bits), 128-byte swizzle, as the MMA warp builds them:
+//   bits  0-13  start address >> 4        bits 16-29  leading byte offset >> 4
+//   bits 32-45  stride byte offset >> 4   bits 46-47  descriptor version (1)   bits 61-63  swizzle mode (2 = 128 B)
+//   K-major operand  (rows of 128 bytes along K, 8-row groups 1024 bytes apart): leading offset unused, stride 1024
+//   MN-major operand (rows of 128 bytes along MN, one row per K index): leading offset = distance between
+//                     64-element column slabs, stride 1024 (8 K indices)
 // Instruction descriptor, kind::f16: fp32 accumulator, A/B both F16 (0) or BF16 (1), A K-major,
 // B K-major or MN-major, M = 128.
 __host__ __device__ constexpr uint32_t umma_idesc(bool bf16, bool b_mn_major, int n) {
@@ -353,7 +335,7 @@ paged_prefill_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
       int nvalid = L - key0;
       if (nvalid > BN) nvalid = BN;
       const int nvb = (nvalid + box_rows - 1) >> box_shift;
-#ifdef KB200_PF_DEBUG_NOTMA
+#ifdef KB200_PF_DEBUG_NOTMA   // bottleneck analysis only: hand over empty tiles instead of loading them
       if (lane == 0) mbar_arrive(B_FULL(s));
       __syncwarp();
       continue;
@@ -547,7 +529,7 @@ paged_prefill_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
       float ls4[4] = {0.f, 0.f, 0.f, 0.f};   // independent partial row sums
       uint64_t ls2[4] = {0ull, 0ull, 0ull, 0ull};   // the same as packed pairs (bit pattern of 0.f, 0.f)
       const uint64_t sl2x2 = pack_f32x2(sl2, sl2), nmsx2 = pack_f32x2(-ms, -ms);
-#ifndef KB200_PF_DEBUG_NOSOFTMAX
+#ifndef KB200_PF_DEBUG_NOSOFTMAX   // (defined in bottleneck-analysis builds only: skips the weights)
       // weights as packed 16-bit pairs over the first 64 columns of S_x: the A operand of P V.
       // S is read a second time, 32 columns at a time (keeping all 128 scores live across the
       // exponentials costs more in registers than the second read costs in time); chunk c of P
