@@ -30,7 +30,7 @@
 extern "C" {
 #endif
 
-#define KB200_ABI_VERSION 1
+#define KB200_ABI_VERSION 2
 
 #if defined(__GNUC__)
 #define KB200_API __attribute__((visibility("default")))
@@ -245,6 +245,15 @@ typedef struct kb200_attn_args {
 
   void* workspace; /* device scratch, >= kb200_attn_workspace_bytes(...), 256-byte aligned */
   uint64_t workspace_bytes;
+
+  /* Block-bidirectional (prefix-LM) mask, the mask_mod / aux_tensors call of
+   * kestrel/models/moondream/text.py:139-172: query row j of a sequence also sees the keys of
+   * its own sequence's rows up to q_visible_until[j] (>= j), on top of the causal part.  Device
+   * int32, NULL for plain causal; indexed [b * q_visible_batch_stride + j] (padded layout) or
+   * by packed row.  kb200_block_visibility builds it from the per-token block ids.  Needs
+   * causal != 0, no window, 16-bit K/V. */
+  const int32_t* q_visible_until;
+  int64_t q_visible_batch_stride;
 } kb200_attn_args;
 
 /* Scratch bytes kb200_paged_attention needs for the given problem bounds. */
@@ -252,6 +261,18 @@ KB200_API uint64_t kb200_attn_workspace_bytes(int64_t batch, int64_t total_q, in
                                     int32_t n_kv_heads, int32_t head_dim, int32_t device);
 
 KB200_API int kb200_paged_attention(const kb200_attn_args* args);
+
+/* ---------------------------------------------------------------------------
+ * Visibility rows of the block-bidirectional mask.  `block_ids` int32 [batch, seqlen] holds,
+ * per prompt position, an image-block id >= 0 or -1 for text
+ * (kestrel/models/moondream/runtime.py:1671-1743); out[b, j] = last position of the run of
+ * equal non-negative ids that contains j, or j itself for text.  A block is a contiguous run
+ * (one per image occurrence, as the reference builds them).  Replaces the mask_mod callable
+ * `attention.block_bidirectional_mask` + aux_tensors = [block_sequence_ids].
+ */
+KB200_API int kb200_block_visibility(const int32_t* block_ids, int64_t ids_row_stride, int64_t batch,
+                                     int64_t seqlen, int32_t* out, int64_t out_row_stride, int32_t device,
+                                     void* stream);
 
 /* ---------------------------------------------------------------------------
  * kb200_paged_attention without a caller-provided scratch buffer.  This entry

@@ -13,7 +13,7 @@ from pathlib import Path
 
 # KB200_LIBRARY selects another build of the same ABI (A/B comparisons of kernel variants).
 LIB_PATH = Path(os.environ.get("KB200_LIBRARY") or Path(__file__).resolve().parent / "libkestrel_b200.so")
-ABI_VERSION = 1
+ABI_VERSION = 2
 
 DTYPE_F32, DTYPE_F16, DTYPE_BF16, DTYPE_E4M3 = 0, 1, 2, 3
 STATIC_SCRATCH_BYTES = 32 * 1024 * 1024  # KB200_STATIC_SCRATCH_BYTES
@@ -33,6 +33,7 @@ EXPORTS = (
     "kb200_copy_pages",
     "kb200_attn_workspace_bytes",
     "kb200_paged_attention",
+    "kb200_block_visibility",
     "kb200_paged_attention_static",
 )
 
@@ -86,6 +87,8 @@ class AttnArgs(C.Structure):
         ("v_scale_per_head", C.c_void_p),
         ("workspace", C.c_void_p),
         ("workspace_bytes", C.c_uint64),
+        ("q_visible_until", C.c_void_p),
+        ("q_visible_batch_stride", C.c_int64),
     ]
 
 
@@ -127,6 +130,8 @@ def _declare(lib: C.CDLL) -> None:
     lib.kb200_copy_pages.argtypes = [C.POINTER(vp), i32, i64, i64, i64, vp, vp, i64, i32, vp]
     lib.kb200_attn_workspace_bytes.restype = C.c_uint64
     lib.kb200_attn_workspace_bytes.argtypes = [i64, i64, i32, i32, i32, i32]
+    lib.kb200_block_visibility.restype = C.c_int
+    lib.kb200_block_visibility.argtypes = [vp, i64, i64, i64, vp, i64, i32, vp]
     lib.kb200_paged_attention.restype = C.c_int
     lib.kb200_paged_attention.argtypes = [C.POINTER(AttnArgs)]
     lib.kb200_paged_attention_static.restype = C.c_int

@@ -122,6 +122,13 @@ uint64_t kb200_attn_workspace_bytes(int64_t batch, int64_t total_q, int32_t n_q_
   return attn_workspace_layout(batch, total_q, n_q_heads, n_kv_heads, head_dim, sms * kAttnMaxWarps).total;
 }
 
+int kb200_block_visibility(const int32_t* block_ids, int64_t ids_row_stride, int64_t batch, int64_t seqlen,
+                           int32_t* out, int64_t out_row_stride, int32_t device, void* stream) {
+  KB200_ENTER(device);
+  return launch_block_visibility(block_ids, ids_row_stride, batch, seqlen, out, out_row_stride,
+                                 static_cast<cudaStream_t>(stream));
+}
+
 int kb200_paged_attention(const kb200_attn_args* args) {
   if (!args) return fail(KB200_ERR_INVALID, "args is null");
   KB200_ENTER(args->device);

@@ -74,6 +74,8 @@ struct AttnParams {
   const int32_t* cu_seqlens_q;
   const float* ks_vec;
   const float* vs_vec;
+  const int32_t* q_vis;   // per query row: last row of its sequence whose key it may see (prefill kernel only)
+  int64_t q_vis_bs;
   float ks, vs, softmax_scale;
   // plan (written by attn_plan_kernel)
   long long* tile_cum;  // [B+1]
@@ -1489,8 +1491,15 @@ inline int launch_paged_attention(const kb200_attn_args* a) {
 
   // Many query rows per sequence (prompt chunks) with 16-bit K/V: the tensor-memory kernel, one
   // CTA per 256 packed rows, no split over keys and no merge.
-  const bool prefill = prefill_enabled() && a->kv_dtype != KB200_DTYPE_E4M3 &&
-                       (int64_t)group * a->seqlen_q >= kPrefillMinPackedRows;
+  const bool block_mask = a->q_visible_until != nullptr;
+  if (block_mask) {
+    KB200_REQUIRE(a->causal != 0 && a->window_left < 0, "the block-bidirectional mask extends the causal mask: "
+                                                       "causal must be set and no window given");
+    if (a->kv_dtype == KB200_DTYPE_E4M3)
+      return fail(KB200_ERR_UNSUPPORTED, "the block-bidirectional mask is not implemented for FP8 K/V");
+  }
+  const bool prefill = block_mask || (prefill_enabled() && a->kv_dtype != KB200_DTYPE_E4M3 &&
+                                      (int64_t)group * a->seqlen_q >= kPrefillMinPackedRows);
   const int tile_n = prefill ? kPrefillTileKeys : tile_n_for(a->kv_dtype, a->head_dim, nw);
   // The transposed decode kernel pays off where the math is the limiter (e4m3 K/V); 16-bit K/V
   // is within a few percent of the HBM roofline with the general kernel already.
@@ -1530,6 +1539,8 @@ inline int launch_paged_attention(const kb200_attn_args* a) {
   p.seqused_k = a->seqused_k;
   p.seqused_q = packed ? nullptr : a->seqused_q;
   p.cu_seqlens_q = a->cu_seqlens_q;
+  p.q_vis = a->q_visible_until;
+  p.q_vis_bs = packed ? 0 : a->q_visible_batch_stride;
   p.ks_vec = a->kv_dtype == KB200_DTYPE_E4M3 ? a->k_scale_per_head : nullptr;
   p.vs_vec = a->kv_dtype == KB200_DTYPE_E4M3 ? a->v_scale_per_head : nullptr;
   p.ks = a->kv_dtype == KB200_DTYPE_E4M3 ? a->k_scale : 1.f;

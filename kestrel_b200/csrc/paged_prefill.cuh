@@ -268,10 +268,12 @@ paged_prefill_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
     const int r0 = row_first + x * kPfTileRows;
     if (r0 >= nrows) { n_x[x] = 0; continue; }
     const int r1 = min(nrows, r0 + kPfTileRows) - 1;
-    int k_end = upper ? min(L, L - sq + r1 / p.group + 1) : L;
+    int j1 = r1 / p.group;   // last query position of the tile; with a block mask it sees up to the end of its block
+    if (p.q_vis) j1 = max(j1, min(sq - 1, p.q_vis[(int64_t)b * p.q_vis_bs + qrow0 + j1]));
+    int k_end = upper ? min(L, L - sq + j1 + 1) : L;
     n_x[x] = k_end > tile_begin * BN ? (k_end - tile_begin * BN + BN - 1) / BN : 0;
   }
-  const int n_tiles = max(n_x[0], n_x[1]);   // n_x[0] <= n_x[1] whenever tile B has rows
+  const int n_tiles = max(n_x[0], n_x[1]);   // n_x[0] <= n_x[1] whenever tile B has rows (limits grow with the row)
 
   // ---- set-up: barriers, tensor memory, Q tiles
   if (tid == 0) {
@@ -462,7 +464,9 @@ paged_prefill_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
     const bool valid = row < nrows;
     const int j = valid ? row / p.group : 0;
     const int g = valid ? row - j * p.group : 0;
-    const int lim = valid ? (upper ? L - sq + j : L - 1) : -1;          // last visible key
+    int jv = j;   // last row of this sequence whose key this row sees
+    if (valid && p.q_vis) jv = max(j, min(sq - 1, p.q_vis[(int64_t)b * p.q_vis_bs + qrow0 + j]));
+    const int lim = valid ? (upper ? L - sq + jv : L - 1) : -1;         // last visible key
     const int lo = p.window_left >= 0 ? lim - p.window_left : 0;         // first visible key
     const float ksc = p.ks_vec ? p.ks_vec[h] : p.ks;
     const float vscale = p.vs_vec ? p.vs_vec[h] : p.vs;

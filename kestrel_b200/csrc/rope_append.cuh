@@ -387,4 +387,36 @@ inline int launch_decode_step_metadata(const int32_t* page_table, int64_t pt_row
   return KB200_OK;
 }
 
+// ---------------------------------------------------------------------------
+// Block-bidirectional mask: out[b, j] = last position of the run of equal, non-negative block
+// ids that contains j (j itself for text, id < 0).  One block of threads per sequence; every
+// thread walks forward from its position to the end of its run (runs are image blocks, a few
+// hundred positions, and the walk is tiny next to the prefill it serves).
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+block_visibility_kernel(const int32_t* __restrict__ ids, int64_t ids_rs, int64_t seqlen, int32_t* __restrict__ out,
+                        int64_t out_rs) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int32_t* row = ids + (int64_t)blockIdx.x * ids_rs;
+  int32_t* dst = out + (int64_t)blockIdx.x * out_rs;
+  for (int64_t j = threadIdx.x; j < seqlen; j += blockDim.x) {
+    const int32_t id = row[j];
+    int64_t e = j;
+    if (id >= 0)
+      while (e + 1 < seqlen && row[e + 1] == id) ++e;
+    dst[j] = (int32_t)e;
+  }
+}
+
+inline int launch_block_visibility(const int32_t* ids, int64_t ids_rs, int64_t batch, int64_t seqlen, int32_t* out,
+                                   int64_t out_rs, cudaStream_t stream) {
+  if (batch == 0 || seqlen == 0) return KB200_OK;
+  KB200_REQUIRE(batch > 0 && seqlen > 0 && batch <= 0x7fffffff && seqlen <= 0x7fffffff, "batch / seqlen out of range");
+  KB200_REQUIRE(ids && out, "null pointer argument");
+  KB200_CUDA_OK(launch_kernel(block_visibility_kernel, dim3((unsigned)batch), dim3(256), 0, stream, ids, ids_rs, seqlen,
+                              out, out_rs));
+  return KB200_OK;
+}
+
 }  // namespace kb200

@@ -437,6 +437,38 @@ def copy_pages(caches: Sequence[torch.Tensor], src_pages, dst_pages) -> None:
 # attention
 # ---------------------------------------------------------------------------
 
+class _BlockBidirectionalMask:
+    """Stand-in for the ``mask_mod`` callable the reference takes from
+    ``get_runtime().attention.block_bidirectional_mask`` (``kestrel/models/moondream/text.py:32``) and passes
+    to ``flash_attn_fwd`` together with ``aux_tensors=[block_sequence_ids]`` for prompts with images: inside an
+    image block (a run of equal ids >= 0) attention is bidirectional, everything else is causal.  It is only
+    ever compared by identity; the mask itself is evaluated inside the prefill kernel."""
+
+    def __repr__(self) -> str:
+        return "kestrel_b200.kernels.block_bidirectional_mask"
+
+
+block_bidirectional_mask = _BlockBidirectionalMask()
+
+
+def block_visibility(block_ids: torch.Tensor, seqlen: Optional[int] = None) -> torch.Tensor:
+    """``out[b, j]`` = last position of the run of equal, non-negative ``block_ids`` containing ``j``
+    (``j`` itself where the id is negative): how far past itself query ``j`` sees under the
+    block-bidirectional mask.  ``block_ids`` int32 ``[B, >= seqlen]`` on the GPU."""
+    dev = _require_cuda("block_ids", block_ids)
+    if block_ids.dtype != torch.int32 or block_ids.ndim != 2 or block_ids.stride(1) != 1:
+        raise ValueError("block_ids must be int32 [batch, seqlen], contiguous in the last dimension")
+    B = block_ids.shape[0]
+    S = block_ids.shape[1] if seqlen is None else int(seqlen)
+    if S > block_ids.shape[1]:
+        raise ValueError("block_ids is shorter than the query rows")
+    out = torch.empty((B, S), dtype=torch.int32, device=block_ids.device)
+    if B and S:
+        _native.check(_native.load().kb200_block_visibility(block_ids.data_ptr(), block_ids.stride(0), B, S,
+                                                            out.data_ptr(), out.stride(0), dev, _stream(dev)))
+    return out
+
+
 _workspaces: dict[tuple[int, int], torch.Tensor] = {}
 _ws_bytes_cache: dict[tuple, int] = {}
 
@@ -491,15 +523,28 @@ def flash_attn_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *,
     tensors with ``H_kv`` entries.  ``paged_kv_non_tma`` and ``pack_gqa`` are accepted and
     ignored (hints to the reference's kernel).  Returns ``(out, lse_or_None)``.
 
+    ``mask_mod=block_bidirectional_mask`` with ``aux_tensors=[block_sequence_ids]`` (int32 ``[B, >= Sq]``, image
+    block id or -1 per query position, ``kestrel/models/moondream/text.py:139-172``) adds bidirectional attention
+    inside each image block to the causal mask (padded layout, 16-bit K/V).
+
     Not implemented (raise ``NotImplementedError``): dense K/V (``page_table=None``),
-    ``cu_seqlens_k``, ``mask_mod`` / ``aux_tensors``, a non-zero right window.
+    ``cu_seqlens_k``, any other ``mask_mod``, a non-zero right window.
     """
     if page_table is None:
         raise NotImplementedError("dense (non-paged) attention is outside the paged-KV path")
     if cu_seqlens_k is not None:
         raise NotImplementedError("cu_seqlens_k is not supported; pass seqused_k")
+    block_ids = None
     if mask_mod is not None or aux_tensors is not None:
-        raise NotImplementedError("mask_mod / aux_tensors (prefix-LM prefill masks) are not supported")
+        if mask_mod is not block_bidirectional_mask:
+            raise NotImplementedError("the only mask_mod supported is attention.block_bidirectional_mask")
+        if not aux_tensors or len(aux_tensors) != 1 or not isinstance(aux_tensors[0], torch.Tensor):
+            raise ValueError("block_bidirectional_mask needs aux_tensors=[block_sequence_ids]")
+        if cu_seqlens_q is not None:
+            raise NotImplementedError("block_bidirectional_mask with packed rows (cu_seqlens_q) is not supported")
+        if window_size_left is not None and window_size_left >= 0:
+            raise NotImplementedError("block_bidirectional_mask cannot be combined with a sliding window")
+        block_ids = aux_tensors[0]
     if seqused_k is None:
         raise ValueError("paged attention requires seqused_k")
     if window_size_right not in (None, 0, -1) :
@@ -616,6 +661,15 @@ def flash_attn_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *,
     a.k_scale_per_head, a.v_scale_per_head = ks_ptr, vs_ptr
     a.workspace = ws.data_ptr()
     a.workspace_bytes = ws.numel()
+    if block_ids is not None:
+        if fp8:
+            raise NotImplementedError("block_bidirectional_mask is not implemented for FP8 K/V")
+        if _require_cuda("block_sequence_ids", block_ids) != dev or block_ids.ndim != 2 or block_ids.shape[0] < B:
+            raise ValueError("block_sequence_ids must be an int32 [batch, >= seqlen_q] tensor on q's device")
+        vis = block_visibility(block_ids[:B], Sq)   # kept alive until the launch below is enqueued
+        a.q_visible_until = vis.data_ptr()
+        a.q_visible_batch_stride = vis.stride(0)
+        a.causal = 1   # the block mask extends the causal one (the reference passes causal=False next to mask_mod)
     _native.check(lib.kb200_paged_attention(C.byref(a)))
     return out, lse
 
@@ -654,6 +708,7 @@ class _RotaryOps:
 
 class _AttentionOps:
     flash_attn_fwd = staticmethod(flash_attn_fwd)
+    block_bidirectional_mask = block_bidirectional_mask
 
     def __getattr__(self, item: str):
         raise NotImplementedError(f"kestrel_kernels.attention.{item} is outside the paged-KV path")

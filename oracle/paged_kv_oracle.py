@@ -230,7 +230,8 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
                     window_left: Optional[int] = None,
                     k_scale=None, v_scale=None,
                     seqused_q: Optional[torch.Tensor] = None,
-                    return_lse: bool = False):
+                    return_lse: bool = False,
+                    block_ids: Optional[torch.Tensor] = None):
     """fp32 paged attention.
 
     ``q [B, Sq, H_q, D]``; pools ``[n_pages, H_kv, P, D]`` (float, or FP8 codes as
@@ -241,6 +242,12 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
     keys ``>= L - Sq_b + j - W``.  Rows ``j >= seqused_q[b]`` and sequences with
     ``L == 0`` give zeros.  Returns fp32 ``[B, Sq, H_q, D]`` (and the natural-log
     LSE ``[B, H_q, Sq]`` when asked).
+
+    ``block_ids [B, >= Sq]`` (int, image-block id >= 0 or -1 per query row) adds the
+    block-bidirectional mask of ``kestrel/models/moondream/text.py:139-172``: inside a run of
+    equal non-negative ids every row also sees the keys of the run's later rows (the mask
+    callable itself lives in the absent wheel; this is its description at the call site and
+    in ``kestrel/models/moondream/runtime.py:1671-1679`` -- parity unpinned).
     """
     B, Sq, Hq, D = q.shape
     Hkv = k_cache.shape[1]
@@ -269,8 +276,15 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
         key = torch.arange(L).view(1, 1, L)
         row = torch.arange(sq).view(1, sq, 1)
         limit = L - sq + row
+        if block_ids is not None:
+            ids = block_ids[b, :sq].tolist()
+            run_end = list(range(sq))
+            for jj in range(sq - 2, -1, -1):
+                if ids[jj] >= 0 and ids[jj + 1] == ids[jj]:
+                    run_end[jj] = run_end[jj + 1]
+            limit = L - sq + torch.tensor(run_end).view(1, sq, 1)
         mask = torch.zeros(1, sq, L, dtype=torch.bool)
-        if causal or window_left is not None:
+        if causal or window_left is not None or block_ids is not None:
             mask |= key > limit
         if window_left is not None:
             mask |= key < (limit - int(window_left))

@@ -62,8 +62,9 @@ def test_runtime_object_has_the_reference_entry_points():
     assert callable(rt.attention.flash_attn_fwd)
     with pytest.raises(NotImplementedError):
         rt.sampling.sample_step_from_logits
+    assert rt.attention.block_bidirectional_mask is kernels.block_bidirectional_mask
     with pytest.raises(NotImplementedError):
-        rt.attention.block_bidirectional_mask
+        rt.attention.flash_attn_varlen_func
 
 
 def test_cpu_tensors_are_rejected_loudly():

@@ -118,3 +118,76 @@ def test_prefill_ignores_garbage_past_the_sequence_end():
                                     seqused_k=p["seqused_k"].to(DEV), causal=True)
     want = O.paged_attention(p["q"].to(torch.bfloat16).float(), p["k_pool"], p["v_pool"], p["page_table"], p["seqused_k"])
     assert_close(out, want, "garbage past the end")
+
+
+def _image_prompt_ids(B, Sq, layouts):
+    """block ids per position: ``layouts[b]`` is a list of (start, length, id) image blocks."""
+    ids = torch.full((B, Sq), -1, dtype=torch.int32)
+    for b, blocks in enumerate(layouts):
+        for start, n, bid in blocks:
+            ids[b, start:start + n] = bid
+    return ids
+
+
+def test_block_visibility_rows():
+    ids = torch.tensor([[0, 0, 0, -1, -1, 1, 1, -1], [-1, 3, 3, 3, 3, 3, 3, 3]], dtype=torch.int32, device=DEV)
+    got = kernels.block_visibility(ids).cpu().tolist()
+    assert got == [[2, 2, 2, 3, 4, 6, 6, 7], [0, 7, 7, 7, 7, 7, 7, 7]]
+    assert kernels.block_visibility(ids, 4).cpu().tolist() == [[2, 2, 2, 3], [0, 3, 3, 3]]
+
+
+@pytest.mark.parametrize("head_dim,group,heads_kv", [(64, 1, 8), (128, 4, 2)])
+def test_prefill_block_bidirectional_mask(head_dim, group, heads_kv):
+    # whole prompts (no cached prefix): BOS + a 729-position image + text; two images between text; text only;
+    # a short padded row
+    Sq = 900
+    lengths = [900, 900, 300, 40]
+    layouts = [[(0, 730, 0)], [(5, 200, 0), (400, 333, 1)], [], [(1, 30, 2)]]
+    ids = _image_prompt_ids(len(lengths), Sq, layouts)
+    p = make_paged_problem(seed=21, batch=len(lengths), len_lo=0, len_hi=0, n_q_heads=group * heads_kv,
+                           n_kv_heads=heads_kv, head_dim=head_dim, page_size=16, seqlen_q=Sq, dtype=torch.bfloat16,
+                           lengths=lengths)
+    sq = torch.tensor(lengths, dtype=torch.int32)
+    q = p["q"].to(torch.bfloat16).to(DEV)
+    rt = kernels.get_runtime()
+    out, _ = rt.attention.flash_attn_fwd(
+        q, p["k_pool"].to(torch.bfloat16).to(DEV).permute(0, 2, 1, 3), p["v_pool"].to(torch.bfloat16).to(DEV).permute(0, 2, 1, 3),
+        page_table=p["page_table"].to(DEV), seqused_q=sq.to(DEV), seqused_k=p["seqused_k"].to(DEV), paged_kv_non_tma=True,
+        causal=False, pack_gqa=False, mask_mod=rt.attention.block_bidirectional_mask, aux_tensors=[ids.to(DEV)])
+    want = O.paged_attention(p["q"].to(torch.bfloat16).float(), p["k_pool"], p["v_pool"], p["page_table"], p["seqused_k"],
+                             seqused_q=sq, block_ids=ids)
+    causal_only = O.paged_attention(p["q"].to(torch.bfloat16).float(), p["k_pool"], p["v_pool"], p["page_table"],
+                                    p["seqused_k"], seqused_q=sq)
+    assert (want[0, :700] - causal_only[0, :700]).abs().max() > 0.05   # the mask matters
+    assert torch.equal(want[2, :300], causal_only[2, :300])            # and leaves text-only prompts alone
+    for b, n in enumerate(lengths):
+        assert_close(out[b, :n], want[b, :n], f"block mask, sequence {b}")
+
+
+def test_prefill_block_mask_on_a_chunk_after_a_cached_prefix():
+    # the ids index the query rows of this call; keys before the chunk are plain causal context
+    Sq, L = 256, 256 + 333
+    ids = _image_prompt_ids(1, Sq, [[(10, 200, 0)]])
+    p = make_paged_problem(seed=22, batch=1, len_lo=0, len_hi=0, n_q_heads=8, n_kv_heads=2, head_dim=128, page_size=16,
+                           seqlen_q=Sq, dtype=torch.bfloat16, lengths=[L])
+    out, _ = kernels.flash_attn_fwd(
+        p["q"].to(torch.bfloat16).to(DEV), p["k_pool"].to(torch.bfloat16).to(DEV).permute(0, 2, 1, 3),
+        p["v_pool"].to(torch.bfloat16).to(DEV).permute(0, 2, 1, 3), page_table=p["page_table"].to(DEV),
+        seqused_k=p["seqused_k"].to(DEV), mask_mod=kernels.block_bidirectional_mask, aux_tensors=[ids.to(DEV)])
+    want = O.paged_attention(p["q"].to(torch.bfloat16).float(), p["k_pool"], p["v_pool"], p["page_table"], p["seqused_k"],
+                             block_ids=ids)
+    assert_close(out, want, "block mask on a chunk")
+
+
+def test_block_mask_argument_errors():
+    q = torch.zeros(1, 4, 2, 64, device=DEV, dtype=torch.bfloat16)
+    pool = torch.zeros(4, 16, 2, 64, device=DEV, dtype=torch.bfloat16)
+    kw = dict(page_table=torch.zeros(1, 2, dtype=torch.int32, device=DEV), seqused_k=torch.tensor([4], dtype=torch.int32, device=DEV))
+    with pytest.raises(NotImplementedError, match="only mask_mod"):
+        kernels.flash_attn_fwd(q, pool, pool, mask_mod=lambda *a: True, aux_tensors=[], **kw)
+    with pytest.raises(ValueError, match="aux_tensors"):
+        kernels.flash_attn_fwd(q, pool, pool, mask_mod=kernels.block_bidirectional_mask, **kw)
+    with pytest.raises(NotImplementedError, match="FP8"):
+        kernels.flash_attn_fwd(q, pool.view(torch.uint8)[..., :64], pool.view(torch.uint8)[..., :64],
+                               mask_mod=kernels.block_bidirectional_mask,
+                               aux_tensors=[torch.zeros(1, 4, dtype=torch.int32, device=DEV)], k_scale=1.0, v_scale=1.0, **kw)
