@@ -275,28 +275,72 @@ paged_prefill_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
   }
   const int n_tiles = max(n_x[0], n_x[1]);   // n_x[0] <= n_x[1] whenever tile B has rows (limits grow with the row)
 
-  // ---- set-up: barriers, tensor memory, Q tiles
-  if (tid == 0) {
-    for (int s = 0; s < RING; ++s) {
-      mbar_init(B_FULL(s), 1);
-      mbar_init(B_EMPTY(s), 1);
+  // ---- set-up.  The TMA warp initialises the barriers and starts the first K/V tiles at once, so
+  // that they are in flight while the other warps bring Q in and tensor memory is allocated.
+  // =========================== TMA producer (warp 8) ===========================
+  // ring entries alternate K_0, V_0, K_1, V_1, ...
+  const int page_sz = p.page_size;
+  const int p_shift = 31 - __clz(page_sz);
+  const int box_rows = page_sz < BN ? page_sz : BN;
+  const int box_shift = 31 - __clz(box_rows);
+  const int boxes_per_tile = BN >> box_shift;
+  auto produce = [&](int idx) -> bool {   // warp-wide; false when the ring slot never came free
+    const int s = idx % RING;
+    if (idx >= RING && !mbar_wait_bounded(B_EMPTY(s), (uint32_t)((idx / RING) - 1) & 1u)) {
+      if (lane == 0) report(KB200_STATUS_WAIT_TIMEOUT, idx, KID_PREFILL);
+      return false;
     }
-    for (int x = 0; x < 2; ++x) {
-      mbar_init(B_SREADY(x), 1);
-      mbar_init(B_PREADY(x), 128);
-      mbar_init(B_PVDONE(x), 1);
+    const int kv = idx & 1;
+    const int key0 = (tile_begin + (idx >> 1)) * BN;
+    int nvalid = L - key0;
+    if (nvalid > BN) nvalid = BN;
+    const int nvb = (nvalid + box_rows - 1) >> box_shift;
+#ifdef KB200_PF_DEBUG_NOTMA   // bottleneck analysis only: hand over empty tiles instead of loading them
+    if (lane == 0) mbar_arrive(B_FULL(s));
+    __syncwarp();
+    return true;
+#endif
+    if (lane == 0) mbar_expect_tx(B_FULL(s), (uint32_t)((nvb << box_shift) * HD * 2));
+    __syncwarp();
+    const uint32_t dst0 = sbase + SM::OFF_KV + (uint32_t)s * SM::KV_TILE;
+    for (int j = lane; j < boxes_per_tile * NH; j += 32) {
+      const int i = j / NH, half = j - i * NH;
+      if (i >= nvb) continue;
+      const int key = key0 + (i << box_shift);
+      const int page = p.page_table[(int64_t)b * p.pt_rs + (key >> p_shift)];
+      if ((unsigned)page >= (unsigned long long)p.n_pages) report(KB200_STATUS_BAD_PAGE, page, KID_PREFILL);
+      const uint32_t dst = dst0 + (uint32_t)half * (BN * 128) + (uint32_t)(i << box_shift) * 128;
+      tma_load_4d(dst, kv ? &tmV : &tmK, B_FULL(s), half * 64, key & (page_sz - 1), h, page);
     }
-    fence_barrier_init();
-  }
-  if (warp == 9) {
-    tmem_alloc(sbase + SM::OFF_TMEM, TMEM_COLS);
-    tmem_relinquish();
-  }
-  {
+    return true;
+  };
+  const int n_early = min(RING, 2 * n_tiles);   // ring entries that need no free slot
+  if (warp == 8) {
+    if (lane == 0) {
+      for (int s = 0; s < RING; ++s) {
+        mbar_init(B_FULL(s), 1);
+        mbar_init(B_EMPTY(s), 1);
+      }
+      for (int x = 0; x < 2; ++x) {
+        mbar_init(B_SREADY(x), 1);
+        mbar_init(B_PREADY(x), 128);
+        mbar_init(B_PVDONE(x), 1);
+      }
+      fence_barrier_init();
+      fence_proxy_async();
+    }
+    __syncwarp();
+    for (int idx = 0; idx < n_early; ++idx) produce(idx);
+  } else {
+    if (warp == 9) {
+      tmem_alloc(sbase + SM::OFF_TMEM, TMEM_COLS);
+      tmem_relinquish();
+    }
     // Q rows -> shared memory in the K-major 128-byte-swizzled operand layout (tile A, then tile B);
     // rows past the segment's end are zero
     constexpr int CH = HD * 2 / 16;   // 16-byte chunks per row
-    for (int i = tid; i < kPfCtaRows * CH; i += kPrefillThreads) {
+    const int qt = tid < 256 ? tid : tid - 32;   // 288 threads share the copy
+    for (int i = qt; i < kPfCtaRows * CH; i += kPrefillThreads - 32) {
       const int rr = i / CH, c = i - rr * CH;
       const int x = rr >> 7, r = rr & 127;
       const int row = row_first + rr;
@@ -319,42 +363,8 @@ paged_prefill_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp == 8) {
-    // =========================== TMA producer ===========================
-    // ring entries alternate K_0, V_0, K_1, V_1, ...
-    const int P = p.page_size;
-    const int p_shift = 31 - __clz(P);
-    const int box_rows = P < BN ? P : BN;
-    const int box_shift = 31 - __clz(box_rows);
-    const int boxes_per_tile = BN >> box_shift;
-    for (int idx = 0; idx < 2 * n_tiles; ++idx) {
-      const int s = idx % RING;
-      if (idx >= RING && !mbar_wait_bounded(B_EMPTY(s), (uint32_t)((idx / RING) - 1) & 1u)) {
-        if (lane == 0) report(KB200_STATUS_WAIT_TIMEOUT, idx, KID_PREFILL);
-        break;
-      }
-      const int kv = idx & 1;
-      const int key0 = (tile_begin + (idx >> 1)) * BN;
-      int nvalid = L - key0;
-      if (nvalid > BN) nvalid = BN;
-      const int nvb = (nvalid + box_rows - 1) >> box_shift;
-#ifdef KB200_PF_DEBUG_NOTMA   // bottleneck analysis only: hand over empty tiles instead of loading them
-      if (lane == 0) mbar_arrive(B_FULL(s));
-      __syncwarp();
-      continue;
-#endif
-      if (lane == 0) mbar_expect_tx(B_FULL(s), (uint32_t)((nvb << box_shift) * HD * 2));
-      __syncwarp();
-      const uint32_t dst0 = sbase + SM::OFF_KV + (uint32_t)s * SM::KV_TILE;
-      for (int j = lane; j < boxes_per_tile * NH; j += 32) {
-        const int i = j / NH, half = j - i * NH;
-        if (i >= nvb) continue;
-        const int key = key0 + (i << box_shift);
-        const int page = p.page_table[(int64_t)b * p.pt_rs + (key >> p_shift)];
-        if ((unsigned)page >= (unsigned long long)p.n_pages) report(KB200_STATUS_BAD_PAGE, page, KID_PREFILL);
-        const uint32_t dst = dst0 + (uint32_t)half * (BN * 128) + (uint32_t)(i << box_shift) * 128;
-        tma_load_4d(dst, kv ? &tmV : &tmK, B_FULL(s), half * 64, key & (P - 1), h, page);
-      }
-    }
+    for (int idx = n_early; idx < 2 * n_tiles; ++idx)
+      if (!produce(idx)) break;
   } else if (warp == 9) {
     // =========================== MMA issuer ===========================
     // Order per tile i:  PV_A(i)  QK_A(i+1)  PV_B(i)  QK_B(i+1): while one Q tile's softmax runs, the
