@@ -339,21 +339,34 @@ paged_prefill_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
     // Q rows -> shared memory in the K-major 128-byte-swizzled operand layout (tile A, then tile B);
     // rows past the segment's end are zero
     constexpr int CH = HD * 2 / 16;   // 16-byte chunks per row
-    const int qt = tid < 256 ? tid : tid - 32;   // 288 threads share the copy
-    for (int i = qt; i < kPfCtaRows * CH; i += kPrefillThreads - 32) {
+    constexpr int NCOPY = kPrefillThreads - 32;   // 288 threads share the copy
+    constexpr int PER = (kPfCtaRows * CH + NCOPY - 1) / NCOPY;
+    const int qt = tid < 256 ? tid : tid - 32;
+    // all of a thread's loads are issued before the first store, so their latencies overlap
+    uint4 val[PER];
+#pragma unroll
+    for (int u = 0; u < PER; ++u) {
+      const int i = qt + u * NCOPY;
       const int rr = i / CH, c = i - rr * CH;
-      const int x = rr >> 7, r = rr & 127;
       const int row = row_first + rr;
-      uint4 val = make_uint4(0u, 0u, 0u, 0u);
-      if (row < nrows) {
+      val[u] = make_uint4(0u, 0u, 0u, 0u);
+      if (i < kPfCtaRows * CH && row < nrows) {
         const int j = row / p.group, g = row - j * p.group;
         const char* src = p.q + 2 * ((int64_t)b * p.q_bs + (int64_t)(qrow0 + j) * p.q_rs +
                                      (int64_t)(h * p.group + g) * p.q_hs) + 16 * c;
-        val = *reinterpret_cast<const uint4*>(src);
+        val[u] = *reinterpret_cast<const uint4*>(src);
       }
-      const uint32_t off = SM::OFF_Q + (uint32_t)x * SM::Q_TILE + (uint32_t)(c >> 3) * SM::SLAB + (uint32_t)r * 128 +
-                           (uint32_t)(((c & 7) ^ (r & 7)) << 4);
-      *reinterpret_cast<uint4*>(sgen + off) = val;
+    }
+#pragma unroll
+    for (int u = 0; u < PER; ++u) {
+      const int i = qt + u * NCOPY;
+      if (i < kPfCtaRows * CH) {
+        const int rr = i / CH, c = i - rr * CH;
+        const int x = rr >> 7, r = rr & 127;
+        const uint32_t off = SM::OFF_Q + (uint32_t)x * SM::Q_TILE + (uint32_t)(c >> 3) * SM::SLAB + (uint32_t)r * 128 +
+                             (uint32_t)(((c & 7) ^ (r & 7)) << 4);
+        *reinterpret_cast<uint4*>(sgen + off) = val[u];
+      }
     }
     fence_proxy_async();   // generic-proxy writes above are read by the tensor core (async proxy)
   }
