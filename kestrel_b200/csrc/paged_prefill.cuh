@@ -275,8 +275,8 @@ paged_prefill_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
   }
   const int n_tiles = max(n_x[0], n_x[1]);   // n_x[0] <= n_x[1] whenever tile B has rows (limits grow with the row)
 
-  // ---- set-up.  The TMA warp initialises the barriers and starts the first K/V tiles at once, so
-  // that they are in flight while the other warps bring Q in and tensor memory is allocated.
+  // ---- set-up.  The TMA warp starts on the K/V tiles at once, so that they are in flight while the
+  // other warps bring Q in and tensor memory is allocated.
   // =========================== TMA producer (warp 8) ===========================
   // ring entries alternate K_0, V_0, K_1, V_1, ...
   const int page_sz = p.page_size;
@@ -284,6 +284,11 @@ paged_prefill_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
   const int box_rows = page_sz < BN ? page_sz : BN;
   const int box_shift = 31 - __clz(box_rows);
   const int boxes_per_tile = BN >> box_shift;
+  // Page indices are fetched 32 table entries at a time (one per lane) and handed to the boxes by
+  // shuffle, so a tile does not wait for its own dependent table load.
+  int win_base = -1, win_page = 0;   // table slot of lane 0's entry; this lane's entry
+  const int64_t pt_row = (int64_t)b * p.pt_rs;
+  const int n_slots = (L + page_sz - 1) >> p_shift;   // table entries that hold pages of this sequence
   auto produce = [&](int idx) -> bool {   // warp-wide; false when the ring slot never came free
     const int s = idx % RING;
     if (idx >= RING && !mbar_wait_bounded(B_EMPTY(s), (uint32_t)((idx / RING) - 1) & 1u)) {
@@ -300,37 +305,47 @@ paged_prefill_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
     __syncwarp();
     return true;
 #endif
+    const int slot0 = key0 >> p_shift;
+    const bool windowed = boxes_per_tile <= 32;
+    if (windowed && (win_base < 0 || slot0 < win_base || slot0 + boxes_per_tile > win_base + 32)) {
+      win_base = slot0;
+      win_page = win_base + lane < n_slots ? p.page_table[pt_row + win_base + lane] : 0;
+    }
     if (lane == 0) mbar_expect_tx(B_FULL(s), (uint32_t)((nvb << box_shift) * HD * 2));
     __syncwarp();
     const uint32_t dst0 = sbase + SM::OFF_KV + (uint32_t)s * SM::KV_TILE;
-    for (int j = lane; j < boxes_per_tile * NH; j += 32) {
+    for (int j0 = 0; j0 < boxes_per_tile * NH; j0 += 32) {   // uniform trip count: the shuffle below is warp-wide
+      const int j = j0 + lane;
       const int i = j / NH, half = j - i * NH;
-      if (i >= nvb) continue;
       const int key = key0 + (i << box_shift);
-      const int page = p.page_table[(int64_t)b * p.pt_rs + (key >> p_shift)];
+      int page;
+      if (windowed) page = __shfl_sync(0xffffffffu, win_page, ((key >> p_shift) - win_base) & 31);
+      else page = (j < boxes_per_tile * NH && i < nvb) ? p.page_table[pt_row + (key >> p_shift)] : 0;
+      if (j >= boxes_per_tile * NH || i >= nvb) continue;
       if ((unsigned)page >= (unsigned long long)p.n_pages) report(KB200_STATUS_BAD_PAGE, page, KID_PREFILL);
       const uint32_t dst = dst0 + (uint32_t)half * (BN * 128) + (uint32_t)(i << box_shift) * 128;
       tma_load_4d(dst, kv ? &tmV : &tmK, B_FULL(s), half * 64, key & (page_sz - 1), h, page);
     }
     return true;
   };
-  const int n_early = min(RING, 2 * n_tiles);   // ring entries that need no free slot
-  if (warp == 8) {
-    if (lane == 0) {
-      for (int s = 0; s < RING; ++s) {
-        mbar_init(B_FULL(s), 1);
-        mbar_init(B_EMPTY(s), 1);
-      }
-      for (int x = 0; x < 2; ++x) {
-        mbar_init(B_SREADY(x), 1);
-        mbar_init(B_PREADY(x), 128);
-        mbar_init(B_PVDONE(x), 1);
-      }
-      fence_barrier_init();
-      fence_proxy_async();
+  if (tid == 0) {
+    for (int s = 0; s < RING; ++s) {
+      mbar_init(B_FULL(s), 1);
+      mbar_init(B_EMPTY(s), 1);
     }
-    __syncwarp();
-    for (int idx = 0; idx < n_early; ++idx) produce(idx);
+    for (int x = 0; x < 2; ++x) {
+      mbar_init(B_SREADY(x), 1);
+      mbar_init(B_PREADY(x), 128);
+      mbar_init(B_PVDONE(x), 1);
+    }
+    fence_barrier_init();
+    fence_proxy_async();
+  }
+  __syncthreads();   // barriers exist; nothing slow has started yet, so nobody waits here
+  if (warp == 8) {
+    // the other warps only meet this one again at the exit: their set-up barrier leaves it out
+    for (int idx = 0; idx < 2 * n_tiles; ++idx)
+      if (!produce(idx)) break;
   } else {
     if (warp == 9) {
       tmem_alloc(sbase + SM::OFF_TMEM, TMEM_COLS);
@@ -369,15 +384,14 @@ paged_prefill_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
       }
     }
     fence_proxy_async();   // generic-proxy writes above are read by the tensor core (async proxy)
+    tc_fence_before();
+    asm volatile("bar.sync 1, %0;" ::"n"(kPrefillThreads - 32) : "memory");   // warps 0-7 and 9
+    tc_fence_after();
   }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_base = warp == 8 ? 0u : *tmem_slot;
 
   if (warp == 8) {
-    for (int idx = n_early; idx < 2 * n_tiles; ++idx)
-      if (!produce(idx)) break;
+    // (the producer has run to completion above)
   } else if (warp == 9) {
     // =========================== MMA issuer ===========================
     // Order per tile i:  PV_A(i)  QK_A(i+1)  PV_B(i)  QK_B(i+1): while one Q tile's softmax runs, the
