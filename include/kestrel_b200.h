@@ -260,6 +260,11 @@ typedef struct kb200_attn_args {
 KB200_API uint64_t kb200_attn_workspace_bytes(int64_t batch, int64_t total_q, int32_t n_q_heads,
                                     int32_t n_kv_heads, int32_t head_dim, int32_t device);
 
+/* Scratch bytes the call described by `args` needs (workspace fields ignored): at most the bound
+ * above, and much less for prefill-shaped calls (many query rows per sequence, 16-bit K/V), which
+ * keep no split-KV partials.  0 on invalid arguments. */
+KB200_API uint64_t kb200_attn_workspace_bytes_for(const kb200_attn_args* args);
+
 KB200_API int kb200_paged_attention(const kb200_attn_args* args);
 
 /* ---------------------------------------------------------------------------
@@ -295,7 +300,7 @@ KB200_API int kb200_block_visibility(const int32_t* block_ids, int64_t ids_row_s
  * API or through any library.
  *
  * Limits and rules:
- *   - the problem must fit: kb200_attn_workspace_bytes(batch, total_q, ...) <=
+ *   - the problem must fit: kb200_attn_workspace_bytes_for(args) <=
  *     KB200_STATIC_SCRATCH_BYTES (decode batches of up to 188 sequences at
  *     32 query / 8 KV heads, head_dim 128), otherwise KB200_ERR_WORKSPACE with a message saying how
  *     much was needed;

@@ -32,6 +32,7 @@ EXPORTS = (
     "kb200_rope_append",
     "kb200_copy_pages",
     "kb200_attn_workspace_bytes",
+    "kb200_attn_workspace_bytes_for",
     "kb200_paged_attention",
     "kb200_block_visibility",
     "kb200_paged_attention_static",
@@ -130,6 +131,8 @@ def _declare(lib: C.CDLL) -> None:
     lib.kb200_copy_pages.argtypes = [C.POINTER(vp), i32, i64, i64, i64, vp, vp, i64, i32, vp]
     lib.kb200_attn_workspace_bytes.restype = C.c_uint64
     lib.kb200_attn_workspace_bytes.argtypes = [i64, i64, i32, i32, i32, i32]
+    lib.kb200_attn_workspace_bytes_for.restype = C.c_uint64
+    lib.kb200_attn_workspace_bytes_for.argtypes = [C.POINTER(AttnArgs)]
     lib.kb200_block_visibility.restype = C.c_int
     lib.kb200_block_visibility.argtypes = [vp, i64, i64, i64, vp, i64, i32, vp]
     lib.kb200_paged_attention.restype = C.c_int

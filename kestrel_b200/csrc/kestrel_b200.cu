@@ -122,6 +122,15 @@ uint64_t kb200_attn_workspace_bytes(int64_t batch, int64_t total_q, int32_t n_q_
   return attn_workspace_layout(batch, total_q, n_q_heads, n_kv_heads, head_dim, sms * kAttnMaxWarps).total;
 }
 
+uint64_t kb200_attn_workspace_bytes_for(const kb200_attn_args* args) {
+  if (!args || args->struct_bytes != sizeof(kb200_attn_args)) return 0;
+  if (args->batch <= 0 || args->total_q <= 0 || args->n_q_heads <= 0 || args->n_kv_heads <= 0 || args->head_dim <= 0)
+    return 0;
+  int sms = 0;
+  if (device_sm_count(args->device, &sms) != KB200_OK) return 0;
+  return attn_workspace_need(args, sms);
+}
+
 int kb200_block_visibility(const int32_t* block_ids, int64_t ids_row_stride, int64_t batch, int64_t seqlen,
                            int32_t* out, int64_t out_row_stride, int32_t device, void* stream) {
   KB200_ENTER(device);
@@ -176,8 +185,7 @@ int kb200_paged_attention_static(const kb200_attn_args* args) {
                 sizeof(kb200_attn_args));
   KB200_ENTER(args->device);
   if (args->batch > 0 && args->total_q > 0) {
-    const uint64_t need = kb200_attn_workspace_bytes(args->batch, args->total_q, args->n_q_heads, args->n_kv_heads,
-                                                     args->head_dim, args->device);
+    const uint64_t need = kb200_attn_workspace_bytes_for(args);
     if (need == 0) return fail(KB200_ERR_INVALID, "cannot size the scratch for these arguments");
     if (need > KB200_STATIC_SCRATCH_BYTES)
       return fail(KB200_ERR_WORKSPACE,

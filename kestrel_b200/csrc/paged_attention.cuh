@@ -1446,6 +1446,22 @@ int launch_prefill_variant(const CUtensorMap& tmK, const CUtensorMap& tmV, const
                            cudaStream_t stream);
 constexpr int kPrefillRowsPerSeg = 256, kPrefillTileKeys = 128, kPrefillMinPackedRows = 64;
 
+// Which kernel serves a call: many query rows per sequence with 16-bit K/V (or a block mask) go to
+// the tensor-memory prefill kernel, one CTA per 256 packed rows, no split over keys and no merge.
+inline bool use_prefill_kernel(const kb200_attn_args* a) {
+  if (a->q_visible_until != nullptr) return true;
+  if (!prefill_enabled() || a->kv_dtype == KB200_DTYPE_E4M3 || a->n_kv_heads <= 0) return false;
+  return (int64_t)(a->n_q_heads / a->n_kv_heads) * a->seqlen_q >= kPrefillMinPackedRows;
+}
+
+// Scratch bytes this very call needs: the plan arrays, plus the split-KV partials unless the prefill
+// kernel serves it.
+inline uint64_t attn_workspace_need(const kb200_attn_args* a, int sms) {
+  const AttnWorkspace wl = attn_workspace_layout(a->batch, a->total_q, a->n_q_heads, a->n_kv_heads, a->head_dim,
+                                                 sms * kAttnMaxWarps);
+  return use_prefill_kernel(a) ? wl.part_ml : wl.total;
+}
+
 inline int launch_paged_attention(const kb200_attn_args* a) {
   KB200_REQUIRE(a != nullptr, "args is null");
   KB200_REQUIRE(a->struct_bytes == sizeof(kb200_attn_args), "kb200_attn_args size mismatch: got %u, built with %zu",
@@ -1484,13 +1500,12 @@ inline int launch_paged_attention(const kb200_attn_args* a) {
   const int group = a->n_q_heads / a->n_kv_heads;
   const AttnWorkspace wl = attn_workspace_layout(a->batch, a->total_q, a->n_q_heads, a->n_kv_heads, a->head_dim,
                                                  grid * kAttnMaxWarps);
-  if (!a->workspace || a->workspace_bytes < wl.total)
-    return fail(KB200_ERR_WORKSPACE, "workspace too small: need %zu bytes, got %llu", wl.total,
+  const uint64_t ws_need = attn_workspace_need(a, sms);
+  if (!a->workspace || a->workspace_bytes < ws_need)
+    return fail(KB200_ERR_WORKSPACE, "workspace too small: need %llu bytes, got %llu", (unsigned long long)ws_need,
                 (unsigned long long)a->workspace_bytes);
   KB200_REQUIRE((reinterpret_cast<uintptr_t>(a->workspace) & 255) == 0, "workspace must be 256-byte aligned");
 
-  // Many query rows per sequence (prompt chunks) with 16-bit K/V: the tensor-memory kernel, one
-  // CTA per 256 packed rows, no split over keys and no merge.
   const bool block_mask = a->q_visible_until != nullptr;
   if (block_mask) {
     KB200_REQUIRE(a->causal != 0 && a->window_left < 0, "the block-bidirectional mask extends the causal mask: "
@@ -1498,8 +1513,7 @@ inline int launch_paged_attention(const kb200_attn_args* a) {
     if (a->kv_dtype == KB200_DTYPE_E4M3)
       return fail(KB200_ERR_UNSUPPORTED, "the block-bidirectional mask is not implemented for FP8 K/V");
   }
-  const bool prefill = block_mask || (prefill_enabled() && a->kv_dtype != KB200_DTYPE_E4M3 &&
-                                      (int64_t)group * a->seqlen_q >= kPrefillMinPackedRows);
+  const bool prefill = use_prefill_kernel(a);
   const int tile_n = prefill ? kPrefillTileKeys : tile_n_for(a->kv_dtype, a->head_dim, nw);
   // The transposed decode kernel pays off where the math is the limiter (e4m3 K/V); 16-bit K/V
   // is within a few percent of the HBM roofline with the general kernel already.

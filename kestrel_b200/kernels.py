@@ -622,13 +622,7 @@ def flash_attn_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *,
         vs_f, vs_ptr = scale_arg(v_scale, "v_scale")
 
     stream = _stream(dev)
-    wkey = (B, total_q, Hq, Hkv, D, dev)
-    nbytes = _ws_bytes_cache.get(wkey)
     lib = _native.load()
-    if nbytes is None:
-        nbytes = int(lib.kb200_attn_workspace_bytes(B, total_q, Hq, Hkv, D, dev))
-        _ws_bytes_cache[wkey] = nbytes
-    ws = _workspace(dev, stream, nbytes)
 
     a = _native.AttnArgs()
     a.struct_bytes = C.sizeof(_native.AttnArgs)
@@ -659,8 +653,6 @@ def flash_attn_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *,
     a.window_left = int(window_size_left) if window_size_left is not None and window_size_left >= 0 else -1
     a.k_scale, a.v_scale = ks_f, vs_f
     a.k_scale_per_head, a.v_scale_per_head = ks_ptr, vs_ptr
-    a.workspace = ws.data_ptr()
-    a.workspace_bytes = ws.numel()
     if block_ids is not None:
         if fp8:
             raise NotImplementedError("block_bidirectional_mask is not implemented for FP8 K/V")
@@ -670,6 +662,15 @@ def flash_attn_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *,
         a.q_visible_until = vis.data_ptr()
         a.q_visible_batch_stride = vis.stride(0)
         a.causal = 1   # the block mask extends the causal one (the reference passes causal=False next to mask_mod)
+    # scratch: sized for this very call (prefill-shaped calls need only the plan arrays)
+    wkey = (B, total_q, Sq, Hq, Hkv, D, a.kv_dtype, block_ids is not None, dev)
+    nbytes = _ws_bytes_cache.get(wkey)
+    if nbytes is None:
+        nbytes = int(lib.kb200_attn_workspace_bytes_for(C.byref(a)))
+        _ws_bytes_cache[wkey] = nbytes
+    ws = _workspace(dev, stream, nbytes)
+    a.workspace = ws.data_ptr()
+    a.workspace_bytes = ws.numel()
     _native.check(lib.kb200_paged_attention(C.byref(a)))
     return out, lse
 

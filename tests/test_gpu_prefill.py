@@ -191,3 +191,21 @@ def test_block_mask_argument_errors():
         kernels.flash_attn_fwd(q, pool.view(torch.uint8)[..., :64], pool.view(torch.uint8)[..., :64],
                                mask_mod=kernels.block_bidirectional_mask,
                                aux_tensors=[torch.zeros(1, 4, dtype=torch.int32, device=DEV)], k_scale=1.0, v_scale=1.0, **kw)
+
+
+def test_prefill_calls_need_only_the_plan_arrays_as_scratch():
+    import ctypes as C
+    lib = _native.load()
+    a = _native.AttnArgs()
+    a.struct_bytes = C.sizeof(_native.AttnArgs)
+    a.device = torch.cuda.current_device()
+    a.batch, a.total_q, a.seqlen_q = 64, 64 * 1024, 1024
+    a.n_q_heads, a.n_kv_heads, a.head_dim, a.page_size = 32, 8, 128, 16
+    a.q_dtype = a.kv_dtype = _native.DTYPE_BF16
+    bound = int(lib.kb200_attn_workspace_bytes(a.batch, a.total_q, 32, 8, 128, a.device))
+    need = int(lib.kb200_attn_workspace_bytes_for(C.byref(a)))
+    assert 0 < need < 64 * 1024 < bound            # a few plan arrays against gigabytes of split-KV partials
+    a.kv_dtype = _native.DTYPE_E4M3                 # FP8 K/V stays on the split-KV kernels
+    assert int(lib.kb200_attn_workspace_bytes_for(C.byref(a))) == bound
+    a.kv_dtype, a.seqlen_q, a.total_q = _native.DTYPE_BF16, 1, 64  # decode
+    assert int(lib.kb200_attn_workspace_bytes_for(C.byref(a))) == int(lib.kb200_attn_workspace_bytes(64, 64, 32, 8, 128, a.device))
