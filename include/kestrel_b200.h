@@ -251,7 +251,7 @@ typedef struct kb200_attn_args {
    * its own sequence's rows up to q_visible_until[j] (>= j), on top of the causal part.  Device
    * int32, NULL for plain causal; indexed [b * q_visible_batch_stride + j] (padded layout) or
    * by packed row.  kb200_block_visibility builds it from the per-token block ids.  Needs
-   * causal != 0, no window, 16-bit K/V. */
+   * causal != 0 and no window. */
   const int32_t* q_visible_until;
   int64_t q_visible_batch_stride;
 } kb200_attn_args;
@@ -261,8 +261,8 @@ KB200_API uint64_t kb200_attn_workspace_bytes(int64_t batch, int64_t total_q, in
                                     int32_t n_kv_heads, int32_t head_dim, int32_t device);
 
 /* Scratch bytes the call described by `args` needs (workspace fields ignored): at most the bound
- * above, and much less for prefill-shaped calls (many query rows per sequence, 16-bit K/V), which
- * keep no split-KV partials.  0 on invalid arguments. */
+ * above, and much less for prefill-shaped calls (many query rows per sequence), which keep no
+ * split-KV partials.  0 on invalid arguments. */
 KB200_API uint64_t kb200_attn_workspace_bytes_for(const kb200_attn_args* args);
 
 KB200_API int kb200_paged_attention(const kb200_attn_args* args);

@@ -1441,7 +1441,7 @@ inline int launch_attn_dispatch(bool d128, int nw, const CUtensorMap& tmK, const
 
 // paged_prefill.cuh
 bool prefill_enabled();
-template <int HD, bool BF16>
+template <int HD, bool BF16, bool KV8>
 int launch_prefill_variant(const CUtensorMap& tmK, const CUtensorMap& tmV, const AttnParams& p, int grid, int dev,
                            cudaStream_t stream);
 constexpr int kPrefillRowsPerSeg = 256, kPrefillTileKeys = 128, kPrefillMinPackedRows = 64;
@@ -1450,7 +1450,7 @@ constexpr int kPrefillRowsPerSeg = 256, kPrefillTileKeys = 128, kPrefillMinPacke
 // the tensor-memory prefill kernel, one CTA per 256 packed rows, no split over keys and no merge.
 inline bool use_prefill_kernel(const kb200_attn_args* a) {
   if (a->q_visible_until != nullptr) return true;
-  if (!prefill_enabled() || a->kv_dtype == KB200_DTYPE_E4M3 || a->n_kv_heads <= 0) return false;
+  if (!prefill_enabled() || a->n_kv_heads <= 0) return false;
   return (int64_t)(a->n_q_heads / a->n_kv_heads) * a->seqlen_q >= kPrefillMinPackedRows;
 }
 
@@ -1510,8 +1510,6 @@ inline int launch_paged_attention(const kb200_attn_args* a) {
   if (block_mask) {
     KB200_REQUIRE(a->causal != 0 && a->window_left < 0, "the block-bidirectional mask extends the causal mask: "
                                                        "causal must be set and no window given");
-    if (a->kv_dtype == KB200_DTYPE_E4M3)
-      return fail(KB200_ERR_UNSUPPORTED, "the block-bidirectional mask is not implemented for FP8 K/V");
   }
   const bool prefill = use_prefill_kernel(a);
   const int tile_n = prefill ? kPrefillTileKeys : tile_n_for(a->kv_dtype, a->head_dim, nw);
@@ -1594,11 +1592,18 @@ inline int launch_paged_attention(const kb200_attn_args* a) {
     const int64_t nseg = packed ? (int64_t)a->n_kv_heads * ((group * a->total_q + kPrefillRowsPerSeg - 1) / kPrefillRowsPerSeg + a->batch)
                                 : a->batch * (int64_t)a->n_kv_heads * ((group * (int64_t)a->seqlen_q + kPrefillRowsPerSeg - 1) / kPrefillRowsPerSeg);
     KB200_REQUIRE(nseg <= 0x7fffffff, "too many segments");
-    const bool bf = a->kv_dtype == KB200_DTYPE_BF16;
-    if (d128) rc = bf ? launch_prefill_variant<128, true>(tmK, tmV, p, (int)nseg, a->device, stream)
-                      : launch_prefill_variant<128, false>(tmK, tmV, p, (int)nseg, a->device, stream);
-    else rc = bf ? launch_prefill_variant<64, true>(tmK, tmV, p, (int)nseg, a->device, stream)
-                 : launch_prefill_variant<64, false>(tmK, tmV, p, (int)nseg, a->device, stream);
+    const bool bf = a->q_dtype == KB200_DTYPE_BF16;
+    if (a->kv_dtype == KB200_DTYPE_E4M3) {
+      if (d128) rc = bf ? launch_prefill_variant<128, true, true>(tmK, tmV, p, (int)nseg, a->device, stream)
+                        : launch_prefill_variant<128, false, true>(tmK, tmV, p, (int)nseg, a->device, stream);
+      else rc = bf ? launch_prefill_variant<64, true, true>(tmK, tmV, p, (int)nseg, a->device, stream)
+                   : launch_prefill_variant<64, false, true>(tmK, tmV, p, (int)nseg, a->device, stream);
+    } else {
+      if (d128) rc = bf ? launch_prefill_variant<128, true, false>(tmK, tmV, p, (int)nseg, a->device, stream)
+                        : launch_prefill_variant<128, false, false>(tmK, tmV, p, (int)nseg, a->device, stream);
+      else rc = bf ? launch_prefill_variant<64, true, false>(tmK, tmV, p, (int)nseg, a->device, stream)
+                   : launch_prefill_variant<64, false, false>(tmK, tmV, p, (int)nseg, a->device, stream);
+    }
     return rc;   // every segment is written by its own CTA: nothing to merge
   }
   if (decode8)  // e4m3 only (the kernel template also covers 16-bit K/V; measured no faster there)

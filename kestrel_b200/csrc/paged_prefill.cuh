@@ -35,19 +35,26 @@ namespace kb200 {
 constexpr int kPfTileRows = 128;    // packed query rows per Q tile (MMA M)
 constexpr int kPfCtaRows = 256;     // two Q tiles per CTA
 constexpr int kPrefillKeys = 128;   // keys per tile (MMA N of the first product)
-constexpr int kPrefillThreads = 320;  // 2 x 4 softmax warps, 1 TMA warp, 1 MMA warp
+// 2 x 4 softmax warps, 1 TMA warp, 1 MMA warp; FP8 K/V adds 4 warps that widen the tiles to 16 bits
+constexpr int kPfCopyThreads = 288;   // warps 0-7 and 9 copy Q and meet at the set-up barrier
+constexpr int pf_threads(bool kv8) { return kv8 ? 448 : 320; }
 
-template <int HD>
+template <int HD, bool KV8>
 struct PrefillSmem {
-  static constexpr int NH = HD * 2 / 128;                       // 128-byte slabs per row
+  static constexpr int NH = HD * 2 / 128;                       // 128-byte slabs per 16-bit row
   static constexpr int SLAB = kPfTileRows * 128;                // bytes of one 128-row slab
   static constexpr int Q_TILE = NH * SLAB;
-  static constexpr int KV_TILE = NH * kPrefillKeys * 128;       // one K or V tile
-  static constexpr int RING = HD == 128 ? 5 : 8;                // K/V tiles in flight (K0 V0 K1 V1 ...)
+  static constexpr int KV_TILE = NH * kPrefillKeys * 128;       // one K or V tile, 16-bit
+  // 16-bit K/V tiles in flight (K0 V0 K1 V1 ...); with FP8 pools they are filled by the widening warps
+  static constexpr int RING = KV8 ? (HD == 128 ? 3 : 6) : (HD == 128 ? 5 : 8);
+  static constexpr int RB8 = HD;                                // bytes of one e4m3 row (128 or 64)
+  static constexpr int STG_TILE = kPrefillKeys * RB8;           // one e4m3 tile as the TMA delivers it
+  static constexpr int NSTG = KV8 ? (HD == 128 ? 4 : 8) : 0;
   static constexpr int OFF_Q = 0;
   static constexpr int OFF_KV = 2 * Q_TILE;
-  static constexpr int OFF_BAR = OFF_KV + RING * KV_TILE;
-  static constexpr int N_BARS = 2 * RING + 6;
+  static constexpr int OFF_STG = OFF_KV + RING * KV_TILE;
+  static constexpr int OFF_BAR = OFF_STG + NSTG * STG_TILE;
+  static constexpr int N_BARS = 2 * RING + 6 + 2 * NSTG;
   static constexpr int OFF_TMEM = OFF_BAR + 8 * N_BARS;
   static constexpr int BYTES = OFF_TMEM + 16 + 1024;            // + alignment slack
 };
@@ -206,11 +213,15 @@ __host__ __device__ constexpr uint32_t umma_idesc(bool bf16, bool b_mn_major, in
          ((uint32_t)(n >> 3) << 17) | ((uint32_t)(kPfTileRows >> 4) << 24);
 }
 
-template <int HD, bool BF16>
-__global__ void __launch_bounds__(kPrefillThreads, 1)
+// BF16: dtype of q and out.  KV8: K/V pools hold e4m3 codes; the tiles are widened to f16 in shared memory
+// (exact), the tensor core then runs on f16 operands (q is converted once, as in the decode kernels)
+// and the dequantisation scales are folded into the softmax scale (K) and the final normalisation (V).
+template <int HD, bool BF16, bool KV8>
+__global__ void __launch_bounds__(pf_threads(KV8), 1)
 paged_prefill_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                      const __grid_constant__ AttnParams p) {
-  using SM = PrefillSmem<HD>;
+  using SM = PrefillSmem<HD, KV8>;
+  constexpr bool MMA_BF16 = BF16 && !KV8;   // operand type of both products
   constexpr int NH = SM::NH;
   constexpr int RING = SM::RING;
   constexpr int BN = kPrefillKeys;
@@ -231,6 +242,8 @@ paged_prefill_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
   auto B_SREADY = [&](int x) { return bar + 8u * (2 * RING + x); };
   auto B_PREADY = [&](int x) { return bar + 8u * (2 * RING + 2 + x); };
   auto B_PVDONE = [&](int x) { return bar + 8u * (2 * RING + 4 + x); };
+  auto B_SFULL = [&](int s) { return bar + 8u * (2 * RING + 6 + s); };               // e4m3 staging tiles
+  auto B_SEMPTY = [&](int s) { return bar + 8u * (2 * RING + 6 + SM::NSTG + s); };
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(sgen + SM::OFF_TMEM);
 
   pdl_launch_dependents();
@@ -290,8 +303,9 @@ paged_prefill_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
   const int64_t pt_row = (int64_t)b * p.pt_rs;
   const int n_slots = (L + page_sz - 1) >> p_shift;   // table entries that hold pages of this sequence
   auto produce = [&](int idx) -> bool {   // warp-wide; false when the ring slot never came free
-    const int s = idx % RING;
-    if (idx >= RING && !mbar_wait_bounded(B_EMPTY(s), (uint32_t)((idx / RING) - 1) & 1u)) {
+    constexpr int NSLOT = KV8 ? SM::NSTG : RING;
+    const int s = idx % NSLOT;
+    if (idx >= NSLOT && !mbar_wait_bounded(KV8 ? B_SEMPTY(s) : B_EMPTY(s), (uint32_t)((idx / NSLOT) - 1) & 1u)) {
       if (lane == 0) report(KB200_STATUS_WAIT_TIMEOUT, idx, KID_PREFILL);
       return false;
     }
@@ -300,8 +314,9 @@ paged_prefill_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
     int nvalid = L - key0;
     if (nvalid > BN) nvalid = BN;
     const int nvb = (nvalid + box_rows - 1) >> box_shift;
+    const uint32_t full = KV8 ? B_SFULL(s) : B_FULL(s);
 #ifdef KB200_PF_DEBUG_NOTMA   // bottleneck analysis only: hand over empty tiles instead of loading them
-    if (lane == 0) mbar_arrive(B_FULL(s));
+    if (lane == 0) mbar_arrive(full);
     __syncwarp();
     return true;
 #endif
@@ -311,27 +326,34 @@ paged_prefill_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
       win_base = slot0;
       win_page = win_base + lane < n_slots ? p.page_table[pt_row + win_base + lane] : 0;
     }
-    if (lane == 0) mbar_expect_tx(B_FULL(s), (uint32_t)((nvb << box_shift) * HD * 2));
+    constexpr int NHB = KV8 ? 1 : NH;                        // TMA boxes per row
+    constexpr int ROWB = KV8 ? SM::RB8 : 128;                // bytes of one box row in shared memory
+    if (lane == 0) mbar_expect_tx(full, (uint32_t)((nvb << box_shift) * HD * (KV8 ? 1 : 2)));
     __syncwarp();
-    const uint32_t dst0 = sbase + SM::OFF_KV + (uint32_t)s * SM::KV_TILE;
-    for (int j0 = 0; j0 < boxes_per_tile * NH; j0 += 32) {   // uniform trip count: the shuffle below is warp-wide
+    const uint32_t dst0 = KV8 ? sbase + SM::OFF_STG + (uint32_t)s * SM::STG_TILE
+                              : sbase + SM::OFF_KV + (uint32_t)s * SM::KV_TILE;
+    for (int j0 = 0; j0 < boxes_per_tile * NHB; j0 += 32) {   // uniform trip count: the shuffle below is warp-wide
       const int j = j0 + lane;
-      const int i = j / NH, half = j - i * NH;
+      const int i = j / NHB, half = j - i * NHB;
       const int key = key0 + (i << box_shift);
       int page;
       if (windowed) page = __shfl_sync(0xffffffffu, win_page, ((key >> p_shift) - win_base) & 31);
-      else page = (j < boxes_per_tile * NH && i < nvb) ? p.page_table[pt_row + (key >> p_shift)] : 0;
-      if (j >= boxes_per_tile * NH || i >= nvb) continue;
+      else page = (j < boxes_per_tile * NHB && i < nvb) ? p.page_table[pt_row + (key >> p_shift)] : 0;
+      if (j >= boxes_per_tile * NHB || i >= nvb) continue;
       if ((unsigned)page >= (unsigned long long)p.n_pages) report(KB200_STATUS_BAD_PAGE, page, KID_PREFILL);
-      const uint32_t dst = dst0 + (uint32_t)half * (BN * 128) + (uint32_t)(i << box_shift) * 128;
-      tma_load_4d(dst, kv ? &tmV : &tmK, B_FULL(s), half * 64, key & (page_sz - 1), h, page);
+      const uint32_t dst = dst0 + (uint32_t)half * (BN * 128) + (uint32_t)(i << box_shift) * ROWB;
+      tma_load_4d(dst, kv ? &tmV : &tmK, full, half * 64, key & (page_sz - 1), h, page);
     }
     return true;
   };
   if (tid == 0) {
     for (int s = 0; s < RING; ++s) {
-      mbar_init(B_FULL(s), 1);
+      mbar_init(B_FULL(s), KV8 ? 128 : 1);   // filled by the TMA unit, or by the 128 widening threads
       mbar_init(B_EMPTY(s), 1);
+    }
+    for (int s = 0; s < SM::NSTG; ++s) {
+      mbar_init(B_SFULL(s), 1);
+      mbar_init(B_SEMPTY(s), 128);
     }
     for (int x = 0; x < 2; ++x) {
       mbar_init(B_SREADY(x), 1);
@@ -346,6 +368,38 @@ paged_prefill_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
     // the other warps only meet this one again at the exit: their set-up barrier leaves it out
     for (int idx = 0; idx < 2 * n_tiles; ++idx)
       if (!produce(idx)) break;
+  } else if (KV8 && warp >= 10) {
+    // =========================== widening warps (FP8 pools): one key row per thread ===========================
+    // e4m3 tile as delivered by the TMA unit (rows of RB8 bytes, swizzled) -> f16 tile in the operand
+    // layout of the MMAs (rows of 256 bytes in two 128-byte-swizzled slabs, or one slab for head_dim 64)
+    constexpr int RB8 = SM::RB8;
+    const int r = (warp - 10) * 32 + lane;
+    for (int idx = 0; idx < 2 * n_tiles; ++idx) {
+      const int s8 = idx % SM::NSTG, c = idx % RING;
+      bool got = mbar_wait_bounded(B_SFULL(s8), (uint32_t)(idx / SM::NSTG) & 1u);
+      if (got && idx >= RING) got = mbar_wait_bounded(B_EMPTY(c), (uint32_t)((idx / RING) - 1) & 1u);
+      if (!got) {
+        if (lane == 0) report(KB200_STATUS_WAIT_TIMEOUT, idx, KID_PREFILL);
+        break;
+      }
+      const uint8_t* src = sgen + SM::OFF_STG + s8 * SM::STG_TILE + r * RB8;
+      uint8_t* dst = sgen + SM::OFF_KV + c * SM::KV_TILE + r * 128;
+#pragma unroll
+      for (int ch = 0; ch < RB8 / 16; ++ch) {
+        const uint4 x = *reinterpret_cast<const uint4*>(src + ((ch ^ (int)swz<RB8>(r)) << 4));
+        uint4 lo4, hi4;   // elements 16ch .. 16ch+7 and 16ch+8 .. 16ch+15 as f16
+        e4m3x4_to_f16x4(x.x, lo4.x, lo4.y);
+        e4m3x4_to_f16x4(x.y, lo4.z, lo4.w);
+        e4m3x4_to_f16x4(x.z, hi4.x, hi4.y);
+        e4m3x4_to_f16x4(x.w, hi4.z, hi4.w);
+        const int d0 = 2 * ch, d1 = 2 * ch + 1;   // 16-byte chunks of the f16 row
+        *reinterpret_cast<uint4*>(dst + (d0 >> 3) * (BN * 128) + (((d0 & 7) ^ (r & 7)) << 4)) = lo4;
+        *reinterpret_cast<uint4*>(dst + (d1 >> 3) * (BN * 128) + (((d1 & 7) ^ (r & 7)) << 4)) = hi4;
+      }
+      fence_proxy_async();          // the tensor core reads what was just written
+      mbar_arrive(B_FULL(c));
+      mbar_arrive(B_SEMPTY(s8));
+    }
   } else {
     if (warp == 9) {
       tmem_alloc(sbase + SM::OFF_TMEM, TMEM_COLS);
@@ -354,7 +408,7 @@ paged_prefill_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
     // Q rows -> shared memory in the K-major 128-byte-swizzled operand layout (tile A, then tile B);
     // rows past the segment's end are zero
     constexpr int CH = HD * 2 / 16;   // 16-byte chunks per row
-    constexpr int NCOPY = kPrefillThreads - 32;   // 288 threads share the copy
+    constexpr int NCOPY = kPfCopyThreads;
     constexpr int PER = (kPfCtaRows * CH + NCOPY - 1) / NCOPY;
     const int qt = tid < 256 ? tid : tid - 32;
     // all of a thread's loads are issued before the first store, so their latencies overlap
@@ -370,6 +424,12 @@ paged_prefill_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
         const char* src = p.q + 2 * ((int64_t)b * p.q_bs + (int64_t)(qrow0 + j) * p.q_rs +
                                      (int64_t)(h * p.group + g) * p.q_hs) + 16 * c;
         val[u] = *reinterpret_cast<const uint4*>(src);
+        if constexpr (KV8 && BF16) {   // bf16 -> f16 (exact unless |q| > 65504 or below the f16 subnormals)
+          uint32_t* w32 = reinterpret_cast<uint32_t*>(&val[u]);
+#pragma unroll
+          for (int e = 0; e < 4; ++e)
+            w32[e] = pack2<false>(bf16_bits_to_float(w32[e] & 0xffffu), bf16_bits_to_float(w32[e] >> 16));
+        }
       }
     }
 #pragma unroll
@@ -385,19 +445,19 @@ paged_prefill_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
     }
     fence_proxy_async();   // generic-proxy writes above are read by the tensor core (async proxy)
     tc_fence_before();
-    asm volatile("bar.sync 1, %0;" ::"n"(kPrefillThreads - 32) : "memory");   // warps 0-7 and 9
+    asm volatile("bar.sync 1, %0;" ::"n"(kPfCopyThreads) : "memory");   // warps 0-7 and 9
     tc_fence_after();
   }
-  const uint32_t tmem_base = warp == 8 ? 0u : *tmem_slot;
+  const uint32_t tmem_base = (warp == 8 || warp >= 10) ? 0u : *tmem_slot;
 
-  if (warp == 8) {
-    // (the producer has run to completion above)
+  if (warp == 8 || warp >= 10) {
+    // (the producer and the widening warps have run to completion above)
   } else if (warp == 9) {
     // =========================== MMA issuer ===========================
     // Order per tile i:  PV_A(i)  QK_A(i+1)  PV_B(i)  QK_B(i+1): while one Q tile's softmax runs, the
     // tensor core works on the other's products.
-    constexpr uint32_t IDESC_QK = umma_idesc(BF16, false, BN);
-    constexpr uint32_t IDESC_PV = umma_idesc(BF16, true, HD);
+    constexpr uint32_t IDESC_QK = umma_idesc(MMA_BF16, false, BN);
+    constexpr uint32_t IDESC_PV = umma_idesc(MMA_BF16, true, HD);
     bool ok = true;
     auto kv_addr = [&](int idx) { return sbase + SM::OFF_KV + (uint32_t)(idx % RING) * SM::KV_TILE; };
     auto kv_wait = [&](int idx) {
@@ -518,27 +578,56 @@ paged_prefill_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
       ok = mbar_wait_bounded(B_SREADY(x), (uint32_t)it & 1u);
       if (!ok) break;
       tc_fence_after();
-      float s[BN];
-      tmem_ld128(s_tmem, s);
       const int key0 = (tile_begin + it) * BN;
-      if (key0 + BN - 1 > lim || key0 < lo) {
-#pragma unroll
-        for (int i = 0; i < BN; ++i) {
-          const int kk = key0 + i;
-          if (kk > lim || kk < lo) s[i] = -INFINITY;
-        }
-      }
-      // eight independent running maxima: a single chain of 128 dependent fmax would cost ~500 cycles
+      const bool masked = key0 + BN - 1 > lim || key0 < lo;
+      // pass 1: the row maximum; eight independent chains of three-input maxima (one chain of 128
+      // dependent fmax would cost ~500 cycles)
       float mx8[8];
+      if constexpr (KV8) {
+        // (448 threads leave 128 registers per thread: 32 scores at a time, the next load in flight)
 #pragma unroll
-      for (int i = 0; i < 8; ++i) mx8[i] = s[i];
+        for (int k = 0; k < 8; ++k) mx8[k] = -INFINITY;
+        uint32_t raw[2][32];
+        tmem_ld32_nowait(s_tmem, raw[0]);
 #pragma unroll
-      for (int i = 8; i + 16 <= BN; i += 16) {
+        for (int c = 0; c < BN / 32; ++c) {
+          tc_wait_ld();
+          if (c + 1 < BN / 32) tmem_ld32_nowait(s_tmem + 32u * (c + 1), raw[(c + 1) & 1]);
+          float v[32];
 #pragma unroll
-        for (int k = 0; k < 8; ++k) mx8[k] = max3(mx8[k], s[i + k], s[i + 8 + k]);
+          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(raw[c & 1][i]);
+          if (masked) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const int kk = key0 + 32 * c + i;
+              if (kk > lim || kk < lo) v[i] = -INFINITY;
+            }
+          }
+#pragma unroll
+          for (int k = 0; k < 8; ++k) mx8[k] = max3(mx8[k], v[k], v[8 + k]);
+#pragma unroll
+          for (int k = 0; k < 8; ++k) mx8[k] = max3(mx8[k], v[16 + k], v[24 + k]);
+        }
+      } else {
+        float s[BN];   // all 128 scores of the row at once
+        tmem_ld128(s_tmem, s);
+        if (masked) {
+#pragma unroll
+          for (int i = 0; i < BN; ++i) {
+            const int kk = key0 + i;
+            if (kk > lim || kk < lo) s[i] = -INFINITY;
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) mx8[i] = s[i];
+#pragma unroll
+        for (int i = 8; i + 16 <= BN; i += 16) {
+#pragma unroll
+          for (int k = 0; k < 8; ++k) mx8[k] = max3(mx8[k], s[i + k], s[i + 8 + k]);
+        }
+#pragma unroll
+        for (int k = 0; k < 8; ++k) mx8[k] = fmaxf(mx8[k], s[BN - 8 + k]);
       }
-#pragma unroll
-      for (int k = 0; k < 8; ++k) mx8[k] = fmaxf(mx8[k], s[BN - 8 + k]);
       const float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])),
                              fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
       if (it == 0) {
@@ -575,7 +664,6 @@ paged_prefill_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
       // S is read a second time, 32 columns at a time (keeping all 128 scores live across the
       // exponentials costs more in registers than the second read costs in time); chunk c of P
       // lands on columns [16c, 16c+16), inside S columns that are already in registers.
-      const bool masked = key0 + BN - 1 > lim || key0 < lo;
       uint32_t raw[2][32];   // the load of chunk c + 1 is in flight while chunk c is turned into weights
       tmem_ld32_nowait(s_tmem, raw[0]);
 #pragma unroll
@@ -599,7 +687,7 @@ paged_prefill_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
           unpack_f32x2(fma_f32x2(pack_f32x2(v[2 * i], v[2 * i + 1]), sl2x2, nmsx2), x0, x1);
           const float p0 = ex2(x0), p1 = ex2(x1);                  // exp2(-inf) = 0 for masked keys
           ls2[i & 3] = add_f32x2(ls2[i & 3], pack_f32x2(p0, p1));
-          w[i] = pack2<BF16>(p0, p1);
+          w[i] = pack2<MMA_BF16>(p0, p1);
         }
         tmem_st16u(s_tmem + 16u * c, w);
       }
@@ -674,17 +762,17 @@ inline bool prefill_enabled() {
   return on;
 }
 
-template <int HD, bool BF16>
+template <int HD, bool BF16, bool KV8>
 inline int launch_prefill_variant(const CUtensorMap& tmK, const CUtensorMap& tmV, const AttnParams& p, int grid,
                                   int dev, cudaStream_t stream) {
-  using SM = PrefillSmem<HD>;
-  auto kern = paged_prefill_kernel<HD, BF16>;
+  using SM = PrefillSmem<HD, KV8>;
+  auto kern = paged_prefill_kernel<HD, BF16, KV8>;
   static bool done[64] = {};
   if (!done[dev & 63]) {
     KB200_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SM::BYTES));
     done[dev & 63] = true;
   }
-  KB200_CUDA_OK(launch_kernel(kern, dim3(grid), dim3(kPrefillThreads), SM::BYTES, stream, tmK, tmV, p));
+  KB200_CUDA_OK(launch_kernel(kern, dim3(grid), dim3(pf_threads(KV8)), SM::BYTES, stream, tmK, tmV, p));
   return KB200_OK;
 }
 

@@ -525,7 +525,7 @@ def flash_attn_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *,
 
     ``mask_mod=block_bidirectional_mask`` with ``aux_tensors=[block_sequence_ids]`` (int32 ``[B, >= Sq]``, image
     block id or -1 per query position, ``kestrel/models/moondream/text.py:139-172``) adds bidirectional attention
-    inside each image block to the causal mask (padded layout, 16-bit K/V).
+    inside each image block to the causal mask (padded layout).
 
     Not implemented (raise ``NotImplementedError``): dense K/V (``page_table=None``),
     ``cu_seqlens_k``, any other ``mask_mod``, a non-zero right window.
@@ -654,8 +654,6 @@ def flash_attn_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *,
     a.k_scale, a.v_scale = ks_f, vs_f
     a.k_scale_per_head, a.v_scale_per_head = ks_ptr, vs_ptr
     if block_ids is not None:
-        if fp8:
-            raise NotImplementedError("block_bidirectional_mask is not implemented for FP8 K/V")
         if _require_cuda("block_sequence_ids", block_ids) != dev or block_ids.ndim != 2 or block_ids.shape[0] < B:
             raise ValueError("block_sequence_ids must be an int32 [batch, >= seqlen_q] tensor on q's device")
         vis = block_visibility(block_ids[:B], Sq)   # kept alive until the launch below is enqueued

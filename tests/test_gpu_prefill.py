@@ -187,10 +187,10 @@ def test_block_mask_argument_errors():
         kernels.flash_attn_fwd(q, pool, pool, mask_mod=lambda *a: True, aux_tensors=[], **kw)
     with pytest.raises(ValueError, match="aux_tensors"):
         kernels.flash_attn_fwd(q, pool, pool, mask_mod=kernels.block_bidirectional_mask, **kw)
-    with pytest.raises(NotImplementedError, match="FP8"):
-        kernels.flash_attn_fwd(q, pool.view(torch.uint8)[..., :64], pool.view(torch.uint8)[..., :64],
-                               mask_mod=kernels.block_bidirectional_mask,
-                               aux_tensors=[torch.zeros(1, 4, dtype=torch.int32, device=DEV)], k_scale=1.0, v_scale=1.0, **kw)
+    with pytest.raises(NotImplementedError, match="packed rows"):
+        kernels.flash_attn_fwd(q[0], pool, pool, mask_mod=kernels.block_bidirectional_mask,
+                               aux_tensors=[torch.zeros(1, 4, dtype=torch.int32, device=DEV)],
+                               cu_seqlens_q=torch.tensor([0, 4], dtype=torch.int32, device=DEV), **kw)
 
 
 def test_prefill_calls_need_only_the_plan_arrays_as_scratch():
@@ -205,7 +205,57 @@ def test_prefill_calls_need_only_the_plan_arrays_as_scratch():
     bound = int(lib.kb200_attn_workspace_bytes(a.batch, a.total_q, 32, 8, 128, a.device))
     need = int(lib.kb200_attn_workspace_bytes_for(C.byref(a)))
     assert 0 < need < 64 * 1024 < bound            # a few plan arrays against gigabytes of split-KV partials
-    a.kv_dtype = _native.DTYPE_E4M3                 # FP8 K/V stays on the split-KV kernels
-    assert int(lib.kb200_attn_workspace_bytes_for(C.byref(a))) == bound
+    a.kv_dtype = _native.DTYPE_E4M3                 # FP8 pools: the same kernel, tiles widened on the fly
+    assert int(lib.kb200_attn_workspace_bytes_for(C.byref(a))) == need
     a.kv_dtype, a.seqlen_q, a.total_q = _native.DTYPE_BF16, 1, 64  # decode
     assert int(lib.kb200_attn_workspace_bytes_for(C.byref(a))) == int(lib.kb200_attn_workspace_bytes(64, 64, 32, 8, 128, a.device))
+
+
+@pytest.mark.parametrize("head_dim", [128, 64])
+@pytest.mark.parametrize("qdtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("per_head", [True, False])
+def test_prefill_fp8_kv(head_dim, qdtype, per_head):
+    lengths = [128, 129, 200, 729 + 128, 1000, 143, 2048]
+    p = make_paged_problem(seed=31, batch=len(lengths), len_lo=0, len_hi=0, n_q_heads=32, n_kv_heads=8,
+                           head_dim=head_dim, page_size=16, seqlen_q=128, dtype=qdtype, lengths=lengths, outlier_frac=0.01)
+    if per_head:
+        ks = p["k_pool"].abs().amax(dim=(0, 2, 3)) / 448
+        vs = p["v_pool"].abs().amax(dim=(0, 2, 3)) / 448
+    else:
+        ks = float(p["k_pool"].abs().max() / 448)
+        vs = float(p["v_pool"].abs().max() / 448)
+    out, want = run_case(p, qdtype, kv="fp8", scales=(ks, vs))
+    assert_close(out, want, f"fp8 prefill D={head_dim} {qdtype} per_head={per_head}")
+
+
+@pytest.mark.parametrize("page_size,seqlen_q,group,heads_kv", [(16, 37, 4, 2), (64, 64, 1, 4), (256, 100, 8, 1), (4, 33, 2, 3),
+                                                               (1, 40, 4, 2)])
+def test_prefill_fp8_kv_shapes_and_pages(page_size, seqlen_q, group, heads_kv):
+    lengths = [seqlen_q, seqlen_q + 17, 3 * seqlen_q + 500, max(1, seqlen_q - 5), 7, 0]
+    p = make_paged_problem(seed=32 + seqlen_q, batch=len(lengths), len_lo=0, len_hi=0, n_q_heads=group * heads_kv,
+                           n_kv_heads=heads_kv, head_dim=128, page_size=page_size, seqlen_q=seqlen_q,
+                           dtype=torch.bfloat16, lengths=lengths)
+    out, want = run_case(p, torch.bfloat16, kv="fp8", scales=(0.02, 0.03))
+    assert_close(out, want, f"fp8 P={page_size} Sq={seqlen_q} G={group}")
+
+
+def test_prefill_fp8_kv_windows_and_block_mask():
+    lengths = [400, 1500]
+    p = make_paged_problem(seed=33, batch=2, len_lo=0, len_hi=0, n_q_heads=16, n_kv_heads=4, head_dim=128, page_size=16,
+                           seqlen_q=48, dtype=torch.bfloat16, lengths=lengths)
+    out, want = run_case(p, torch.bfloat16, kv="fp8", scales=(0.02, 0.03), window=100)
+    assert_close(out, want, "fp8 window")
+    Sq = 300
+    ids = _image_prompt_ids(1, Sq, [[(3, 250, 0)]])
+    p = make_paged_problem(seed=34, batch=1, len_lo=0, len_hi=0, n_q_heads=8, n_kv_heads=2, head_dim=64, page_size=16,
+                           seqlen_q=Sq, dtype=torch.bfloat16, lengths=[Sq])
+    kq = O.fp8_quantise(p["k_pool"].permute(0, 2, 1, 3), 0.02).permute(0, 2, 1, 3).contiguous()
+    vq = O.fp8_quantise(p["v_pool"].permute(0, 2, 1, 3), 0.03).permute(0, 2, 1, 3).contiguous()
+    out, _ = kernels.flash_attn_fwd(
+        p["q"].to(torch.bfloat16).to(DEV), kq.to(DEV).view(torch.float8_e4m3fn).permute(0, 2, 1, 3),
+        vq.to(DEV).view(torch.float8_e4m3fn).permute(0, 2, 1, 3), page_table=p["page_table"].to(DEV),
+        seqused_k=p["seqused_k"].to(DEV), mask_mod=kernels.block_bidirectional_mask, aux_tensors=[ids.to(DEV)],
+        k_scale=0.02, v_scale=0.03)
+    want = O.paged_attention(p["q"].to(torch.bfloat16).float(), kq, vq, p["page_table"], p["seqused_k"], block_ids=ids,
+                             k_scale=0.02, v_scale=0.03)
+    assert_close(out, want, "fp8 block mask")
