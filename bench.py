@@ -27,7 +27,8 @@ seen during the timed region and a CPU baseline (the oracle timed on the host co
 then paged attention of the chunk's queries over prefix + chunk): compute-bound, reported in TFLOP/s
 against the measured bf16 tensor peak.  ``pf4`` is the prefill phase of configuration 4 (512 requests
 on a shared 729-token prefix, suffixes U[32,256] appended in chunks of up to 128 tokens, D=64);
-``pf_long`` is 32 sequences appending a 512-token chunk on 4096 cached tokens, D=128.
+``pf_long`` is 32 sequences appending a 512-token chunk on 4096 cached tokens, D=128 (``pf_long_fp8``: the same
+on FP8 e4m3 pools).
 """
 
 from __future__ import annotations
@@ -80,6 +81,8 @@ PREFILL_WORKLOADS = {
                     desc="32 sequences append a 512-token chunk on 4096 cached tokens; rotary + append + paged "
                          "attention, bf16, 32/8 heads, D=128, page 16"),
 }
+PREFILL_WORKLOADS["pf_long_fp8"] = dict(PREFILL_WORKLOADS["pf_long"], kv="fp8",
+                                        desc=PREFILL_WORKLOADS["pf_long"]["desc"].replace("bf16", "FP8 e4m3 pools (per-head scales), bf16 q"))
 FALLBACK_BF16_TFLOPS = 1590.0
 
 
@@ -523,7 +526,10 @@ class PrefillWorkload:
         self.pt = PageTable(n_pages=self.n_pages, page_size=PAGE, max_batch_size=self.B + 2, device=device)
         order = torch.randperm(len(self.pt.free_pages), generator=g).tolist()
         self.pt.free_pages = [self.pt.free_pages[i] for i in order]
-        self.cache = PagedKVCache(self.pt, n_heads=HKV, head_dim=self.D, dtype=torch.bfloat16, pool=self.pool)
+        fp8 = cfg.get("kv") == "fp8"
+        kw = dict(k_scale=[0.011] * HKV, v_scale=[0.012] * HKV) if fp8 else {}   # N(0,1) rows: absmax ~ 5 = 448 * 0.011
+        self.cache = PagedKVCache(self.pt, n_heads=HKV, head_dim=self.D,
+                                  dtype=torch.float8_e4m3fn if fp8 else torch.bfloat16, pool=self.pool, **kw)
         self.rows = []
         share = name == "pf4"
         owner = None
@@ -540,8 +546,13 @@ class PrefillWorkload:
         self.pt.commit_block_table()
         dg = torch.Generator(device=device).manual_seed(77 + rank)
         # the cached prefix (random K/V written straight into the pool pages)
-        self.cache.k_cache.copy_(torch.randn(self.cache.k_cache.shape, generator=dg, device=device, dtype=torch.bfloat16))
-        self.cache.v_cache.copy_(torch.randn(self.cache.v_cache.shape, generator=dg, device=device, dtype=torch.bfloat16))
+        if fp8:   # codes of moderate magnitude (no NaN patterns)
+            for c in (self.cache.k_cache, self.cache.v_cache):
+                c.view(torch.uint8).copy_(torch.randint(0, 0x70, c.shape, generator=dg, device=device, dtype=torch.uint8)
+                                          | (torch.randint(0, 2, c.shape, generator=dg, device=device, dtype=torch.uint8) << 7))
+        else:
+            self.cache.k_cache.copy_(torch.randn(self.cache.k_cache.shape, generator=dg, device=device, dtype=torch.bfloat16))
+            self.cache.v_cache.copy_(torch.randn(self.cache.v_cache.shape, generator=dg, device=device, dtype=torch.bfloat16))
         # cos/sin table in the layout of kestrel/models/moondream/rope.py: cos of rot/2 frequencies, then sin
         inv_freq = 1.0 / (1.5e6 ** (torch.arange(0, cfg["rot"], 2, dtype=torch.float32) / cfg["rot"]))
         freqs = torch.arange(self.prefix + cfg["hi"] + 1, dtype=torch.float32).unsqueeze(1) * inv_freq
@@ -584,11 +595,13 @@ class PrefillWorkload:
         q, k, v = q.unflatten(-1, (HQ, self.D)), k.unflatten(-1, (HKV, self.D)), v.unflatten(-1, (HKV, self.D))
         if not attn_only:
             self.kernels.rope_reshape_and_cache(ps["pos"], q, k, v, self.table, self.cache.k_cache.permute(0, 2, 1, 3),
-                                                self.cache.v_cache.permute(0, 2, 1, 3), ps["slots"], "auto",
-                                                write_k=False)
+                                                self.cache.v_cache.permute(0, 2, 1, 3), ps["slots"],
+                                                self.cache._kv_cache_dtype, self.cache.k_scale_tensor.view(-1),
+                                                self.cache.v_scale_tensor.view(-1), write_k=False)
         self.kernels.flash_attn_fwd(q, self.cache.k_cache.permute(0, 2, 1, 3), self.cache.v_cache.permute(0, 2, 1, 3),
                                     page_table=ps["page_table"], seqused_k=ps["seqused_k"], cu_seqlens_q=ps["cu"],
-                                    max_seqlen_q=ps["max_q"], causal=True, out=out)
+                                    max_seqlen_q=ps["max_q"], causal=True, out=out, k_scale=self.cache.k_scale,
+                                    v_scale=self.cache.v_scale)
 
     def step_device(self, attn_only=False):
         for ps in self.passes:
@@ -725,7 +738,9 @@ def run_prefill(args) -> None:
     line = {
         "metric": "paged append+prefill-attn TFLOP/s", "value": value, "unit": "TFLOP/s", "n_gpus": world,
         "steps": args.steps, "warmup": warm, "ms_per_step": ms_all / args.steps, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "bf16 operands, fp32 accumulate and softmax", "data": "synthetic",
+        "scaling": "weak", "vs_baseline": None,
+        "dtype": ("e4m3 K/V widened to f16 operands" if cfg.get("kv") == "fp8" else "bf16 operands") + ", fp32 accumulate and softmax",
+        "data": "synthetic",
         "config": {"workload": f"{args.workload}: {cfg['desc']}", "passes_per_step": len(wl.passes),
                    "tokens_per_step": wl.tokens, "pool_pages": wl.n_pages, "launch": "eager",
                    "flops": "4 * head_dim * n_q_heads * visible (query, key) pairs (causal): useful work only",
