@@ -8,8 +8,9 @@
 // 128 rows; packed row r = j * group + g is query position j of head h * group + g,
 // so one pass over the keys serves the whole GQA group.  Per 128-key tile:
 //
-//   TMA warp        K and V page boxes -> 128-byte-swizzled shared memory (a ring of
-//                   K_0 V_0 K_1 V_1 ... tiles shared by both Q tiles)
+//   2 TMA warps     K and V page boxes -> 128-byte-swizzled shared memory (a ring of
+//                   K_0 V_0 K_1 V_1 ... tiles shared by both Q tiles; one warp issues the K
+//                   tiles, the other the V tiles)
 //   MMA warp        S_x = Q_x K^T (tcgen05.mma, M=128 N=128, operands from shared-memory
 //                   descriptors, accumulator in tensor memory) and O_x += P_x V with
 //                   P_x read from tensor memory (it overlays S_x), which halves the
@@ -35,9 +36,10 @@ namespace kb200 {
 constexpr int kPfTileRows = 128;    // packed query rows per Q tile (MMA M)
 constexpr int kPfCtaRows = 256;     // two Q tiles per CTA
 constexpr int kPrefillKeys = 128;   // keys per tile (MMA N of the first product)
-// 2 x 4 softmax warps, 1 TMA warp, 1 MMA warp; FP8 K/V adds 4 warps that widen the tiles to 16 bits
+// 2 x 4 softmax warps (0-7), a TMA warp (8), the MMA warp (9), then either a second TMA warp (10: 16-bit
+// pools, where it takes the V tiles) or 4 warps (10-13: FP8 pools) that widen the tiles to 16 bits
 constexpr int kPfCopyThreads = 288;   // warps 0-7 and 9 copy Q and meet at the set-up barrier
-constexpr int pf_threads(bool kv8) { return kv8 ? 448 : 320; }
+constexpr int pf_threads(bool kv8) { return kv8 ? 448 : 352; }
 
 template <int HD, bool KV8>
 struct PrefillSmem {
@@ -364,9 +366,13 @@ paged_prefill_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
     fence_proxy_async();
   }
   __syncthreads();   // barriers exist; nothing slow has started yet, so nobody waits here
-  if (warp == 8) {
-    // the other warps only meet this one again at the exit: their set-up barrier leaves it out
-    for (int idx = 0; idx < 2 * n_tiles; ++idx)
+  if (warp == 8 || (!KV8 && warp == 10)) {
+    // 16-bit pools: two producer warps, one for the K tiles (even ring entries) and one for the V tiles;
+    // issuing a tile's copies costs a warp ~130 cycles per box, too much for one warp at 32 boxes per
+    // tile pair.  FP8 pools have half the boxes and one producer.  The other warps only meet the
+    // producers again at the exit: their set-up barrier leaves them out.
+    constexpr int NPROD = KV8 ? 1 : 2;
+    for (int idx = warp == 8 ? 0 : 1; idx < 2 * n_tiles; idx += NPROD)
       if (!produce(idx)) break;
   } else if (KV8 && warp >= 10) {
     // =========================== widening warps (FP8 pools): one key row per thread ===========================
@@ -411,6 +417,7 @@ paged_prefill_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
     constexpr int NCOPY = kPfCopyThreads;
     constexpr int PER = (kPfCtaRows * CH + NCOPY - 1) / NCOPY;
     const int qt = tid < 256 ? tid : tid - 32;
+    const int gshift = (p.group & (p.group - 1)) == 0 ? 31 - __clz(p.group) : -1;   // GQA groups are powers of two as a rule
     // all of a thread's loads are issued before the first store, so their latencies overlap
     uint4 val[PER];
 #pragma unroll
@@ -420,7 +427,7 @@ paged_prefill_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
       const int row = row_first + rr;
       val[u] = make_uint4(0u, 0u, 0u, 0u);
       if (i < kPfCtaRows * CH && row < nrows) {
-        const int j = row / p.group, g = row - j * p.group;
+        const int j = gshift >= 0 ? row >> gshift : row / p.group, g = row - j * p.group;
         const char* src = p.q + 2 * ((int64_t)b * p.q_bs + (int64_t)(qrow0 + j) * p.q_rs +
                                      (int64_t)(h * p.group + g) * p.q_hs) + 16 * c;
         val[u] = *reinterpret_cast<const uint4*>(src);
@@ -451,7 +458,7 @@ paged_prefill_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
   const uint32_t tmem_base = (warp == 8 || warp >= 10) ? 0u : *tmem_slot;
 
   if (warp == 8 || warp >= 10) {
-    // (the producer and the widening warps have run to completion above)
+    // (the producers and the widening warps have run to completion above)
   } else if (warp == 9) {
     // =========================== MMA issuer ===========================
     // Order per tile i:  PV_A(i)  QK_A(i+1)  PV_B(i)  QK_B(i+1): while one Q tile's softmax runs, the
