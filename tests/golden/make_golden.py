@@ -1,8 +1,8 @@
 """Generates the golden fixtures in this directory from the reference's own torch path.
 
-Run once, in a container that has the reference tree (default ``/root/reference``):
+Run once, in a container that has the reference tree:
 
-    python tests/golden/make_golden.py [--reference /path/to/kestrel]
+    python tests/golden/make_golden.py --reference /path/to/kestrel
 
 It imports the UNMODIFIED ``kestrel/kv_cache.py`` of the reference with a stub
 ``kestrel_kernels`` whose kernels are ``None`` -- which makes ``PagedKVCache.update``
@@ -375,7 +375,7 @@ def rope_vectors(root: str) -> dict[str, np.ndarray]:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="root of the m87-labs/kestrel source tree")
     args = ap.parse_args()
     kc = import_reference(args.reference)
     out: dict[str, np.ndarray] = {}
