@@ -259,3 +259,71 @@ def test_prefill_fp8_kv_windows_and_block_mask():
     want = O.paged_attention(p["q"].to(torch.bfloat16).float(), kq, vq, p["page_table"], p["seqused_k"], block_ids=ids,
                              k_scale=0.02, v_scale=0.03)
     assert_close(out, want, "fp8 block mask")
+
+
+def test_prefill_in_a_cuda_graph_with_changing_lengths():
+    # lengths and page indices are read on the device: one captured graph serves calls with other lengths
+    Sq = 64
+    lengths = [700, 130, 64]
+    p = make_paged_problem(seed=41, batch=3, len_lo=0, len_hi=0, n_q_heads=8, n_kv_heads=2, head_dim=128, page_size=16,
+                           seqlen_q=Sq, dtype=torch.bfloat16, lengths=lengths)
+    q = p["q"].to(torch.bfloat16).to(DEV)
+    k = p["k_pool"].to(torch.bfloat16).to(DEV).permute(0, 2, 1, 3)
+    v = p["v_pool"].to(torch.bfloat16).to(DEV).permute(0, 2, 1, 3)
+    table, sk = p["page_table"].to(DEV), p["seqused_k"].to(DEV)
+    out = torch.empty_like(q)
+    stream = torch.cuda.Stream()
+    stream.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(stream):
+        kernels.flash_attn_fwd(q, k, v, page_table=table, seqused_k=sk, causal=True, out=out)   # sizes the scratch
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            kernels.flash_attn_fwd(q, k, v, page_table=table, seqused_k=sk, causal=True, out=out)
+    torch.cuda.current_stream().wait_stream(stream)
+    for new_lengths in ([700, 130, 64], [300, 100, 50], [64, 65, 33]):   # within the pages each sequence owns
+        sk.copy_(torch.tensor(new_lengths, dtype=torch.int32))
+        out.fill_(float("nan"))
+        graph.replay()
+        torch.cuda.synchronize()
+        want = O.paged_attention(p["q"].to(torch.bfloat16).float(), p["k_pool"], p["v_pool"], p["page_table"],
+                                 torch.tensor(new_lengths, dtype=torch.int32))
+        assert_close(out, want, f"graph replay with lengths {new_lengths}")
+
+
+def test_prefill_through_the_allocation_free_entry_point():
+    import ctypes as C
+    import math
+    lib = _native.load()
+    Sq = 256
+    lengths = [1000, 300]
+    p = make_paged_problem(seed=42, batch=2, len_lo=0, len_hi=0, n_q_heads=32, n_kv_heads=8, head_dim=64, page_size=16,
+                           seqlen_q=Sq, dtype=torch.bfloat16, lengths=lengths)
+    q = p["q"].to(torch.bfloat16).to(DEV)
+    k = p["k_pool"].to(torch.bfloat16).to(DEV)
+    v = p["v_pool"].to(torch.bfloat16).to(DEV)
+    table, sk = p["page_table"].to(DEV), p["seqused_k"].to(DEV)
+    out = torch.full_like(q, float("nan"))
+    kv_view = k.permute(0, 2, 1, 3)
+    a = _native.AttnArgs()
+    a.struct_bytes = C.sizeof(_native.AttnArgs)
+    a.device = q.device.index
+    a.stream = torch.cuda.current_stream().cuda_stream
+    a.q, a.out = q.data_ptr(), out.data_ptr()
+    a.q_batch_stride, a.q_row_stride, a.q_head_stride = q.stride(0), q.stride(1), q.stride(2)
+    a.o_batch_stride, a.o_row_stride, a.o_head_stride = out.stride(0), out.stride(1), out.stride(2)
+    a.k_cache, a.v_cache = k.data_ptr(), v.data_ptr()
+    a.kv_page_stride, a.kv_token_stride, a.kv_head_stride = kv_view.stride(0), kv_view.stride(1), kv_view.stride(2)
+    a.n_pages = k.shape[0]
+    a.page_table, a.pt_row_stride, a.seqused_k = table.data_ptr(), table.stride(0), sk.data_ptr()
+    a.batch, a.total_q, a.seqlen_q = 2, 2 * Sq, Sq
+    a.n_q_heads, a.n_kv_heads, a.head_dim, a.page_size = 32, 8, 64, 16
+    a.q_dtype = a.kv_dtype = _native.DTYPE_BF16
+    a.softmax_scale, a.causal, a.window_left = 1.0 / math.sqrt(64), 1, -1
+    a.k_scale = a.v_scale = 1.0
+    # the generic bound for these dimensions exceeds what a prefill-shaped call really needs
+    assert int(lib.kb200_attn_workspace_bytes_for(C.byref(a))) < 4096
+    _native.check(lib.kb200_paged_attention_static(C.byref(a)))
+    torch.cuda.synchronize()
+    want = O.paged_attention(p["q"].to(torch.bfloat16).float(), p["k_pool"], p["v_pool"], p["page_table"], p["seqused_k"])
+    assert_close(out, want, "static entry point, prefill-shaped call")
