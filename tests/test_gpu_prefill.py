@@ -327,3 +327,58 @@ def test_prefill_through_the_allocation_free_entry_point():
     torch.cuda.synchronize()
     want = O.paged_attention(p["q"].to(torch.bfloat16).float(), p["k_pool"], p["v_pool"], p["page_table"], p["seqused_k"])
     assert_close(out, want, "static entry point, prefill-shaped call")
+
+
+def test_config4_full_size_prefill_chunk_sampled_and_repaged():
+    """Configuration 4's prefill at full size: 512 requests, a shared 729-token prefix (45 full pages
+    referenced by every page-table row, the partly filled 46th page private per request) and the first
+    chunk of each request's suffix (U[32,256], at most 128 tokens) as one packed call.  Eight requests
+    are checked against the oracle; moving every private page to another physical page must not
+    change one output bit."""
+    g = torch.Generator().manual_seed(4004)
+    B, P, hq, hkv, D, prefix = 512, 16, 32, 8, 64, 729
+    suffix = torch.randint(32, 257, (B,), generator=g)
+    chunk = suffix.clamp(max=128)
+    L = prefix + chunk
+    shared = prefix // P
+    own = (L + P - 1) // P - shared
+    n_pages = 1 + shared + int(own.sum())
+    table = torch.zeros(B, int((L.max() + P - 1) // P), dtype=torch.int32)
+    table[:, :shared] = torch.arange(1, shared + 1, dtype=torch.int32)
+    perm = (torch.randperm(n_pages - 1 - shared, generator=g) + 1 + shared).to(torch.int32)
+    cur = 0
+    for b in range(B):
+        n = int(own[b])
+        table[b, shared:shared + n] = perm[cur:cur + n]
+        cur += n
+    k_pool = torch.randn(n_pages, hkv, P, D, generator=g).to(torch.bfloat16)
+    v_pool = torch.randn(n_pages, hkv, P, D, generator=g).to(torch.bfloat16)
+    total = int(chunk.sum())
+    q = torch.randn(total, hq, D, generator=g).to(torch.bfloat16)
+    cu = torch.zeros(B + 1, dtype=torch.int32)
+    cu[1:] = chunk.cumsum(0)
+
+    def run(kp, vp, tb):
+        out, _ = kernels.flash_attn_fwd(q.to(DEV), kp.to(DEV).permute(0, 2, 1, 3), vp.to(DEV).permute(0, 2, 1, 3),
+                                        page_table=tb.to(DEV), seqused_k=L.to(torch.int32).to(DEV), cu_seqlens_q=cu.to(DEV),
+                                        max_seqlen_q=128, causal=True)
+        return out.cpu()
+
+    out = run(k_pool, v_pool, table)
+    for b in [0, 1, 7, 100, 255, 256, 400, 511]:
+        n = int(chunk[b])
+        qb = torch.zeros(1, 128, hq, D)
+        qb[0, :n] = q[int(cu[b]):int(cu[b]) + n].float()
+        want = O.paged_attention(qb, k_pool.float(), v_pool.float(), table[b:b + 1], L[b:b + 1].to(torch.int32),
+                                 seqused_q=torch.tensor([n]))
+        assert_close(out[int(cu[b]):int(cu[b]) + n], want[0, :n], f"request {b}")
+    # physical re-paging of the private pages
+    move = torch.arange(n_pages)
+    priv = torch.arange(1 + shared, n_pages)
+    move[priv] = priv[torch.randperm(priv.numel(), generator=g)]
+    k2, v2 = torch.empty_like(k_pool), torch.empty_like(v_pool)
+    k2[move] = k_pool
+    v2[move] = v_pool
+    table2 = move.to(torch.int32)[table.long()]
+    out2 = run(k2, v2, table2)
+    assert torch.equal(out.view(torch.int16), out2.view(torch.int16))
