@@ -435,7 +435,6 @@ class GpuWorkload:
         self.step_no += 1
 
     def _run_layers(self, pos: torch.Tensor, record_attn: bool, host: bool) -> None:
-        from kestrel_b200.attention import paged_attention
         slots = self.pt.build_slot_mapping(self.batch_idx, pos)
         self.pt.populate_paged_kv_metadata(batch_idx=self.batch_idx, input_pos=pos[:, -1].to(torch.int32),
                                            out_page_table=self.meta_pt, out_seqused_k=self.meta_sk)

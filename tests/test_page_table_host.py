@@ -5,7 +5,6 @@ import gc
 import json
 import threading
 
-import numpy as np
 import pytest
 import torch
 
