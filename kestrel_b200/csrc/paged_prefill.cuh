@@ -252,8 +252,10 @@ paged_prefill_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
   pdl_wait();   // the plan, and the append before it, must have completed
 
   // ---- which segment is this CTA?
-  const int seg = blockIdx.x;
-  if (seg >= p.seg_cum[p.batch]) return;   // uniform over the CTA; nothing allocated yet
+  // CTAs are handed out in block order: taking the segments from the back puts the later row blocks
+  // of a sequence, which see more keys under the causal mask, first and keeps the tail of the grid short
+  const int seg = p.seg_cum[p.batch] - 1 - (int)blockIdx.x;
+  if (seg < 0) return;   // uniform over the CTA; nothing allocated yet
   int b;
   if (p.uniform_nseg > 0) {
     b = seg / p.uniform_nseg;
