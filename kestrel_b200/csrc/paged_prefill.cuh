@@ -589,6 +589,7 @@ paged_prefill_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
       tc_fence_after();
       const int key0 = (tile_begin + it) * BN;
       const bool masked = key0 + BN - 1 > lim || key0 < lo;
+      const int c_hi = lim - key0, c_lo = lo - key0;   // visible columns of this tile: c_lo <= column <= c_hi
       // pass 1: the row maximum; eight independent chains of three-input maxima (one chain of 128
       // dependent fmax would cost ~500 cycles)
       float mx8[8];
@@ -606,10 +607,14 @@ paged_prefill_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
 #pragma unroll
           for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(raw[c & 1][i]);
           if (masked) {
+            if (c_lo <= 0) {   // only the upper limit cuts this tile (plain causal, or the window starts before it)
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              const int kk = key0 + 32 * c + i;
-              if (kk > lim || kk < lo) v[i] = -INFINITY;
+              for (int i = 0; i < 32; ++i)
+                if (32 * c + i > c_hi) v[i] = -INFINITY;
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                if (32 * c + i > c_hi || 32 * c + i < c_lo) v[i] = -INFINITY;
             }
           }
 #pragma unroll
@@ -621,10 +626,14 @@ paged_prefill_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
         float s[BN];   // all 128 scores of the row at once
         tmem_ld128(s_tmem, s);
         if (masked) {
+          if (c_lo <= 0) {   // only the upper limit cuts this tile (plain causal, or the window starts before it)
 #pragma unroll
-          for (int i = 0; i < BN; ++i) {
-            const int kk = key0 + i;
-            if (kk > lim || kk < lo) s[i] = -INFINITY;
+            for (int i = 0; i < BN; ++i)
+              if (i > c_hi) s[i] = -INFINITY;
+          } else {
+#pragma unroll
+            for (int i = 0; i < BN; ++i)
+              if (i > c_hi || i < c_lo) s[i] = -INFINITY;
           }
         }
 #pragma unroll
@@ -683,10 +692,14 @@ paged_prefill_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
 #pragma unroll
         for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(raw[c & 1][i]);
         if (masked) {
+          if (c_lo <= 0) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const int kk = key0 + 32 * c + i;
-            if (kk > lim || kk < lo) v[i] = -INFINITY;
+            for (int i = 0; i < 32; ++i)
+              if (32 * c + i > c_hi) v[i] = -INFINITY;
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (32 * c + i > c_hi || 32 * c + i < c_lo) v[i] = -INFINITY;
           }
         }
         uint32_t w[16];
