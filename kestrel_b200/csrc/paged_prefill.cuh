@@ -231,6 +231,10 @@ paged_prefill_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
   constexpr float kRescaleStep = 8.f;   // the running maximum is only raised when it grew by 2^8
   constexpr uint32_t TMEM_COLS = 512;
   constexpr uint32_t S_COL = 0, O_COL = 2 * BN;   // S_A, S_B, then O_A, O_B (128 columns reserved each)
+  // head_dim 64 leaves 64 spare columns next to each O: P gets them instead of overlaying S, so the
+  // next Q K^T of a tile can be issued before its P V and the tile's softmax restarts ~800 cycles earlier
+  constexpr bool PSEP = HD == 64;
+  constexpr uint32_t P_OFF = PSEP ? O_COL + 64 : S_COL;   // + x * 128: first column of P_x
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -494,12 +498,12 @@ paged_prefill_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
       }
       __syncwarp();
     };
+    auto wait_p = [&](int x, int i) { ok = ok && mbar_wait_bounded(B_PREADY(x), (uint32_t)i & 1u); };
     auto pv = [&](int x, int i, int ksteps) {   // O_x (+)= P_x V_i
-      ok = ok && mbar_wait_bounded(B_PREADY(x), (uint32_t)i & 1u);
       if (!ok) return;
       tc_fence_after();
       if (lane == 0) {
-        const uint32_t p_tmem = tmem_base + S_COL + (uint32_t)x * BN;   // P overlays the first 64 columns of S_x
+        const uint32_t p_tmem = tmem_base + P_OFF + (uint32_t)x * 128;   // (overlays the first 64 columns of S_x unless PSEP)
         const uint32_t v_lo = (kv_addr(2 * i + 1) >> 4) | kLboV;
         const uint32_t o_tmem = tmem_base + O_COL + (uint32_t)x * 128;
         if (ksteps == BN / 16) {
@@ -547,18 +551,38 @@ paged_prefill_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
         __syncwarp();
       }
       const bool more = i + 1 < n_tiles;
-      if (i < n_x[0]) pv(0, i, ksteps);
-      if (more) kv_wait(2 * (i + 1));
-      if (!ok) break;
-      if (i + 1 < n_x[0]) qk(0, i + 1);
-      if (i < n_x[1]) pv(1, i, ksteps);
-      if (!ok) break;
-      if (lane == 0) tc_commit(B_EMPTY((2 * i + 1) % RING));   // V_i has been read by both tiles
-      __syncwarp();
-      if (more) {
-        if (i + 1 < n_x[1]) qk(1, i + 1);
-        if (lane == 0) tc_commit(B_EMPTY((2 * i + 2) % RING));  // K_{i+1} likewise
+      if constexpr (PSEP) {
+        // P_x has columns of its own: once the softmax has let go of S_x the next Q K^T goes first
+        if (more) kv_wait(2 * (i + 1));
+#pragma unroll
+        for (int x = 0; x < 2; ++x) {
+          if (i < n_x[x]) {
+            wait_p(x, i);
+            if (!ok) break;
+            if (i + 1 < n_x[x]) qk(x, i + 1);
+            pv(x, i, ksteps);
+          }
+        }
+        if (!ok) break;
+        if (lane == 0) {
+          tc_commit(B_EMPTY((2 * i + 1) % RING));             // V_i has been read by both tiles
+          if (more) tc_commit(B_EMPTY((2 * i + 2) % RING));   // K_{i+1} likewise
+        }
         __syncwarp();
+      } else {
+        if (i < n_x[0]) { wait_p(0, i); pv(0, i, ksteps); }
+        if (more) kv_wait(2 * (i + 1));
+        if (!ok) break;
+        if (i + 1 < n_x[0]) qk(0, i + 1);
+        if (i < n_x[1]) { wait_p(1, i); pv(1, i, ksteps); }
+        if (!ok) break;
+        if (lane == 0) tc_commit(B_EMPTY((2 * i + 1) % RING));   // V_i has been read by both tiles
+        __syncwarp();
+        if (more) {
+          if (i + 1 < n_x[1]) qk(1, i + 1);
+          if (lane == 0) tc_commit(B_EMPTY((2 * i + 2) % RING));  // K_{i+1} likewise
+          __syncwarp();
+        }
       }
     }
     if (!ok && lane == 0) report(KB200_STATUS_WAIT_TIMEOUT, seg, KID_PREFILL);
@@ -580,6 +604,7 @@ paged_prefill_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
     const uint32_t s_tmem = tmem_base + lane_base + S_COL + (uint32_t)x * BN;
     const uint32_t o_tmem = tmem_base + lane_base + O_COL + (uint32_t)x * 128;
+    const uint32_t p_st = tmem_base + lane_base + P_OFF + (uint32_t)x * 128;   // where this row's weights go
     const int n_mine = n_x[x];
     float m = -INFINITY, l = 0.f;
     bool ok = true;
@@ -711,7 +736,7 @@ paged_prefill_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
           ls2[i & 3] = add_f32x2(ls2[i & 3], pack_f32x2(p0, p1));
           w[i] = pack2<MMA_BF16>(p0, p1);
         }
-        tmem_st16u(s_tmem + 16u * c, w);
+        tmem_st16u(p_st + 16u * c, w);
       }
       tc_wait_st();
 #else
