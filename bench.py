@@ -187,7 +187,8 @@ def algorithmic_bytes(lengths_after: torch.Tensor, *, layers: int, kv_bytes: int
 # ----------------------------------------------------------------------------------------------
 
 class GpuWorkload:
-    def __init__(self, name: str, device: torch.device, rank: int, total_steps: int, budget_frac: float = 0.78):
+    def __init__(self, name: str, device: torch.device, rank: int, total_steps: int, budget_frac: float = 0.78,
+                 share_prefix: bool = True):
         from kestrel_b200.kv_cache import KVMemoryPool, PagedKVCache, PageTable, copy_kv_pages
         from kestrel_b200 import kernels
 
@@ -270,6 +271,10 @@ class GpuWorkload:
                 self.rows.append(r)
         self.pt.commit_block_table()
         self.batch_idx = torch.tensor(self.rows, dtype=torch.int64, device=device)
+        # pages of the cached prefix that every request of the batch maps (0 without a prefix cache): the
+        # attention call reads them once for the whole batch
+        self.shared_pages = (self.pt.common_prefix_pages(self.rows, min_tokens=int(self.len0.min()))
+                             if prefix and share_prefix else 0)
         self._fill(prefix, copy_kv_pages)
         # per-step inputs, resident in HBM (one set per layer so no layer reuses another's rows)
         self.q = [self._randn(self.B, self.sq, HQ, self.D).to(torch.bfloat16) for _ in range(self.layers_n)]
@@ -299,7 +304,7 @@ class GpuWorkload:
         for ev in self.in_free:
             ev.record(torch.cuda.current_stream(device))
         self.attn_events: list[tuple[torch.cuda.Event, torch.cuda.Event]] = []
-        self.launches_per_step = 2 + self.layers_n * 4
+        self.launches_per_step = 2 + self.layers_n * (7 if self.shared_pages else 4)
 
     def _randn(self, *shape):
         x = torch.randn(*shape, generator=self.dg, device=self.device)
@@ -401,7 +406,8 @@ class GpuWorkload:
                 self.kernels.flash_attn_fwd(
                     self.q[l], cache.k_cache.permute(0, 2, 1, 3), cache.v_cache.permute(0, 2, 1, 3),
                     page_table=self.meta_pt, seqused_k=self.meta_sk, causal=True, softmax_scale=scale,
-                    k_scale=cache.k_scale, v_scale=cache.v_scale, out=self.out[l])
+                    k_scale=cache.k_scale, v_scale=cache.v_scale, out=self.out[l],
+                    shared_prefix_pages=self.shared_pages)
 
         with torch.cuda.stream(stream):
             self.kernels.reserve_attention_workspace(batch=self.B, total_q=self.B * self.sq, n_q_heads=HQ,
@@ -463,7 +469,7 @@ class GpuWorkload:
             out, _ = self.kernels.flash_attn_fwd(
                 q, cache.k_cache.permute(0, 2, 1, 3), cache.v_cache.permute(0, 2, 1, 3), page_table=self.meta_pt,
                 seqused_k=self.meta_sk, causal=True, softmax_scale=scale, k_scale=cache.k_scale, v_scale=cache.v_scale,
-                out=self.out[l])
+                out=self.out[l], shared_prefix_pages=self.shared_pages)
             if record_attn:
                 e1.record()
                 self.attn_events.append((e0, e1))
@@ -878,6 +884,8 @@ def main() -> None:
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="launch the timed steps eagerly instead of replaying a CUDA graph")
+    ap.add_argument("--no-shared-prefix", action="store_true",
+                    help="cfg4: read the cached prefix once per request (plain calls) instead of once per batch")
     ap.add_argument("--batch", type=int, default=0, help="override the workload's batch (profiling on a small case)")
     ap.add_argument("--layers", type=int, default=0, help="override the workload's layer count (profiling)")
     args = ap.parse_args()
@@ -915,7 +923,7 @@ def main() -> None:
     cfg = WORKLOADS[args.workload]
     e2e_steps = 0 if args.no_e2e else max(3, min(args.steps, 5))
     total_steps = 3 * args.warmup + args.steps + e2e_steps + 4
-    wl = GpuWorkload(args.workload, device, rank, total_steps)
+    wl = GpuWorkload(args.workload, device, rank, total_steps, share_prefix=not args.no_shared_prefix)
 
     def barrier():
         torch.cuda.synchronize(device)
@@ -999,6 +1007,7 @@ def main() -> None:
         "config": {"workload": f"{args.workload}: {cfg['desc']}", "n_layer_pools": wl.n_pools,
                    "layers": wl.layers_n, "pool_pages": wl.n_pages, "sequences_per_gpu": wl.B,
                    "launch": "CUDA graph replay" if use_graph else "eager",
+                   "shared_prefix_pages": wl.shared_pages,
                    "l2_policy": "inputs larger than L2 (every layer streams a multi-GB pool)"
                    if wl.n_pages * HKV * PAGE * wl.D * wl.kv_bytes * 2 > 256e6 else
                    "working set near L2 size; see tokens/s rather than GB/s"},

@@ -30,7 +30,7 @@
 extern "C" {
 #endif
 
-#define KB200_ABI_VERSION 2
+#define KB200_ABI_VERSION 3
 
 #if defined(__GNUC__)
 #define KB200_API __attribute__((visibility("default")))
@@ -59,7 +59,8 @@ enum {
   KB200_STATUS_BAD_PAGE = 2,    /* a page index outside [0, n_pages) (access skipped / zero filled) */
   KB200_STATUS_BAD_ROW = 4,     /* a page-table row index outside the table (row skipped) */
   KB200_STATUS_WAIT_TIMEOUT = 8, /* a bounded wait on a shared-memory barrier ran out */
-  KB200_STATUS_BAD_POSITION = 16 /* rotary: a position outside the cos/sin table (clamped) */
+  KB200_STATUS_BAD_POSITION = 16, /* rotary: a position outside the cos/sin table (clamped) */
+  KB200_STATUS_BAD_PREFIX = 32   /* attention: shared_prefix_pages covers keys a query row may not see */
 };
 
 KB200_API int kb200_abi_version(void);
@@ -254,6 +255,20 @@ typedef struct kb200_attn_args {
    * causal != 0 and no window. */
   const int32_t* q_visible_until;
   int64_t q_visible_batch_stride;
+
+  /* Shared cached prefix (extension; the reference has no counterpart).  A promise by the caller:
+   * the first shared_prefix_pages entries of every page-table row of this call are the same
+   * physical pages (requests attached to one radix-cache prefix, kestrel/models/moondream/
+   * runtime.py:1572-1623), all of them full, and every query row sees all of their keys
+   * (seqused_k[b] - seqlen_q >= shared_prefix_pages * page_size under the causal mask).  The
+   * call then reads those pages once for the whole batch: one pass of all query rows over the
+   * prefix keys on the tensor-memory kernel, one pass per sequence over the remaining keys, and
+   * a combine by the two log-sum-exps.  Same result as 0 up to rounding of the partial outputs
+   * to q's dtype.  Ignored (plain path) with cu_seqlens_q, seqused_q, a window, a block mask,
+   * fewer than 64 packed query rows in the batch, or q rows that are not evenly spaced across
+   * the batch.  A sequence that breaks the promise sets KB200_STATUS_BAD_PREFIX. */
+  int32_t shared_prefix_pages;
+  int32_t reserved0;
 } kb200_attn_args;
 
 /* Scratch bytes kb200_paged_attention needs for the given problem bounds. */

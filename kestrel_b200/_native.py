@@ -13,12 +13,12 @@ from pathlib import Path
 
 # KB200_LIBRARY selects another build of the same ABI (A/B comparisons of kernel variants).
 LIB_PATH = Path(os.environ.get("KB200_LIBRARY") or Path(__file__).resolve().parent / "libkestrel_b200.so")
-ABI_VERSION = 2
+ABI_VERSION = 3
 
 DTYPE_F32, DTYPE_F16, DTYPE_BF16, DTYPE_E4M3 = 0, 1, 2, 3
 STATIC_SCRATCH_BYTES = 32 * 1024 * 1024  # KB200_STATIC_SCRATCH_BYTES
 
-STATUS_BAD_SLOT, STATUS_BAD_PAGE, STATUS_BAD_ROW, STATUS_WAIT_TIMEOUT, STATUS_BAD_POSITION = 1, 2, 4, 8, 16
+STATUS_BAD_SLOT, STATUS_BAD_PAGE, STATUS_BAD_ROW, STATUS_WAIT_TIMEOUT, STATUS_BAD_POSITION, STATUS_BAD_PREFIX = 1, 2, 4, 8, 16, 32
 
 # Every symbol include/kestrel_b200.h declares.
 EXPORTS = (
@@ -90,6 +90,8 @@ class AttnArgs(C.Structure):
         ("workspace_bytes", C.c_uint64),
         ("q_visible_until", C.c_void_p),
         ("q_visible_batch_stride", C.c_int64),
+        ("shared_prefix_pages", C.c_int32),
+        ("reserved0", C.c_int32),
     ]
 
 

@@ -91,6 +91,10 @@ struct AttnParams {
   int batch, seqlen_q, hq, hkv, group, page_size, causal, window_left, q_is_bf16, n_workers, tile_n;
   int rows_per_seg;  // query rows per segment: 16 (general kernel) or 8 (decode kernel)
   int uniform_nseg;  // segments per sequence when that is the same for all (padded q, no seqused_q), else 0
+  // Shared-prefix passes.  k_skip: the first k_skip keys of every sequence are served by another pass
+  // (page_table already points past their pages; lengths are taken relative to them).
+  // fixed_klen >= 0: every sequence has exactly that many keys (seqused_k is not read).
+  int k_skip, fixed_klen;
 };
 
 // ---------------------------------------------------------------------------
@@ -218,7 +222,8 @@ __global__ void __launch_bounds__(256) attn_plan_kernel(const AttnParams p) {
     long long cnt_t = 0;
     int cnt_s = 0;
     if (b < p.batch) {
-      int L = p.seqused_k[b];
+      int L = p.fixed_klen >= 0 ? p.fixed_klen : p.seqused_k[b] - p.k_skip;
+      const int L_rel = L;
       if (L < 0) L = 0;
       int sq, row0 = 0;
       if (p.cu_seqlens_q) {
@@ -229,6 +234,9 @@ __global__ void __launch_bounds__(256) attn_plan_kernel(const AttnParams p) {
         if (p.seqused_q) sq = min(sq, p.seqused_q[b]);
       }
       if (sq < 0) sq = 0;
+      // a query row that cannot see all of the skipped prefix under the causal mask (or a sequence
+      // shorter than the prefix) breaks the caller's promise: results for it are undefined
+      if (p.k_skip > 0 && L_rel < (p.causal ? sq : 0)) report(KB200_STATUS_BAD_PREFIX, b, KID_ATTN_PLAN);
       int t0 = 0;
       if (p.window_left >= 0) {
         int kmin = L - sq - p.window_left;
@@ -1456,10 +1464,172 @@ inline bool use_prefill_kernel(const kb200_attn_args* a) {
 
 // Scratch bytes this very call needs: the plan arrays, plus the split-KV partials unless the prefill
 // kernel serves it.
-inline uint64_t attn_workspace_need(const kb200_attn_args* a, int sms) {
+inline uint64_t attn_pass_workspace_need(const kb200_attn_args* a, int sms) {
   const AttnWorkspace wl = attn_workspace_layout(a->batch, a->total_q, a->n_q_heads, a->n_kv_heads, a->head_dim,
                                                  sms * kAttnMaxWarps);
   return use_prefill_kernel(a) ? wl.part_ml : wl.total;
+}
+
+// ---------------------------------------------------------------------------
+// Shared cached prefix: the batch's common leading pages are read once.
+//   pass 1  all B * Sq query rows as one sequence over the prefix keys, no mask (tensor-memory
+//           prefill kernel), output and log-sum-exp into scratch
+//   pass 2  every sequence over its remaining keys (page table and lengths shifted), output in
+//           place, log-sum-exp into scratch (or the caller's buffer)
+//   combine out = (o1 e^{l1} + o2 e^{l2}) / (e^{l1} + e^{l2})
+// ---------------------------------------------------------------------------
+inline bool shared_prefix_applies(const kb200_attn_args* a) {
+  if (a->shared_prefix_pages <= 0) return false;
+  if (a->cu_seqlens_q || a->seqused_q || a->window_left >= 0 || a->q_visible_until) return false;
+  if (!prefill_enabled() || a->n_kv_heads <= 0 || a->n_q_heads % a->n_kv_heads != 0) return false;
+  if ((int64_t)(a->n_q_heads / a->n_kv_heads) * a->batch * a->seqlen_q < kPrefillMinPackedRows) return false;
+  if (a->batch * (int64_t)a->seqlen_q > 0x7fffffff / (a->n_q_heads / a->n_kv_heads)) return false;
+  if (a->seqlen_q > 1 && a->q_batch_stride != (int64_t)a->seqlen_q * a->q_row_stride) return false;
+  if ((int64_t)a->shared_prefix_pages * a->page_size > 0x3fffffff) return false;
+  return true;
+}
+
+struct SharedPrefixPlan {
+  kb200_attn_args pre, rest;   // the two passes
+  size_t o1, lse1, lse2, ws1, ws2, total;   // scratch layout
+};
+
+inline SharedPrefixPlan shared_prefix_plan(const kb200_attn_args* a, int sms) {
+  auto up = [](size_t x) { return (x + 255) & ~size_t(255); };
+  SharedPrefixPlan sp;
+  const int64_t rows = a->batch * (int64_t)a->seqlen_q;
+  sp.pre = *a;
+  sp.pre.shared_prefix_pages = 0;
+  sp.pre.batch = 1;
+  sp.pre.total_q = rows;
+  sp.pre.seqlen_q = (int32_t)rows;
+  sp.pre.q_batch_stride = 0;
+  sp.pre.q_row_stride = a->seqlen_q > 1 ? a->q_row_stride : a->q_batch_stride;
+  sp.pre.o_batch_stride = 0;
+  sp.pre.o_row_stride = (int64_t)a->n_q_heads * a->head_dim;
+  sp.pre.o_head_stride = a->head_dim;
+  sp.pre.seqused_k = nullptr;
+  sp.pre.causal = 0;
+  sp.rest = *a;
+  sp.rest.shared_prefix_pages = 0;
+  sp.rest.page_table = a->page_table + a->shared_prefix_pages;
+  size_t off = 0;
+  sp.o1 = off; off = up(off + (size_t)rows * a->n_q_heads * a->head_dim * 2);
+  sp.lse1 = off; off = up(off + sizeof(float) * rows * a->n_q_heads);
+  sp.lse2 = off; off = up(off + sizeof(float) * rows * a->n_q_heads);
+  sp.ws1 = off; off = up(off + attn_pass_workspace_need(&sp.pre, sms));
+  sp.ws2 = off; off = up(off + attn_pass_workspace_need(&sp.rest, sms));
+  sp.total = off;
+  return sp;
+}
+
+// Scratch bytes this very call needs: the plan arrays, plus the split-KV partials unless the prefill
+// kernel serves it; with a shared prefix, both passes' scratch plus the first pass's output.
+inline uint64_t attn_workspace_need(const kb200_attn_args* a, int sms) {
+  if (shared_prefix_applies(a)) return shared_prefix_plan(a, sms).total;
+  return attn_pass_workspace_need(a, sms);
+}
+
+struct CombineParams {
+  const char* o1;      // [rows, hq, hd] contiguous, q's dtype
+  char* out;           // the second pass's output, combined in place
+  const float* lse1;   // [hq, rows]
+  float* lse2;         // [batch, hq, sq]; receives the combined value when write_lse is set
+  int64_t o_bs, o_rs, o_hs;
+  int64_t rows;
+  int sq, hq, hd, q_is_bf16, write_lse;
+};
+
+// one thread per 8 consecutive elements of one (row, head)
+__global__ void __launch_bounds__(256) attn_combine_kernel(const CombineParams c) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int chunks = c.hd / 8;
+  const int64_t total = c.rows * c.hq * chunks;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int ch = (int)(i % chunks);
+    const int64_t rh = i / chunks;
+    const int h = (int)(rh % c.hq);
+    const int64_t row = rh / c.hq;
+    const int64_t b = row / c.sq;
+    const int j = (int)(row - b * c.sq);
+    const float l1 = c.lse1[(int64_t)h * c.rows + row];
+    float* l2p = c.lse2 + (b * c.hq + h) * c.sq + j;
+    const float l2 = *l2p;
+    const float m = fmaxf(l1, l2);
+    float w1 = 0.f, w2 = 0.f, lse = -INFINITY;
+    if (m != -INFINITY) {
+      const float e1 = __expf(l1 - m), e2 = __expf(l2 - m);
+      const float inv = 1.f / (e1 + e2);
+      w1 = e1 * inv;
+      w2 = e2 * inv;
+      lse = m + logf(e1 + e2);
+    }
+    const uint4 a = *reinterpret_cast<const uint4*>(c.o1 + 2 * ((row * c.hq + h) * c.hd + 8 * ch));
+    char* dst = c.out + 2 * (b * c.o_bs + j * c.o_rs + h * c.o_hs + 8 * ch);
+    const uint4 d = *reinterpret_cast<const uint4*>(dst);
+    const uint32_t* aw = reinterpret_cast<const uint32_t*>(&a);
+    const uint32_t* dw = reinterpret_cast<const uint32_t*>(&d);
+    uint4 r;
+    uint32_t* rw = reinterpret_cast<uint32_t*>(&r);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      float a0, a1, d0, d1;
+      if (c.q_is_bf16) {
+        a0 = bf16_bits_to_float(aw[e] & 0xffffu); a1 = bf16_bits_to_float(aw[e] >> 16);
+        d0 = bf16_bits_to_float(dw[e] & 0xffffu); d1 = bf16_bits_to_float(dw[e] >> 16);
+        rw[e] = pack2<true>(a0 * w1 + d0 * w2, a1 * w1 + d1 * w2);
+      } else {
+        const __half2 ah = *reinterpret_cast<const __half2*>(&aw[e]), dh = *reinterpret_cast<const __half2*>(&dw[e]);
+        a0 = __low2float(ah); a1 = __high2float(ah);
+        d0 = __low2float(dh); d1 = __high2float(dh);
+        rw[e] = pack2<false>(a0 * w1 + d0 * w2, a1 * w1 + d1 * w2);
+      }
+    }
+    *reinterpret_cast<uint4*>(dst) = r;
+    if (c.write_lse && ch == 0) *l2p = lse;
+  }
+}
+
+inline int launch_attention_pass(const kb200_attn_args* a, int k_skip, int fixed_klen);
+
+inline int launch_shared_prefix_attention(const kb200_attn_args* a) {
+  int sms = 0;
+  if (int rc = device_sm_count(a->device, &sms)) return rc;
+  KB200_REQUIRE(a->q && a->out && a->page_table && a->seqused_k, "null pointer argument");
+  KB200_REQUIRE(a->head_dim == 64 || a->head_dim == 128, "head_dim must be 64 or 128");
+  SharedPrefixPlan sp = shared_prefix_plan(a, sms);
+  if (!a->workspace || a->workspace_bytes < sp.total)
+    return fail(KB200_ERR_WORKSPACE, "workspace too small: need %llu bytes, got %llu", (unsigned long long)sp.total,
+                (unsigned long long)a->workspace_bytes);
+  KB200_REQUIRE((reinterpret_cast<uintptr_t>(a->workspace) & 255) == 0, "workspace must be 256-byte aligned");
+  char* ws = static_cast<char*>(a->workspace);
+  const int k_skip = a->shared_prefix_pages * a->page_size;
+  sp.pre.out = ws + sp.o1;
+  sp.pre.lse = reinterpret_cast<float*>(ws + sp.lse1);
+  sp.pre.workspace = ws + sp.ws1;
+  sp.pre.workspace_bytes = sp.ws2 - sp.ws1;
+  sp.rest.lse = a->lse ? a->lse : reinterpret_cast<float*>(ws + sp.lse2);
+  sp.rest.workspace = ws + sp.ws2;
+  sp.rest.workspace_bytes = sp.total - sp.ws2;
+  if (int rc = launch_attention_pass(&sp.pre, 0, k_skip)) return rc;
+  if (int rc = launch_attention_pass(&sp.rest, k_skip, -1)) return rc;
+  CombineParams c;
+  c.o1 = ws + sp.o1;
+  c.out = static_cast<char*>(a->out);
+  c.lse1 = sp.pre.lse;
+  c.lse2 = sp.rest.lse;
+  c.o_bs = a->o_batch_stride; c.o_rs = a->o_row_stride; c.o_hs = a->o_head_stride;
+  c.rows = a->batch * (int64_t)a->seqlen_q;
+  c.sq = a->seqlen_q; c.hq = a->n_q_heads; c.hd = a->head_dim;
+  c.q_is_bf16 = a->q_dtype == KB200_DTYPE_BF16;
+  c.write_lse = a->lse != nullptr;
+  const int64_t items = c.rows * c.hq * (c.hd / 8);
+  int64_t blocks = (items + 255) / 256;
+  if (blocks > sms * 8) blocks = sms * 8;
+  KB200_CUDA_OK(launch_kernel(attn_combine_kernel, dim3((unsigned)blocks), dim3(256), 0,
+                              static_cast<cudaStream_t>(a->stream), c));
+  return KB200_OK;
 }
 
 inline int launch_paged_attention(const kb200_attn_args* a) {
@@ -1467,8 +1637,20 @@ inline int launch_paged_attention(const kb200_attn_args* a) {
   KB200_REQUIRE(a->struct_bytes == sizeof(kb200_attn_args), "kb200_attn_args size mismatch: got %u, built with %zu",
                 a->struct_bytes, sizeof(kb200_attn_args));
   if (a->batch == 0 || a->total_q == 0) return KB200_OK;
+  KB200_REQUIRE(a->shared_prefix_pages >= 0, "shared_prefix_pages must be non-negative");
+  if (shared_prefix_applies(a)) return launch_shared_prefix_attention(a);
+  return launch_attention_pass(a, 0, -1);
+}
+
+// One attention pass.  k_skip / fixed_klen: see AttnParams (0 / -1 for a plain call).
+inline int launch_attention_pass(const kb200_attn_args* a, int k_skip, int fixed_klen) {
+  KB200_REQUIRE(a != nullptr, "args is null");
+  KB200_REQUIRE(a->struct_bytes == sizeof(kb200_attn_args), "kb200_attn_args size mismatch: got %u, built with %zu",
+                a->struct_bytes, sizeof(kb200_attn_args));
+  if (a->batch == 0 || a->total_q == 0) return KB200_OK;
   KB200_REQUIRE(a->batch > 0 && a->batch < (1 << 30), "batch out of range");
-  KB200_REQUIRE(a->q && a->out && a->k_cache && a->v_cache && a->page_table && a->seqused_k, "null pointer argument");
+  KB200_REQUIRE(a->q && a->out && a->k_cache && a->v_cache && a->page_table && (a->seqused_k || fixed_klen >= 0),
+                "null pointer argument");
   KB200_REQUIRE(a->q_dtype == KB200_DTYPE_F16 || a->q_dtype == KB200_DTYPE_BF16, "q must be F16 or BF16");
   KB200_REQUIRE(a->kv_dtype == KB200_DTYPE_E4M3 || a->kv_dtype == a->q_dtype,
                 "K/V dtype must equal q dtype or be E4M3");
@@ -1500,7 +1682,7 @@ inline int launch_paged_attention(const kb200_attn_args* a) {
   const int group = a->n_q_heads / a->n_kv_heads;
   const AttnWorkspace wl = attn_workspace_layout(a->batch, a->total_q, a->n_q_heads, a->n_kv_heads, a->head_dim,
                                                  grid * kAttnMaxWarps);
-  const uint64_t ws_need = attn_workspace_need(a, sms);
+  const uint64_t ws_need = attn_pass_workspace_need(a, sms);
   if (!a->workspace || a->workspace_bytes < ws_need)
     return fail(KB200_ERR_WORKSPACE, "workspace too small: need %llu bytes, got %llu", (unsigned long long)ws_need,
                 (unsigned long long)a->workspace_bytes);
@@ -1582,6 +1764,8 @@ inline int launch_paged_attention(const kb200_attn_args* a) {
   p.rows_per_seg = prefill ? kPrefillRowsPerSeg : decode8 ? kDecodeRows : kRowsPerSeg;
   p.uniform_nseg = (packed || a->seqused_q) ? 0
                    : a->n_kv_heads * ((group * a->seqlen_q + p.rows_per_seg - 1) / p.rows_per_seg);
+  p.k_skip = k_skip;
+  p.fixed_klen = fixed_klen;
 
   cudaStream_t stream = static_cast<cudaStream_t>(a->stream);
   KB200_CUDA_OK(launch_kernel(attn_plan_kernel, dim3(1), dim3(256), 0, stream, p));

@@ -512,7 +512,8 @@ def flash_attn_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *,
                    mask_mod: Any = None, aux_tensors: Any = None,
                    out: Optional[torch.Tensor] = None,
                    return_lse: bool = False,
-                   max_seqlen_q: Optional[int] = None):
+                   max_seqlen_q: Optional[int] = None,
+                   shared_prefix_pages: int = 0):
     """Paged attention with the call surface the reference uses for ``flash_attn_fwd``
     (``kestrel/ops/attention.py:69-86``, ``kestrel/models/moondream/text.py:158-185``).
 
@@ -526,6 +527,10 @@ def flash_attn_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *,
     ``mask_mod=block_bidirectional_mask`` with ``aux_tensors=[block_sequence_ids]`` (int32 ``[B, >= Sq]``, image
     block id or -1 per query position, ``kestrel/models/moondream/text.py:139-172``) adds bidirectional attention
     inside each image block to the causal mask (padded layout).
+
+    ``shared_prefix_pages=n`` (extension): the caller promises that the first ``n`` page-table entries of every
+    row are the same full pages (requests attached to one cached prefix, see ``PageTable.common_prefix_pages``)
+    and that every query row sees all of their keys; the prefix is then read once for the whole batch.
 
     Not implemented (raise ``NotImplementedError``): dense K/V (``page_table=None``),
     ``cu_seqlens_k``, any other ``mask_mod``, a non-zero right window.
@@ -660,8 +665,13 @@ def flash_attn_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *,
         a.q_visible_until = vis.data_ptr()
         a.q_visible_batch_stride = vis.stride(0)
         a.causal = 1   # the block mask extends the causal one (the reference passes causal=False next to mask_mod)
+    if shared_prefix_pages:
+        if shared_prefix_pages < 0 or shared_prefix_pages > page_table.shape[1]:
+            raise ValueError("shared_prefix_pages must lie in [0, page_table.shape[1]]")
+        a.shared_prefix_pages = int(shared_prefix_pages)
     # scratch: sized for this very call (prefill-shaped calls need only the plan arrays)
-    wkey = (B, total_q, Sq, Hq, Hkv, D, a.kv_dtype, block_ids is not None, dev)
+    wkey = (B, total_q, Sq, Hq, Hkv, D, a.kv_dtype, block_ids is not None, dev, int(shared_prefix_pages),
+            q_strides, seqused_q is None, a.window_left)
     nbytes = _ws_bytes_cache.get(wkey)
     if nbytes is None:
         nbytes = int(lib.kb200_attn_workspace_bytes_for(C.byref(a)))

@@ -315,6 +315,28 @@ class PageTable:
     def get_pages(self, batch_idx: int, start: int, end: int) -> list[int]:
         return self._page_table_cpu_tensor[batch_idx, start:end].tolist()
 
+    def common_prefix_pages(self, batch_indices: Sequence[int], min_tokens: int | None = None) -> int:
+        """Number of leading pages that all the given rows map to the same physical pages (host table).
+
+        These are the pages of a cached prefix the rows were attached to with ``map_pages``
+        (``kestrel/models/moondream/runtime.py:1572-1623``).  ``min_tokens`` caps the answer at the pages
+        that lie entirely below that token count: pass the smallest ``seqused_k - seqlen_q`` of the
+        step so that every query row sees every key of the prefix.  The result is what
+        ``flash_attn_fwd(shared_prefix_pages=...)`` expects; it only changes when rows are mapped or
+        released, so a scheduler computes it once per batch composition, not per step.
+        """
+        rows = list(batch_indices)
+        if len(rows) < 2:
+            return 0
+        n = min(len(self.page_table_cpu[r]) for r in rows)
+        if min_tokens is not None:
+            n = min(n, max(0, int(min_tokens)) // self.page_size)
+        if n <= 0:
+            return 0
+        tab = self._page_table_cpu_np[rows, :n]
+        same = (tab == tab[0]).all(axis=0)
+        return int(n if same.all() else same.argmin())
+
     # ------------------------------------------------------------------ rows and pages
     def allocate(self) -> int:
         row = self.free_batch_idx.pop()
