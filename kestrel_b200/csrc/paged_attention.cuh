@@ -177,6 +177,9 @@ __device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], 
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
   }
 }
+__device__ __forceinline__ void prefetch_l1(const void* ptr) {
+  asm volatile("prefetch.global.L1 [%0];" ::"l"(ptr));
+}
 __device__ __forceinline__ float ex2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -282,7 +285,7 @@ __global__ void __launch_bounds__(256) attn_plan_kernel(const AttnParams p) {
 
 // Position of a warp inside the flat tile space (identical on all 32 lanes).
 struct Cursor {
-  int b, seg, nseg, t, nt, tile0, L, sq, nmb, segbase;
+  int b, seg, nseg, t, nt, tile0, L, sq, nmb, segbase, qr;   // qr: first packed query row of the sequence
 };
 
 __device__ __forceinline__ void cursor_load_seq(const AttnParams& p, Cursor& c) {
@@ -290,16 +293,26 @@ __device__ __forceinline__ void cursor_load_seq(const AttnParams& p, Cursor& c) 
   c.tile0 = p.tile0[c.b];
   c.L = p.klen[c.b];
   c.sq = p.sq[c.b];
+  c.qr = p.cu_seqlens_q ? p.qrow0[c.b] : 0;   // loaded with the rest: no dependent load where Q is addressed
   c.nmb = (p.group * c.sq + p.rows_per_seg - 1) / p.rows_per_seg;
   c.nseg = p.hkv * c.nmb;
   c.segbase = p.seg_cum[c.b];
 }
 
+// Finds the sequence and segment that own flat tile g.  Called by all 32 lanes of a warp with
+// the same g: the search over tile_cum is 32-way (one probe per lane, a vote per round), two
+// dependent loads for up to 1024 sequences where a binary search would chain ten.
 __device__ __forceinline__ void cursor_locate(const AttnParams& p, Cursor& c, long long g) {
+  const int lane = threadIdx.x & 31;
   int lo = 0, hi = p.batch;  // tile_cum[lo] <= g < tile_cum[hi]
   while (hi - lo > 1) {
-    const int mid = (lo + hi) >> 1;
-    if (p.tile_cum[mid] <= g) lo = mid; else hi = mid;
+    const int step = (hi - lo + 31) >> 5;
+    const int idx = lo + (lane + 1) * step;
+    const bool le = idx < hi && p.tile_cum[idx] <= g;
+    const int cnt = __popc(__ballot_sync(0xffffffffu, le));   // probes are monotone: the first cnt lanes vote yes
+    const int nlo = lo + cnt * step;
+    hi = min(hi, nlo + step);
+    lo = nlo;
   }
   c.b = lo;
   cursor_load_seq(p, c);
@@ -438,11 +451,8 @@ paged_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
   const int my_tiles = (int)(r1 - r0);
 
   TileProducer<T, KVB> prod(p, &tmK, &tmV, my_stage0, bar0, lane, r0, my_tiles);
+  Cursor cc = prod.pc;   // consumer side: starts where the producer starts
   for (int s = 0; s < NS && prod.more(); ++s) prod.issue(s);
-
-  // ---- consumer side
-  Cursor cc;
-  cursor_locate(p, cc, r0);
 
   uint32_t qf[NQF][4];
   float o[NOT][4];
@@ -478,9 +488,9 @@ paged_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
       for (int i = 0; i < NOT; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
       // Q fragments, straight from global memory (4 KB per segment at most)
       const int64_t qb = (int64_t)cc.b * p.q_bs;
-      const char* q0 = p.q + 2 * (qb + (int64_t)(p.qrow0[cc.b] + j0) * p.q_rs +
+      const char* q0 = p.q + 2 * (qb + (int64_t)(cc.qr + j0) * p.q_rs +
                                   (int64_t)(h * p.group + row0 % p.group) * p.q_hs);
-      const char* q1 = p.q + 2 * (qb + (int64_t)(p.qrow0[cc.b] + j1) * p.q_rs +
+      const char* q1 = p.q + 2 * (qb + (int64_t)(cc.qr + j1) * p.q_rs +
                                   (int64_t)(h * p.group + row1 % p.group) * p.q_hs);
       if constexpr (KVB == 2) {
 #pragma unroll
@@ -508,6 +518,16 @@ paged_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
           qf[ch][0] = a.x; qf[ch][1] = b.x; qf[ch][2] = a.y; qf[ch][3] = b.y;
         }
       }
+    }
+
+    // Last tile of this segment and the next segment belongs to the same sequence: pull its Q rows
+    // into L1 now, so that the loads at the segment switch do not wait for L2.
+    if (cc.t == cc.nt - 1 && cc.seg + 1 < cc.nseg && it + 1 < my_tiles && (c4 < 2 || HD == 128)) {
+      const int ns = cc.seg + 1, nh = ns / cc.nmb;
+      const int r = (ns - nh * cc.nmb) * kRowsPerSeg + g8 + (c4 & 1) * 8;
+      if (r < p.group * cc.sq)
+        prefetch_l1(p.q + 2 * ((int64_t)cc.b * p.q_bs + (int64_t)(cc.qr + r / p.group) * p.q_rs +
+                               (int64_t)(nh * p.group + r % p.group) * p.q_hs) + (c4 >> 1) * 128);
     }
 
     const int stage = it % NS;
@@ -690,7 +710,7 @@ paged_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
         const float i0 = l0 > 0.f ? vscale / l0 : 0.f;
         const float i1 = l1 > 0.f ? vscale / l1 : 0.f;
         const int64_t ob = (int64_t)cc.b * p.o_bs;
-        const int qr = p.qrow0[cc.b];
+        const int qr = cc.qr;
         const int j0 = row0 / p.group, j1 = row1 / p.group;
         const int hq0 = h * p.group + row0 % p.group, hq1 = h * p.group + row1 % p.group;
         char* out0 = p.out + 2 * (ob + (int64_t)(qr + j0) * p.o_rs + (int64_t)hq0 * p.o_hs);
@@ -832,10 +852,8 @@ paged_attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
   const int my_tiles = (int)(r1 - r0);
 
   TileProducer<T, KVB> prod(p, &tmK, &tmV, my_stage0, bar0, lane, r0, my_tiles);
+  Cursor cc = prod.pc;   // consumer side: starts where the producer starts
   for (int s = 0; s < NS && prod.more(); ++s) prod.issue(s);
-
-  Cursor cc;
-  cursor_locate(p, cc, r0);
 
   // lane-constant parts of the ldmatrix addresses
   const int mi = lane >> 3;                                  // which of the four 8x8 matrices this lane addresses
@@ -874,7 +892,7 @@ paged_attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
       // B fragments of Q^T: this thread supplies row (mb*8 + g8)
       const int qr = mb * kDecodeRows + g8;
       const bool qvalid = qr < nrows;
-      const char* qrow = p.q + 2 * ((int64_t)cc.b * p.q_bs + (int64_t)(p.qrow0[cc.b] + qr / p.group) * p.q_rs +
+      const char* qrow = p.q + 2 * ((int64_t)cc.b * p.q_bs + (int64_t)(cc.qr + qr / p.group) * p.q_rs +
                                     (int64_t)(h * p.group + qr % p.group) * p.q_hs);
       if constexpr (KVB == 2) {
 #pragma unroll
@@ -896,6 +914,16 @@ paged_attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
           qb[ch][1] = a.y;
         }
       }
+    }
+
+    // Last tile of this segment and the next segment belongs to the same sequence: pull its Q row
+    // into L1 now, so that the loads at the segment switch do not wait for L2.
+    if (cc.t == cc.nt - 1 && cc.seg + 1 < cc.nseg && it + 1 < my_tiles && (c4 == 0 || (HD == 128 && c4 == 1))) {
+      const int ns = cc.seg + 1, nh = ns / cc.nmb;
+      const int r = (ns - nh * cc.nmb) * kDecodeRows + g8;
+      if (r < p.group * cc.sq)
+        prefetch_l1(p.q + 2 * ((int64_t)cc.b * p.q_bs + (int64_t)(cc.qr + r / p.group) * p.q_rs +
+                               (int64_t)(nh * p.group + r % p.group) * p.q_hs) + c4 * 128);
     }
 
     const int stage = it % NS;
@@ -1088,7 +1116,7 @@ paged_attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
       if (whole) {
         const float i0 = l0 > 0.f ? vscale / l0 : 0.f;
         const float i1 = l1 > 0.f ? vscale / l1 : 0.f;
-        const int qrow_base = p.qrow0[cc.b];
+        const int qrow_base = cc.qr;
         const int hq0 = h * p.group + q0 % p.group, hq1 = h * p.group + q1 % p.group;
         const int64_t ob = (int64_t)cc.b * p.o_bs;
         char* out0 = p.out + 2 * (ob + (int64_t)(qrow_base + q0 / p.group) * p.o_rs + (int64_t)hq0 * p.o_hs);
