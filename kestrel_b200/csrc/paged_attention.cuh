@@ -417,7 +417,6 @@ paged_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
   constexpr int kAttnWarps = NW;
   constexpr int TILE_N = T::TILE_N;
   constexpr int RB = T::RB;
-  constexpr int NH = T::NH;
   constexpr int NT8 = TILE_N / 8;    // score n-tiles per tile
   constexpr int NKS = TILE_N / 16;   // k-steps of P V
   constexpr int NOT = HD / 8;        // output n-tiles
@@ -1180,81 +1179,83 @@ paged_attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
 }
 
 // ---------------------------------------------------------------------------
-// Merge: one block per segment.  Segments written directly are skipped,
+// Merge: blocks stride over the segments.  Segments written directly are skipped,
 // segments without keys are zero-filled, the others combine their partials.
 // ---------------------------------------------------------------------------
 template <int HD>
 __global__ void __launch_bounds__(128) attn_merge_kernel(const AttnParams p) {
-  const int seg = blockIdx.x;
   pdl_wait();
   pdl_launch_dependents();
   const int nseg_total = p.seg_cum[p.batch];
-  if (seg >= nseg_total) return;
-  int lo = 0, hi = p.batch;
-  if (p.uniform_nseg > 0) {
-    lo = seg / p.uniform_nseg;  // no dependent loads on the common path
-  } else {
-    while (hi - lo > 1) {
-      const int mid = (lo + hi) >> 1;
-      if (p.seg_cum[mid] <= seg) lo = mid; else hi = mid;
-    }
-  }
-  const int b = lo;
-  const int sq = p.sq[b];
-  const int nmb = (p.group * sq + p.rows_per_seg - 1) / p.rows_per_seg;
-  const int sib = seg - p.seg_cum[b];
-  const int h = sib / nmb, mb = sib - h * nmb;
-  const int nt = p.nt[b];
   const long long total = p.tile_cum[p.batch];
-  int wf = 0, wl = -1;
-  if (nt > 0) {
-    const long long t0 = p.tile_cum[b] + (long long)sib * nt;
-    const long long t1 = t0 + nt;
-    wf = (int)(((t0 + 1) * p.n_workers - 1) / total);
-    wl = (int)((t1 * p.n_workers - 1) / total);
-    if (wf == wl) return;  // written by the attention kernel itself
-  }
-  const int nrows = p.group * sq;
-  const float vscale = p.vs_vec ? p.vs_vec[h] : p.vs;
-  const int qr = p.qrow0[b];
-  constexpr float kLn2 = 0.6931471805599453f;
-  // A worker between wf and wl whose range is empty (fewer tiles than workers) wrote nothing.
-  const bool all_have = total >= p.n_workers;
-  auto has_tiles = [&](int wi) {
-    return all_have || (long long)wi * total / p.n_workers < (long long)(wi + 1) * total / p.n_workers;
-  };
-  // one work item = 4 consecutive d of one query row; the partial loads of an item are independent
-  constexpr int kQuads = HD / 4;
-  for (int item = threadIdx.x; item < p.rows_per_seg * kQuads; item += 128) {
-    const int rl = item / kQuads, d = (item - rl * kQuads) * 4;
-    const int row = mb * p.rows_per_seg + rl;
-    if (row >= nrows) continue;
-    float M = -INFINITY;
-    for (int wi = wf; wi <= wl; ++wi)
-      if (has_tiles(wi)) M = fmaxf(M, p.part_ml[((int64_t)seg + wi) * (kRowsPerSeg * 2) + rl * 2]);
-    float L = 0.f;
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (M != -INFINITY) {
-      for (int wi = wf; wi <= wl; ++wi) {
-        if (!has_tiles(wi)) continue;
-        const int64_t slot = (int64_t)seg + wi;
-        const float2 ml = *reinterpret_cast<const float2*>(p.part_ml + slot * (kRowsPerSeg * 2) + rl * 2);
-        if (ml.x == -INFINITY) continue;
-        const float wgt = ex2(ml.x - M);
-        const float4 o = *reinterpret_cast<const float4*>(p.part_o + slot * (kRowsPerSeg * HD) + rl * HD + d);
-        L += wgt * ml.y;
-        acc.x += wgt * o.x; acc.y += wgt * o.y; acc.z += wgt * o.z; acc.w += wgt * o.w;
+  // blocks stride over the segments: most segments of a batch of short sequences were written by
+  // the attention kernel itself and only cost the look-up below
+  for (int seg = blockIdx.x; seg < nseg_total; seg += gridDim.x) {
+    int lo = 0, hi = p.batch;
+    if (p.uniform_nseg > 0) {
+      lo = seg / p.uniform_nseg;  // no dependent loads on the common path
+    } else {
+      while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (p.seg_cum[mid] <= seg) lo = mid; else hi = mid;
       }
     }
-    const float inv = L > 0.f ? vscale / L : 0.f;
-    const int j = row / p.group, hq = h * p.group + row % p.group;
-    const int64_t oi = (int64_t)b * p.o_bs + (int64_t)(qr + j) * p.o_rs + (int64_t)hq * p.o_hs + d;
-    uint2 packed;
-    if (p.q_is_bf16) packed = make_uint2(pack2<true>(acc.x * inv, acc.y * inv), pack2<true>(acc.z * inv, acc.w * inv));
-    else packed = make_uint2(pack2<false>(acc.x * inv, acc.y * inv), pack2<false>(acc.z * inv, acc.w * inv));
-    *reinterpret_cast<uint2*>(p.out + 2 * oi) = packed;
-    if (p.lse && d == 0)
-      p.lse[(int64_t)b * p.lse_bs + (int64_t)hq * p.lse_hs + qr + j] = L > 0.f ? M * kLn2 + logf(L) : -INFINITY;
+    const int b = lo;
+    const int sq = p.sq[b];
+    const int nmb = (p.group * sq + p.rows_per_seg - 1) / p.rows_per_seg;
+    const int sib = seg - p.seg_cum[b];
+    const int h = sib / nmb, mb = sib - h * nmb;
+    const int nt = p.nt[b];
+    int wf = 0, wl = -1;
+    if (nt > 0) {
+      const long long t0 = p.tile_cum[b] + (long long)sib * nt;
+      const long long t1 = t0 + nt;
+      wf = (int)(((t0 + 1) * p.n_workers - 1) / total);
+      wl = (int)((t1 * p.n_workers - 1) / total);
+      if (wf == wl) continue;  // written by the attention kernel itself
+    }
+    const int nrows = p.group * sq;
+    const float vscale = p.vs_vec ? p.vs_vec[h] : p.vs;
+    const int qr = p.qrow0[b];
+    constexpr float kLn2 = 0.6931471805599453f;
+    // A worker between wf and wl whose range is empty (fewer tiles than workers) wrote nothing.
+    const bool all_have = total >= p.n_workers;
+    auto has_tiles = [&](int wi) {
+      return all_have || (long long)wi * total / p.n_workers < (long long)(wi + 1) * total / p.n_workers;
+    };
+    // one work item = 4 consecutive d of one query row; the partial loads of an item are independent
+    constexpr int kQuads = HD / 4;
+    for (int item = threadIdx.x; item < p.rows_per_seg * kQuads; item += 128) {
+      const int rl = item / kQuads, d = (item - rl * kQuads) * 4;
+      const int row = mb * p.rows_per_seg + rl;
+      if (row >= nrows) continue;
+      float M = -INFINITY;
+      for (int wi = wf; wi <= wl; ++wi)
+        if (has_tiles(wi)) M = fmaxf(M, p.part_ml[((int64_t)seg + wi) * (kRowsPerSeg * 2) + rl * 2]);
+      float L = 0.f;
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (M != -INFINITY) {
+        for (int wi = wf; wi <= wl; ++wi) {
+          if (!has_tiles(wi)) continue;
+          const int64_t slot = (int64_t)seg + wi;
+          const float2 ml = *reinterpret_cast<const float2*>(p.part_ml + slot * (kRowsPerSeg * 2) + rl * 2);
+          if (ml.x == -INFINITY) continue;
+          const float wgt = ex2(ml.x - M);
+          const float4 o = *reinterpret_cast<const float4*>(p.part_o + slot * (kRowsPerSeg * HD) + rl * HD + d);
+          L += wgt * ml.y;
+          acc.x += wgt * o.x; acc.y += wgt * o.y; acc.z += wgt * o.z; acc.w += wgt * o.w;
+        }
+      }
+      const float inv = L > 0.f ? vscale / L : 0.f;
+      const int j = row / p.group, hq = h * p.group + row % p.group;
+      const int64_t oi = (int64_t)b * p.o_bs + (int64_t)(qr + j) * p.o_rs + (int64_t)hq * p.o_hs + d;
+      uint2 packed;
+      if (p.q_is_bf16) packed = make_uint2(pack2<true>(acc.x * inv, acc.y * inv), pack2<true>(acc.z * inv, acc.w * inv));
+      else packed = make_uint2(pack2<false>(acc.x * inv, acc.y * inv), pack2<false>(acc.z * inv, acc.w * inv));
+      *reinterpret_cast<uint2*>(p.out + 2 * oi) = packed;
+      if (p.lse && d == 0)
+        p.lse[(int64_t)b * p.lse_bs + (int64_t)hq * p.lse_hs + qr + j] = L > 0.f ? M * kLn2 + logf(L) : -INFINITY;
+    }
   }
 }
 
@@ -1796,7 +1797,10 @@ inline int launch_attention_pass(const kb200_attn_args* a, int k_skip, int fixed
   p.fixed_klen = fixed_klen;
 
   cudaStream_t stream = static_cast<cudaStream_t>(a->stream);
-  KB200_CUDA_OK(launch_kernel(attn_plan_kernel, dim3(1), dim3(256), 0, stream, p));
+  // one sequence of a fixed length on the prefill kernel (the prefix pass of a shared-prefix call)
+  // has nothing to plan: the kernel derives its segments from the launch parameters
+  const bool no_plan = prefill && fixed_klen >= 0 && a->batch == 1 && p.uniform_nseg > 0;
+  if (!no_plan) KB200_CUDA_OK(launch_kernel(attn_plan_kernel, dim3(1), dim3(256), 0, stream, p));
 
   int rc;
   const bool d128 = a->head_dim == 128;
@@ -1831,8 +1835,9 @@ inline int launch_attention_pass(const kb200_attn_args* a, int k_skip, int fixed
   const int64_t max_seg = packed ? attn_max_segments(a->batch, a->total_q, a->n_q_heads, a->n_kv_heads)
                                  : a->batch * a->n_kv_heads * ((group * (int64_t)a->seqlen_q + p.rows_per_seg - 1) / p.rows_per_seg);
   KB200_REQUIRE(max_seg <= 0x7fffffff, "too many segments");
-  if (d128) KB200_CUDA_OK(launch_kernel(attn_merge_kernel<128>, dim3((unsigned)max_seg), dim3(128), 0, stream, p));
-  else KB200_CUDA_OK(launch_kernel(attn_merge_kernel<64>, dim3((unsigned)max_seg), dim3(128), 0, stream, p));
+  const int64_t merge_blocks = max_seg < (int64_t)sms * 16 ? max_seg : (int64_t)sms * 16;   // 16 x 128 threads fill an SM
+  if (d128) KB200_CUDA_OK(launch_kernel(attn_merge_kernel<128>, dim3((unsigned)merge_blocks), dim3(128), 0, stream, p));
+  else KB200_CUDA_OK(launch_kernel(attn_merge_kernel<64>, dim3((unsigned)merge_blocks), dim3(128), 0, stream, p));
   return KB200_OK;
 }
 

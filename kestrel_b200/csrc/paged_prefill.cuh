@@ -258,7 +258,9 @@ paged_prefill_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
   // ---- which segment is this CTA?
   // CTAs are handed out in block order: taking the segments from the back puts the later row blocks
   // of a sequence, which see more keys under the causal mask, first and keeps the tail of the grid short
-  const int seg = p.seg_cum[p.batch] - 1 - (int)blockIdx.x;
+  // (one sequence of a fixed length, the prefix pass of a shared-prefix call, needs no plan launch)
+  const bool no_plan = p.fixed_klen >= 0 && p.batch == 1;
+  const int seg = (no_plan ? p.uniform_nseg : p.seg_cum[p.batch]) - 1 - (int)blockIdx.x;
   if (seg < 0) return;   // uniform over the CTA; nothing allocated yet
   int b;
   if (p.uniform_nseg > 0) {
@@ -271,10 +273,11 @@ paged_prefill_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
     }
     b = lo;
   }
-  const int sq = p.sq[b], L = p.klen[b], qrow0 = p.qrow0[b];
+  const int sq = no_plan ? p.seqlen_q : p.sq[b], L = no_plan ? p.fixed_klen : p.klen[b];
+  const int qrow0 = no_plan ? 0 : p.qrow0[b];
   const int nrows = p.group * sq;
   const int nmb = (nrows + kPfCtaRows - 1) / kPfCtaRows;
-  const int sib = seg - p.seg_cum[b];
+  const int sib = seg - (no_plan ? 0 : p.seg_cum[b]);
   const int h = sib / nmb, mb = sib - h * nmb;
   const int row_first = mb * kPfCtaRows;
   const bool upper = p.causal || p.window_left >= 0;
@@ -385,10 +388,11 @@ paged_prefill_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
     // e4m3 tile as delivered by the TMA unit (rows of RB8 bytes, swizzled) -> f16 tile in the operand
     // layout of the MMAs (rows of 256 bytes in two 128-byte-swizzled slabs, or one slab for head_dim 64)
     constexpr int RB8 = SM::RB8;
+    constexpr int NSTG = SM::NSTG > 0 ? SM::NSTG : 1;   // (this branch is only taken with a staging ring)
     const int r = (warp - 10) * 32 + lane;
     for (int idx = 0; idx < 2 * n_tiles; ++idx) {
-      const int s8 = idx % SM::NSTG, c = idx % RING;
-      bool got = mbar_wait_bounded(B_SFULL(s8), (uint32_t)(idx / SM::NSTG) & 1u);
+      const int s8 = idx % NSTG, c = idx % RING;
+      bool got = mbar_wait_bounded(B_SFULL(s8), (uint32_t)(idx / NSTG) & 1u);
       if (got && idx >= RING) got = mbar_wait_bounded(B_EMPTY(c), (uint32_t)((idx / RING) - 1) & 1u);
       if (!got) {
         if (lane == 0) report(KB200_STATUS_WAIT_TIMEOUT, idx, KID_PREFILL);
