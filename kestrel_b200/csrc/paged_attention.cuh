@@ -95,6 +95,9 @@ struct AttnParams {
   // (page_table already points past their pages; lengths are taken relative to them).
   // fixed_klen >= 0: every sequence has exactly that many keys (seqused_k is not read).
   int k_skip, fixed_klen;
+  // 256-byte rows (16-bit K/V, head_dim 128) with pages at least a tile long: the tensor maps are
+  // 5-D (64 elements, token, 128-byte half, head, page) and one box brings both halves of a page
+  int merged_halves;
 };
 
 // ---------------------------------------------------------------------------
@@ -151,6 +154,14 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* tm,
       "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
       " [%0], [%1, {%3, %4, %5, %6}], [%2];"
       ::"r"(dst), "l"(reinterpret_cast<uint64_t>(tm)), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap* tm, uint32_t bar, int c0,
+                                            int c1, int c2, int c3, int c4) {
+  asm volatile(
+      "cp.async.bulk.tensor.5d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(tm)), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
       : "memory");
 }
 __device__ __forceinline__ void ldsm_x4(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, uint32_t addr) {
@@ -356,49 +367,61 @@ struct TileProducer {
   const CUtensorMap* tmK;
   const CUtensorMap* tmV;
   uint32_t stage0, bar0;
-  int lane, P, box_rows, nbox, my_tiles, issued, pg;
+  // page size and box height are powers of two: shifts instead of divisions on the per-tile path
+  int lane, p_shift, box_shift, box_rows, nbox, hb_shift, my_tiles, issued, pg, h;
+  const int32_t* pt_row;   // page-table row of the sequence the cursor is in
   Cursor pc;
 
   __device__ __forceinline__ TileProducer(const AttnParams& p_, const CUtensorMap* k, const CUtensorMap* v,
                                           uint32_t stage0_, uint32_t bar0_, int lane_, long long r0, int my_tiles_)
       : p(p_), tmK(k), tmV(v), stage0(stage0_), bar0(bar0_), lane(lane_), my_tiles(my_tiles_), issued(0) {
-    P = p.page_size;
-    box_rows = P < TILE_N ? P : TILE_N;
-    nbox = (TILE_N / box_rows) * NH * 2;
+    p_shift = 31 - __clz(p.page_size);
+    box_rows = p.page_size < TILE_N ? p.page_size : TILE_N;
+    box_shift = 31 - __clz(box_rows);
+    hb_shift = (NH == 2 && !p.merged_halves) ? 1 : 0;   // log2 of the boxes per (page, K|V)
+    nbox = (TILE_N >> box_shift) << (hb_shift + 1);
     cursor_locate(p, pc, r0);
+    enter_segment();
     pg = lane < nbox ? page_for(lane) : 0;
   }
+  __device__ __forceinline__ void enter_segment() {
+    h = pc.seg / pc.nmb;
+    pt_row = p.page_table + (int64_t)pc.b * p.pt_rs;
+  }
   __device__ __forceinline__ int page_for(int j) const {
-    const int i = j / (NH * 2);
-    const int key = (pc.tile0 + pc.t) * TILE_N + i * box_rows;
+    const int i = j >> (hb_shift + 1);
+    const int key = (pc.tile0 + pc.t) * TILE_N + (i << box_shift);
     if (key >= pc.L) return 0;
-    return p.page_table[(int64_t)pc.b * p.pt_rs + key / P];
+    return pt_row[key >> p_shift];
   }
   __device__ __forceinline__ void issue(int stage) {
     const uint32_t sbase = stage0 + (uint32_t)stage * T::STAGE_BYTES;
     const uint32_t bar = bar0 + 8u * stage;
     const int k0 = (pc.tile0 + pc.t) * TILE_N;
-    const int h = pc.seg / pc.nmb;
     int nvalid = pc.L - k0;
     if (nvalid > TILE_N) nvalid = TILE_N;
-    const int nvb = (nvalid + box_rows - 1) / box_rows;
-    if (lane == 0) mbar_expect_tx(bar, (uint32_t)(nvb * box_rows * T::ROW_BYTES * 2));
+    const int nvb = (nvalid + box_rows - 1) >> box_shift;
+    if (lane == 0) mbar_expect_tx(bar, (uint32_t)((nvb << box_shift) * T::ROW_BYTES * 2));
     __syncwarp();
     for (int j = lane; j < nbox; j += 32) {
-      const int i = j / (NH * 2);
+      const int i = j >> (hb_shift + 1);
       if (i >= nvb) continue;
-      const int sub = j - i * (NH * 2);
-      const int kv = sub / NH, half = sub - kv * NH;
-      const int key = k0 + i * box_rows;
+      const int sub = j & ((2 << hb_shift) - 1);
+      const int kv = sub >> hb_shift, half = sub & ((1 << hb_shift) - 1);
+      const int key = k0 + (i << box_shift);
       const int page = (j == lane) ? pg : page_for(j);
       if ((unsigned)page >= (unsigned long long)p.n_pages) report(KB200_STATUS_BAD_PAGE, page, KID_ATTN);
       const uint32_t dst = sbase + (uint32_t)kv * T::KV_TILE_BYTES + (uint32_t)half * (TILE_N * RB) +
-                           (uint32_t)(i * box_rows) * RB;
-      tma_load_4d(dst, kv ? tmV : tmK, bar, half * (RB / KVB), key % P, h, page);
+                           (uint32_t)(i << box_shift) * RB;
+      if (NH == 2 && p.merged_halves)   // (the box is the whole tile: [half][token][128 bytes], as two boxes would leave it)
+        tma_load_5d(dst, kv ? tmV : tmK, bar, 0, key & (p.page_size - 1), 0, h, page);
+      else
+        tma_load_4d(dst, kv ? tmV : tmK, bar, half * (RB / KVB), key & (p.page_size - 1), h, page);
     }
     ++issued;
     if (issued < my_tiles) {
       cursor_advance(p, pc);
+      if (pc.t == 0) enter_segment();   // (a new segment, possibly of a new sequence)
       pg = lane < nbox ? page_for(lane) : 0;
     }
   }
@@ -1284,8 +1307,9 @@ struct TmapKey {
   int64_t page_stride, token_stride, head_stride, n_pages;
   int32_t page_size, hkv, hd, dtype, device;
   int32_t box_rows = 0;   // filled in by get_pool_tmap
+  int32_t merged = 0;     // 5-D map whose box spans both 128-byte halves of a 256-byte row
   bool operator==(const TmapKey& o) const {
-    return box_rows == o.box_rows && base == o.base && page_stride == o.page_stride && token_stride == o.token_stride &&
+    return box_rows == o.box_rows && merged == o.merged && base == o.base && page_stride == o.page_stride && token_stride == o.token_stride &&
            head_stride == o.head_stride && n_pages == o.n_pages && page_size == o.page_size &&
            hkv == o.hkv && hd == o.hd && dtype == o.dtype && device == o.device;
   }
@@ -1296,16 +1320,17 @@ struct TmapKeyHash {
     auto mix = [&](uint64_t v) { h ^= v + 0x9e3779b97f4a7c15ull + (h << 6) + (h >> 2); };
     mix((uint64_t)k.page_stride); mix((uint64_t)k.token_stride); mix((uint64_t)k.head_stride);
     mix((uint64_t)k.n_pages); mix((uint64_t)k.page_size); mix((uint64_t)k.hkv); mix((uint64_t)k.hd);
-    mix((uint64_t)k.dtype); mix((uint64_t)k.device); mix((uint64_t)k.box_rows);
+    mix((uint64_t)k.dtype); mix((uint64_t)k.device); mix((uint64_t)k.box_rows); mix((uint64_t)k.merged);
     return h;
   }
 };
 
 // One tensor map per pool view: dims (innermost first) D, P, H_kv, n_pages;
 // box = (128 bytes of D, min(P, TILE_N) tokens, 1 head, 1 page), 128-byte swizzle.
-inline int get_pool_tmap(const TmapKey& key_in, int tile_n, CUtensorMap* out) {
+inline int get_pool_tmap(const TmapKey& key_in, int tile_n, bool merged, CUtensorMap* out) {
   TmapKey key = key_in;
   key.box_rows = key.page_size < tile_n ? key.page_size : tile_n;
+  key.merged = merged ? 1 : 0;
   static std::mutex mu;
   static std::unordered_map<TmapKey, CUtensorMap, TmapKeyHash> cache;
   {
@@ -1330,9 +1355,21 @@ inline int get_pool_tmap(const TmapKey& key_in, int tile_n, CUtensorMap* out) {
   CUtensorMapSwizzle sw = rb == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
                           : rb == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B;
   CUtensorMap tm;
-  CUresult r = enc(&tm, dt, 4, const_cast<void*>(key.base), dims, strides, box, estr,
-                   CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  CUresult r;
+  if (merged) {
+    // a 256-byte row as two 128-byte halves: dims 64 elements, token, half (stride 128 bytes), head, page
+    cuuint64_t dims5[5] = {64u, (cuuint64_t)key.page_size, 2u, (cuuint64_t)key.hkv, (cuuint64_t)key.n_pages};
+    cuuint64_t strides5[4] = {(cuuint64_t)(key.token_stride * es), 128u, (cuuint64_t)(key.head_stride * es),
+                              (cuuint64_t)(key.page_stride * es)};
+    cuuint32_t box5[5] = {64u, (cuuint32_t)box_rows, 2u, 1u, 1u};
+    cuuint32_t estr5[5] = {1u, 1u, 1u, 1u, 1u};
+    r = enc(&tm, dt, 5, const_cast<void*>(key.base), dims5, strides5, box5, estr5, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  } else {
+    r = enc(&tm, dt, 4, const_cast<void*>(key.base), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  }
   if (r != CUDA_SUCCESS) return fail(KB200_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
   {
     std::lock_guard<std::mutex> lk(mu);
@@ -1449,6 +1486,15 @@ inline int launch_decode_dispatch(bool d128, int nw, const CUtensorMap& tmK, con
                                   const AttnParams& p, int grid, int dev, cudaStream_t stream) {
   return d128 ? launch_decode_hd<KVB, BF16, 128>(nw, tmK, tmV, p, grid, dev, stream)
               : launch_decode_hd<KVB, BF16, 64>(nw, tmK, tmV, p, grid, dev, stream);
+}
+
+// KB200_MERGED_BOXES=0 keeps one TMA box per 128-byte half (for A/B checks).
+inline bool merged_boxes_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("KB200_MERGED_BOXES");
+    return !(e && e[0] == '0');
+  }();
+  return on;
 }
 
 // Segments of up to 8 query rows run the transposed decode kernel; KB200_DECODE8=0 forces the
@@ -1738,10 +1784,12 @@ inline int launch_attention_pass(const kb200_attn_args* a, int k_skip, int fixed
   }
   TmapKey key{a->k_cache, a->kv_page_stride, a->kv_token_stride, a->kv_head_stride, a->n_pages,
               P, a->n_kv_heads, a->head_dim, a->kv_dtype, a->device};
+  // 256-byte rows and pages at least a tile long: one box per (page, K|V) instead of one per half
+  const bool merged = !prefill && a->head_dim * es == 256 && P >= tile_n && merged_boxes_enabled();
   CUtensorMap tmK, tmV;
-  if (int rc = get_pool_tmap(key, tile_n, &tmK)) return rc;
+  if (int rc = get_pool_tmap(key, tile_n, merged, &tmK)) return rc;
   key.base = a->v_cache;
-  if (int rc = get_pool_tmap(key, tile_n, &tmV)) return rc;
+  if (int rc = get_pool_tmap(key, tile_n, merged, &tmV)) return rc;
 
   char* ws = static_cast<char*>(a->workspace);
   AttnParams p;
@@ -1795,6 +1843,7 @@ inline int launch_attention_pass(const kb200_attn_args* a, int k_skip, int fixed
                    : a->n_kv_heads * ((group * a->seqlen_q + p.rows_per_seg - 1) / p.rows_per_seg);
   p.k_skip = k_skip;
   p.fixed_klen = fixed_klen;
+  p.merged_halves = merged ? 1 : 0;
 
   cudaStream_t stream = static_cast<cudaStream_t>(a->stream);
   // one sequence of a fixed length on the prefill kernel (the prefix pass of a shared-prefix call)
