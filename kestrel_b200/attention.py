@@ -19,6 +19,7 @@ def paged_attention(
     paged_kv_seqlens_q: torch.Tensor | None = None,
     cu_seqlens_q: torch.Tensor | None = None,
     sliding_window: int | None = None,
+    shared_prefix_pages: int = 0,
 ) -> torch.Tensor:
     """Attend ``query [B, H_q, S, D]`` (batched) or packed rows against one paged K/V layer.
 
@@ -29,6 +30,9 @@ def paged_attention(
     ``sliding_window`` keys up to its own position.  With ``cu_seqlens_q`` the rows of
     all sequences are packed along the first axis and the result is reshaped back to
     ``[B, S, H_q, D]``.  Returns ``[B, S, H_q, D]`` in the query dtype.
+
+    ``shared_prefix_pages`` (not in the reference): leading page-table entries that every row of the
+    batch maps to the same full pages; they are then read once for the whole batch (see ``flash_attn_fwd``).
     """
     q = query.transpose(1, 2)
     seqused_q = paged_kv_seqlens_q
@@ -54,6 +58,7 @@ def paged_attention(
         k_scale=getattr(paged_kv_layer, "k_scale", None),
         v_scale=getattr(paged_kv_layer, "v_scale", None),
         max_seqlen_q=query.shape[2] if cu_seqlens_q is not None else None,
+        shared_prefix_pages=shared_prefix_pages,
     )
     if cu_seqlens_q is not None:
         out = out.reshape(query.shape[0], query.shape[2], *out.shape[-2:])

@@ -18,6 +18,22 @@
 
 namespace kb200 {
 
+// Exact n / d for 0 <= n < 2^31 and a divisor fixed at launch: one wide multiply and a shift
+// (m = floor(2^(31+s) / d) + 1 with s = ceil(log2 d); the error term n * (m d - 2^(31+s)) stays below 2^(31+s)).
+struct FastDiv {
+  uint32_t d, m, sh;
+  __host__ static FastDiv make(uint32_t d_) {
+    FastDiv f;
+    f.d = d_ ? d_ : 1;
+    uint32_t s = 0;
+    while ((1ull << s) < f.d) ++s;
+    f.sh = 31 + s;
+    f.m = (uint32_t)((1ull << f.sh) / f.d + 1);
+    return f;
+  }
+  __device__ __forceinline__ uint32_t div(uint32_t n) const { return (uint32_t)(((uint64_t)n * m) >> sh); }
+};
+
 struct RopeAppendParams {
   char* q;            // [T, Hq, D] rows, rotated in place (may be null: no query rotation)
   char* k;            // [T, Hkv, D] rows
@@ -35,6 +51,9 @@ struct RopeAppendParams {
   int64_t num_tokens, n_slots_total;
   int32_t n_q_heads, n_kv_heads, head_dim, rot_dim, page_size, n_scales;
   int32_t positions_is_i64, write_k, quant;
+  int32_t cs_vec;                 // cos/sin rows can be read 16 bytes at a time
+  FastDiv d_token, d_rot, d_pass, d_copy, d_page;   // per_token, rot/pass/copy items per head, page_size
+  int64_t token_base;             // first token of this launch (launches are cut below 2^31 items)
 };
 
 template <typename In>
@@ -99,20 +118,18 @@ __global__ void __launch_bounds__(256) rope_append_kernel(const RopeAppendParams
   pdl_wait();
   pdl_launch_dependents();
   const int half = p.rot_dim / 2;
-  const int rot_items = half / EPT;
+  const int rot_items = (int)p.d_rot.d;
   const int pass_items = (p.head_dim - p.rot_dim) / EPT;
-  const int copy_items = p.head_dim / EPT;
+  const int copy_items = (int)p.d_copy.d;
   const bool append = p.key_cache != nullptr;
   const int q_items = p.q ? p.n_q_heads * rot_items : 0;
-  const int k_items = p.n_kv_heads * (rot_items + (append ? pass_items : 0));
-  const int v_items = append ? p.n_kv_heads * copy_items : 0;
-  const int per_token = q_items + k_items + v_items;
-  const int64_t total = p.num_tokens * per_token;
+  const int per_token = (int)p.d_token.d;
+  const uint32_t total = (uint32_t)(p.num_tokens * per_token);   // < 2^31: the host cuts larger calls
   constexpr int ES = (int)sizeof(In);
-  for (int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; idx < total;
-       idx += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t t = idx / per_token;
-    int r = (int)(idx - t * per_token);
+  for (uint32_t idx = blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += gridDim.x * blockDim.x) {
+    const uint32_t tl = p.d_token.div(idx);
+    int r = (int)(idx - tl * per_token);
+    const int64_t t = p.token_base + tl;
 
     // destination in the pool (K and V items only)
     char* pool_row = nullptr;   // start of the (slot, head 0) row in the K or V pool
@@ -125,6 +142,20 @@ __global__ void __launch_bounds__(256) rope_append_kernel(const RopeAppendParams
         slot = -1;
       }
     }
+    // page and offset of the slot (slots of one call fit 31 bits whenever the pool does)
+    auto pool_base = [&](char* cache, int h) {
+      int64_t page;
+      int off;
+      if (p.n_slots_total < (1ll << 31)) {
+        const uint32_t pg = p.d_page.div((uint32_t)slot);
+        page = pg;
+        off = (int)((uint32_t)slot - pg * p.d_page.d);
+      } else {
+        page = slot / p.page_size;
+        off = (int)(slot - page * p.page_size);
+      }
+      return cache + page * p.page_stride_b + off * p.token_stride_b + h * p.head_stride_b;
+    };
 
     if (r < q_items + p.n_kv_heads * rot_items) {
       // ---- rotation item (Q or K)
@@ -132,12 +163,12 @@ __global__ void __launch_bounds__(256) rope_append_kernel(const RopeAppendParams
       char* row;
       bool is_k = false;
       if (is_q) {
-        h = r / rot_items;
+        h = (int)p.d_rot.div((uint32_t)r);
         c = r - h * rot_items;
         row = p.q + t * p.q_token_stride_b + (int64_t)h * p.head_dim * ES;
       } else {
         r -= q_items;
-        h = r / rot_items;
+        h = (int)p.d_rot.div((uint32_t)r);
         c = r - h * rot_items;
         row = p.k + t * p.k_token_stride_b + (int64_t)h * p.head_dim * ES;
         is_k = true;
@@ -152,12 +183,27 @@ __global__ void __launch_bounds__(256) rope_append_kernel(const RopeAppendParams
       Vec<In, EPT> x1, x2;
       load_vec<In, EPT>(x1, row + (int64_t)c * EPT * ES);
       load_vec<In, EPT>(x2, row + (int64_t)(half + c * EPT) * ES);
+      float co[EPT], si[EPT];
+      if constexpr (EPT % 4 == 0) {
+        if (p.cs_vec) {
+#pragma unroll
+          for (int i = 0; i < EPT / 4; ++i) {
+            *reinterpret_cast<float4*>(&co[4 * i]) = *reinterpret_cast<const float4*>(cs + 4 * i);
+            *reinterpret_cast<float4*>(&si[4 * i]) = *reinterpret_cast<const float4*>(cs + half + 4 * i);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < EPT; ++i) { co[i] = cs[i]; si[i] = cs[half + i]; }
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < EPT; ++i) { co[i] = cs[i]; si[i] = cs[half + i]; }
+      }
 #pragma unroll
       for (int i = 0; i < EPT; ++i) {
-        const float co = cs[i], si = cs[half + i];
         const float a = to_float(x1.e[i]), b = to_float(x2.e[i]);
-        const float y1 = __fsub_rn(__fmul_rn(a, co), __fmul_rn(b, si));
-        const float y2 = __fadd_rn(__fmul_rn(b, co), __fmul_rn(a, si));
+        const float y1 = __fsub_rn(__fmul_rn(a, co[i]), __fmul_rn(b, si[i]));
+        const float y2 = __fadd_rn(__fmul_rn(b, co[i]), __fmul_rn(a, si[i]));
         x1.e[i] = from_float<In>(y1);
         x2.e[i] = from_float<In>(y2);
       }
@@ -166,9 +212,7 @@ __global__ void __launch_bounds__(256) rope_append_kernel(const RopeAppendParams
         store_vec<In, EPT>(row + (int64_t)(half + c * EPT) * ES, x2);
       }
       if (is_k && slot >= 0) {
-        const int64_t page = slot / p.page_size;
-        const int off = (int)(slot - page * p.page_size);
-        pool_row = p.key_cache + page * p.page_stride_b + off * p.token_stride_b + h * p.head_stride_b;
+        pool_row = pool_base(p.key_cache, h);
         if (p.quant) {
           const float s = p.k_scale[p.n_scales == 1 ? 0 : h];
           store_quant<In, EPT>(pool_row + c * EPT, x1, s);
@@ -188,19 +232,16 @@ __global__ void __launch_bounds__(256) rope_append_kernel(const RopeAppendParams
     int h, e0;
     const char* src;
     if (!is_v) {
-      h = r / pass_items;
+      h = (int)p.d_pass.div((uint32_t)r);
       e0 = p.rot_dim + (r - h * pass_items) * EPT;
       src = p.k + t * p.k_token_stride_b + ((int64_t)h * p.head_dim + e0) * ES;
     } else {
       r -= p.n_kv_heads * pass_items;
-      h = r / copy_items;
+      h = (int)p.d_copy.div((uint32_t)r);
       e0 = (r - h * copy_items) * EPT;
       src = p.v + t * p.v_token_stride_b + ((int64_t)h * p.head_dim + e0) * ES;
     }
-    const int64_t page = slot / p.page_size;
-    const int off = (int)(slot - page * p.page_size);
-    pool_row = (is_v ? p.value_cache : p.key_cache) + page * p.page_stride_b + off * p.token_stride_b +
-               h * p.head_stride_b;
+    pool_row = pool_base(is_v ? p.value_cache : p.key_cache, h);
     Vec<In, EPT> x;
     load_vec<In, EPT>(x, src);
     if (p.quant) {
@@ -228,14 +269,36 @@ struct RopeAppendArgs {
   int32_t write_k;
 };
 
+// Blocks of `threads` threads that fit on the current device at once (all SMs).
+template <typename K>
+inline int resident_blocks(K kernel, int threads) {
+  int per_sm = 0, dev = 0, sms = 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, 0) != cudaSuccess || per_sm < 1) per_sm = 4;
+  if (cudaGetDevice(&dev) != cudaSuccess ||
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms < 1)
+    sms = 148;
+  return per_sm * sms;
+}
+
 template <typename In>
-inline int launch_rope_append_typed(const RopeAppendParams& p, bool vec, int64_t items, cudaStream_t stream) {
+inline int launch_rope_append_typed(RopeAppendParams p, bool vec, int64_t per_token, cudaStream_t stream) {
   const int threads = 256;
-  int64_t b = (items + threads - 1) / threads;
-  const int64_t cap = 148 * 16;
-  const int blocks = (int)(b < 1 ? 1 : (b > cap ? cap : b));
-  if (vec) KB200_CUDA_OK(launch_kernel(rope_append_kernel<In, 8>, dim3(blocks), dim3(threads), 0, stream, p));
-  else KB200_CUDA_OK(launch_kernel(rope_append_kernel<In, 1>, dim3(blocks), dim3(threads), 0, stream, p));
+  // the kernel indexes its items with 32 bits: calls above 2^31 items are cut into several launches
+  const int64_t max_tokens = ((1ll << 31) - 1) / per_token;
+  const int64_t all_tokens = p.num_tokens;
+  for (int64_t t0 = 0; t0 < all_tokens; t0 += max_tokens) {
+    p.token_base = t0;
+    p.num_tokens = all_tokens - t0 < max_tokens ? all_tokens - t0 : max_tokens;
+    const int64_t items = p.num_tokens * per_token;
+    int64_t b = (items + threads - 1) / threads;
+    // grid-stride loop: at most one resident wave, so that no SM is left with a part-filled last wave
+    static const int resident8 = resident_blocks(rope_append_kernel<In, 8>, threads);
+    static const int resident1 = resident_blocks(rope_append_kernel<In, 1>, threads);
+    const int64_t cap = vec ? resident8 : resident1;
+    const int blocks = (int)(b < 1 ? 1 : (b > cap ? cap : b));
+    if (vec) KB200_CUDA_OK(launch_kernel(rope_append_kernel<In, 8>, dim3(blocks), dim3(threads), 0, stream, p));
+    else KB200_CUDA_OK(launch_kernel(rope_append_kernel<In, 1>, dim3(blocks), dim3(threads), 0, stream, p));
+  }
   return KB200_OK;
 }
 
@@ -310,11 +373,17 @@ inline int launch_rope_append(const RopeAppendArgs& a, cudaStream_t stream) {
   const int64_t per_token = (int64_t)(p.q ? a.n_q_heads : 0) * (half / ept) +
                             (int64_t)a.n_kv_heads * (half / ept + (append ? (a.head_dim - a.rot_dim) / ept : 0)) +
                             (append ? (int64_t)a.n_kv_heads * (a.head_dim / ept) : 0);
-  KB200_REQUIRE(per_token < (1ll << 30), "row too large");
-  const int64_t items = per_token * a.num_tokens;
-  if (a.in_dtype == KB200_DTYPE_BF16) return launch_rope_append_typed<__nv_bfloat16>(p, vec, items, stream);
-  if (a.in_dtype == KB200_DTYPE_F16) return launch_rope_append_typed<__half>(p, vec, items, stream);
-  return launch_rope_append_typed<float>(p, false, items, stream);
+  KB200_REQUIRE(per_token > 0 && per_token < (1ll << 24), "row too large");
+  p.d_token = FastDiv::make((uint32_t)per_token);
+  p.d_rot = FastDiv::make((uint32_t)(half / ept));
+  p.d_pass = FastDiv::make((uint32_t)((a.head_dim - a.rot_dim) / ept));
+  p.d_copy = FastDiv::make((uint32_t)(a.head_dim / ept));
+  p.d_page = FastDiv::make((uint32_t)p.page_size);
+  p.cs_vec = aligned16(a.cos_sin_cache) && a.cos_sin_row_stride % 4 == 0 && half % 4 == 0;
+  p.token_base = 0;
+  if (a.in_dtype == KB200_DTYPE_BF16) return launch_rope_append_typed<__nv_bfloat16>(p, vec, per_token, stream);
+  if (a.in_dtype == KB200_DTYPE_F16) return launch_rope_append_typed<__half>(p, vec, per_token, stream);
+  return launch_rope_append_typed<float>(p, false, per_token, stream);
 }
 
 // ---------------------------------------------------------------------------
