@@ -11,7 +11,6 @@ import torch
 
 from helpers import make_paged_problem
 from kestrel_b200 import _native, kernels
-from kestrel_b200.kv_cache import PageTable
 from oracle import paged_kv_oracle as O
 from test_gpu_attention import assert_close
 
@@ -209,22 +208,3 @@ def test_through_the_allocation_free_entry_point():
     torch.cuda.synchronize()
     want = O.paged_attention(p["q"].to(torch.bfloat16).float(), p["k_pool"], p["v_pool"], p["page_table"], p["seqused_k"])
     assert_close(out, want, "static entry point, shared prefix")
-
-
-def test_common_prefix_pages_host_helper():
-    pt = PageTable(n_pages=256, page_size=16, max_batch_size=8, device=DEV)
-    owner = pt.allocate()
-    pt.reserve(owner, 729)
-    shared = list(pt.page_table_cpu[owner])[:45]
-    rows = []
-    for extra in (10, 40, 100):
-        r = pt.allocate()
-        pt.map_pages(r, 0, shared)
-        pt.reserve(r, 729 + extra)
-        rows.append(r)
-    assert pt.common_prefix_pages(rows) == 45
-    assert pt.common_prefix_pages(rows, min_tokens=700) == 43
-    assert pt.common_prefix_pages(rows[:1]) == 0
-    other = pt.allocate()
-    pt.reserve(other, 100)
-    assert pt.common_prefix_pages(rows + [other]) == 0

@@ -258,3 +258,33 @@ def test_cow_page_remaps_row_and_queues_copy():
     assert pt.pages_available == before + 2
     with pytest.raises(IndexError):
         pt.cow_page(r1, 0)
+
+
+def test_common_prefix_pages_counts_the_shared_leading_pages():
+    """Rows attached to one cached prefix map the same leading pages; the count feeds flash_attn_fwd's
+    shared_prefix_pages."""
+    pt = PageTable(n_pages=256, page_size=16, max_batch_size=8, device="cpu")
+    owner = pt.allocate()
+    pt.reserve(owner, 729)
+    shared = list(pt.page_table_cpu[owner])[:45]
+    rows = []
+    for extra in (10, 40, 100):
+        r = pt.allocate()
+        pt.map_pages(r, 0, shared)
+        pt.reserve(r, 729 + extra)
+        rows.append(r)
+    assert pt.common_prefix_pages(rows) == 45
+    assert pt.common_prefix_pages(rows, min_tokens=700) == 43   # only pages entirely below 700 tokens
+    assert pt.common_prefix_pages(rows, min_tokens=0) == 0
+    assert pt.common_prefix_pages(rows[:1]) == 0                # one row shares with nobody
+    assert pt.common_prefix_pages([]) == 0
+    other = pt.allocate()
+    pt.reserve(other, 100)
+    assert pt.common_prefix_pages(rows + [other]) == 0
+    # rows that agree on the first pages only
+    a, b = pt.allocate(), pt.allocate()
+    pt.map_pages(a, 0, shared[:10])
+    pt.map_pages(b, 0, shared[:7])
+    pt.reserve(a, 400)
+    pt.reserve(b, 400)
+    assert pt.common_prefix_pages([a, b]) == 7
