@@ -93,8 +93,10 @@ struct AttnParams {
   int uniform_nseg;  // segments per sequence when that is the same for all (padded q, no seqused_q), else 0
   // Shared-prefix passes.  k_skip: the first k_skip keys of every sequence are served by another pass
   // (page_table already points past their pages; lengths are taken relative to them).
-  // fixed_klen >= 0: every sequence has exactly that many keys (seqused_k is not read).
-  int k_skip, fixed_klen;
+  // fixed_klen >= 0: every sequence has exactly that many keys, the last one fixed_klen_last
+  // (seqused_k is not read).  no_plan: the prefill kernel derives its segments from these and the
+  // launch parameters; no plan kernel ran.
+  int k_skip, fixed_klen, fixed_klen_last, no_plan;
   // 256-byte rows (16-bit K/V, head_dim 128) with pages at least a tile long: the tensor maps are
   // 5-D (64 elements, token, 128-byte half, head, page) and one box brings both halves of a page
   int merged_halves;
@@ -236,7 +238,7 @@ __global__ void __launch_bounds__(256) attn_plan_kernel(const AttnParams p) {
     long long cnt_t = 0;
     int cnt_s = 0;
     if (b < p.batch) {
-      int L = p.fixed_klen >= 0 ? p.fixed_klen : p.seqused_k[b] - p.k_skip;
+      int L = p.fixed_klen >= 0 ? (b == p.batch - 1 ? p.fixed_klen_last : p.fixed_klen) : p.seqused_k[b] - p.k_skip;
       const int L_rel = L;
       if (L < 0) L = 0;
       int sq, row0 = 0;
@@ -1566,6 +1568,7 @@ inline bool shared_prefix_applies(const kb200_attn_args* a) {
 
 struct SharedPrefixPlan {
   kb200_attn_args pre, rest;   // the two passes
+  int n_split, pages_first;    // the prefix pass as 1 or 2 sequences of prefix keys (pages_first: pages of the first)
   size_t o1, lse1, lse2, ws1, ws2, total;   // scratch layout
 };
 
@@ -1585,12 +1588,30 @@ inline SharedPrefixPlan shared_prefix_plan(const kb200_attn_args* a, int sms) {
   sp.pre.o_head_stride = a->head_dim;
   sp.pre.seqused_k = nullptr;
   sp.pre.causal = 0;
+  // Few CTAs (one per KV head and 256 packed rows): cut the prefix keys in two at a tile boundary and
+  // run the halves as two sequences over the same query rows, so twice the SMs work half as long.
+  sp.n_split = 1;
+  sp.pages_first = a->shared_prefix_pages;
+  {
+    const int group = a->n_q_heads / a->n_kv_heads;
+    const int64_t ctas = (int64_t)a->n_kv_heads * ((group * rows + kPrefillRowsPerSeg - 1) / kPrefillRowsPerSeg);
+    const int pages_per_tile = kPrefillTileKeys / a->page_size;   // (0 for pages longer than a tile)
+    if (pages_per_tile > 0 && 2 * ctas <= sms && a->shared_prefix_pages >= 4 * pages_per_tile) {
+      const int tiles = (a->shared_prefix_pages + pages_per_tile - 1) / pages_per_tile;
+      sp.pages_first = ((tiles + 1) / 2) * pages_per_tile;
+      sp.n_split = 2;
+      sp.pre.batch = 2;
+      sp.pre.total_q = 2 * rows;
+      sp.pre.pt_row_stride = sp.pages_first;   // the second sequence's row starts where the first one's pages end
+      sp.pre.o_batch_stride = rows * a->n_q_heads * a->head_dim;
+    }
+  }
   sp.rest = *a;
   sp.rest.shared_prefix_pages = 0;
   sp.rest.page_table = a->page_table + a->shared_prefix_pages;
   size_t off = 0;
-  sp.o1 = off; off = up(off + (size_t)rows * a->n_q_heads * a->head_dim * 2);
-  sp.lse1 = off; off = up(off + sizeof(float) * rows * a->n_q_heads);
+  sp.o1 = off; off = up(off + (size_t)sp.n_split * rows * a->n_q_heads * a->head_dim * 2);
+  sp.lse1 = off; off = up(off + sizeof(float) * sp.n_split * rows * a->n_q_heads);
   sp.lse2 = off; off = up(off + sizeof(float) * rows * a->n_q_heads);
   sp.ws1 = off; off = up(off + attn_pass_workspace_need(&sp.pre, sms));
   sp.ws2 = off; off = up(off + attn_pass_workspace_need(&sp.rest, sms));
@@ -1606,13 +1627,13 @@ inline uint64_t attn_workspace_need(const kb200_attn_args* a, int sms) {
 }
 
 struct CombineParams {
-  const char* o1;      // [rows, hq, hd] contiguous, q's dtype
-  char* out;           // the second pass's output, combined in place
-  const float* lse1;   // [hq, rows]
+  const char* o1;      // [n_pre][rows, hq, hd] contiguous, q's dtype: the prefix pass (one or two key ranges)
+  char* out;           // the remainder pass's output, combined in place
+  const float* lse1;   // [n_pre][hq, rows]
   float* lse2;         // [batch, hq, sq]; receives the combined value when write_lse is set
   int64_t o_bs, o_rs, o_hs;
   int64_t rows;
-  int sq, hq, hd, q_is_bf16, write_lse;
+  int sq, hq, hd, q_is_bf16, write_lse, n_pre;
 };
 
 // one thread per 8 consecutive elements of one (row, head)
@@ -1621,6 +1642,7 @@ __global__ void __launch_bounds__(256) attn_combine_kernel(const CombineParams c
   pdl_launch_dependents();
   const int chunks = c.hd / 8;
   const int64_t total = c.rows * c.hq * chunks;
+  const int64_t o1_stride = c.rows * c.hq * c.hd * 2, l1_stride = c.rows * c.hq;   // second key range of the prefix
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
     const int ch = (int)(i % chunks);
     const int64_t rh = i / chunks;
@@ -1629,36 +1651,44 @@ __global__ void __launch_bounds__(256) attn_combine_kernel(const CombineParams c
     const int64_t b = row / c.sq;
     const int j = (int)(row - b * c.sq);
     const float l1 = c.lse1[(int64_t)h * c.rows + row];
+    const float l1b = c.n_pre == 2 ? c.lse1[l1_stride + (int64_t)h * c.rows + row] : -INFINITY;
     float* l2p = c.lse2 + (b * c.hq + h) * c.sq + j;
     const float l2 = *l2p;
-    const float m = fmaxf(l1, l2);
-    float w1 = 0.f, w2 = 0.f, lse = -INFINITY;
+    const float m = fmaxf(fmaxf(l1, l1b), l2);
+    float w1 = 0.f, w1b = 0.f, w2 = 0.f, lse = -INFINITY;
     if (m != -INFINITY) {
-      const float e1 = __expf(l1 - m), e2 = __expf(l2 - m);
-      const float inv = 1.f / (e1 + e2);
+      const float e1 = __expf(l1 - m), e1b = __expf(l1b - m), e2 = __expf(l2 - m);   // exp(-inf) = 0
+      const float inv = 1.f / (e1 + e1b + e2);
       w1 = e1 * inv;
+      w1b = e1b * inv;
       w2 = e2 * inv;
-      lse = m + logf(e1 + e2);
+      lse = m + logf(e1 + e1b + e2);
     }
-    const uint4 a = *reinterpret_cast<const uint4*>(c.o1 + 2 * ((row * c.hq + h) * c.hd + 8 * ch));
+    const char* src = c.o1 + 2 * ((row * c.hq + h) * c.hd + 8 * ch);
+    const uint4 a = *reinterpret_cast<const uint4*>(src);
+    const uint4 ab = c.n_pre == 2 ? *reinterpret_cast<const uint4*>(src + o1_stride) : make_uint4(0u, 0u, 0u, 0u);
     char* dst = c.out + 2 * (b * c.o_bs + j * c.o_rs + h * c.o_hs + 8 * ch);
     const uint4 d = *reinterpret_cast<const uint4*>(dst);
     const uint32_t* aw = reinterpret_cast<const uint32_t*>(&a);
+    const uint32_t* bw = reinterpret_cast<const uint32_t*>(&ab);
     const uint32_t* dw = reinterpret_cast<const uint32_t*>(&d);
     uint4 r;
     uint32_t* rw = reinterpret_cast<uint32_t*>(&r);
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
-      float a0, a1, d0, d1;
+      float a0, a1, b0, b1, d0, d1;
       if (c.q_is_bf16) {
         a0 = bf16_bits_to_float(aw[e] & 0xffffu); a1 = bf16_bits_to_float(aw[e] >> 16);
+        b0 = bf16_bits_to_float(bw[e] & 0xffffu); b1 = bf16_bits_to_float(bw[e] >> 16);
         d0 = bf16_bits_to_float(dw[e] & 0xffffu); d1 = bf16_bits_to_float(dw[e] >> 16);
-        rw[e] = pack2<true>(a0 * w1 + d0 * w2, a1 * w1 + d1 * w2);
+        rw[e] = pack2<true>(a0 * w1 + b0 * w1b + d0 * w2, a1 * w1 + b1 * w1b + d1 * w2);
       } else {
-        const __half2 ah = *reinterpret_cast<const __half2*>(&aw[e]), dh = *reinterpret_cast<const __half2*>(&dw[e]);
+        const __half2 ah = *reinterpret_cast<const __half2*>(&aw[e]), bh = *reinterpret_cast<const __half2*>(&bw[e]),
+                      dh = *reinterpret_cast<const __half2*>(&dw[e]);
         a0 = __low2float(ah); a1 = __high2float(ah);
+        b0 = __low2float(bh); b1 = __high2float(bh);
         d0 = __low2float(dh); d1 = __high2float(dh);
-        rw[e] = pack2<false>(a0 * w1 + d0 * w2, a1 * w1 + d1 * w2);
+        rw[e] = pack2<false>(a0 * w1 + b0 * w1b + d0 * w2, a1 * w1 + b1 * w1b + d1 * w2);
       }
     }
     *reinterpret_cast<uint4*>(dst) = r;
@@ -1666,7 +1696,7 @@ __global__ void __launch_bounds__(256) attn_combine_kernel(const CombineParams c
   }
 }
 
-inline int launch_attention_pass(const kb200_attn_args* a, int k_skip, int fixed_klen);
+inline int launch_attention_pass(const kb200_attn_args* a, int k_skip, int fixed_klen, int fixed_klen_last);
 
 inline int launch_shared_prefix_attention(const kb200_attn_args* a) {
   int sms = 0;
@@ -1687,8 +1717,9 @@ inline int launch_shared_prefix_attention(const kb200_attn_args* a) {
   sp.rest.lse = a->lse ? a->lse : reinterpret_cast<float*>(ws + sp.lse2);
   sp.rest.workspace = ws + sp.ws2;
   sp.rest.workspace_bytes = sp.total - sp.ws2;
-  if (int rc = launch_attention_pass(&sp.pre, 0, k_skip)) return rc;
-  if (int rc = launch_attention_pass(&sp.rest, k_skip, -1)) return rc;
+  const int klen_first = sp.pages_first * a->page_size;
+  if (int rc = launch_attention_pass(&sp.pre, 0, klen_first, sp.n_split == 2 ? k_skip - klen_first : klen_first)) return rc;
+  if (int rc = launch_attention_pass(&sp.rest, k_skip, -1, -1)) return rc;
   CombineParams c;
   c.o1 = ws + sp.o1;
   c.out = static_cast<char*>(a->out);
@@ -1699,6 +1730,7 @@ inline int launch_shared_prefix_attention(const kb200_attn_args* a) {
   c.sq = a->seqlen_q; c.hq = a->n_q_heads; c.hd = a->head_dim;
   c.q_is_bf16 = a->q_dtype == KB200_DTYPE_BF16;
   c.write_lse = a->lse != nullptr;
+  c.n_pre = sp.n_split;
   const int64_t items = c.rows * c.hq * (c.hd / 8);
   int64_t blocks = (items + 255) / 256;
   if (blocks > sms * 8) blocks = sms * 8;
@@ -1714,11 +1746,11 @@ inline int launch_paged_attention(const kb200_attn_args* a) {
   if (a->batch == 0 || a->total_q == 0) return KB200_OK;
   KB200_REQUIRE(a->shared_prefix_pages >= 0, "shared_prefix_pages must be non-negative");
   if (shared_prefix_applies(a)) return launch_shared_prefix_attention(a);
-  return launch_attention_pass(a, 0, -1);
+  return launch_attention_pass(a, 0, -1, -1);
 }
 
-// One attention pass.  k_skip / fixed_klen: see AttnParams (0 / -1 for a plain call).
-inline int launch_attention_pass(const kb200_attn_args* a, int k_skip, int fixed_klen) {
+// One attention pass.  k_skip / fixed_klen / fixed_klen_last: see AttnParams (0 / -1 / -1 for a plain call).
+inline int launch_attention_pass(const kb200_attn_args* a, int k_skip, int fixed_klen, int fixed_klen_last) {
   KB200_REQUIRE(a != nullptr, "args is null");
   KB200_REQUIRE(a->struct_bytes == sizeof(kb200_attn_args), "kb200_attn_args size mismatch: got %u, built with %zu",
                 a->struct_bytes, sizeof(kb200_attn_args));
@@ -1843,12 +1875,14 @@ inline int launch_attention_pass(const kb200_attn_args* a, int k_skip, int fixed
                    : a->n_kv_heads * ((group * a->seqlen_q + p.rows_per_seg - 1) / p.rows_per_seg);
   p.k_skip = k_skip;
   p.fixed_klen = fixed_klen;
+  p.fixed_klen_last = fixed_klen_last;
   p.merged_halves = merged ? 1 : 0;
 
   cudaStream_t stream = static_cast<cudaStream_t>(a->stream);
-  // one sequence of a fixed length on the prefill kernel (the prefix pass of a shared-prefix call)
-  // has nothing to plan: the kernel derives its segments from the launch parameters
-  const bool no_plan = prefill && fixed_klen >= 0 && a->batch == 1 && p.uniform_nseg > 0;
+  // sequences of fixed lengths on the prefill kernel (the prefix pass of a shared-prefix call) have
+  // nothing to plan: the kernel derives its segments from the launch parameters
+  const bool no_plan = prefill && fixed_klen >= 0 && p.uniform_nseg > 0;
+  p.no_plan = no_plan ? 1 : 0;
   if (!no_plan) KB200_CUDA_OK(launch_kernel(attn_plan_kernel, dim3(1), dim3(256), 0, stream, p));
 
   int rc;

@@ -258,9 +258,9 @@ paged_prefill_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
   // ---- which segment is this CTA?
   // CTAs are handed out in block order: taking the segments from the back puts the later row blocks
   // of a sequence, which see more keys under the causal mask, first and keeps the tail of the grid short
-  // (one sequence of a fixed length, the prefix pass of a shared-prefix call, needs no plan launch)
-  const bool no_plan = p.fixed_klen >= 0 && p.batch == 1;
-  const int seg = (no_plan ? p.uniform_nseg : p.seg_cum[p.batch]) - 1 - (int)blockIdx.x;
+  // (sequences of fixed lengths, the prefix pass of a shared-prefix call, need no plan launch)
+  const bool no_plan = p.no_plan != 0;
+  const int seg = (no_plan ? p.batch * p.uniform_nseg : p.seg_cum[p.batch]) - 1 - (int)blockIdx.x;
   if (seg < 0) return;   // uniform over the CTA; nothing allocated yet
   int b;
   if (p.uniform_nseg > 0) {
@@ -273,11 +273,12 @@ paged_prefill_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
     }
     b = lo;
   }
-  const int sq = no_plan ? p.seqlen_q : p.sq[b], L = no_plan ? p.fixed_klen : p.klen[b];
+  const int sq = no_plan ? p.seqlen_q : p.sq[b];
+  const int L = no_plan ? (b == p.batch - 1 ? p.fixed_klen_last : p.fixed_klen) : p.klen[b];
   const int qrow0 = no_plan ? 0 : p.qrow0[b];
   const int nrows = p.group * sq;
   const int nmb = (nrows + kPfCtaRows - 1) / kPfCtaRows;
-  const int sib = seg - (no_plan ? 0 : p.seg_cum[b]);
+  const int sib = seg - (no_plan ? b * p.uniform_nseg : p.seg_cum[b]);
   const int h = sib / nmb, mb = sib - h * nmb;
   const int row_first = mb * kPfCtaRows;
   const bool upper = p.causal || p.window_left >= 0;

@@ -88,6 +88,17 @@ def test_multi_query_rows_and_lse(seqlen_q):
     assert torch.allclose(lse.cpu(), lse_plain.cpu(), atol=2e-3, rtol=1e-3)
 
 
+@pytest.mark.parametrize("page_size,n_shared", [(16, 40), (64, 9), (128, 5)])
+def test_long_prefix_is_cut_in_two_key_ranges(page_size, n_shared):
+    # few CTAs and at least four tiles of prefix keys: the prefix pass runs as two sequences of keys over
+    # the same query rows (three partial results per row to combine); log-sum-exp checked as well
+    p = shared_problem(seed=23, batch=24, n_shared=n_shared, extra_lo=2, extra_hi=150, head_dim=128, seqlen_q=2,
+                       page_size=page_size)
+    (out, lse), (plain, lse_plain), (want, want_lse) = run(p, torch.bfloat16, n_shared, return_lse=True)
+    assert_close(out, want, f"P={page_size}")
+    assert torch.allclose(lse.cpu(), want_lse, atol=2e-3, rtol=1e-3)
+
+
 def test_non_causal_and_suffix_empty():
     # without the causal mask a sequence may consist of the shared pages alone
     p = shared_problem(seed=7, batch=20, n_shared=8, extra_lo=0, extra_hi=0, head_dim=64,
