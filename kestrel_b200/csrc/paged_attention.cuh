@@ -1530,13 +1530,26 @@ template <int HD, bool BF16, bool KV8>
 int launch_prefill_variant(const CUtensorMap& tmK, const CUtensorMap& tmV, const AttnParams& p, int grid, int dev,
                            cudaStream_t stream);
 constexpr int kPrefillRowsPerSeg = 256, kPrefillTileKeys = 128, kPrefillMinPackedRows = 64;
+// Packed query rows per sequence from which the prefill kernel serves a call.  The split-KV kernels
+// read a sequence's K/V once per 16 rows, the prefill kernel once per 256 but with a fixed cost per
+// CTA: measured break-even at 32 rows for head_dim 128 (4096 keys) and near 56 for head_dim 64
+// (729 keys).  KB200_PREFILL_MIN_ROWS overrides, for A/B checks.
+inline int prefill_min_rows(int head_dim) {
+  static const int forced = [] {
+    const char* e = getenv("KB200_PREFILL_MIN_ROWS");
+    const int n = e ? atoi(e) : 0;
+    return n > 0 ? n : 0;
+  }();
+  if (forced) return forced;
+  return head_dim == 128 ? 40 : 56;
+}
 
 // Which kernel serves a call: many query rows per sequence with 16-bit K/V (or a block mask) go to
 // the tensor-memory prefill kernel, one CTA per 256 packed rows, no split over keys and no merge.
 inline bool use_prefill_kernel(const kb200_attn_args* a) {
   if (a->q_visible_until != nullptr) return true;
   if (!prefill_enabled() || a->n_kv_heads <= 0) return false;
-  return (int64_t)(a->n_q_heads / a->n_kv_heads) * a->seqlen_q >= kPrefillMinPackedRows;
+  return (int64_t)(a->n_q_heads / a->n_kv_heads) * a->seqlen_q >= prefill_min_rows(a->head_dim);
 }
 
 // Scratch bytes this very call needs: the plan arrays, plus the split-KV partials unless the prefill
