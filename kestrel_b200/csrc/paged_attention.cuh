@@ -16,10 +16,11 @@
 // Data movement
 //   The pool view [n_pages, P, H_kv, D] is described to the TMA unit once per
 //   pool as a 4-D tensor map; a (page, head) tile of K or V is one
-//   cp.async.bulk.tensor box of P rows x 128 bytes (two boxes when a row is
-//   256 bytes), landing in 128-byte-swizzled shared memory so that ldmatrix is
-//   bank-conflict free.  Each warp owns a ring of NS stages and
-//   refills a stage as soon as it has read it, so 2 tiles per warp are always
+//   cp.async.bulk.tensor box of P rows x 128 bytes (a 256-byte row: two boxes,
+//   or one box of a 5-D map that splits the row into two 128-byte halves),
+//   landing in 128-byte-swizzled shared memory so that ldmatrix is
+//   bank-conflict free.  Each warp owns a ring of NS stages (two) and
+//   refills a stage as soon as it has read it, so one tile per warp is always
 //   in flight behind the one being computed.  Page indices are read one tile
 //   ahead of the copy that needs them.  No multicast, no cluster.
 //
@@ -43,17 +44,20 @@ namespace kb200 {
 constexpr int kAttnMaxWarps = 12;
 constexpr int kRowsPerSeg = 16;   // query rows per segment, general kernel (also the stride of scratch slots)
 constexpr int kDecodeRows = 8;    // query rows per segment, decode kernel
-constexpr int kAttnRingBytes = 192 * 1024;  // shared memory given to the K/V rings of one CTA
+// NW worker warps per CTA, each with a ring of NS stages of kAttnStageBytes(NW) (K tile then V tile).
+// Stages are 8 KB with 8 or 12 warps (two of them per warp: one being read, one in flight) and 16 KB with 4.
+// More bytes in flight do not help: 8 warps x 3 stages (128 KB behind the tiles being read) measured
+// 3-5 % slower than x 2 (64 KB) once the kernel is HBM-bound; the requests queue up in the memory system and
+// the SMs' shares of the bandwidth grow apart.
+constexpr int kAttnStageBytes(int nw) { return nw == 4 ? 16 * 1024 : 8 * 1024; }
 
-// NW worker warps per CTA share the ring: each gets NS stages of
-// kAttnRingBytes / (NW * NS) bytes (8 KB with 8 warps x 3 stages or 12 warps x 2 stages).
 template <int KVB, int HD, int NW, int NS>
 struct AttnTile {
   static constexpr int STAGES = NS;
   static constexpr int ROW_BYTES = HD * KVB;                      // bytes of one token row of one head
   static constexpr int RB = ROW_BYTES > 128 ? 128 : ROW_BYTES;    // swizzled row width in smem
   static constexpr int NH = ROW_BYTES / RB;                       // 128-byte halves per row
-  static constexpr int STAGE_TARGET = kAttnRingBytes / (NW * NS);
+  static constexpr int STAGE_TARGET = kAttnStageBytes(NW);
   static constexpr int TILE_RAW = STAGE_TARGET / (2 * ROW_BYTES);
   static constexpr int TILE_N = TILE_RAW > 64 ? 64 : TILE_RAW;
   static constexpr int KV_TILE_BYTES = TILE_N * ROW_BYTES;
@@ -1389,13 +1393,12 @@ inline DeviceInfo& device_info(int dev) {
 }
 
 inline int tile_n_for(int kv_dtype, int head_dim, int nw) {
-  const int stages = nw == 12 ? 2 : 3;
-  const int raw = kAttnRingBytes / (nw * stages) / (2 * head_dim * dtype_size(kv_dtype));
+  const int raw = kAttnStageBytes(nw) / (2 * head_dim * dtype_size(kv_dtype));
   return raw > 64 ? 64 : raw;
 }
 
 // Worker warps per CTA.  One warp per scheduler (4 warps, 16 KB stages) cannot hide its own MMA/ALU
-// latencies.  bf16/f16 K/V is HBM-bound with 8 warps x 3 stages of 8 KB; e4m3 K/V carries twice the
+// latencies.  bf16/f16 K/V is HBM-bound with 8 warps x 2 stages of 8 KB; e4m3 K/V carries twice the
 // tokens per byte plus the widening to f16, and is fastest with 12 warps x 2 stages of 8 KB.
 inline int attn_warps_for(int kv_dtype, int head_dim) {
   static const int forced = [] {
@@ -1480,7 +1483,7 @@ inline int launch_decode_hd(int nw, const CUtensorMap& tmK, const CUtensorMap& t
                             int dev, cudaStream_t stream) {
   if (nw == 12) return launch_decode_variant<KVB, HD, BF16, 12, 2>(tmK, tmV, p, grid, dev, stream);
   if (nw == 4) return launch_decode_variant<KVB, HD, BF16, 4, 3>(tmK, tmV, p, grid, dev, stream);
-  return launch_decode_variant<KVB, HD, BF16, 8, 3>(tmK, tmV, p, grid, dev, stream);
+  return launch_decode_variant<KVB, HD, BF16, 8, 2>(tmK, tmV, p, grid, dev, stream);
 }
 
 template <int KVB, bool BF16>
@@ -1514,7 +1517,7 @@ inline int launch_attn_hd(int nw, const CUtensorMap& tmK, const CUtensorMap& tmV
                           int dev, cudaStream_t stream) {
   if (nw == 12) return launch_attn_variant<KVB, HD, BF16, 12, 2>(tmK, tmV, p, grid, dev, stream);
   if (nw == 4) return launch_attn_variant<KVB, HD, BF16, 4, 3>(tmK, tmV, p, grid, dev, stream);
-  return launch_attn_variant<KVB, HD, BF16, 8, 3>(tmK, tmV, p, grid, dev, stream);
+  return launch_attn_variant<KVB, HD, BF16, 8, 2>(tmK, tmV, p, grid, dev, stream);
 }
 
 template <int KVB, bool BF16>
