@@ -304,7 +304,7 @@ class GpuWorkload:
         for ev in self.in_free:
             ev.record(torch.cuda.current_stream(device))
         self.attn_events: list[tuple[torch.cuda.Event, torch.cuda.Event]] = []
-        self.launches_per_step = 2 + self.layers_n * (7 if self.shared_pages else 4)
+        self.launches_per_step = 2 + self.layers_n * (6 if self.shared_pages else 4)
 
     def _randn(self, *shape):
         x = torch.randn(*shape, generator=self.dg, device=self.device)
