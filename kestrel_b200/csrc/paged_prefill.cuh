@@ -327,11 +327,6 @@ paged_prefill_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
     if (nvalid > BN) nvalid = BN;
     const int nvb = (nvalid + box_rows - 1) >> box_shift;
     const uint32_t full = KV8 ? B_SFULL(s) : B_FULL(s);
-#ifdef KB200_PF_DEBUG_NOTMA   // bottleneck analysis only: hand over empty tiles instead of loading them
-    if (lane == 0) mbar_arrive(full);
-    __syncwarp();
-    return true;
-#endif
     const int slot0 = key0 >> p_shift;
     const bool windowed = boxes_per_tile <= 32;
     if (windowed && (win_base < 0 || slot0 < win_base || slot0 + boxes_per_tile > win_base + 32)) {
@@ -707,7 +702,6 @@ paged_prefill_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
       float ls4[4] = {0.f, 0.f, 0.f, 0.f};   // independent partial row sums
       uint64_t ls2[4] = {0ull, 0ull, 0ull, 0ull};   // the same as packed pairs (bit pattern of 0.f, 0.f)
       const uint64_t sl2x2 = pack_f32x2(sl2, sl2), nmsx2 = pack_f32x2(-ms, -ms);
-#ifndef KB200_PF_DEBUG_NOSOFTMAX   // (defined in bottleneck-analysis builds only: skips the weights)
       // weights as packed 16-bit pairs over the first 64 columns of S_x: the A operand of P V.
       // S is read a second time, 32 columns at a time (keeping all 128 scores live across the
       // exponentials costs more in registers than the second read costs in time); chunk c of P
@@ -744,9 +738,6 @@ paged_prefill_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
         tmem_st16u(p_st + 16u * c, w);
       }
       tc_wait_st();
-#else
-      ls4[0] = mx + ms;
-#endif
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
         float a, b;
