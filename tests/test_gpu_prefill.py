@@ -38,6 +38,19 @@ def test_prefill_chunk_on_a_cached_prefix(dtype, head_dim):
                                                                (100, 8, 1, 128), (33, 2, 3, 64), (130, 1, 2, 128),
                                                                (21, 6, 2, 128)])
 def test_prefill_shapes_and_gqa(seqlen_q, group, heads_kv, head_dim):
+    _shapes_case(seqlen_q, group, heads_kv, head_dim)
+
+
+# packed rows on either side of the switch between the split-KV kernels and the prefill kernel
+# (40 rows with head_dim 128, 56 with head_dim 64)
+@pytest.mark.parametrize("seqlen_q,group,heads_kv,head_dim", [(9, 4, 2, 128), (10, 4, 2, 128), (12, 4, 2, 128), (15, 4, 2, 128),
+                                                               (39, 1, 3, 128), (40, 1, 3, 128), (13, 4, 2, 64), (14, 4, 2, 64),
+                                                               (55, 1, 4, 64), (56, 1, 4, 64), (63, 1, 4, 64)])
+def test_rows_around_the_kernel_switch(seqlen_q, group, heads_kv, head_dim):
+    _shapes_case(seqlen_q, group, heads_kv, head_dim)
+
+
+def _shapes_case(seqlen_q, group, heads_kv, head_dim):
     lengths = [seqlen_q, seqlen_q + 1, seqlen_q + 15, seqlen_q + 113, 3 * seqlen_q + 500, max(1, seqlen_q - 5), 7]
     p = make_paged_problem(seed=12 + seqlen_q, batch=len(lengths), len_lo=0, len_hi=0, n_q_heads=group * heads_kv,
                            n_kv_heads=heads_kv, head_dim=head_dim, page_size=16, seqlen_q=seqlen_q,
