@@ -10,12 +10,12 @@ fails loudly if it is missing.
 
 from .attention import paged_attention
 from .kernels import get_runtime, install_as_kestrel_kernels
-from .kv_cache import (KVMemoryPool, PagedKVCache, PagedKVLayerSpec, PageTable,
+from .kv_cache import (KVMemoryPool, LayerPagedCache, PagedKVCache, PagedKVLayerSpec, PageTable,
                        allocate_paged_kv_layers, copy_kv_pages)
 from .prefix_cache import CacheNamespace, ImageToken, PagedRadixCache, attach_cached_prefix
 
 __all__ = [
-    "KVMemoryPool", "PagedKVCache", "PagedKVLayerSpec", "PageTable", "allocate_paged_kv_layers",
+    "KVMemoryPool", "LayerPagedCache", "PagedKVCache", "PagedKVLayerSpec", "PageTable", "allocate_paged_kv_layers",
     "copy_kv_pages", "paged_attention", "get_runtime", "install_as_kestrel_kernels",
     "PagedRadixCache", "CacheNamespace", "ImageToken", "attach_cached_prefix",
 ]

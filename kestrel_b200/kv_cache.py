@@ -193,6 +193,43 @@ class PagedKVCache(torch.nn.Module):
         return k_val, v_val
 
 
+class LayerPagedCache(torch.nn.Module):
+    """Adapter that wires a :class:`PagedKVCache` into a text block: the shape checks of
+    ``_LayerPagedCache`` (``kestrel/models/moondream/runtime.py:426-481``) in front of ``update``.
+
+    ``pos_ids`` is ``[S]`` or ``[1, S]`` (shared by the batch) or ``[B, S]``; ``k_val`` / ``v_val`` are
+    ``[B, S, H_kv, D]``.  ``rope_update`` is the same adapter in front of the fused rotary + append.
+    """
+
+    def __init__(self, page_table: "PageTable", n_kv_heads: int, head_dim: int, dtype: torch.dtype,
+                 pool: KVMemoryPool, *, k_scale=None, v_scale=None) -> None:
+        super().__init__()
+        self.cache = PagedKVCache(page_table, n_heads=n_kv_heads, head_dim=head_dim, dtype=dtype, pool=pool,
+                                  k_scale=k_scale, v_scale=v_scale)
+
+    @staticmethod
+    def _positions(pos_ids: torch.Tensor, k_val: torch.Tensor, v_val: torch.Tensor) -> torch.Tensor:
+        if k_val.shape != v_val.shape:
+            raise ValueError("k_val and v_val must match shape")
+        input_pos = torch.atleast_2d(pos_ids)
+        if input_pos.device != k_val.device:
+            input_pos = input_pos.to(device=k_val.device)
+        if input_pos.shape[0] != 1 and input_pos.shape[0] != k_val.shape[0]:
+            raise ValueError(f"Unsupported position shape {pos_ids.shape} for batch size {k_val.shape[0]}")
+        if k_val.shape[1] != input_pos.shape[1]:
+            raise ValueError(f"KV sequence length {k_val.shape[1]} does not match position tensor {input_pos.shape}")
+        return input_pos
+
+    def update(self, pos_ids: torch.Tensor, k_val: torch.Tensor, v_val: torch.Tensor, *, slot_mapping: torch.Tensor):
+        input_pos = self._positions(pos_ids, k_val, v_val)
+        return self.cache.update(input_pos=input_pos, k_val=k_val, v_val=v_val, slot_mapping=slot_mapping)
+
+    def rope_update(self, pos_ids: torch.Tensor, q: torch.Tensor, k_val: torch.Tensor, v_val: torch.Tensor,
+                    cos_sin_cache: torch.Tensor, *, slot_mapping: torch.Tensor, **kwargs):
+        input_pos = self._positions(pos_ids, k_val, v_val)
+        return self.cache.rope_update(input_pos, q, k_val, v_val, cos_sin_cache, slot_mapping=slot_mapping, **kwargs)
+
+
 @dataclass(frozen=True, slots=True)
 class PagedKVLayerSpec:
     """Physical storage shape for one paged-attention producer layer."""

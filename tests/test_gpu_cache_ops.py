@@ -10,7 +10,7 @@ import torch
 
 from helpers import from_np
 from kestrel_b200 import _native, kernels
-from kestrel_b200.kv_cache import KVMemoryPool, PagedKVCache, PageTable, copy_kv_pages
+from kestrel_b200.kv_cache import KVMemoryPool, LayerPagedCache, PagedKVCache, PageTable, copy_kv_pages
 from oracle import paged_kv_oracle as O
 
 pytestmark = pytest.mark.gpu
@@ -254,3 +254,29 @@ def test_cow_through_page_table_then_private_append():
     assert torch.equal(layer.k_cache[src], before)
     assert torch.equal(layer.k_cache[dst][:, :9], before[:, :9])
     assert (layer.k_cache[dst][:, 9] == 3.0).all()
+
+
+@pytest.mark.parametrize("B,pos_1d", [(1, True), (3, False)])
+def test_layer_cache_adapter_appends_like_the_cache_itself(B, pos_1d):
+    """LayerPagedCache.update (the adapter of kestrel/models/moondream/runtime.py:426-481): positions given as
+    [S] (one sequence) or as [B, S]; the pool bytes equal the oracle's append."""
+    S, H, D, P = 5, 4, 64, 16
+    pt = PageTable(n_pages=32, page_size=P, max_batch_size=B + 1, device=DEV)
+    rows = [pt.allocate() for _ in range(B)]
+    for r in rows:
+        pt.reserve(r, 40)
+    pt.commit_block_table()
+    layer = LayerPagedCache(pt, n_kv_heads=H, head_dim=D, dtype=torch.bfloat16, pool=KVMemoryPool(device=DEV))
+    g = torch.Generator().manual_seed(5)
+    k = torch.randn(B, S, H, D, generator=g).to(torch.bfloat16)
+    v = torch.randn(B, S, H, D, generator=g).to(torch.bfloat16)
+    pos = torch.arange(7, 7 + S)
+    pos_b = pos.expand(B, S).contiguous()
+    slots = pt.build_slot_mapping(torch.tensor(rows, device=DEV).view(B, 1).expand(B, S).contiguous(), pos_b.to(DEV))
+    got_k, got_v = layer.update(pos.to(DEV) if pos_1d else pos_b.to(DEV), k.to(DEV), v.to(DEV), slot_mapping=slots)
+    want_k = torch.zeros(32, H, P, D, dtype=torch.bfloat16)
+    want_v = torch.zeros_like(want_k)
+    O.append(want_k, want_v, k.reshape(B * S, H, D), v.reshape(B * S, H, D), slots.cpu().reshape(-1))
+    assert torch.equal(_bits(layer.cache.k_cache.cpu()), _bits(want_k))
+    assert torch.equal(_bits(layer.cache.v_cache.cpu()), _bits(want_v))
+    assert got_k.shape == k.shape and got_v.shape == v.shape

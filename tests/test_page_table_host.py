@@ -8,7 +8,7 @@ import threading
 import pytest
 import torch
 
-from kestrel_b200.kv_cache import (KVMemoryPool, PagedKVCache, PagedKVLayerSpec, PageTable,
+from kestrel_b200.kv_cache import (KVMemoryPool, LayerPagedCache, PagedKVCache, PagedKVLayerSpec, PageTable,
                                    _flatten_bshd_tokens, allocate_paged_kv_layers)
 
 
@@ -288,3 +288,22 @@ def test_common_prefix_pages_counts_the_shared_leading_pages():
     pt.reserve(a, 400)
     pt.reserve(b, 400)
     assert pt.common_prefix_pages([a, b]) == 7
+
+
+def test_layer_cache_adapter_checks_shapes_before_the_append():
+    """The checks of _LayerPagedCache.update (kestrel/models/moondream/runtime.py:451-481), on CPU tensors:
+    they fire before any kernel is reached."""
+    pt = PageTable(n_pages=8, page_size=4, max_batch_size=2, device="cpu")
+    layer = LayerPagedCache(pt, n_kv_heads=2, head_dim=8, dtype=torch.float32, pool=KVMemoryPool(device="cpu"))
+    assert layer.cache.k_cache.shape == (8, 2, 4, 8)
+    k = torch.zeros(2, 3, 2, 8)
+    slots = torch.zeros(2, 3, dtype=torch.int64)
+    with pytest.raises(ValueError, match="k_val and v_val must match shape"):
+        layer.update(torch.arange(3), k, torch.zeros(2, 3, 2, 4), slot_mapping=slots)
+    with pytest.raises(ValueError, match="Unsupported position shape"):
+        layer.update(torch.zeros(3, 3, dtype=torch.int64), k, k, slot_mapping=slots)
+    with pytest.raises(ValueError, match="does not match position tensor"):
+        layer.update(torch.arange(4), k, k, slot_mapping=slots)
+    # well-formed arguments get as far as the kernel, which refuses CPU tensors (no fallback)
+    with pytest.raises(RuntimeError, match="no CPU fallback"):
+        layer.update(torch.arange(3).expand(2, 3), k, k, slot_mapping=slots)
