@@ -12,11 +12,13 @@ from .attention import paged_attention
 from .kernels import get_runtime, install_as_kestrel_kernels
 from .kv_cache import (KVMemoryPool, LayerPagedCache, PagedKVCache, PagedKVLayerSpec, PageTable,
                        allocate_paged_kv_layers, copy_kv_pages)
-from .prefix_cache import CacheNamespace, ImageToken, PagedRadixCache, attach_cached_prefix
+from .prefix_cache import (CacheNamespace, ImageToken, PagedRadixCache, SequenceCacheState, attach_cached_prefix,
+                           finalize_cached_prompt, release_cached_sequence, retain_generated_prefix)
 
 __all__ = [
     "KVMemoryPool", "LayerPagedCache", "PagedKVCache", "PagedKVLayerSpec", "PageTable", "allocate_paged_kv_layers",
     "copy_kv_pages", "paged_attention", "get_runtime", "install_as_kestrel_kernels",
-    "PagedRadixCache", "CacheNamespace", "ImageToken", "attach_cached_prefix",
+    "PagedRadixCache", "CacheNamespace", "ImageToken", "attach_cached_prefix", "SequenceCacheState",
+    "finalize_cached_prompt", "retain_generated_prefix", "release_cached_sequence",
 ]
 __version__ = "0.1.0"

@@ -406,3 +406,77 @@ def attach_cached_prefix(page_table, cache: PagedRadixCache, batch_idx: int, tok
         page_table.cow_page(batch_idx, n_full)
     cache.lock_prefill(match.last_node)
     return skip, n_full, match
+
+
+@dataclass(slots=True)
+class SequenceCacheState:
+    """What a running sequence holds of the cache (the ``cache_lock_node`` / ``cache_owned_page_count``
+    fields of the reference's ``SequenceState``): the node it keeps locked and how many leading pages of
+    its page-table row belong to the tree (``PageTable.erase`` must leave those alone)."""
+    lock_node: TreeNode | None = None
+    cache_owned_page_count: int = 0
+    cache_owned_kv_length: int = 0
+
+
+def finalize_cached_prompt(page_table, cache: PagedRadixCache, batch_idx: int, tokens: list, prompt_kv_len: int,
+                           skip: int, shared_page_count: int, match: MatchResult,
+                           namespace: CacheNamespace | None = None) -> SequenceCacheState:
+    """After the prompt was prefilled: hand its KV to the cache and turn the prefill lock taken by
+    :func:`attach_cached_prefix` into the sequence's lock
+    (``_finalize_cache_after_prefill``, ``kestrel/models/moondream/runtime.py:1745-1815``).
+
+    * whole prompt already cached: nothing to insert, the matched node stays locked;
+    * insert refused or redundant (another sequence was first, or the row does not sit on the tree's
+      pages): keep the lock on the matched node, the row's own pages stay private;
+    * otherwise lock the new node and release the prefill lock; the row's pages up to the end of the
+      prompt now belong to the tree.
+    """
+    if not tokens:
+        return SequenceCacheState()
+    temp = match.last_node if skip > 0 else None
+    if temp is not None and match.matched_kv_length >= prompt_kv_len:
+        cache.lock(temp)
+        cache.unlock_prefill(temp)
+        return SequenceCacheState(temp, shared_page_count, skip)
+    n_pages = -(-prompt_kv_len // page_table.page_size)
+    result = cache.insert(tokens, page_table.get_pages(batch_idx, 0, n_pages), namespace)
+    if result.inserted_pages == 0:
+        if temp is None:
+            return SequenceCacheState()
+        cache.lock(temp)
+        cache.unlock_prefill(temp)
+        return SequenceCacheState(temp, shared_page_count, skip)
+    cache.lock(result.node)
+    if temp is not None:
+        cache.unlock_prefill(temp)
+    return SequenceCacheState(result.node, shared_page_count + result.inserted_pages, prompt_kv_len)
+
+
+def retain_generated_prefix(page_table, cache: PagedRadixCache, batch_idx: int, state: SequenceCacheState,
+                            tokens: list, total_kv_len: int, namespace: CacheNamespace | None = None) -> None:
+    """Make decoded KV eligible for reuse: insert prompt + generated tokens (``tokens``, ``total_kv_len``
+    positions, all already in the row's pages) and move the sequence's lock to the new node
+    (``retain_sequence_prefix``, ``kestrel/models/moondream/runtime.py:2192-2238``).  When the token path
+    already exists on other physical pages nothing is inserted and the row's pages stay private."""
+    if not tokens or total_kv_len <= state.cache_owned_kv_length:
+        return
+    n_pages = -(-total_kv_len // page_table.page_size)
+    result = cache.insert(tokens, page_table.get_pages(batch_idx, 0, n_pages), namespace)
+    if result.inserted_pages == 0:
+        return
+    if result.node is not state.lock_node:
+        cache.lock(result.node)
+        cache.unlock(state.lock_node)
+        state.lock_node = result.node
+    state.cache_owned_page_count = n_pages
+    state.cache_owned_kv_length = total_kv_len
+
+
+def release_cached_sequence(page_table, cache: PagedRadixCache | None, batch_idx: int,
+                            state: SequenceCacheState) -> None:
+    """End of a sequence: one unlock of its node, then the row goes back; pages the tree owns stay
+    allocated (``release_sequence``, ``kestrel/models/moondream/runtime.py:2240-2253``)."""
+    if cache is not None and state.lock_node is not None:
+        cache.unlock(state.lock_node)
+        state.lock_node = None
+    page_table.erase(batch_idx, state.cache_owned_page_count)

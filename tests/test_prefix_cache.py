@@ -7,7 +7,8 @@ import json
 import pytest
 
 from kestrel_b200.kv_cache import PageTable
-from kestrel_b200.prefix_cache import (CacheNamespace, ImageToken, PagedRadixCache, attach_cached_prefix)
+from kestrel_b200.prefix_cache import (CacheNamespace, ImageToken, PagedRadixCache, attach_cached_prefix,
+                                       finalize_cached_prompt, release_cached_sequence, retain_generated_prefix)
 
 
 class Tok:
@@ -199,3 +200,86 @@ def test_attach_cached_prefix_maps_shared_pages_and_queues_cow():
     assert pt.can_reserve_with_eviction(190 * P, big)
     assert pt.reserve(big, 190 * P)
     assert cache.total_cached_pages < 50
+
+
+@pytest.mark.parametrize("P", [1, 16])
+def test_sequence_lifecycle_lookup_finalize_retain_release(P):
+    """The runtime policy around the cache (kestrel/models/moondream/runtime.py:1572-1623, 1745-1815,
+    2192-2253): miss -> insert and lock; hit -> prefill lock becomes the sequence's lock; generated tokens
+    are retained; release unlocks once and frees only private pages."""
+    cache = PagedRadixCache(page_size=P)
+    pt = PageTable(n_pages=4096 if P == 1 else 400, page_size=P, max_batch_size=6, device="cpu", prefix_cache=cache)
+    pages_for = lambda n: -(-n // P)
+    image = [ImageToken(content_hash=9, kv_length_=729)]
+    free0 = pt.pages_available
+
+    # --- request 1: miss
+    r1 = pt.allocate()
+    prompt1 = image + toks(*range(100, 120))                     # 749 positions
+    skip, shared, match = attach_cached_prefix(pt, cache, r1, prompt1, 749)
+    assert (skip, shared) == (0, 0)
+    pt.reserve(r1, 749 + 8)
+    s1 = finalize_cached_prompt(pt, cache, r1, prompt1, 749, skip, shared, match)
+    assert s1.lock_node is not None and s1.cache_owned_page_count == pages_for(749) and s1.lock_node.lock_ref == 1
+    assert cache.evictable_page_count() == 0                     # locked: nothing can be evicted
+
+    # --- request 2: same prompt completely cached (skip capped at prompt - 1)
+    r2 = pt.allocate()
+    skip, shared, match = attach_cached_prefix(pt, cache, r2, prompt1, 749)
+    assert skip == 748 and match.last_node.prefill_lock_ref == 1
+    pt.take_pending_page_copies()
+    pt.reserve(r2, 749 + 8)
+    s2 = finalize_cached_prompt(pt, cache, r2, prompt1, 749, skip, shared, match)
+    assert s2.lock_node is s1.lock_node and s2.cache_owned_page_count == shared
+    assert s2.lock_node.lock_ref == 2 and s2.lock_node.prefill_lock_ref == 0
+
+    # --- request 3: shares the image only; its suffix is inserted below the image node
+    r3 = pt.allocate()
+    prompt3 = image + toks(*range(200, 230))                     # 759 positions
+    skip, shared, match = attach_cached_prefix(pt, cache, r3, prompt3, 759)
+    assert skip == 729 and shared == 729 // P
+    pt.take_pending_page_copies()
+    pt.reserve(r3, 759 + 8)
+    s3 = finalize_cached_prompt(pt, cache, r3, prompt3, 759, skip, shared, match)
+    assert s3.lock_node is not s1.lock_node and s3.cache_owned_page_count == pages_for(759)
+    assert match.last_node.prefill_lock_ref == 0
+
+    # --- request 1 decodes 5 tokens and retains them
+    gen = toks(*range(900, 905))
+    retain_generated_prefix(pt, cache, r1, s1, prompt1 + gen, 749 + 5)
+    assert s1.cache_owned_page_count == pages_for(754) and s1.cache_owned_kv_length == 754
+    assert s1.lock_node is not s2.lock_node and s2.lock_node.lock_ref == 2   # ancestors stay locked through r1's new node
+    retain_generated_prefix(pt, cache, r1, s1, prompt1 + gen, 749 + 5)        # nothing new: no change
+    assert s1.cache_owned_kv_length == 754
+    m = cache.match_prefix(prompt1 + gen)
+    assert m.matched_kv_length == 754
+
+    # --- releases: private pages come back, cache-owned ones stay with the tree
+    for r, st in ((r1, s1), (r2, s2), (r3, s3)):
+        release_cached_sequence(pt, cache, r, st)
+        assert st.lock_node is None
+    assert cache.evictable_page_count() > 0 and cache.reclaimable_page_count() == cache.total_cached_pages
+    assert pt.pages_available == free0 - cache.total_cached_pages
+    freed = cache.evict(10 ** 6)
+    assert freed > 0 and cache.total_cached_pages == 0 and pt.pages_available == free0
+
+
+def test_finalize_keeps_pages_private_when_the_row_is_not_on_the_trees_pages():
+    # a second sequence prefilled the same prompt on its own pages (no lookup): the insert is refused
+    P = 16
+    cache = PagedRadixCache(page_size=P)
+    pt = PageTable(n_pages=200, page_size=P, max_batch_size=4, device="cpu", prefix_cache=cache)
+    prompt = toks(*range(40))
+    states = []
+    for _ in range(2):
+        r = pt.allocate()
+        pt.reserve(r, 48)
+        empty = cache.match_prefix([])
+        states.append((r, finalize_cached_prompt(pt, cache, r, prompt, 40, 0, 0, empty)))
+    (ra, sa), (rb, sb) = states
+    assert sa.cache_owned_page_count == 3 and sb.lock_node is None and sb.cache_owned_page_count == 0
+    free_before = pt.pages_available
+    release_cached_sequence(pt, cache, rb, sb)
+    assert pt.pages_available == free_before + 3          # all of its pages were private
+    release_cached_sequence(pt, cache, ra, sa)
+    assert pt.pages_available == free_before + 3          # the tree keeps the first sequence's pages
