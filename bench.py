@@ -874,13 +874,104 @@ def run_reference_arm(args) -> None:
     print(json.dumps(line), flush=True)
 
 
+# ----------------------------------------------------------------------------------------------
+# yardstick arm: a library kernel on the same pools (not the reference, not on any product path)
+# ----------------------------------------------------------------------------------------------
+
+def _timed(fn, reps: int, device) -> float:
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize(device)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize(device)
+    return e0.elapsed_time(e1) / reps
+
+
+def _page_lists(rows_pages, lengths, device):
+    """flashinfer's CSR description of the page lists: indptr, indices, tokens in the last page."""
+    indptr, indices = [0], []
+    for pages, L in zip(rows_pages, lengths):
+        n = -(-int(L) // PAGE)
+        indices.extend(pages[:n])
+        indptr.append(len(indices))
+    last = [(int(L) - 1) % PAGE + 1 for L in lengths]
+    t = lambda x: torch.tensor(x, dtype=torch.int32, device=device)
+    return t(indptr), t(indices), t(last)
+
+
+def run_yardstick(args) -> None:
+    """``--impl flashinfer``: the image's flashinfer paged attention (decode or prefill wrapper, HND layout)
+    timed on the pools, page lists and queries of our arm, attention calls only, next to ours.  One GPU."""
+    import flashinfer
+    from kestrel_b200 import _native
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    ws = torch.empty(512 << 20, dtype=torch.uint8, device=device)
+    if args.workload in PREFILL_WORKLOADS:
+        wl = PrefillWorkload(args.workload, device, 0)
+        if wl.cache.quantized:
+            raise SystemExit("the prefill yardstick covers the 16-bit workloads")
+        wl.step_device()                                   # fills the pools with the chunks' K/V
+        ours_ms = _timed(lambda: wl.step_device(attn_only=True), max(3, args.steps), device)
+        calls = []
+        for ps in wl.passes:
+            lens = ps["seqused_k"].tolist()
+            indptr, indices, last = _page_lists(ps["page_table"].tolist(), lens, device)
+            w = flashinfer.BatchPrefillWithPagedKVCacheWrapper(ws, "HND")
+            w.plan(ps["cu"], indptr, indices, last, HQ, HKV, wl.D, PAGE, causal=True,
+                   q_data_type=torch.bfloat16, kv_data_type=torch.bfloat16)
+            q = ps["qkv"][:, :HQ * wl.D].unflatten(-1, (HQ, wl.D)).contiguous()
+            calls.append((w, q))
+        kv = (wl.cache.k_cache, wl.cache.v_cache)
+        their_ms = _timed(lambda: [w.run(q, kv) for w, q in calls], max(3, args.steps), device)
+        work, unit = wl.flops / 1e12, "TFLOP/s"
+        per = "all attention calls of a step"
+    else:
+        wl = GpuWorkload(args.workload, device, 0, args.warmup + 6, share_prefix=False)
+        for _ in range(max(1, args.warmup)):
+            wl.step_device()
+        ours_ms = wl.time_attention_launch(max(3, args.steps))
+        lens = wl.lengths_after(wl.step_no - 1).tolist()
+        indptr, indices, last = _page_lists([wl.pt.page_table_cpu[r] for r in wl.rows], lens, device)
+        cache = wl.caches[0]
+        fp8 = cache.quantized
+        kw = dict(k_scale=float(cache.k_scale_tensor.view(-1)[0]), v_scale=float(cache.v_scale_tensor.view(-1)[0])) if fp8 else {}
+        kv = (cache.k_cache, cache.v_cache)
+        if wl.sq == 1:
+            w = flashinfer.BatchDecodeWithPagedKVCacheWrapper(ws, "HND", use_tensor_cores=True)
+            w.plan(indptr, indices, last, HQ, HKV, wl.D, PAGE, q_data_type=torch.bfloat16, kv_data_type=cache.k_cache.dtype)
+            q = wl.q[0].view(wl.B, HQ, wl.D)
+        else:
+            w = flashinfer.BatchPrefillWithPagedKVCacheWrapper(ws, "HND")
+            qo = torch.arange(0, (wl.B + 1) * wl.sq, wl.sq, dtype=torch.int32, device=device)
+            w.plan(qo, indptr, indices, last, HQ, HKV, wl.D, PAGE, causal=True, q_data_type=torch.bfloat16,
+                   kv_data_type=cache.k_cache.dtype)
+            q = wl.q[0].view(wl.B * wl.sq, HQ, wl.D)
+        their_ms = _timed(lambda: w.run(q, kv, **kw), max(3, args.steps), device)
+        work = algorithmic_bytes(wl.lengths_after(wl.step_no - 1), layers=wl.layers_n, kv_bytes=wl.kv_bytes,
+                                 head_dim=wl.D, sq=wl.sq, batch=wl.B)["attn_per_launch"] / 1e9
+        unit, per = "GB/s", "one attention call (one layer)"
+    flags = _native.device_status(0, clear=True)
+    print(json.dumps({
+        "impl": "flashinfer", "version": flashinfer.__version__, "metric": f"paged attention, {per}",
+        "value": work / (their_ms * 1e-3), "unit": unit, "ms": their_ms,
+        "ours": {"value": work / (ours_ms * 1e-3), "unit": unit, "ms": ours_ms},
+        "n_gpus": 1, "config": {"workload": args.workload}, "device_status": list(flags),
+        "note": "library kernel as a yardstick on the same pools and page lists; not the reference implementation",
+    }), flush=True)
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--workload", default="cfg3", choices=sorted(WORKLOADS) + sorted(PREFILL_WORKLOADS))
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "flashinfer"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="launch the timed steps eagerly instead of replaying a CUDA graph")
@@ -889,6 +980,9 @@ def main() -> None:
     ap.add_argument("--batch", type=int, default=0, help="override the workload's batch (profiling on a small case)")
     ap.add_argument("--layers", type=int, default=0, help="override the workload's layer count (profiling)")
     args = ap.parse_args()
+    if args.impl == "flashinfer":
+        run_yardstick(args)
+        return
     if args.workload in PREFILL_WORKLOADS:
         run_prefill(args)
         return
