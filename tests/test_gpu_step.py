@@ -57,7 +57,7 @@ class Stack:
     def rand(self, *shape):
         return torch.randn(*shape, generator=self.g).to(self.dtype)
 
-    def step(self, rows, positions):
+    def step(self, rows, positions, shared_prefix_pages=0):
         """Append ``positions [B, S]`` new tokens for page-table rows ``rows`` and attend; returns max error."""
         B, S = positions.shape
         self.pt.commit_block_table(rows)
@@ -82,7 +82,8 @@ class Stack:
             v = v.view(B, S, self.hkv, self.dim)
             layer.update(pos_dev, k, v, slot_mapping=slots)
             out = paged_attention(q.transpose(1, 2), paged_kv_layer=layer, page_table=self.meta_pt[:B],
-                                  paged_kv_seqlens_k=self.meta_sk[:B], scaling=1.0 / math.sqrt(self.dim))
+                                  paged_kv_seqlens_k=self.meta_sk[:B], scaling=1.0 / math.sqrt(self.dim),
+                                  shared_prefix_pages=shared_prefix_pages)
             ks, vs = self.scales[l]
             O.append(self.mk[l], self.mv[l], k.cpu().reshape(B * S, self.hkv, self.dim),
                      v.cpu().reshape(B * S, self.hkv, self.dim), slots_ref, k_scale=ks, v_scale=vs)
@@ -164,7 +165,7 @@ def test_config4_shape_shared_prefix_with_cow():
     the same appends, so pool contents must match bit for bit and attention within tolerance."""
     from kestrel_b200.prefix_cache import ImageToken, PagedRadixCache, attach_cached_prefix
 
-    n_req, P, hq, hkv, D = 12, 16, 32, 8, 64
+    n_req, P, hq, hkv, D = 20, 16, 32, 8, 64
     prefix = 729
     cache = PagedRadixCache(page_size=P)
     st = Stack(n_layers=2, n_pages=900, page_size=P, max_batch=n_req + 2, hq=hq, hkv=hkv, dim=D, dtype=torch.bfloat16,
@@ -212,6 +213,12 @@ def test_config4_shape_shared_prefix_with_cow():
                 O.append(st.mk[l], st.mv[l], k.cpu()[0], v.cpu()[0], slots_ref)
     for step in range(3):
         st.step(rows, torch.tensor([[prefix + s + step] for s in suffix]))
+    # the same steps with the shared pages read once for the whole batch: the scheduler asks the page
+    # table which leading pages all rows map alike
+    n_common = st.pt.common_prefix_pages(rows, min_tokens=prefix + min(suffix))
+    assert n_common == 45
+    for step in range(3, 5):
+        st.step(rows, torch.tensor([[prefix + s + step] for s in suffix]), shared_prefix_pages=n_common)
     st.check_pools_bit_exact()
     # the shared pages were never written after the prefix was stored
     for r in rows:
