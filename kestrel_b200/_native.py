@@ -7,12 +7,10 @@ different ABI version, or a call fails, the caller gets an exception.
 from __future__ import annotations
 
 import ctypes as C
-import os
 import threading
 from pathlib import Path
 
-# KB200_LIBRARY selects another build of the same ABI (A/B comparisons of kernel variants).
-LIB_PATH = Path(os.environ.get("KB200_LIBRARY") or Path(__file__).resolve().parent / "libkestrel_b200.so")
+LIB_PATH = Path(__file__).resolve().parent / "libkestrel_b200.so"
 ABI_VERSION = 3
 
 DTYPE_F32, DTYPE_F16, DTYPE_BF16, DTYPE_E4M3 = 0, 1, 2, 3

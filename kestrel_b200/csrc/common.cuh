@@ -10,6 +10,7 @@
 #include <stdio.h>
 #include <stdarg.h>
 #include <stdlib.h>
+#include <mutex>
 
 #include "../../include/kestrel_b200.h"
 
@@ -92,18 +93,9 @@ __device__ __forceinline__ void report(int bit, int value, int kernel_id) {
 // programmatic-stream-serialization attribute and calls pdl_wait() before it touches global
 // memory, so its launch latency and shared-memory prologue overlap the tail of the kernel
 // before it; results are unchanged because nothing is read or written before the wait.
-// KB200_PDL=0 in the environment turns the attribute off.
 // ---------------------------------------------------------------------------
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
-
-inline bool pdl_enabled() {
-  static const bool on = [] {
-    const char* e = getenv("KB200_PDL");
-    return !(e && e[0] == '0');
-  }();
-  return on;
-}
 
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
@@ -115,11 +107,29 @@ inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
+
+// cudaFuncSetAttribute(MaxDynamicSharedMemorySize) once per (kernel, device), safe under concurrent
+// first calls from several threads.
+struct SmemAttrOnce {
+  std::once_flag flags[64];
+  cudaError_t results[64] = {};
+  template <typename K>
+  int ensure(K kernel, int smem_bytes, int dev) {
+    const int i = dev & 63;
+    std::call_once(flags[i], [&] {
+      results[i] = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+    });
+    if (results[i] != cudaSuccess)
+      return fail(KB200_ERR_CUDA, "cudaFuncSetAttribute(max dynamic shared memory) failed: %s",
+                  cudaGetErrorString(results[i]));
+    return KB200_OK;
+  }
+};
 
 enum KernelId : int {
   KID_APPEND = 1,

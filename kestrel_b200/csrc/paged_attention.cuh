@@ -31,6 +31,7 @@
 //   normalisation.  Softmax is the usual online form in fp32, base 2.
 #pragma once
 
+#include <algorithm>
 #include <cstdlib>
 #include <type_traits>
 #include <mutex>
@@ -45,11 +46,11 @@ constexpr int kAttnMaxWarps = 12;
 constexpr int kRowsPerSeg = 16;   // query rows per segment, general kernel (also the stride of scratch slots)
 constexpr int kDecodeRows = 8;    // query rows per segment, decode kernel
 // NW worker warps per CTA, each with a ring of NS stages of kAttnStageBytes(NW) (K tile then V tile).
-// Stages are 8 KB with 8 or 12 warps (two of them per warp: one being read, one in flight) and 16 KB with 4.
+// Stages are 8 KB (two of them per warp: one being read, one in flight).
 // More bytes in flight do not help: 8 warps x 3 stages (128 KB behind the tiles being read) measured
 // 3-5 % slower than x 2 (64 KB) once the kernel is HBM-bound; the requests queue up in the memory system and
 // the SMs' shares of the bandwidth grow apart.
-constexpr int kAttnStageBytes(int nw) { return nw == 4 ? 16 * 1024 : 8 * 1024; }
+constexpr int kAttnStageBytes(int) { return 8 * 1024; }
 
 template <int KVB, int HD, int NW, int NS>
 struct AttnTile {
@@ -1401,12 +1402,6 @@ inline int tile_n_for(int kv_dtype, int head_dim, int nw) {
 // latencies.  bf16/f16 K/V is HBM-bound with 8 warps x 2 stages of 8 KB; e4m3 K/V carries twice the
 // tokens per byte plus the widening to f16, and is fastest with 12 warps x 2 stages of 8 KB.
 inline int attn_warps_for(int kv_dtype, int head_dim) {
-  static const int forced = [] {
-    const char* e = getenv("KB200_ATTN_WARPS");
-    const int v = e ? atoi(e) : 0;
-    return (v == 4 || v == 8 || v == 12) ? v : 0;
-  }();
-  if (forced) return forced;
   (void)head_dim;
   return kv_dtype == KB200_DTYPE_E4M3 ? 12 : 8;
 }
@@ -1455,11 +1450,8 @@ inline int launch_attn_variant(const CUtensorMap& tmK, const CUtensorMap& tmV, c
                                int dev, cudaStream_t stream) {
   using T = AttnTile<KVB, HD, NW, NS>;
   auto kern = paged_attn_kernel<KVB, HD, BF16, NW, NS>;
-  static bool done[64] = {};
-  if (!done[dev & 63]) {
-    KB200_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM_BYTES));
-    done[dev & 63] = true;
-  }
+  static SmemAttrOnce once;
+  if (int rc = once.ensure(kern, T::SMEM_BYTES, dev)) return rc;
   KB200_CUDA_OK(launch_kernel(kern, dim3(grid), dim3(NW * 32), T::SMEM_BYTES, stream, tmK, tmV, p));
   return KB200_OK;
 }
@@ -1469,11 +1461,8 @@ inline int launch_decode_variant(const CUtensorMap& tmK, const CUtensorMap& tmV,
                                  int dev, cudaStream_t stream) {
   using T = AttnTile<KVB, HD, NW, NS>;
   auto kern = paged_attn_decode_kernel<KVB, HD, BF16, NW, NS>;
-  static bool done[64] = {};
-  if (!done[dev & 63]) {
-    KB200_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM_BYTES));
-    done[dev & 63] = true;
-  }
+  static SmemAttrOnce once;
+  if (int rc = once.ensure(kern, T::SMEM_BYTES, dev)) return rc;
   KB200_CUDA_OK(launch_kernel(kern, dim3(grid), dim3(NW * 32), T::SMEM_BYTES, stream, tmK, tmV, p));
   return KB200_OK;
 }
@@ -1482,7 +1471,6 @@ template <int KVB, bool BF16, int HD>
 inline int launch_decode_hd(int nw, const CUtensorMap& tmK, const CUtensorMap& tmV, const AttnParams& p, int grid,
                             int dev, cudaStream_t stream) {
   if (nw == 12) return launch_decode_variant<KVB, HD, BF16, 12, 2>(tmK, tmV, p, grid, dev, stream);
-  if (nw == 4) return launch_decode_variant<KVB, HD, BF16, 4, 3>(tmK, tmV, p, grid, dev, stream);
   return launch_decode_variant<KVB, HD, BF16, 8, 2>(tmK, tmV, p, grid, dev, stream);
 }
 
@@ -1493,30 +1481,10 @@ inline int launch_decode_dispatch(bool d128, int nw, const CUtensorMap& tmK, con
               : launch_decode_hd<KVB, BF16, 64>(nw, tmK, tmV, p, grid, dev, stream);
 }
 
-// KB200_MERGED_BOXES=0 keeps one TMA box per 128-byte half (for A/B checks).
-inline bool merged_boxes_enabled() {
-  static const bool on = [] {
-    const char* e = getenv("KB200_MERGED_BOXES");
-    return !(e && e[0] == '0');
-  }();
-  return on;
-}
-
-// Segments of up to 8 query rows run the transposed decode kernel; KB200_DECODE8=0 forces the
-// general 16-row kernel (for A/B checks).
-inline bool decode8_enabled() {
-  static const bool on = [] {
-    const char* e = getenv("KB200_DECODE8");
-    return !(e && e[0] == '0');
-  }();
-  return on;
-}
-
 template <int KVB, bool BF16, int HD>
 inline int launch_attn_hd(int nw, const CUtensorMap& tmK, const CUtensorMap& tmV, const AttnParams& p, int grid,
                           int dev, cudaStream_t stream) {
   if (nw == 12) return launch_attn_variant<KVB, HD, BF16, 12, 2>(tmK, tmV, p, grid, dev, stream);
-  if (nw == 4) return launch_attn_variant<KVB, HD, BF16, 4, 3>(tmK, tmV, p, grid, dev, stream);
   return launch_attn_variant<KVB, HD, BF16, 8, 2>(tmK, tmV, p, grid, dev, stream);
 }
 
@@ -1536,23 +1504,20 @@ constexpr int kPrefillRowsPerSeg = 256, kPrefillTileKeys = 128, kPrefillMinPacke
 // Packed query rows per sequence from which the prefill kernel serves a call.  The split-KV kernels
 // read a sequence's K/V once per 16 rows, the prefill kernel once per 256 but with a fixed cost per
 // CTA: measured break-even at 32 rows for head_dim 128 (4096 keys) and near 56 for head_dim 64
-// (729 keys).  KB200_PREFILL_MIN_ROWS overrides, for A/B checks.
-inline int prefill_min_rows(int head_dim) {
-  static const int forced = [] {
-    const char* e = getenv("KB200_PREFILL_MIN_ROWS");
-    const int n = e ? atoi(e) : 0;
-    return n > 0 ? n : 0;
-  }();
-  if (forced) return forced;
-  return head_dim == 128 ? 40 : 56;
-}
+// (729 keys).
+inline int prefill_min_rows(int head_dim) { return head_dim == 128 ? 40 : 56; }
 
 // Which kernel serves a call: many query rows per sequence with 16-bit K/V (or a block mask) go to
 // the tensor-memory prefill kernel, one CTA per 256 packed rows, no split over keys and no merge.
 inline bool use_prefill_kernel(const kb200_attn_args* a) {
   if (a->q_visible_until != nullptr) return true;
   if (!prefill_enabled() || a->n_kv_heads <= 0) return false;
-  return (int64_t)(a->n_q_heads / a->n_kv_heads) * a->seqlen_q >= prefill_min_rows(a->head_dim);
+  // Packed rows: seqlen_q is only an upper bound (the reference's packed call passes none at all,
+  // kestrel/ops/attention.py:69-86, and the shim then sets it to total_q); the mean rows per
+  // sequence says which kernel has less work.
+  int64_t rows = a->seqlen_q;
+  if (a->cu_seqlens_q && a->batch > 0) rows = std::min<int64_t>(rows, (a->total_q + a->batch - 1) / a->batch);
+  return (int64_t)(a->n_q_heads / a->n_kv_heads) * rows >= prefill_min_rows(a->head_dim);
 }
 
 // Scratch bytes this very call needs: the plan arrays, plus the split-KV partials unless the prefill
@@ -1785,6 +1750,10 @@ inline int launch_attention_pass(const kb200_attn_args* a, int k_skip, int fixed
   if (P <= 0 || P > 256 || (P & (P - 1)) != 0)
     return fail(KB200_ERR_UNSUPPORTED, "page_size %d is not supported (power of two, at most 256)", P);
   KB200_REQUIRE(a->seqlen_q > 0 && a->total_q > 0, "seqlen_q and total_q must be positive");
+  // the scratch is sized from total_q: it must describe the rows the kernels will visit
+  KB200_REQUIRE(a->cu_seqlens_q != nullptr || a->total_q == a->batch * (int64_t)a->seqlen_q,
+                "total_q (%lld) must equal batch * seqlen_q (%lld) in the padded layout", (long long)a->total_q,
+                (long long)(a->batch * (int64_t)a->seqlen_q));
   KB200_REQUIRE(a->n_pages > 0, "n_pages must be positive");
   const int es = dtype_size(a->kv_dtype);
   KB200_REQUIRE(aligned16(a->k_cache) && aligned16(a->v_cache), "K/V pools must be 16-byte aligned");
@@ -1820,7 +1789,7 @@ inline int launch_attention_pass(const kb200_attn_args* a, int k_skip, int fixed
   const int tile_n = prefill ? kPrefillTileKeys : tile_n_for(a->kv_dtype, a->head_dim, nw);
   // The transposed decode kernel pays off where the math is the limiter (e4m3 K/V); 16-bit K/V
   // is within a few percent of the HBM roofline with the general kernel already.
-  const bool decode8 = !prefill && decode8_enabled() && a->kv_dtype == KB200_DTYPE_E4M3 &&
+  const bool decode8 = !prefill && a->kv_dtype == KB200_DTYPE_E4M3 &&
                        (int64_t)group * a->seqlen_q <= kDecodeRows;
   {
     // every copy lands on a 128-byte boundary of shared memory
@@ -1833,7 +1802,7 @@ inline int launch_attention_pass(const kb200_attn_args* a, int k_skip, int fixed
   TmapKey key{a->k_cache, a->kv_page_stride, a->kv_token_stride, a->kv_head_stride, a->n_pages,
               P, a->n_kv_heads, a->head_dim, a->kv_dtype, a->device};
   // 256-byte rows and pages at least a tile long: one box per (page, K|V) instead of one per half
-  const bool merged = !prefill && a->head_dim * es == 256 && P >= tile_n && merged_boxes_enabled();
+  const bool merged = !prefill && a->head_dim * es == 256 && P >= tile_n;
   CUtensorMap tmK, tmV;
   if (int rc = get_pool_tmap(key, tile_n, merged, &tmK)) return rc;
   key.base = a->v_cache;

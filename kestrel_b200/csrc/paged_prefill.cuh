@@ -810,11 +810,8 @@ inline int launch_prefill_variant(const CUtensorMap& tmK, const CUtensorMap& tmV
                                   int dev, cudaStream_t stream) {
   using SM = PrefillSmem<HD, KV8>;
   auto kern = paged_prefill_kernel<HD, BF16, KV8>;
-  static bool done[64] = {};
-  if (!done[dev & 63]) {
-    KB200_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SM::BYTES));
-    done[dev & 63] = true;
-  }
+  static SmemAttrOnce once;
+  if (int rc = once.ensure(kern, SM::BYTES, dev)) return rc;
   KB200_CUDA_OK(launch_kernel(kern, dim3(grid), dim3(pf_threads(KV8)), SM::BYTES, stream, tmK, tmV, p));
   return KB200_OK;
 }

@@ -451,7 +451,8 @@ class _BlockBidirectionalMask:
 block_bidirectional_mask = _BlockBidirectionalMask()
 
 
-def block_visibility(block_ids: torch.Tensor, seqlen: Optional[int] = None) -> torch.Tensor:
+def block_visibility(block_ids: torch.Tensor, seqlen: Optional[int] = None,
+                     out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``out[b, j]`` = last position of the run of equal, non-negative ``block_ids`` containing ``j``
     (``j`` itself where the id is negative): how far past itself query ``j`` sees under the
     block-bidirectional mask.  ``block_ids`` int32 ``[B, >= seqlen]`` on the GPU."""
@@ -462,7 +463,10 @@ def block_visibility(block_ids: torch.Tensor, seqlen: Optional[int] = None) -> t
     S = block_ids.shape[1] if seqlen is None else int(seqlen)
     if S > block_ids.shape[1]:
         raise ValueError("block_ids is shorter than the query rows")
-    out = torch.empty((B, S), dtype=torch.int32, device=block_ids.device)
+    if out is None:
+        out = torch.empty((B, S), dtype=torch.int32, device=block_ids.device)
+    elif out.dtype != torch.int32 or out.shape != (B, S) or out.stride(1) != 1 or _require_cuda("out", out) != dev:
+        raise ValueError("out must be an int32 [batch, seqlen] tensor on block_ids' device")
     if B and S:
         _native.check(_native.load().kb200_block_visibility(block_ids.data_ptr(), block_ids.stride(0), B, S,
                                                             out.data_ptr(), out.stride(0), dev, _stream(dev)))
@@ -470,29 +474,40 @@ def block_visibility(block_ids: torch.Tensor, seqlen: Optional[int] = None) -> t
 
 
 _workspaces: dict[tuple[int, int], torch.Tensor] = {}
+_retired_workspaces: list[torch.Tensor] = []   # outgrown buffers: a captured graph may still point at them
 _ws_bytes_cache: dict[tuple, int] = {}
+_WS_BYTES_CACHE_MAX = 1024
 
 
 def _workspace(dev: int, stream: int, nbytes: int) -> torch.Tensor:
+    """Scratch buffer of one (device, stream).  It only ever grows, and a buffer that was handed out
+    is never given back to the allocator: a CUDA graph captured earlier keeps its address."""
     key = (dev, stream)
     ws = _workspaces.get(key)
     if ws is None or ws.numel() < nbytes:
         # grow geometrically so steady-state decode never reallocates
         size = max(nbytes, 2 * ws.numel() if ws is not None else 0, 1 << 20)
+        if ws is not None:
+            _retired_workspaces.append(ws)
         ws = torch.empty(size, dtype=torch.uint8, device=torch.device("cuda", dev))
         _workspaces[key] = ws
     return ws
 
 
 def reserve_attention_workspace(*, batch: int, total_q: int, n_q_heads: int, n_kv_heads: int,
-                                head_dim: int, device: torch.device | int | None = None) -> int:
-    """Pre-size the scratch buffer of the current stream (call before CUDA-graph capture so that
-    no allocation happens inside it).  Returns the byte count."""
+                                head_dim: int, device: torch.device | int | None = None,
+                                stream: "torch.cuda.Stream | None" = None, extra_bytes: int = 0) -> int:
+    """Pre-size the scratch buffer of ``stream`` (default: the current stream of ``device``) for the
+    largest problem that will run there, so that no allocation happens inside the op.  Call it on
+    the stream the CUDA graph is captured on, before the capture.  ``extra_bytes`` adds room for
+    calls that need more than the split-KV bound (a shared-prefix call's first-pass output, a
+    block-mask call's visibility rows).  Returns the byte count reserved."""
     dev = torch.cuda.current_device() if device is None else torch.device(device).index if not isinstance(device, int) else device
     if dev is None:
         dev = torch.cuda.current_device()
     n = int(_native.load().kb200_attn_workspace_bytes(batch, total_q, n_q_heads, n_kv_heads, head_dim, dev))
-    _workspace(dev, _stream(dev), n)
+    n += int(extra_bytes)
+    _workspace(dev, stream.cuda_stream if stream is not None else _stream(dev), n)
     return n
 
 
@@ -552,8 +567,11 @@ def flash_attn_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *,
         block_ids = aux_tensors[0]
     if seqused_k is None:
         raise ValueError("paged attention requires seqused_k")
-    if window_size_right not in (None, 0, -1) :
+    if window_size_right not in (None, 0, -1):
         raise NotImplementedError("only window_size_right in (None, 0) is supported")
+    if window_size_left is not None and window_size_left >= 0 and not causal and window_size_right != 0:
+        # FlashAttention reads (left >= 0, right < 0, causal=False) as "unbounded to the right"
+        raise NotImplementedError("a left window needs window_size_right=0 (as the reference passes) or causal=True")
     dev = _require_cuda("q", q)
     for nm, t in (("k", k), ("v", v), ("page_table", page_table), ("seqused_k", seqused_k)):
         if _require_cuda(nm, t) != dev:
@@ -661,9 +679,6 @@ def flash_attn_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *,
     if block_ids is not None:
         if _require_cuda("block_sequence_ids", block_ids) != dev or block_ids.ndim != 2 or block_ids.shape[0] < B:
             raise ValueError("block_sequence_ids must be an int32 [batch, >= seqlen_q] tensor on q's device")
-        vis = block_visibility(block_ids[:B], Sq)   # kept alive until the launch below is enqueued
-        a.q_visible_until = vis.data_ptr()
-        a.q_visible_batch_stride = vis.stride(0)
         a.causal = 1   # the block mask extends the causal one (the reference passes causal=False next to mask_mod)
     if shared_prefix_pages:
         if shared_prefix_pages < 0 or shared_prefix_pages > page_table.shape[1]:
@@ -674,11 +689,22 @@ def flash_attn_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *,
             q_strides, seqused_q is None, a.window_left)
     nbytes = _ws_bytes_cache.get(wkey)
     if nbytes is None:
+        if block_ids is not None:
+            a.q_visible_until = q.data_ptr()   # any non-null value: it selects the kernel the size depends on
         nbytes = int(lib.kb200_attn_workspace_bytes_for(C.byref(a)))
-        _ws_bytes_cache[wkey] = nbytes
-    ws = _workspace(dev, stream, nbytes)
+        if len(_ws_bytes_cache) >= _WS_BYTES_CACHE_MAX:
+            _ws_bytes_cache.clear()
+        _ws_bytes_cache[wkey] = nbytes = (nbytes + 255) & ~255
+    vis_bytes = ((B * Sq * 4 + 255) & ~255) if block_ids is not None else 0
+    ws = _workspace(dev, stream, nbytes + vis_bytes)
+    if block_ids is not None:
+        # the visibility rows live behind the kernel scratch in the same per-stream buffer
+        vis = ws[nbytes:nbytes + B * Sq * 4].view(torch.int32).view(B, Sq)
+        block_visibility(block_ids[:B], Sq, out=vis)
+        a.q_visible_until = vis.data_ptr()
+        a.q_visible_batch_stride = vis.stride(0)
     a.workspace = ws.data_ptr()
-    a.workspace_bytes = ws.numel()
+    a.workspace_bytes = nbytes
     _native.check(lib.kb200_paged_attention(C.byref(a)))
     return out, lse
 

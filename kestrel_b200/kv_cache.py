@@ -307,6 +307,11 @@ class PageTable:
                 f"Prefix caching requires page_size=1, got {page_size}. "
                 "With page_size>1, partial page reuse would cause leaks or corruption."
             )
+            cache_page_size = getattr(prefix_cache, "page_size", page_size) if page_granular else page_size
+            assert cache_page_size == page_size, (
+                f"Prefix cache works on pages of {cache_page_size} positions, the page table on pages of "
+                f"{page_size}: a match would map pages that cover other positions than the tree recorded."
+            )
             prefix_cache._free_pages_sink = self.free_pages_to_pool
             self.prefix_cache = prefix_cache
 
@@ -382,6 +387,8 @@ class PageTable:
         return row
 
     def _take_pages(self, count: int) -> list[int]:
+        if count <= 0:   # free_pages[-0:] would be the whole list
+            return []
         taken = self.free_pages[-count:]
         del self.free_pages[-count:]
         return taken
@@ -443,6 +450,18 @@ class PageTable:
         self.capacity[batch_idx] = max(self.capacity[batch_idx], stop * self.page_size)
         self.page_table_cpu[batch_idx].extend(physical_pages)
         self.num_blocks_per_row[batch_idx] = max(int(self.num_blocks_per_row[batch_idx]), stop)
+        self._dirty_rows.add(batch_idx)
+
+    def unmap_pages(self, batch_idx: int, keep: int) -> None:
+        """Drop the row's entries from logical page ``keep`` on WITHOUT freeing them: the inverse of
+        :meth:`map_pages` for pages that stay with their owner (a prefix-cache attach that failed)."""
+        row = self.page_table_cpu[batch_idx]
+        if keep >= len(row):
+            return
+        self._page_table_cpu_np[batch_idx, keep:len(row)] = -1
+        del row[keep:]
+        self.capacity[batch_idx] = keep * self.page_size
+        self.num_blocks_per_row[batch_idx] = keep
         self._dirty_rows.add(batch_idx)
 
     def free_pages_to_pool(self, pages: tuple[int, ...] | list[int]) -> None:

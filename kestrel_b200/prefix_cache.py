@@ -70,7 +70,7 @@ class TreeNode:
     parent: Optional["TreeNode"] = None
     tokens: tuple = ()
     start: int = 0          # first KV position of this node on its root path
-    kv_len: int = 0
+    kv_len: int = -1        # KV positions covered; -1: one per page (the reference's page-size-1 invariant)
     physical_pages: tuple = ()
     lock_ref: int = 0
     prefill_lock_ref: int = 0
@@ -78,8 +78,14 @@ class TreeNode:
     heap_version: int = 0
     namespace: CacheNamespace | None = None
 
+    def __post_init__(self) -> None:
+        if self.kv_len < 0:
+            self.kv_len = len(self.physical_pages)
+
     @property
     def total_kv_length(self) -> int:
+        """KV positions in this node (``len(physical_pages)`` at page size 1, as
+        ``kestrel/prefix_cache/radix_cache.py:34-37``)."""
         return self.kv_len
 
     def is_leaf(self) -> bool:
@@ -401,10 +407,19 @@ def attach_cached_prefix(page_table, cache: PagedRadixCache, batch_idx: int, tok
     if skip <= 0:
         return 0, 0, match
     n_full, partial = divmod(skip, P)
-    page_table.map_pages(batch_idx, 0, match.matched_pages[: n_full + (1 if partial else 0)])
-    if partial:
-        page_table.cow_page(batch_idx, n_full)
+    # Lock first: the copy-on-write below allocates a page, and an allocation may evict idle leaves --
+    # the matched node among them while it is unlocked (the reference allocates nothing between
+    # map_pages and lock_prefill, kestrel/models/moondream/runtime.py:1607-1615).
     cache.lock_prefill(match.last_node)
+    held = len(page_table.page_table_cpu[batch_idx])
+    try:
+        page_table.map_pages(batch_idx, 0, match.matched_pages[: n_full + (1 if partial else 0)])
+        if partial:
+            page_table.cow_page(batch_idx, n_full)
+    except Exception:
+        cache.unlock_prefill(match.last_node)
+        page_table.unmap_pages(batch_idx, held)
+        raise
     return skip, n_full, match
 
 

@@ -307,3 +307,17 @@ def test_layer_cache_adapter_checks_shapes_before_the_append():
     # well-formed arguments get as far as the kernel, which refuses CPU tensors (no fallback)
     with pytest.raises(RuntimeError, match="no CPU fallback"):
         layer.update(torch.arange(3).expand(2, 3), k, k, slot_mapping=slots)
+
+
+def test_allocating_zero_pages_takes_nothing():
+    pt = PageTable(n_pages=8, page_size=4, max_batch_size=3, device="cpu")
+    before = list(pt.free_pages)
+    assert pt.allocate_pages(0) == []
+    assert pt.free_pages == before
+
+
+def test_page_granular_cache_must_use_the_tables_page_size():
+    from kestrel_b200.prefix_cache import PagedRadixCache
+    with pytest.raises(AssertionError):
+        PageTable(n_pages=8, page_size=16, max_batch_size=3, device="cpu", prefix_cache=PagedRadixCache(page_size=4))
+    PageTable(n_pages=8, page_size=16, max_batch_size=3, device="cpu", prefix_cache=PagedRadixCache(page_size=16))

@@ -283,3 +283,41 @@ def test_finalize_keeps_pages_private_when_the_row_is_not_on_the_trees_pages():
     assert pt.pages_available == free_before + 3          # all of its pages were private
     release_cached_sequence(pt, cache, ra, sa)
     assert pt.pages_available == free_before + 3          # the tree keeps the first sequence's pages
+
+
+def test_attach_with_an_empty_free_list_cannot_evict_the_prefix_it_just_matched():
+    """The partial-page copy allocates a page; with nothing free the allocation evicts idle leaves.
+    The matched leaf must already be locked then, or its pages would be freed while the row maps them."""
+    P, n_pages = 16, 5
+    cache = PagedRadixCache(page_size=P)
+    pt = PageTable(n_pages=n_pages, page_size=P, max_batch_size=4, device="cpu", prefix_cache=cache)
+    owner = pt.allocate()
+    pt.reserve(owner, 40)                                   # 3 pages: positions 0..39
+    prompt40 = toks(*range(40))
+    st = finalize_cached_prompt(pt, cache, owner, prompt40, 40, 0, 0, cache.match_prefix(prompt40))
+    release_cached_sequence(pt, cache, owner, st)           # the tree owns the three pages, nothing is locked
+    drained = pt.allocate_pages(pt.pages_available)         # nothing free: the only evictable node is that leaf
+    assert pt.pages_available == 0 and cache.evictable_page_count() == 3
+    row = pt.allocate()
+    prompt50 = toks(*range(50))
+    with pytest.raises(RuntimeError):
+        attach_cached_prefix(pt, cache, row, prompt50, 50)  # the copy cannot get a page; the prefix survives
+    assert cache.total_cached_pages == 3 and cache.evictable_page_count() == 3
+    assert pt.page_table_cpu[row] == [] and pt.capacity[row] == 0
+    assert not set(pt.free_pages) & {p for r in pt.page_table_cpu for p in r}
+    # with one free page the attach succeeds: two shared pages, a private copy of the third
+    pt.free_pages_to_pool(drained[:1])
+    skip, n_shared, match = attach_cached_prefix(pt, cache, row, prompt50, 50)
+    assert (skip, n_shared) == (40, 2)
+    src, dst = pt.take_pending_page_copies()
+    assert len(src) == 1 and src[0] != dst[0]
+    assert not set(pt.free_pages) & set(pt.page_table_cpu[row])
+    assert cache.total_cached_pages == 3
+    cache.unlock_prefill(match.last_node)
+
+
+def test_tree_node_reports_its_kv_length_like_the_reference():
+    from kestrel_b200.prefix_cache import TreeNode
+    assert TreeNode(physical_pages=(1, 2, 3)).total_kv_length == 3     # one position per page unless told otherwise
+    assert TreeNode().total_kv_length == 0
+    assert TreeNode(physical_pages=(7,), kv_len=9).total_kv_length == 9
