@@ -309,8 +309,8 @@ class PageTable:
             )
             cache_page_size = getattr(prefix_cache, "page_size", page_size) if page_granular else page_size
             assert cache_page_size == page_size, (
-                f"Prefix cache works on pages of {cache_page_size} positions, the page table on pages of "
-                f"{page_size}: a match would map pages that cover other positions than the tree recorded."
+                f"Prefix caching requires page_size={cache_page_size} (the page size of the cache), got {page_size}. "
+                "A match would map pages that cover other positions than the tree recorded."
             )
             prefix_cache._free_pages_sink = self.free_pages_to_pool
             self.prefix_cache = prefix_cache

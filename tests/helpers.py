@@ -50,3 +50,34 @@ def make_paged_problem(*, seed: int, batch: int, len_lo: int, len_hi: int, n_q_h
         "k_pool": k_pool, "v_pool": v_pool, "q": q, "page_table": page_table,
         "seqused_k": torch.tensor(lengths, dtype=torch.int32), "lengths": lengths, "n_pages": n_pages,
     }
+
+
+def import_staged_reference():
+    """The reference's own ``kestrel.kv_cache`` / ``kestrel.ops.attention`` / ``kestrel.prefix_cache`` modules
+    (byte copies staged by ``oracle/stage_reference.py``) imported UNMODIFIED on top of this library:
+    ``kestrel_b200.install_as_kestrel_kernels()`` registers the shim under the name they bind at import
+    time (``kestrel/kv_cache.py:10-17``).  ``kestrel/__init__.py`` is not staged (it imports every model),
+    so the package objects are made here.  Returns ``(kv_cache, ops.attention, prefix_cache)`` or ``None``
+    when nothing is staged."""
+    import importlib
+    import sys
+    import types
+    from pathlib import Path
+
+    root = Path(__file__).resolve().parent.parent / "oracle" / "_ref" / "kestrel"
+    if not (root / "kv_cache.py").exists():
+        return None
+    import kestrel_b200
+
+    kestrel_b200.install_as_kestrel_kernels()
+    if getattr(sys.modules.get("kestrel"), "__path__", None) != [str(root)]:
+        for name in [m for m in sys.modules if m == "kestrel" or m.startswith("kestrel.")]:
+            del sys.modules[name]
+        pkg = types.ModuleType("kestrel")
+        pkg.__path__ = [str(root)]
+        sys.modules["kestrel"] = pkg
+        rt = types.ModuleType("kestrel.runtime")          # kestrel/runtime/__init__.py pulls the model runtimes
+        rt.__path__ = [str(root / "runtime")]
+        sys.modules["kestrel.runtime"] = rt
+    return (importlib.import_module("kestrel.kv_cache"), importlib.import_module("kestrel.ops.attention"),
+            importlib.import_module("kestrel.prefix_cache"))

@@ -111,6 +111,59 @@ def test_fp8_quantise_on_append_is_code_exact(in_dtype, per_head, dim):
     assert torch.equal(got_k[page, :, off], t[5])
 
 
+@pytest.mark.parametrize("path", ["append", "rope_append"])
+def test_fp8_codes_of_every_finite_bf16_value_through_the_kernel(path):
+    """All 65 280 finite bf16 values, each divided by a handful of scales (powers of two, where the quotient
+    is exact, and others, where it lands on and next to rounding ties), through the append kernels: the
+    codes must equal the oracle's -- and torch's own cast of the clamped fp32 quotient -- byte for byte."""
+    bits = torch.arange(0x10000, dtype=torch.int32)
+    bits = bits[(bits & 0x7F80) != 0x7F80]                     # drop Inf / NaN
+    assert bits.numel() == 65280
+    vals = bits.to(torch.int16).view(torch.bfloat16)
+    heads, dim, page_size = 8, 64, 16
+    per_token = heads * dim
+    tokens = -(-vals.numel() // per_token)
+    x = torch.zeros(tokens * per_token, dtype=torch.bfloat16)
+    x[: vals.numel()] = vals
+    x = x.view(tokens, heads, dim)
+    n_pages = tokens // page_size + 3
+    slots = torch.arange(page_size, page_size + tokens, dtype=torch.int64).view(1, tokens)
+    scale_sets = [
+        [1.0] * heads, [0.5] * heads, [2.0 ** -7] * heads,
+        [0.0123, 1.0 / 3.0, 0.3, 7.7, 1.0 / 448.0, 3.0, 0.0491, 123.456],   # per KV head
+        [5.0 / 448.0] * heads, [20.0 / 448.0] * heads,
+    ]
+    table = O.precompute_freqs_cis(32, 4, 1.5e6)               # Moondream: 32 of 64 dims rotated
+    pos = torch.zeros(tokens, dtype=torch.int64)
+    for scales in scale_sets:
+        pool = KVMemoryPool(device=DEV)
+        pt = PageTable(n_pages=n_pages, page_size=page_size, max_batch_size=2, device=DEV)
+        cache = PagedKVCache(pt, n_heads=heads, head_dim=dim, dtype=torch.float8_e4m3fn, pool=pool,
+                             k_scale=scales, v_scale=scales[::-1])
+        xk = x.unsqueeze(0).to(DEV)
+        xv = x.flip(0).contiguous().unsqueeze(0).to(DEV)
+        if path == "append":
+            cache.update(slots, xk, xv, slot_mapping=slots.to(DEV))
+        else:
+            # position 0 rotates by angle 0 (cos 1, sin 0): the values survive, only the sign of a zero may
+            # change, so the expectation below goes through the oracle's rotary as well
+            kernels.rope_reshape_and_cache(pos.to(DEV), None, xk.clone(), xv, table.to(DEV),
+                                           cache.k_cache.permute(0, 2, 1, 3), cache.v_cache.permute(0, 2, 1, 3),
+                                           slots.view(-1).to(DEV), "fp8_e4m3", cache.k_scale_tensor, cache.v_scale_tensor)
+        want_k = torch.zeros(n_pages, heads, page_size, dim, dtype=torch.uint8)
+        want_v = torch.zeros_like(want_k)
+        ks, vs = torch.tensor(scales), torch.tensor(scales[::-1])
+        x_k = x if path == "append" else O.rotary_embedding(pos, x, table)
+        O.append(want_k, want_v, x_k, x.flip(0), slots, k_scale=ks, v_scale=vs)
+        got_k = cache.k_cache.view(torch.uint8).cpu()
+        got_v = cache.v_cache.view(torch.uint8).cpu()
+        assert torch.equal(got_k, want_k), (scales[0], int((got_k != want_k).sum()))
+        assert torch.equal(got_v, want_v), (scales[0], int((got_v != want_v).sum()))
+        cast = (x_k.float() / ks.view(1, heads, 1)).clamp(-448, 448).to(torch.float8_e4m3fn).view(torch.uint8)
+        flat = got_k[1:1 + -(-tokens // page_size)].permute(0, 2, 1, 3).reshape(-1, heads, dim)[:tokens]
+        assert torch.equal(flat, cast)
+
+
 def test_append_reports_out_of_range_slot_without_faulting():
     pool = KVMemoryPool(device=DEV)
     pt = PageTable(n_pages=4, page_size=4, max_batch_size=2, device=DEV)

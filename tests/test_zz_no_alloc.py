@@ -5,7 +5,8 @@ KV pool at start-up, a C host without a device allocator, code running inside a 
 For them the library carries a fixed 32 MiB scratch array in its device image.  This test drives
 that entry point through the C ABI (a hand-filled ``kb200_attn_args``), twice in a row because all
 calls share the one array, and checks the results against the ordinary entry point, which gets a
-caller-allocated workspace.  It is collected last on purpose and needs no state from other tests.
+caller-allocated workspace, and against the CPU oracle.  It is collected last on purpose and needs no
+state from other tests.
 """
 
 import ctypes as C
@@ -16,6 +17,7 @@ import torch
 
 from helpers import make_paged_problem
 from kestrel_b200 import _native
+from oracle import paged_kv_oracle as O
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda"
@@ -105,6 +107,11 @@ def test_static_scratch_matches_caller_workspace_twice_in_a_row(kv):
         _close(got, want)
         # the same work, the same reduction order: the two entry points agree to the last bit
         assert torch.equal(got.view(torch.int16), want.view(torch.int16))
+        # and both are right: the fp32 oracle on the same pools
+        ref = O.paged_attention(q.cpu().float(), k.cpu(), v.cpu(), p["page_table"], p["seqused_k"],
+                                k_scale=None if ks is None else ks.cpu(), v_scale=None if vs is None else vs.cpu())
+        _close(got.cpu(), ref)
+        assert (got.float().cpu() - ref).abs().max().item() <= ABS_TOL
     flags = _native.device_status(dev, clear=True)
     assert flags[0] == 0, flags
 
