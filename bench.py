@@ -52,10 +52,33 @@ if str(ROOT) not in sys.path:
 
 NOMINAL_HBM_GBS = 8000.0
 FALLBACK_HBM_GBS = 6650.0
-# DRAM read+write bytes of one attention launch divided by its algorithmic bytes, from the ncu captures
-# summarised under profiles/ (reduced FP8 case: 1.0053; bf16 config 2: 1.0071).  Traffic grows with the
-# tokens attended, so a full launch is that ratio times its algorithmic bytes.
-DRAM_TRAFFIC_RATIO = {"fp8": 1.0053, "bf16": 1.0071}
+# DRAM read+write bytes of one attention launch divided by its algorithmic bytes come from the ncu captures
+# summarised under profiles/ (each summary states the ratio and the sha256 of the kernel source it was taken
+# with).  Traffic grows with the tokens attended, so a full launch is that ratio times its algorithmic bytes.
+TRAFFIC_PROFILES = {"fp8": "profiles/paged_attn_decode_kernel_fp8_cfg3_reduced.md",
+                    "bf16": "profiles/paged_attn_kernel_bf16_cfg2.md"}
+KERNEL_SOURCE = "kestrel_b200/csrc/paged_attention.cuh"
+
+
+def dram_traffic_ratio(kv: str) -> dict:
+    """{"ratio", "profile", "stale"}: the ratio a profile summary records, and whether the kernel source
+    changed since (the summary names the sha256 of the source it was captured with)."""
+    import hashlib
+    import re
+    path = ROOT / TRAFFIC_PROFILES[kv]
+    out = {"ratio": None, "profile": TRAFFIC_PROFILES[kv], "stale": None}
+    if not path.exists():
+        return out
+    text = path.read_text()
+    m = re.search(r"DRAM traffic . algorithmic bytes[^0-9]*([0-9]+\.[0-9]+)", text)
+    if m:
+        out["ratio"] = float(m.group(1))
+    m = re.search(r"kernel source sha256[^0-9a-f]*([0-9a-f]{64})", text)
+    if m:
+        now = hashlib.sha256((ROOT / KERNEL_SOURCE).read_bytes()).hexdigest()
+        out["stale"] = now != m.group(1)
+    return out
+
 
 WORKLOADS = {
     # name: batch, len range, layers, kv dtype, head_dim, seqlen_q, outliers, pool factor
@@ -198,7 +221,9 @@ class GpuWorkload:
         self.B, self.D, self.sq, self.layers_n = cfg["batch"], cfg["head_dim"], cfg["sq"], cfg["layers"]
         self.kv_dtype = torch.float8_e4m3fn if cfg["kv"] == "fp8" else torch.bfloat16
         self.kv_bytes = 1 if cfg["kv"] == "fp8" else 2
-        g = torch.Generator().manual_seed(1000 + int(name[3:]) + 7919 * rank)
+        # context lengths and the page permutation are the same on every rank (the per-GPU work of a
+        # weak-scaling run must not depend on the rank's draw); the K/V/Q data below is seeded per rank
+        g = torch.Generator().manual_seed(1000 + int(name[3:]))
         prefix = cfg.get("prefix", 0)
         suffix = torch.randint(cfg["lo"], cfg["hi"] + 1, (self.B,), generator=g)
         self.len0 = suffix + prefix                      # context before the first timed/warm-up step
@@ -275,6 +300,7 @@ class GpuWorkload:
         # attention call reads them once for the whole batch
         self.shared_pages = (self.pt.common_prefix_pages(self.rows, min_tokens=int(self.len0.min()))
                              if prefix and share_prefix else 0)
+        self.shared_tokens = (prefix // PAGE) * PAGE if prefix else 0   # KV tokens on pages every request maps
         self._fill(prefix, copy_kv_pages)
         # per-step inputs, resident in HBM (one set per layer so no layer reuses another's rows)
         self.q = [self._randn(self.B, self.sq, HQ, self.D).to(torch.bfloat16) for _ in range(self.layers_n)]
@@ -521,7 +547,7 @@ class PrefillWorkload:
         self.kernels, self.cfg, self.device = kernels, PREFILL_WORKLOADS[name], device
         cfg = self.cfg
         self.B, self.D, self.prefix, self.chunk = cfg["batch"], cfg["head_dim"], cfg["prefix"], cfg["chunk"]
-        g = torch.Generator().manual_seed(2000 + rank)
+        g = torch.Generator().manual_seed(2000)   # the same request lengths on every rank
         self.suffix = torch.randint(cfg["lo"], cfg["hi"] + 1, (self.B,), generator=g)
         own_pages = (self.prefix % PAGE + self.suffix + PAGE - 1) // PAGE        # pages a request writes
         shared_full = self.prefix // PAGE
@@ -770,69 +796,198 @@ def run_prefill(args) -> None:
 
 
 # ----------------------------------------------------------------------------------------------
-# CPU arm: the oracle (a port of the reference's torch path) on a bounded sample of the workload
+# CPU arm: the reference's own torch path where it has one (slot mapping, append), a vectorised torch
+# restatement where it has none (FP8 quantise, metadata, attention), on a bounded sample of the workload
 # ----------------------------------------------------------------------------------------------
 
+def _staged_reference_kv_cache():
+    """The reference's unmodified ``kestrel/kv_cache.py`` (staged under oracle/_ref by oracle/stage_reference.py)
+    bound to a ``kestrel_kernels`` stub without kernels, which makes ``PagedKVCache.update`` take its torch
+    path (``kestrel/kv_cache.py:216-220``).  Loaded under a private package name; None when nothing is staged."""
+    import importlib
+    import types
+    root = ROOT / "oracle" / "_ref" / "kestrel"
+    if not (root / "kv_cache.py").exists():
+        return None
+    saved = {k: sys.modules.get(k) for k in ("kestrel_kernels", "kestrel", "kestrel.kv_cache", "kestrel.device",
+                                             "kestrel.utils", "kestrel.utils.buffers")}
+    try:
+        stub = types.ModuleType("kestrel_kernels")
+        rt = types.SimpleNamespace(cache=types.SimpleNamespace(reshape_and_cache_flash=None, build_paged_kv_metadata=None))
+        stub.get_runtime = lambda: rt
+        sys.modules["kestrel_kernels"] = stub
+        pkg = types.ModuleType("kestrel")
+        pkg.__path__ = [str(root)]
+        sys.modules["kestrel"] = pkg
+        for k in ("kestrel.kv_cache", "kestrel.device", "kestrel.utils", "kestrel.utils.buffers"):
+            sys.modules.pop(k, None)
+        return importlib.import_module("kestrel.kv_cache")
+    except Exception:
+        return None
+    finally:
+        for k, v in saved.items():
+            if v is None:
+                sys.modules.pop(k, None)
+            else:
+                sys.modules[k] = v
+
+
 class CpuWorkload:
-    def __init__(self, name: str, sample_batch: int, seed_rank: int = 0):
-        from oracle import paged_kv_oracle as O
-        self.O = O
+    """One layer of one decode step on ``sample_batch`` sequences drawn like the workload's.
+
+    * slot mapping and bf16 append: the reference's own ``PageTable.build_slot_mapping`` /
+      ``PagedKVCache.update`` torch path when the staged modules are present (``kind`` "reference+port"),
+      else the same index arithmetic restated in torch (``kind`` "port");
+    * FP8 quantise-on-append: ``(x / scale).clamp(-448, 448).to(float8_e4m3fn)`` (the reference's torch
+      path refuses FP8, ``kestrel/kv_cache.py:212-215``);
+    * metadata: the torch restatement of ``kestrel/models/qwen35/runtime.py:1165-1170``;
+    * attention: per sequence, gather ITS pages only, dequantise with ``view(float8_e4m3fn).float()``,
+      one batched matmul per product over the KV heads, fp32 softmax (the reference has no CPU attention).
+    """
+
+    def __init__(self, name: str, sample_batch: int):
         self.cfg = cfg = WORKLOADS[name]
         self.B = min(sample_batch, cfg["batch"])
         self.D, self.sq = cfg["head_dim"], cfg["sq"]
-        self.kv_bytes = 1 if cfg["kv"] == "fp8" else 2
+        self.fp8 = cfg["kv"] == "fp8"
+        self.kv_bytes = 1 if self.fp8 else 2
         g = torch.Generator().manual_seed(1000 + int(name[3:]))
         prefix = cfg.get("prefix", 0)
         full = torch.randint(cfg["lo"], cfg["hi"] + 1, (cfg["batch"],), generator=g) + prefix
         self.len0 = full[: self.B]
-        pages = int(((self.len0 + 64 + PAGE - 1) // PAGE).sum()) + 2
-        perm = (torch.randperm(pages - 1, generator=g) + 1).to(torch.int32)
-        width = int(((self.len0 + 64 + PAGE - 1) // PAGE).max())
-        self.table = torch.zeros(self.B + 1, width, dtype=torch.int32)
-        cur = 0
-        for b in range(self.B):
-            n = int((self.len0[b] + 64 + PAGE - 1) // PAGE)
-            self.table[b + 1, :n] = perm[cur:cur + n]
-            cur += n
-        shape = (pages, HKV, PAGE, self.D)
-        if cfg["kv"] == "fp8":
-            self.kc = torch.randint(0, 0x77, shape, generator=g, dtype=torch.uint8)
-            self.vc = torch.randint(0, 0x77, shape, generator=g, dtype=torch.uint8)
-            self.ks = torch.full((HKV,), 0.2)
-            self.vs = torch.full((HKV,), 0.2)
+        n_pages = int(((self.len0 + 64 + PAGE - 1) // PAGE).sum()) + 2
+        self.n_pages = n_pages
+        self.kc_mod = _staged_reference_kv_cache()
+        kv_dtype = torch.float8_e4m3fn if self.fp8 else torch.bfloat16
+        if self.kc_mod is not None:
+            kc = self.kc_mod
+            self.pt = kc.PageTable(n_pages=n_pages, page_size=PAGE, max_batch_size=self.B + 1, device="cpu")
+            order = torch.randperm(len(self.pt.free_pages), generator=g).tolist()
+            self.pt.free_pages = [self.pt.free_pages[i] for i in order]
+            kw = dict(k_scale=0.2, v_scale=0.2) if self.fp8 else {}
+            self.layer = kc.PagedKVCache(self.pt, n_heads=HKV, head_dim=self.D, dtype=kv_dtype,
+                                         pool=kc.KVMemoryPool(device="cpu"), **kw)
+            self.rows = [self.pt.allocate() for _ in range(self.B)]
+            for r, L in zip(self.rows, self.len0.tolist()):
+                self.pt.reserve(r, int(L) + 64)
+            self.pt.commit_block_table(self.rows)
+            self.table = self.pt.page_table
+            self.kc, self.vc = self.layer.k_cache, self.layer.v_cache
         else:
-            self.kc = torch.randn(shape, generator=g).to(torch.bfloat16)
-            self.vc = torch.randn(shape, generator=g).to(torch.bfloat16)
-            self.ks = self.vs = None
+            perm = (torch.randperm(n_pages - 1, generator=g) + 1).to(torch.int32)
+            width = int(((self.len0 + 64 + PAGE - 1) // PAGE).max())
+            self.table = torch.zeros(self.B + 1, width, dtype=torch.int32)
+            cur = 0
+            for b in range(self.B):
+                n = int((self.len0[b] + 64 + PAGE - 1) // PAGE)
+                self.table[b + 1, :n] = perm[cur:cur + n]
+                cur += n
+            self.rows = list(range(1, self.B + 1))
+            self.kc = torch.zeros(n_pages, HKV, PAGE, self.D, dtype=kv_dtype)
+            self.vc = torch.zeros_like(self.kc)
+        shape = (n_pages, HKV, PAGE, self.D)
+        if self.fp8:
+            for c in (self.kc, self.vc):
+                c.view(torch.uint8).copy_(torch.randint(0, 0x77, shape, generator=g, dtype=torch.uint8))
+            self.ks = self.vs = 0.2
+        else:
+            self.kc.copy_(torch.randn(shape, generator=g).to(torch.bfloat16))
+            self.vc.copy_(torch.randn(shape, generator=g).to(torch.bfloat16))
+            self.ks = self.vs = 1.0
+        self.batch_idx = torch.tensor(self.rows, dtype=torch.int64)
         self.q = torch.randn(self.B, self.sq, HQ, self.D, generator=g).to(torch.bfloat16)
         self.k_new = torch.randn(self.B, self.sq, HKV, self.D, generator=g).to(torch.bfloat16)
         self.v_new = torch.randn(self.B, self.sq, HKV, self.D, generator=g).to(torch.bfloat16)
+        self.meta_pt = torch.zeros(self.B, self.table.shape[1], dtype=torch.int32)
+        self.meta_sk = torch.zeros(self.B, dtype=torch.int32)
+        self.out = torch.empty(self.B, self.sq, HQ, self.D, dtype=torch.bfloat16)
         self.step_no = 0
+
+    @property
+    def kind(self) -> str:
+        return "reference+port" if self.kc_mod is not None else "port"
 
     def lengths_after(self, step_no: int) -> torch.Tensor:
         return self.len0 + (step_no % 8 + 1) * self.sq
 
+    def _slot_mapping(self, pos: torch.Tensor) -> torch.Tensor:
+        if self.kc_mod is not None:
+            return self.pt.build_slot_mapping(self.batch_idx, pos)
+        page = self.table[self.batch_idx.view(-1, 1).expand_as(pos).reshape(-1), (pos // PAGE).reshape(-1)]
+        return (page.to(torch.int64) * PAGE + (pos % PAGE).reshape(-1)).view_as(pos)
+
+    def _append(self, pos: torch.Tensor, slots: torch.Tensor) -> None:
+        if self.fp8:
+            flat = slots.reshape(-1)
+            kq = (self.k_new.float() / self.ks).clamp(-448, 448).to(torch.float8_e4m3fn).view(-1, HKV, self.D)
+            vq = (self.v_new.float() / self.vs).clamp(-448, 448).to(torch.float8_e4m3fn).view(-1, HKV, self.D)
+            kview = self.kc.view(torch.uint8).permute(0, 2, 1, 3)
+            vview = self.vc.view(torch.uint8).permute(0, 2, 1, 3)
+            kview[flat // PAGE, flat % PAGE] = kq.view(torch.uint8)
+            vview[flat // PAGE, flat % PAGE] = vq.view(torch.uint8)
+        elif self.kc_mod is not None:
+            self.layer.update(input_pos=pos, k_val=self.k_new, v_val=self.v_new, slot_mapping=slots)
+        else:
+            flat = slots.reshape(-1)
+            self.kc.permute(0, 2, 1, 3)[flat // PAGE, flat % PAGE] = self.k_new.view(-1, HKV, self.D)
+            self.vc.permute(0, 2, 1, 3)[flat // PAGE, flat % PAGE] = self.v_new.view(-1, HKV, self.D)
+
+    def _metadata(self, pos: torch.Tensor) -> None:
+        self.meta_sk.copy_(pos[:, -1].to(torch.int32) + 1)
+        self.meta_pt.copy_(self.table[self.batch_idx])      # the restatement copies whole rows
+
+    def _attention(self) -> None:
+        group = HQ // HKV
+        scale = 1.0 / math.sqrt(self.D)
+        for b in range(self.B):
+            L = int(self.meta_sk[b])
+            pages = self.meta_pt[b, : -(-L // PAGE)].to(torch.int64)
+            K = self.kc[pages].float().permute(1, 0, 2, 3).reshape(HKV, -1, self.D)[:, :L]      # [H_kv, L, D]
+            V = self.vc[pages].float().permute(1, 0, 2, 3).reshape(HKV, -1, self.D)[:, :L]
+            q = self.q[b].float().view(self.sq, HKV, group, self.D).permute(1, 0, 2, 3).reshape(HKV, self.sq * group, self.D)
+            s = torch.matmul(q, K.transpose(1, 2)) * (scale * self.ks)                           # [H_kv, sq*g, L]
+            if self.sq > 1:
+                j = torch.arange(self.sq).repeat_interleave(group).view(1, -1, 1)
+                s = s.masked_fill(torch.arange(L).view(1, 1, L) > (L - self.sq + j), float("-inf"))
+            o = torch.matmul(torch.softmax(s, dim=-1), V) * self.vs                              # [H_kv, sq*g, D]
+            self.out[b] = o.view(HKV, self.sq, group, self.D).permute(1, 0, 2, 3).reshape(self.sq, HQ, self.D).to(torch.bfloat16)
+
     def step(self) -> None:
-        """One layer of one step: slot mapping, append, metadata, gather + attention."""
         t = self.step_no % 8
         pos = (self.len0 + t * self.sq).view(-1, 1) + torch.arange(self.sq).view(1, -1)
-        self.O.decode_step(self.q.float(), self.k_new, self.v_new, self.kc, self.vc, self.table,
-                           torch.arange(1, self.B + 1), pos, k_scale=self.ks, v_scale=self.vs)
+        slots = self._slot_mapping(pos)
+        self._append(pos, slots)
+        self._metadata(pos)
+        self._attention()
         self.step_no += 1
+
+    def matmul_bound_seconds(self) -> float:
+        """Time of the two batched matmuls alone on operands of this sample's shapes that are already
+        gathered and fp32: what a torch CPU attention cannot beat on these cores."""
+        group = HQ // HKV
+        lens = self.lengths_after(0).tolist()
+        ops = [(torch.randn(HKV, self.sq * group, self.D), torch.randn(HKV, int(L), self.D)) for L in lens]
+        best = float("inf")
+        for _ in range(3):
+            t0 = time.perf_counter()
+            for q, K in ops:
+                s = torch.matmul(q, K.transpose(1, 2))
+                torch.matmul(s, K)
+            best = min(best, time.perf_counter() - t0)
+        return best
 
 
 def time_cpu(name: str, steps: int, warmup: int, target_seconds: float = 12.0) -> dict:
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
     cfg = WORKLOADS[name]
-    sample_b = 2 if cfg["hi"] >= 16384 else 4
-    w = CpuWorkload(name, sample_b)
+    w = CpuWorkload(name, 8)
     for _ in range(max(1, min(warmup, 2))):
         w.step()
     t0 = time.perf_counter()
     w.step()
     one = time.perf_counter() - t0
-    reps = max(1, min(steps, int(target_seconds / max(one, 1e-3))))
+    reps = max(3, min(max(steps, 3), int(target_seconds / max(one, 1e-3))))
     times = []
     byts = []
     for _ in range(reps):
@@ -844,18 +999,18 @@ def time_cpu(name: str, steps: int, warmup: int, target_seconds: float = 12.0) -
                                       batch=w.B)["per_step"])
     med = statistics.median(times)
     gbs = statistics.median(byts) / med / 1e9
-    return {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "port",
-            "sample": f"{w.B} of {cfg['batch']} sequences, 1 of {cfg['layers']} layers, {reps} steps "
-                      f"(oracle: torch CPU restatement of the reference path, {cores} threads)",
+    bound = w.matmul_bound_seconds()
+    return {"value": gbs, "unit": "GB/s", "cores": cores, "kind": w.kind,
+            "sample": f"{w.B} of {cfg['batch']} sequences, 1 of {cfg['layers']} layers, {reps} steps; "
+                      + ("slot mapping" + ("" if w.fp8 else " and append") + " by the reference's own torch path, "
+                         if w.kc_mod is not None else "")
+                      + f"{'FP8 quantise, ' if w.fp8 else ''}metadata and attention as vectorised torch, {cores} threads",
             "ms_per_sample_step": med * 1e3, "tokens_per_s": w.B * w.sq / med / cfg["layers"],
-            "steps": reps}
+            "matmul_bound_gbs": statistics.median(byts) / bound / 1e9, "steps": reps}
 
-
-# ----------------------------------------------------------------------------------------------
-# main
-# ----------------------------------------------------------------------------------------------
 
 def run_reference_arm(args) -> None:
+    """``--impl reference``: the CPU arm alone (rank 0 only; other ranks exit without work)."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
@@ -867,7 +1022,7 @@ def run_reference_arm(args) -> None:
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": cfg["kv"], "data": "synthetic",
         "config": {"workload": f"{args.workload}: {cfg['desc']}", "timing": "host wall clock on a bounded sample"},
         "tokens_per_s": res["tokens_per_s"],
-        "cpu_baseline": {k: res[k] for k in ("value", "unit", "cores", "kind", "sample")},
+        "cpu_baseline": {k: res[k] for k in ("value", "unit", "cores", "kind", "sample", "matmul_bound_gbs")},
         "e2e": {"value": res["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -965,6 +1120,193 @@ def run_yardstick(args) -> None:
     }), flush=True)
 
 
+def unique_kv_tokens(wl, lengths_after: torch.Tensor) -> int:
+    """KV tokens a step must fetch from HBM at least once: pages shared by the whole batch count once."""
+    shared = wl.shared_tokens
+    return int(lengths_after.sum()) - (wl.B - 1) * shared if shared else int(lengths_after.sum())
+
+
+def measure_decode(name: str, args, device, rank: int, world: int, dist, *, steps: int, e2e_steps: int) -> dict | None:
+    """Builds the workload, times ``steps`` steps (CUDA events, graph replay unless --no-graph), the attention
+    calls alone (roofline) and ``e2e_steps`` steps through the public API with host buffers.  Every rank runs
+    it; rank 0 gets the record, the others None."""
+    from kestrel_b200 import _native
+    local = device.index
+    cfg = WORKLOADS[name]
+    warm = max(3, args.warmup)
+    total_steps = 3 * warm + steps + e2e_steps + 4
+    wl = GpuWorkload(name, device, rank, total_steps, share_prefix=not args.no_shared_prefix)
+
+    def barrier():
+        torch.cuda.synchronize(device)
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize(device)
+
+    use_graph = not args.no_graph
+    for _ in range(warm):
+        wl.step_device()
+    if use_graph:
+        wl.capture_graph()
+        wl.step_graph()   # one untimed replay (the graph continues where the eager warm-up stopped)
+    step_fn = wl.step_graph if use_graph else wl.step_device
+    barrier()
+    sampler = ClockSampler(physical_gpu_index(local))
+    if rank == 0:
+        sampler.start()
+    first_step = wl.step_no
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(steps):
+        step_fn()
+    stop.record()
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    elapsed_ms = start.elapsed_time(stop)
+    ab = lambda lens: algorithmic_bytes(lens, layers=wl.layers_n, kv_bytes=wl.kv_bytes, head_dim=wl.D, sq=wl.sq, batch=wl.B)
+    total_bytes = sum(ab(wl.lengths_after(first_step + i))["per_step"] for i in range(steps))
+    # roofline of the dominant kernel: the attention calls alone, at the lengths of the last step
+    attn_reps = max(3, min(200, int(400 / max(0.05, elapsed_ms / steps))))
+    attn_avg_ms = wl.time_attention_launch(attn_reps)
+    last = wl.lengths_after(wl.step_no - 1)
+    attn_bytes = ab(last)["attn_per_launch"]
+    tok_bytes = 2 * HKV * wl.D * wl.kv_bytes
+    attn_unique = attn_bytes - (int(last.sum()) - unique_kv_tokens(wl, last)) * tok_bytes
+    step_unique = ab(last)["per_step"] - wl.layers_n * (attn_bytes - attn_unique)
+
+    e2e = None
+    if e2e_steps:
+        for _ in range(warm):
+            wl.step_e2e()
+        barrier()
+        first_e2e = wl.step_no
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for _ in range(e2e_steps):
+            wl.step_e2e()
+        t1.record()
+        barrier()
+        e2e = (t0.elapsed_time(t1), sum(ab(wl.lengths_after(first_e2e + i))["per_step"] for i in range(e2e_steps)))
+
+    flags = _native.device_status(local, clear=True)
+    if flags[0] != 0:
+        raise SystemExit(f"kernel diagnostics reported a problem in {name}: {flags}")
+
+    # whole job: every rank's bytes over the slowest rank's time; per-rank figures alongside
+    stats = torch.tensor([elapsed_ms, float(total_bytes), e2e[0] if e2e else 0.0, float(e2e[1]) if e2e else 0.0],
+                         dtype=torch.float64, device=device)
+    if dist is not None:
+        gathered = [torch.empty_like(stats) for _ in range(world)]
+        dist.all_gather(gathered, stats)
+        per = torch.stack(gathered).cpu()
+    else:
+        per = stats.cpu().view(1, -1)
+    h2d, d2h = wl.e2e_bytes()
+    launches = wl.launches_per_step * steps
+    n_pools, n_pages, shared_pages, layers_n, B, sq, D = wl.n_pools, wl.n_pages, wl.shared_pages, wl.layers_n, wl.B, wl.sq, wl.D
+    kv_bytes = wl.kv_bytes
+    step_fn = ab = None   # (both hold the workload)
+    del wl
+    import gc
+    gc.collect()
+    torch.cuda.empty_cache()
+    if rank != 0:
+        return None
+
+    peak, peak_kind = measured_hbm_peak()
+    ms_all = float(per[:, 0].max())
+    bytes_all = float(per[:, 1].sum())
+    value = bytes_all / (ms_all * 1e-3) / 1e9
+    ms_per_step = ms_all / steps
+    logical = attn_bytes / (attn_avg_ms * 1e-3) / 1e9
+    achieved = attn_unique / (attn_avg_ms * 1e-3) / 1e9
+    traffic = dram_traffic_ratio(cfg["kv"])
+    rec = {
+        "value": value, "unit": "GB/s", "ms_per_step": ms_per_step, "steps": steps,
+        "tokens_per_s": world * B * sq / (ms_per_step * 1e-3),
+        "pct_of_8TBps": 100.0 * value / world / NOMINAL_HBM_GBS, "pct_of_measured_hbm": 100.0 * value / world / peak,
+        "bytes_per_step_per_gpu": float(per[0, 1]) / steps,
+        "per_rank": [{"ms_per_step": float(r[0]) / steps, "gbs": float(r[1]) / (float(r[0]) * 1e-3) / 1e9} for r in per],
+        "dtype": "fp8_e4m3 KV, bf16 q/out, f16 mma, fp32 softmax" if cfg["kv"] == "fp8" else "bf16",
+        "config": {"workload": f"{name}: {cfg['desc']}", "n_layer_pools": n_pools, "layers": layers_n,
+                   "pool_pages": n_pages, "sequences_per_gpu": B, "context_lengths": "same draw on every rank",
+                   "launch": "CUDA graph replay" if use_graph else "eager", "shared_prefix_pages": shared_pages,
+                   "l2_policy": "inputs larger than L2 (every layer streams a multi-GB pool)"
+                   if n_pages * HKV * PAGE * D * kv_bytes * 2 > 256e6 else
+                   "working set near L2 size; see tokens/s rather than GB/s"},
+        "gpu_launches": launches, "clocks": clocks,
+        "roofline": {"bound": "hbm",
+                     "kernel": ("paged_attn_decode_kernel" if cfg["kv"] == "fp8" and sq * 4 <= 8 else "paged_attn_kernel")
+                               + " (+ its merge launch" + (", the prefix pass on paged_prefill_kernel" if shared_pages else "") + ")",
+                     "achieved": achieved, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak,
+                     "traffic": None if traffic["ratio"] is None else traffic["ratio"] * attn_unique,
+                     "traffic_source": f"{traffic['profile']}: ncu dram__bytes_read+write of a reduced launch of the same "
+                                       "kernel over its algorithmic bytes, scaled by tokens",
+                     "traffic_profile_stale": traffic["stale"],
+                     "launch_ms_avg": attn_avg_ms, "algorithmic_bytes_per_launch": attn_unique,
+                     "timing": f"graph of {layers_n} attention calls replayed {attn_reps}x, CUDA events"},
+    }
+    if shared_pages:
+        rec["unique_bytes_per_step"] = step_unique
+        rec["unique_gbs"] = step_unique / (ms_per_step * 1e-3) / 1e9
+        rec["roofline"]["logical_bytes_per_launch"] = attn_bytes
+        rec["roofline"]["logical_gbs"] = logical
+        rec["roofline"]["bytes"] = ("unique: the pages every request shares are counted once per launch, which is how "
+                                    "often the kernel reads them; `value` counts them once per request (logical bytes)")
+    if e2e is not None:
+        e_ms, e_bytes = float(per[:, 2].max()), float(per[:, 3].sum())
+        rec["e2e"] = {"value": e_bytes / (e_ms * 1e-3) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d,
+                      "d2h_bytes_per_step": d2h, "ms_per_step": e_ms / e2e_steps, "steps": e2e_steps,
+                      "tokens_per_s": world * B * sq / (e_ms / e2e_steps * 1e-3)}
+    return rec
+
+
+def measure_prefill_record(name: str, args, device, rank: int, world: int, dist) -> dict | None:
+    """Sub-record of a prefill workload (compute-bound mode of the same op), timed like run_prefill."""
+    from kestrel_b200 import _native
+    wl = PrefillWorkload(name, device, rank)
+    warm = max(3, args.warmup)
+    steps = max(args.steps, 10)
+
+    def timed(fn, n):
+        for _ in range(warm):
+            fn()
+        torch.cuda.synchronize(device)
+        if dist is not None:
+            dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        torch.cuda.synchronize(device)
+        return e0.elapsed_time(e1) / n
+
+    ms = timed(wl.step_device, steps)
+    attn_ms = timed(lambda: wl.step_device(attn_only=True), steps)
+    flags = _native.device_status(device.index, clear=True)
+    if flags[0] != 0:
+        raise SystemExit(f"kernel diagnostics reported a problem in {name}: {flags}")
+    t = torch.tensor([ms], dtype=torch.float64, device=device)
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    flops, tokens, n_pass = wl.flops, wl.tokens, len(wl.passes)
+    del wl
+    torch.cuda.empty_cache()
+    if rank != 0:
+        return None
+    peak, peak_kind = measured_bf16_peak()
+    ms_all = t.item()
+    return {"metric": "paged append+prefill-attn TFLOP/s", "value": world * flops / (ms_all * 1e-3) / 1e12, "unit": "TFLOP/s",
+            "ms_per_step": ms_all, "steps": steps, "tokens_per_s": world * tokens / (ms_all * 1e-3),
+            "config": {"workload": f"{name}: {PREFILL_WORKLOADS[name]['desc']}", "passes_per_step": n_pass},
+            "roofline": {"bound": "tensor", "kernel": "paged_prefill_kernel", "achieved": flops / (attn_ms * 1e-3) / 1e12,
+                         "peak": peak, "peak_kind": peak_kind, "unit": "TFLOP/s",
+                         "frac": flops / (attn_ms * 1e-3) / 1e12 / peak, "traffic": None,
+                         "launch_ms_avg": attn_ms / n_pass, "algorithmic_flops_per_step": flops,
+                         "timing": "attention calls of a step alone, CUDA events"}}
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -977,6 +1319,8 @@ def main() -> None:
     ap.add_argument("--no-graph", action="store_true", help="launch the timed steps eagerly instead of replaying a CUDA graph")
     ap.add_argument("--no-shared-prefix", action="store_true",
                     help="cfg4: read the cached prefix once per request (plain calls) instead of once per batch")
+    ap.add_argument("--only", action="store_true",
+                    help="measure the named workload alone (no `workloads` map with the other configurations)")
     ap.add_argument("--batch", type=int, default=0, help="override the workload's batch (profiling on a small case)")
     ap.add_argument("--layers", type=int, default=0, help="override the workload's layer count (profiling)")
     args = ap.parse_args()
@@ -987,6 +1331,7 @@ def main() -> None:
         run_prefill(args)
         return
     if args.batch or args.layers:
+        args.only = True
         WORKLOADS[args.workload] = dict(WORKLOADS[args.workload])
         if args.batch:
             WORKLOADS[args.workload]["batch"] = args.batch
@@ -1014,120 +1359,43 @@ def main() -> None:
 
     from kestrel_b200 import _native
     _native.load()
-    cfg = WORKLOADS[args.workload]
     e2e_steps = 0 if args.no_e2e else max(3, min(args.steps, 5))
-    total_steps = 3 * args.warmup + args.steps + e2e_steps + 4
-    wl = GpuWorkload(args.workload, device, rank, total_steps, share_prefix=not args.no_shared_prefix)
+    head = measure_decode(args.workload, args, device, rank, world, dist, steps=args.steps, e2e_steps=e2e_steps)
 
-    def barrier():
-        torch.cuda.synchronize(device)
-        if dist is not None:
-            dist.barrier()
-        torch.cuda.synchronize(device)
-
-    use_graph = not args.no_graph
-    for _ in range(args.warmup):
-        wl.step_device()
-    if use_graph:
-        wl.capture_graph()
-        wl.step_graph()   # one untimed replay (the graph continues where the eager warm-up stopped)
-    step_fn = wl.step_graph if use_graph else wl.step_device
-    barrier()
-    sampler = ClockSampler(physical_gpu_index(local))
-    if rank == 0:
-        sampler.start()
-    first_step = wl.step_no
-    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    start.record()
-    for _ in range(args.steps):
-        step_fn()
-    stop.record()
-    barrier()
-    clocks = sampler.stop() if rank == 0 else None
-    elapsed_ms = start.elapsed_time(stop)
-    step_bytes = [algorithmic_bytes(wl.lengths_after(first_step + i), layers=wl.layers_n, kv_bytes=wl.kv_bytes,
-                                    head_dim=wl.D, sq=wl.sq, batch=wl.B) for i in range(args.steps)]
-    total_bytes = sum(b["per_step"] for b in step_bytes)
-    # roofline of the dominant kernel: the attention calls alone, at the lengths of the last step
-    attn_reps = max(3, min(20, int(2000 / max(1.0, elapsed_ms / args.steps))))
-    attn_ms = [wl.time_attention_launch(attn_reps)]
-    attn_bytes = algorithmic_bytes(wl.lengths_after(wl.step_no - 1), layers=wl.layers_n, kv_bytes=wl.kv_bytes,
-                                   head_dim=wl.D, sq=wl.sq, batch=wl.B)["attn_per_launch"]
-
-    # end-to-end: host buffers in, host result out, every step
-    e2e = None
-    if e2e_steps:
-        for _ in range(args.warmup):
-            wl.step_e2e()
-        barrier()
-        first_e2e = wl.step_no
-        t0 = torch.cuda.Event(enable_timing=True)
-        t1 = torch.cuda.Event(enable_timing=True)
-        t0.record()
-        for _ in range(e2e_steps):
-            wl.step_e2e()
-        t1.record()
-        barrier()
-        e2e_ms = t0.elapsed_time(t1)
-        e2e_bytes = sum(algorithmic_bytes(wl.lengths_after(first_e2e + i), layers=wl.layers_n, kv_bytes=wl.kv_bytes,
-                                          head_dim=wl.D, sq=wl.sq, batch=wl.B)["per_step"] for i in range(e2e_steps))
-        e2e = (e2e_ms, e2e_bytes)
-
-    flags = _native.device_status(local, clear=True)
-    if flags[0] != 0:
-        raise SystemExit(f"kernel diagnostics reported a problem: {flags}")
-
-    # aggregate over ranks: max time, summed bytes (no-ops without a process group)
-    from kestrel_b200.sharding import combine_step_stats
-    elapsed_ms, total_bytes = combine_step_stats(elapsed_ms, total_bytes, device)
-    e2e_ms_all, e2e_bytes_all = combine_step_stats(e2e[0] if e2e else 0.0, e2e[1] if e2e else 0.0, device)
+    # the other configurations, same process, same box: sub-records under "workloads"
+    extra = {}
+    if not args.only:
+        for name in ("cfg5", "cfg2", "cfg4"):
+            if name == args.workload:
+                continue
+            one_layer = WORKLOADS[name]["layers"] == 1
+            rec = measure_decode(name, args, device, rank, world, dist, steps=max(args.steps, 50) if one_layer else args.steps,
+                                 e2e_steps=0 if args.no_e2e else 3)
+            if rec is not None:
+                rec.pop("clocks", None)
+                extra[name] = rec
+        for name in ("pf_long", "pf_long_fp8", "pf4"):
+            rec = measure_prefill_record(name, args, device, rank, world, dist)
+            if rec is not None:
+                extra[name] = rec
     if rank != 0:
         if dist is not None:
             dist.destroy_process_group()
         return
 
-    peak, peak_kind = measured_hbm_peak()
-    value = total_bytes / (elapsed_ms * 1e-3) / 1e9
-    ms_per_step = elapsed_ms / args.steps
-    tok_s = world * wl.B * wl.sq / (ms_per_step * 1e-3)
-    attn_avg_ms = statistics.mean(attn_ms)
-    achieved = attn_bytes / (attn_avg_ms * 1e-3) / 1e9
-    h2d, d2h = wl.e2e_bytes()
-    line = {
-        "metric": "paged append+decode-attn HBM GB/s", "value": value, "unit": "GB/s", "n_gpus": world,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "fp8_e4m3 KV, bf16 q/out, f16 mma, fp32 softmax"
-        if cfg["kv"] == "fp8" else "bf16", "data": "synthetic",
-        "config": {"workload": f"{args.workload}: {cfg['desc']}", "n_layer_pools": wl.n_pools,
-                   "layers": wl.layers_n, "pool_pages": wl.n_pages, "sequences_per_gpu": wl.B,
-                   "launch": "CUDA graph replay" if use_graph else "eager",
-                   "shared_prefix_pages": wl.shared_pages,
-                   "l2_policy": "inputs larger than L2 (every layer streams a multi-GB pool)"
-                   if wl.n_pages * HKV * PAGE * wl.D * wl.kv_bytes * 2 > 256e6 else
-                   "working set near L2 size; see tokens/s rather than GB/s"},
-        "tokens_per_s": tok_s, "pct_of_8TBps": 100.0 * value / world / NOMINAL_HBM_GBS,
-        "pct_of_measured_hbm": 100.0 * value / world / peak,
-        "gpu_launches": wl.launches_per_step * args.steps,
-        "clocks": clocks,
-        "roofline": {"bound": "hbm",
-                     "kernel": ("paged_attn_decode_kernel" if cfg["kv"] == "fp8" and cfg["sq"] * 4 <= 8 else
-                                "paged_attn_kernel") + " (+ its plan and merge launches)",
-                     "achieved": achieved, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
-                     "frac": achieved / peak, "traffic": DRAM_TRAFFIC_RATIO[cfg["kv"]] * attn_bytes,
-                     "traffic_source": "ncu dram__bytes_read+write of a reduced launch of the same kernel, "
-                                       "scaled by tokens (profiles/)",
-                     "launch_ms_avg": attn_avg_ms, "algorithmic_bytes_per_launch": attn_bytes,
-                     "timing": f"graph of {wl.layers_n} attention calls replayed {attn_reps}x, CUDA events"},
-    }
-    if e2e_steps:
-        e2e_val = e2e_bytes_all / (e2e_ms_all * 1e-3) / 1e9
-        line["e2e"] = {"value": e2e_val, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                       "ms_per_step": e2e_ms_all / e2e_steps, "steps": e2e_steps,
-                       "tokens_per_s": world * wl.B * wl.sq / (e2e_ms_all / e2e_steps * 1e-3)}
+    line = {"metric": "paged append+decode-attn HBM GB/s", "value": head["value"], "unit": "GB/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": head["ms_per_step"], "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": head["dtype"], "data": "synthetic"}
+    for k in ("config", "tokens_per_s", "pct_of_8TBps", "pct_of_measured_hbm", "bytes_per_step_per_gpu", "per_rank",
+              "gpu_launches", "clocks", "roofline", "e2e", "unique_bytes_per_step", "unique_gbs"):
+        if k in head:
+            line[k] = head[k]
+    if extra:
+        line["workloads"] = extra
+        line["gpu_launches"] += sum(r.get("gpu_launches", 0) for r in extra.values())
     if world == 1 and not args.no_cpu_baseline:
         cb = time_cpu(args.workload, steps=50, warmup=1)
-        line["cpu_baseline"] = {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")}
-        line["cpu_baseline"]["tokens_per_s"] = cb["tokens_per_s"]
+        line["cpu_baseline"] = {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample", "tokens_per_s", "matmul_bound_gbs")}
     print(json.dumps(line), flush=True)
     if dist is not None:
         dist.destroy_process_group()
