@@ -30,7 +30,7 @@
 extern "C" {
 #endif
 
-#define KB200_ABI_VERSION 3
+#define KB200_ABI_VERSION 4
 
 #if defined(__GNUC__)
 #define KB200_API __attribute__((visibility("default")))
@@ -293,6 +293,32 @@ KB200_API int kb200_paged_attention(const kb200_attn_args* args);
 KB200_API int kb200_block_visibility(const int32_t* block_ids, int64_t ids_row_stride, int64_t batch,
                                      int64_t seqlen, int32_t* out, int64_t out_row_stride, int32_t device,
                                      void* stream);
+
+/* ---------------------------------------------------------------------------
+ * Sampling hand-off: one token per row from the logits of a decode step.
+ * Replaces kestrel_kernels' sampling.sample_step_from_logits(logits, temperatures,
+ * top_ps, out=, generator=, logprobs_out=) as called right after the decoder stack
+ * (kestrel/scheduler/scheduler.py:2986-2991, kestrel/scheduler/spatial.py:105-123).
+ *
+ *   logits        device [batch, vocab] of `logits_dtype` (F32/F16/BF16), row stride given
+ *   temperatures  device fp32 [batch]; <= 1e-6 (kestrel/scheduler/scheduler.py:55) means
+ *                 greedy: the first arg-max of the row, log-probability 0
+ *   top_ps        device fp32 [batch]; the nucleus is {i : p_i >= tau} with tau the largest
+ *                 probability whose tokens-at-or-above hold at least top_p of the mass
+ *                 (>= 1: the whole vocabulary)
+ *   uniforms      device fp32 [batch] in [0, 1): the row's random number (the Python
+ *                 wrapper draws them from the caller's torch generator); the token is
+ *                 the first one, in vocabulary order, whose running nucleus mass exceeds
+ *                 u * nucleus_mass
+ *   out_ids       device int64 [batch]
+ *   logprobs      device fp32 [batch] or NULL: logits[id] / T - logsumexp(logits / T) over the
+ *                 whole vocabulary (kestrel/scheduler/scheduler.py:3020-3042)
+ * Deterministic: all masses are summed in 64-bit fixed point.  vocab <= 2^20.
+ */
+KB200_API int kb200_sample_step_from_logits(
+    const void* logits, int32_t logits_dtype, int64_t batch, int64_t vocab, int64_t row_stride,
+    const float* temperatures, const float* top_ps, const float* uniforms, int64_t* out_ids,
+    float* logprobs, int32_t device, void* stream);
 
 /* ---------------------------------------------------------------------------
  * kb200_paged_attention without a caller-provided scratch buffer.  This entry

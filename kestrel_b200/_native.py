@@ -11,7 +11,7 @@ import threading
 from pathlib import Path
 
 LIB_PATH = Path(__file__).resolve().parent / "libkestrel_b200.so"
-ABI_VERSION = 3
+ABI_VERSION = 4
 
 DTYPE_F32, DTYPE_F16, DTYPE_BF16, DTYPE_E4M3 = 0, 1, 2, 3
 STATIC_SCRATCH_BYTES = 32 * 1024 * 1024  # KB200_STATIC_SCRATCH_BYTES
@@ -34,6 +34,7 @@ EXPORTS = (
     "kb200_paged_attention",
     "kb200_block_visibility",
     "kb200_paged_attention_static",
+    "kb200_sample_step_from_logits",
 )
 
 
@@ -137,6 +138,8 @@ def _declare(lib: C.CDLL) -> None:
     lib.kb200_block_visibility.argtypes = [vp, i64, i64, i64, vp, i64, i32, vp]
     lib.kb200_paged_attention.restype = C.c_int
     lib.kb200_paged_attention.argtypes = [C.POINTER(AttnArgs)]
+    lib.kb200_sample_step_from_logits.restype = C.c_int
+    lib.kb200_sample_step_from_logits.argtypes = [vp, i32, i64, i64, i64, vp, vp, vp, vp, vp, i32, vp]
     lib.kb200_paged_attention_static.restype = C.c_int
     lib.kb200_paged_attention_static.argtypes = [C.POINTER(AttnArgs)]
 

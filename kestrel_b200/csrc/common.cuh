@@ -141,6 +141,7 @@ enum KernelId : int {
   KID_ATTN_MERGE = 7,
   KID_ROPE_APPEND = 8,
   KID_PREFILL = 9,
+  KID_SAMPLE = 10,
 };
 
 }  // namespace kb200

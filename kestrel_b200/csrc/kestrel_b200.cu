@@ -5,6 +5,7 @@
 #include "rope_append.cuh"
 #include "paged_attention.cuh"
 #include "paged_prefill.cuh"
+#include "sampling.cuh"
 
 using namespace kb200;
 
@@ -136,6 +137,15 @@ int kb200_block_visibility(const int32_t* block_ids, int64_t ids_row_stride, int
   KB200_ENTER(device);
   return launch_block_visibility(block_ids, ids_row_stride, batch, seqlen, out, out_row_stride,
                                  static_cast<cudaStream_t>(stream));
+}
+
+int kb200_sample_step_from_logits(const void* logits, int32_t logits_dtype, int64_t batch, int64_t vocab,
+                                  int64_t row_stride, const float* temperatures, const float* top_ps,
+                                  const float* uniforms, int64_t* out_ids, float* logprobs, int32_t device,
+                                  void* stream) {
+  KB200_ENTER(device);
+  return launch_sample_step(logits, logits_dtype, batch, vocab, row_stride, temperatures, top_ps, uniforms, out_ids,
+                            logprobs, static_cast<cudaStream_t>(stream));
 }
 
 int kb200_paged_attention(const kb200_attn_args* args) {

@@ -63,7 +63,8 @@ struct AttnTile {
   static constexpr int TILE_N = TILE_RAW > 64 ? 64 : TILE_RAW;
   static constexpr int KV_TILE_BYTES = TILE_N * ROW_BYTES;
   static constexpr int STAGE_BYTES = 2 * KV_TILE_BYTES;           // K then V
-  static constexpr int SMEM_BYTES = NW * NS * STAGE_BYTES + NW * NS * 8 + 1024;
+  static constexpr int PLAN_OFF = (NW * NS * STAGE_BYTES + NW * NS * 8 + 15) & ~15;   // in-kernel plan, after the barriers
+  static constexpr int SMEM_BYTES = PLAN_OFF + 1024;                                  // + plan_smem_bytes(batch) at launch
 };
 
 struct AttnParams {
@@ -90,6 +91,7 @@ struct AttnParams {
   int* sq;              // [B] valid query rows
   int* qrow0;           // [B] first packed query row (0 in the padded layout)
   int* klen;            // [B] keys
+  int* bound_rec;       // [n_workers][8]: where each worker's range starts (written by the attention kernel for the merge)
   float* part_ml;       // [slots][16][2]  (scaled max in log2 units, sum)
   float* part_o;        // [slots][16][HD] unnormalised
   int64_t n_pages;
@@ -105,7 +107,37 @@ struct AttnParams {
   // 256-byte rows (16-bit K/V, head_dim 128) with pages at least a tile long: the tensor maps are
   // 5-D (64 elements, token, 128-byte half, head, page) and one box brings both halves of a page
   int merged_halves;
+  // plan_in_kernel: every CTA of the attention kernel computes the plan itself into shared memory
+  // (no plan launch; CTA 0 also stores it for the merge kernel); else attn_plan_kernel ran first
+  int plan_in_kernel;
+  long long total_q;     // rows of q (bounds the packed row ranges)
 };
+
+// Where the attention kernels read the plan from: shared memory (built by the CTA itself) or the
+// scratch arrays a plan launch filled.  Generic pointers serve both.
+struct PlanView {
+  const long long* tile_cum;
+  const int* seg_cum;
+  const int* nt;
+  const int* tile0;
+  const int* sq;
+  const int* qrow0;
+  const int* klen;
+};
+struct PlanOut {
+  long long* tile_cum;
+  int* seg_cum;
+  int* nt;
+  int* tile0;
+  int* sq;
+  int* qrow0;
+  int* klen;
+};
+constexpr int kPlanSmemMaxBatch = 1024;   // largest batch whose plan the attention kernels keep in shared memory
+__host__ __device__ constexpr int plan_smem_bytes(int batch) {
+  // tile_cum (B+1) x 8, then seg_cum (B+1) x 4 and five arrays of B ints, then the scan scratch
+  return ((((batch + 1) * 8 + (batch + 1) * 4 + 5 * batch * 4 + 7) & ~7) + 448 + 15) & ~15;   // 448 >= sizeof(PlanScan)
+}
 
 // ---------------------------------------------------------------------------
 // PTX helpers
@@ -226,19 +258,38 @@ __device__ __forceinline__ float bf16_bits_to_float(uint32_t bits16) { return __
 
 // ---------------------------------------------------------------------------
 // Plan: per-sequence tile/segment counts and their exclusive prefix sums.
-// One block; sequences are scanned 256 at a time with a running carry.
+// One block of NT threads; sequences are scanned NT at a time with a running carry.
+// Runs either as its own one-block launch (large batches) or at the start of every CTA of the
+// attention kernels, which then keep the result in shared memory.
 // ---------------------------------------------------------------------------
-__global__ void __launch_bounds__(256) attn_plan_kernel(const AttnParams p) {
-  __shared__ long long warp_t[8];
-  __shared__ int warp_s[8];
-  __shared__ long long carry_t;
-  __shared__ int carry_s;
+struct PlanScan {
+  long long warp_t[32];
+  int warp_s[32];
+  long long carry_t;
+  int carry_s;
+  int bad;
+};
+static_assert(sizeof(PlanScan) <= 448, "plan_smem_bytes reserves 448 bytes for the scan scratch");
+
+template <int NT>
+__device__ __forceinline__ void build_plan(const AttnParams& p, const PlanOut& o, PlanScan& sc, bool reporter) {
   const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
-  pdl_wait();   // the plan arrays may still be read by the merge kernel of the previous call
-  pdl_launch_dependents();
-  if (tid == 0) { carry_t = 0; carry_s = 0; }
+  if (tid == 0) { sc.carry_t = 0; sc.carry_s = 0; sc.bad = 0; }
   __syncthreads();
-  for (int base = 0; base < p.batch; base += 256) {
+  if (p.cu_seqlens_q) {
+    // Packed rows: the row ranges must be non-negative, ascending and inside q.  Anything else would
+    // make more segments than the scratch was sized for: such a call computes nothing.
+    int bad = 0;
+    for (int b = tid; b < p.batch; b += NT) {
+      const int r0 = p.cu_seqlens_q[b], r1 = p.cu_seqlens_q[b + 1];
+      if (r0 < 0 || r1 < r0 || (long long)r1 > p.total_q) bad = 1;
+    }
+    if (bad) sc.bad = 1;
+    __syncthreads();
+    if (sc.bad && reporter && tid == 0) report(KB200_STATUS_BAD_ROW, -1, KID_ATTN_PLAN);
+  }
+  const bool drop_all = sc.bad != 0;
+  for (int base = 0; base < p.batch; base += NT) {
     const int b = base + tid;
     long long cnt_t = 0;
     int cnt_s = 0;
@@ -254,10 +305,10 @@ __global__ void __launch_bounds__(256) attn_plan_kernel(const AttnParams p) {
         sq = p.seqlen_q;
         if (p.seqused_q) sq = min(sq, p.seqused_q[b]);
       }
-      if (sq < 0) sq = 0;
+      if (sq < 0 || drop_all) sq = 0;
       // a query row that cannot see all of the skipped prefix under the causal mask (or a sequence
       // shorter than the prefix) breaks the caller's promise: results for it are undefined
-      if (p.k_skip > 0 && L_rel < (p.causal ? sq : 0)) report(KB200_STATUS_BAD_PREFIX, b, KID_ATTN_PLAN);
+      if (p.k_skip > 0 && L_rel < (p.causal ? sq : 0) && reporter) report(KB200_STATUS_BAD_PREFIX, b, KID_ATTN_PLAN);
       int t0 = 0;
       if (p.window_left >= 0) {
         int kmin = L - sq - p.window_left;
@@ -267,11 +318,11 @@ __global__ void __launch_bounds__(256) attn_plan_kernel(const AttnParams p) {
       const int nmb = (p.group * sq + p.rows_per_seg - 1) / p.rows_per_seg;
       cnt_s = p.hkv * nmb;
       cnt_t = (long long)ntile * cnt_s;
-      p.nt[b] = ntile;
-      p.tile0[b] = t0;
-      p.sq[b] = sq;
-      p.qrow0[b] = row0;
-      p.klen[b] = L;
+      o.nt[b] = ntile;
+      o.tile0[b] = t0;
+      o.sq[b] = sq;
+      o.qrow0[b] = row0;
+      o.klen[b] = L;
     }
     // inclusive warp scans
     long long it = cnt_t;
@@ -282,23 +333,60 @@ __global__ void __launch_bounds__(256) attn_plan_kernel(const AttnParams p) {
       int us = __shfl_up_sync(0xffffffffu, is, d);
       if (lane >= d) { it += ut; is += us; }
     }
-    if (lane == 31) { warp_t[wid] = it; warp_s[wid] = is; }
+    if (lane == 31) { sc.warp_t[wid] = it; sc.warp_s[wid] = is; }
     __syncthreads();
-    long long off_t = carry_t;
-    int off_s = carry_s;
-    for (int w = 0; w < wid; ++w) { off_t += warp_t[w]; off_s += warp_s[w]; }
+    long long off_t = sc.carry_t;
+    int off_s = sc.carry_s;
+    for (int w = 0; w < wid; ++w) { off_t += sc.warp_t[w]; off_s += sc.warp_s[w]; }
     if (b < p.batch) {
-      p.tile_cum[b] = off_t + it - cnt_t;
-      p.seg_cum[b] = off_s + is - cnt_s;
+      o.tile_cum[b] = off_t + it - cnt_t;
+      o.seg_cum[b] = off_s + is - cnt_s;
     }
     __syncthreads();
-    if (tid == 255) { carry_t = off_t + it; carry_s = off_s + is; }
+    if (tid == NT - 1) { sc.carry_t = off_t + it; sc.carry_s = off_s + is; }
     __syncthreads();
   }
   if (tid == 0) {
-    p.tile_cum[p.batch] = carry_t;
-    p.seg_cum[p.batch] = carry_s;
+    o.tile_cum[p.batch] = sc.carry_t;
+    o.seg_cum[p.batch] = sc.carry_s;
   }
+  __syncthreads();
+}
+
+__global__ void __launch_bounds__(256) attn_plan_kernel(const AttnParams p) {
+  __shared__ PlanScan sc;
+  pdl_wait();   // the plan arrays may still be read by the merge kernel of the previous call
+  pdl_launch_dependents();
+  const PlanOut o{p.tile_cum, p.seg_cum, p.nt, p.tile0, p.sq, p.qrow0, p.klen};
+  build_plan<256>(p, o, sc, true);
+}
+
+// Plan of an attention CTA: built into shared memory at `plan_smem` (plan_in_kernel; CTA 0 also stores
+// it in the scratch arrays for the merge kernel) or taken from the scratch arrays.  Block-wide.
+template <int NT>
+__device__ __forceinline__ PlanView attention_cta_plan(const AttnParams& p, uint8_t* plan_smem) {
+  if (!p.plan_in_kernel) return PlanView{p.tile_cum, p.seg_cum, p.nt, p.tile0, p.sq, p.qrow0, p.klen};
+  const int B = p.batch;
+  long long* tc = reinterpret_cast<long long*>(plan_smem);
+  int* ints = reinterpret_cast<int*>(tc + (B + 1));
+  const PlanOut o{tc, ints, ints + (B + 1), ints + (B + 1) + B, ints + (B + 1) + 2 * B, ints + (B + 1) + 3 * B,
+                  ints + (B + 1) + 4 * B};
+  PlanScan& sc = *reinterpret_cast<PlanScan*>(plan_smem + (((B + 1) * 8 + (B + 1) * 4 + 5 * B * 4 + 7) & ~7));
+  build_plan<NT>(p, o, sc, blockIdx.x == 0);
+  if (blockIdx.x == 0) {
+    for (int b = threadIdx.x; b <= B; b += NT) {
+      p.tile_cum[b] = o.tile_cum[b];
+      p.seg_cum[b] = o.seg_cum[b];
+      if (b < B) {
+        p.nt[b] = o.nt[b];
+        p.tile0[b] = o.tile0[b];
+        p.sq[b] = o.sq[b];
+        p.qrow0[b] = o.qrow0[b];
+        p.klen[b] = o.klen[b];
+      }
+    }
+  }
+  return PlanView{o.tile_cum, o.seg_cum, o.nt, o.tile0, o.sq, o.qrow0, o.klen};
 }
 
 // Position of a warp inside the flat tile space (identical on all 32 lanes).
@@ -306,51 +394,59 @@ struct Cursor {
   int b, seg, nseg, t, nt, tile0, L, sq, nmb, segbase, qr;   // qr: first packed query row of the sequence
 };
 
-__device__ __forceinline__ void cursor_load_seq(const AttnParams& p, Cursor& c) {
-  c.nt = p.nt[c.b];
-  c.tile0 = p.tile0[c.b];
-  c.L = p.klen[c.b];
-  c.sq = p.sq[c.b];
-  c.qr = p.cu_seqlens_q ? p.qrow0[c.b] : 0;   // loaded with the rest: no dependent load where Q is addressed
+__device__ __forceinline__ void cursor_load_seq(const AttnParams& p, const PlanView& pv, Cursor& c) {
+  c.nt = pv.nt[c.b];
+  c.tile0 = pv.tile0[c.b];
+  c.L = pv.klen[c.b];
+  c.sq = pv.sq[c.b];
+  c.qr = p.cu_seqlens_q ? pv.qrow0[c.b] : 0;   // loaded with the rest: no dependent load where Q is addressed
   c.nmb = (p.group * c.sq + p.rows_per_seg - 1) / p.rows_per_seg;
   c.nseg = p.hkv * c.nmb;
-  c.segbase = p.seg_cum[c.b];
+  c.segbase = pv.seg_cum[c.b];
 }
 
 // Finds the sequence and segment that own flat tile g.  Called by all 32 lanes of a warp with
 // the same g: the search over tile_cum is 32-way (one probe per lane, a vote per round), two
 // dependent loads for up to 1024 sequences where a binary search would chain ten.
-__device__ __forceinline__ void cursor_locate(const AttnParams& p, Cursor& c, long long g) {
+__device__ __forceinline__ void cursor_locate(const AttnParams& p, const PlanView& pv, Cursor& c, long long g) {
   const int lane = threadIdx.x & 31;
   int lo = 0, hi = p.batch;  // tile_cum[lo] <= g < tile_cum[hi]
   while (hi - lo > 1) {
     const int step = (hi - lo + 31) >> 5;
     const int idx = lo + (lane + 1) * step;
-    const bool le = idx < hi && p.tile_cum[idx] <= g;
+    const bool le = idx < hi && pv.tile_cum[idx] <= g;
     const int cnt = __popc(__ballot_sync(0xffffffffu, le));   // probes are monotone: the first cnt lanes vote yes
     const int nlo = lo + cnt * step;
     hi = min(hi, nlo + step);
     lo = nlo;
   }
   c.b = lo;
-  cursor_load_seq(p, c);
-  const long long off = g - p.tile_cum[lo];
+  cursor_load_seq(p, pv, c);
+  const long long off = g - pv.tile_cum[lo];
   c.seg = (int)(off / c.nt);
   c.t = (int)(off - (long long)c.seg * c.nt);
 }
 
 // Moves to the next tile; only called while tiles remain, so a non-empty
 // sequence always follows.
-__device__ __forceinline__ void cursor_advance(const AttnParams& p, Cursor& c) {
+__device__ __forceinline__ void cursor_advance(const AttnParams& p, const PlanView& pv, Cursor& c) {
   if (++c.t < c.nt) return;
   c.t = 0;
   if (++c.seg < c.nseg) return;
   c.seg = 0;
   while (++c.b < p.batch) {
-    cursor_load_seq(p, c);
+    cursor_load_seq(p, pv, c);
     if (c.nt > 0 && c.nseg > 0) return;
   }
   c.b = p.batch - 1;  // not reached when the caller counts tiles correctly
+}
+
+// What the merge kernel needs to know about the tile a worker's range starts at: written by lane 0 of
+// every worker whose range starts inside [0, total), read by the merge block of that boundary.
+__device__ __forceinline__ void write_boundary_record(const AttnParams& p, int w, const Cursor& c) {
+  int4* rec = reinterpret_cast<int4*>(p.bound_rec + 8 * (size_t)w);
+  rec[0] = make_int4(c.b, c.seg, c.t, c.nt);
+  rec[1] = make_int4(c.sq, c.qr, c.segbase, c.nmb);
 }
 
 template <int RB>
@@ -371,6 +467,7 @@ struct TileProducer {
   static constexpr int RB = T::RB;
   static constexpr int NH = T::NH;
   const AttnParams& p;
+  const PlanView& pv;
   const CUtensorMap* tmK;
   const CUtensorMap* tmV;
   uint32_t stage0, bar0;
@@ -379,15 +476,16 @@ struct TileProducer {
   const int32_t* pt_row;   // page-table row of the sequence the cursor is in
   Cursor pc;
 
-  __device__ __forceinline__ TileProducer(const AttnParams& p_, const CUtensorMap* k, const CUtensorMap* v,
-                                          uint32_t stage0_, uint32_t bar0_, int lane_, long long r0, int my_tiles_)
-      : p(p_), tmK(k), tmV(v), stage0(stage0_), bar0(bar0_), lane(lane_), my_tiles(my_tiles_), issued(0) {
+  __device__ __forceinline__ TileProducer(const AttnParams& p_, const PlanView& pv_, const CUtensorMap* k,
+                                          const CUtensorMap* v, uint32_t stage0_, uint32_t bar0_, int lane_,
+                                          long long r0, int my_tiles_)
+      : p(p_), pv(pv_), tmK(k), tmV(v), stage0(stage0_), bar0(bar0_), lane(lane_), my_tiles(my_tiles_), issued(0) {
     p_shift = 31 - __clz(p.page_size);
     box_rows = p.page_size < TILE_N ? p.page_size : TILE_N;
     box_shift = 31 - __clz(box_rows);
     hb_shift = (NH == 2 && !p.merged_halves) ? 1 : 0;   // log2 of the boxes per (page, K|V)
     nbox = (TILE_N >> box_shift) << (hb_shift + 1);
-    cursor_locate(p, pc, r0);
+    cursor_locate(p, pv, pc, r0);
     enter_segment();
     pg = lane < nbox ? page_for(lane) : 0;
   }
@@ -427,7 +525,7 @@ struct TileProducer {
     }
     ++issued;
     if (issued < my_tiles) {
-      cursor_advance(p, pc);
+      cursor_advance(p, pv, pc);
       if (pc.t == 0) enter_segment();   // (a new segment, possibly of a new sequence)
       pg = lane < nbox ? page_for(lane) : 0;
     }
@@ -468,19 +566,28 @@ paged_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
     fence_proxy_async();
   }
   __syncthreads();
-  // No block-wide barrier below this line: warps are independent workers.
   pdl_launch_dependents();
-  pdl_wait();   // the plan (and, before it, the append) must have completed
+  pdl_wait();   // the append (and a plan launch, if there was one) must have completed
+  const PlanView plan = attention_cta_plan<NW * 32>(p, smem_raw + (smem_base - smem_u32(smem_raw)) + T::PLAN_OFF);
+  // No block-wide barrier below this line: warps are independent workers.
 
-  const long long total = p.tile_cum[p.batch];
+  const long long total = plan.tile_cum[p.batch];
   const int w = blockIdx.x * kAttnWarps + warp;
   const long long r0 = (long long)w * total / p.n_workers;
   const long long r1 = (long long)(w + 1) * total / p.n_workers;
-  if (r0 >= r1) return;
+  if (r0 >= r1) {
+    if (w > 0 && r0 < total) {   // an empty range still marks a boundary the merge kernel may have to handle
+      Cursor c0;
+      cursor_locate(p, plan, c0, r0);
+      if (lane == 0) write_boundary_record(p, w, c0);
+    }
+    return;
+  }
   const int my_tiles = (int)(r1 - r0);
 
-  TileProducer<T, KVB> prod(p, &tmK, &tmV, my_stage0, bar0, lane, r0, my_tiles);
+  TileProducer<T, KVB> prod(p, plan, &tmK, &tmV, my_stage0, bar0, lane, r0, my_tiles);
   Cursor cc = prod.pc;   // consumer side: starts where the producer starts
+  if (lane == 0 && w > 0) write_boundary_record(p, w, cc);
   for (int s = 0; s < NS && prod.more(); ++s) prod.issue(s);
 
   uint32_t qf[NQF][4];
@@ -745,6 +852,9 @@ paged_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
         char* out0 = p.out + 2 * (ob + (int64_t)(qr + j0) * p.o_rs + (int64_t)hq0 * p.o_hs);
         char* out1 = p.out + 2 * (ob + (int64_t)(qr + j1) * p.o_rs + (int64_t)hq1 * p.o_hs);
         const bool obf = KVB == 2 ? BF16 : (p.q_is_bf16 != 0);
+        constexpr float kLn2 = 0.6931471805599453f;
+        const float lse0 = l0 > 0.f ? m0 * sl2 * kLn2 + logf(l0) : -INFINITY;
+        const float lse1 = l1 > 0.f ? m1 * sl2 * kLn2 + logf(l1) : -INFINITY;
         if constexpr (KVB == 2) {
 #pragma unroll
           for (int i = 0; i < NOT; ++i) {
@@ -767,11 +877,8 @@ paged_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
           }
         }
         if (p.lse && c4 == 0) {
-          constexpr float kLn2 = 0.6931471805599453f;
-          if (valid0) p.lse[(int64_t)cc.b * p.lse_bs + (int64_t)hq0 * p.lse_hs + qr + j0] =
-              l0 > 0.f ? m0 * sl2 * kLn2 + logf(l0) : -INFINITY;
-          if (valid1) p.lse[(int64_t)cc.b * p.lse_bs + (int64_t)hq1 * p.lse_hs + qr + j1] =
-              l1 > 0.f ? m1 * sl2 * kLn2 + logf(l1) : -INFINITY;
+          if (valid0) p.lse[(int64_t)cc.b * p.lse_bs + (int64_t)hq0 * p.lse_hs + qr + j0] = lse0;
+          if (valid1) p.lse[(int64_t)cc.b * p.lse_bs + (int64_t)hq1 * p.lse_hs + qr + j1] = lse1;
         }
       } else {
         const int64_t slot = (int64_t)seg_id + w;
@@ -803,7 +910,7 @@ paged_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
       }
       fresh = true;
     }
-    if (it + 1 < my_tiles) cursor_advance(p, cc);
+    if (it + 1 < my_tiles) cursor_advance(p, plan, cc);
   }
 }
 
@@ -869,19 +976,28 @@ paged_attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
     fence_proxy_async();
   }
   __syncthreads();
-  // No block-wide barrier below this line: warps are independent workers.
   pdl_launch_dependents();
-  pdl_wait();   // the plan (and, before it, the append) must have completed
+  pdl_wait();   // the append (and a plan launch, if there was one) must have completed
+  const PlanView plan = attention_cta_plan<NW * 32>(p, smem_raw + (smem_base - smem_u32(smem_raw)) + T::PLAN_OFF);
+  // No block-wide barrier below this line: warps are independent workers.
 
-  const long long total = p.tile_cum[p.batch];
+  const long long total = plan.tile_cum[p.batch];
   const int w = blockIdx.x * NW + warp;
   const long long r0 = (long long)w * total / p.n_workers;
   const long long r1 = (long long)(w + 1) * total / p.n_workers;
-  if (r0 >= r1) return;
+  if (r0 >= r1) {
+    if (w > 0 && r0 < total) {   // an empty range still marks a boundary the merge kernel may have to handle
+      Cursor c0;
+      cursor_locate(p, plan, c0, r0);
+      if (lane == 0) write_boundary_record(p, w, c0);
+    }
+    return;
+  }
   const int my_tiles = (int)(r1 - r0);
 
-  TileProducer<T, KVB> prod(p, &tmK, &tmV, my_stage0, bar0, lane, r0, my_tiles);
+  TileProducer<T, KVB> prod(p, plan, &tmK, &tmV, my_stage0, bar0, lane, r0, my_tiles);
   Cursor cc = prod.pc;   // consumer side: starts where the producer starts
+  if (lane == 0 && w > 0) write_boundary_record(p, w, cc);
   for (int s = 0; s < NS && prod.more(); ++s) prod.issue(s);
 
   // lane-constant parts of the ldmatrix addresses
@@ -1151,31 +1267,32 @@ paged_attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
         char* out0 = p.out + 2 * (ob + (int64_t)(qrow_base + q0 / p.group) * p.o_rs + (int64_t)hq0 * p.o_hs);
         char* out1 = p.out + 2 * (ob + (int64_t)(qrow_base + q1 / p.group) * p.o_rs + (int64_t)hq1 * p.o_hs);
         const bool obf = KVB == 2 ? BF16 : (p.q_is_bf16 != 0);
+        constexpr float kLn2 = 0.6931471805599453f;
+        float lse0 = l0 > 0.f ? m0 * sl2 * kLn2 + logf(l0) : -INFINITY;
+        float lse1 = l1 > 0.f ? m1 * sl2 * kLn2 + logf(l1) : -INFINITY;
+        {
 #pragma unroll
-        for (int i = 0; i < NDT; ++i) {
-          const int d = KVB == 2 ? 16 * i + g8 : 16 * i + 2 * g8;
-          if constexpr (KVB == 2) {
-            if (v0) {
-              *reinterpret_cast<uint16_t*>(out0 + 2 * d) = (uint16_t)(pack2<BF16>(o[i][0] * i0, 0.f) & 0xffffu);
-              *reinterpret_cast<uint16_t*>(out0 + 2 * (d + dstep)) = (uint16_t)(pack2<BF16>(o[i][2] * i0, 0.f) & 0xffffu);
+          for (int i = 0; i < NDT; ++i) {
+            const int d = KVB == 2 ? 16 * i + g8 : 16 * i + 2 * g8;
+            const float a0 = o[i][0] * i0, a2 = o[i][2] * i0, b1 = o[i][1] * i1, b3 = o[i][3] * i1;
+            if constexpr (KVB == 2) {
+              if (v0) {
+                *reinterpret_cast<uint16_t*>(out0 + 2 * d) = (uint16_t)(pack2<BF16>(a0, 0.f) & 0xffffu);
+                *reinterpret_cast<uint16_t*>(out0 + 2 * (d + dstep)) = (uint16_t)(pack2<BF16>(a2, 0.f) & 0xffffu);
+              }
+              if (v1) {
+                *reinterpret_cast<uint16_t*>(out1 + 2 * d) = (uint16_t)(pack2<BF16>(b1, 0.f) & 0xffffu);
+                *reinterpret_cast<uint16_t*>(out1 + 2 * (d + dstep)) = (uint16_t)(pack2<BF16>(b3, 0.f) & 0xffffu);
+              }
+            } else {
+              if (v0) *reinterpret_cast<uint32_t*>(out0 + 2 * d) = obf ? pack2<true>(a0, a2) : pack2<false>(a0, a2);
+              if (v1) *reinterpret_cast<uint32_t*>(out1 + 2 * d) = obf ? pack2<true>(b1, b3) : pack2<false>(b1, b3);
             }
-            if (v1) {
-              *reinterpret_cast<uint16_t*>(out1 + 2 * d) = (uint16_t)(pack2<BF16>(o[i][1] * i1, 0.f) & 0xffffu);
-              *reinterpret_cast<uint16_t*>(out1 + 2 * (d + dstep)) = (uint16_t)(pack2<BF16>(o[i][3] * i1, 0.f) & 0xffffu);
-            }
-          } else {
-            if (v0) *reinterpret_cast<uint32_t*>(out0 + 2 * d) =
-                obf ? pack2<true>(o[i][0] * i0, o[i][2] * i0) : pack2<false>(o[i][0] * i0, o[i][2] * i0);
-            if (v1) *reinterpret_cast<uint32_t*>(out1 + 2 * d) =
-                obf ? pack2<true>(o[i][1] * i1, o[i][3] * i1) : pack2<false>(o[i][1] * i1, o[i][3] * i1);
           }
         }
         if (p.lse && g8 == 0) {
-          constexpr float kLn2 = 0.6931471805599453f;
-          if (v0) p.lse[(int64_t)cc.b * p.lse_bs + (int64_t)hq0 * p.lse_hs + qrow_base + q0 / p.group] =
-              l0 > 0.f ? m0 * sl2 * kLn2 + logf(l0) : -INFINITY;
-          if (v1) p.lse[(int64_t)cc.b * p.lse_bs + (int64_t)hq1 * p.lse_hs + qrow_base + q1 / p.group] =
-              l1 > 0.f ? m1 * sl2 * kLn2 + logf(l1) : -INFINITY;
+          if (v0) p.lse[(int64_t)cc.b * p.lse_bs + (int64_t)hq0 * p.lse_hs + qrow_base + q0 / p.group] = lse0;
+          if (v1) p.lse[(int64_t)cc.b * p.lse_bs + (int64_t)hq1 * p.lse_hs + qrow_base + q1 / p.group] = lse1;
         }
       } else {
         const int64_t slot = (int64_t)(cc.segbase + cc.seg) + w;
@@ -1204,87 +1321,97 @@ paged_attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
       }
       fresh = true;
     }
-    if (it + 1 < my_tiles) cursor_advance(p, cc);
+    if (it + 1 < my_tiles) cursor_advance(p, plan, cc);
   }
 }
 
 // ---------------------------------------------------------------------------
-// Merge: blocks stride over the segments.  Segments written directly are skipped,
-// segments without keys are zero-filled, the others combine their partials.
+// Merge.  A segment that lies inside one warp's tile range was normalised and written by the
+// attention kernel.  Only a segment cut by a range boundary left partials, so the blocks stride
+// over the W - 1 boundaries, not over the segments: boundary w (the first tile of worker w) is
+// handled when it falls strictly inside a segment and is the first boundary to do so.  A second
+// loop zero-fills the rows of sequences without visible keys.
 // ---------------------------------------------------------------------------
 template <int HD>
 __global__ void __launch_bounds__(128) attn_merge_kernel(const AttnParams p) {
   pdl_wait();
   pdl_launch_dependents();
-  const int nseg_total = p.seg_cum[p.batch];
   const long long total = p.tile_cum[p.batch];
-  // blocks stride over the segments: most segments of a batch of short sequences were written by
-  // the attention kernel itself and only cost the look-up below
-  for (int seg = blockIdx.x; seg < nseg_total; seg += gridDim.x) {
-    int lo = 0, hi = p.batch;
-    if (p.uniform_nseg > 0) {
-      lo = seg / p.uniform_nseg;  // no dependent loads on the common path
-    } else {
-      while (hi - lo > 1) {
-        const int mid = (lo + hi) >> 1;
-        if (p.seg_cum[mid] <= seg) lo = mid; else hi = mid;
-      }
-    }
-    const int b = lo;
-    const int sq = p.sq[b];
-    const int nmb = (p.group * sq + p.rows_per_seg - 1) / p.rows_per_seg;
-    const int sib = seg - p.seg_cum[b];
-    const int h = sib / nmb, mb = sib - h * nmb;
-    const int nt = p.nt[b];
-    int wf = 0, wl = -1;
-    if (nt > 0) {
-      const long long t0 = p.tile_cum[b] + (long long)sib * nt;
-      const long long t1 = t0 + nt;
-      wf = (int)(((t0 + 1) * p.n_workers - 1) / total);
-      wl = (int)((t1 * p.n_workers - 1) / total);
-      if (wf == wl) continue;  // written by the attention kernel itself
-    }
-    const int nrows = p.group * sq;
-    const float vscale = p.vs_vec ? p.vs_vec[h] : p.vs;
-    const int qr = p.qrow0[b];
-    constexpr float kLn2 = 0.6931471805599453f;
-    // A worker between wf and wl whose range is empty (fewer tiles than workers) wrote nothing.
-    const bool all_have = total >= p.n_workers;
-    auto has_tiles = [&](int wi) {
-      return all_have || (long long)wi * total / p.n_workers < (long long)(wi + 1) * total / p.n_workers;
-    };
-    // one work item = 4 consecutive d of one query row; the partial loads of an item are independent
-    constexpr int kQuads = HD / 4;
-    for (int item = threadIdx.x; item < p.rows_per_seg * kQuads; item += 128) {
-      const int rl = item / kQuads, d = (item - rl * kQuads) * 4;
-      const int row = mb * p.rows_per_seg + rl;
-      if (row >= nrows) continue;
-      float M = -INFINITY;
-      for (int wi = wf; wi <= wl; ++wi)
-        if (has_tiles(wi)) M = fmaxf(M, p.part_ml[((int64_t)seg + wi) * (kRowsPerSeg * 2) + rl * 2]);
-      float L = 0.f;
-      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (M != -INFINITY) {
-        for (int wi = wf; wi <= wl; ++wi) {
-          if (!has_tiles(wi)) continue;
-          const int64_t slot = (int64_t)seg + wi;
-          const float2 ml = *reinterpret_cast<const float2*>(p.part_ml + slot * (kRowsPerSeg * 2) + rl * 2);
-          if (ml.x == -INFINITY) continue;
-          const float wgt = ex2(ml.x - M);
-          const float4 o = *reinterpret_cast<const float4*>(p.part_o + slot * (kRowsPerSeg * HD) + rl * HD + d);
-          L += wgt * ml.y;
-          acc.x += wgt * o.x; acc.y += wgt * o.y; acc.z += wgt * o.z; acc.w += wgt * o.w;
+  constexpr float kLn2 = 0.6931471805599453f;
+  constexpr int kQuads = HD / 4;
+  if (total > 0) {
+    for (int w = blockIdx.x + 1; w < p.n_workers; w += gridDim.x) {
+      const long long g = (long long)w * total / p.n_workers;
+      if (g <= 0 || g >= total) continue;
+      // where tile g lies: the record the worker that starts there left (no search, one load)
+      const int4* rec = reinterpret_cast<const int4*>(p.bound_rec + 8 * (size_t)w);
+      const int4 ra = rec[0], rb = rec[1];
+      Cursor c;
+      c.b = ra.x; c.seg = ra.y; c.t = ra.z; c.nt = ra.w;
+      c.sq = rb.x; c.qr = rb.y; c.segbase = rb.z; c.nmb = rb.w;
+      if (c.t == 0) continue;       // the boundary coincides with the segment's first tile: not a cut
+      const long long t0 = g - c.t, t1 = t0 + c.nt;   // the segment's tiles
+      if ((long long)(w - 1) * total / p.n_workers > t0) continue;   // an earlier boundary cuts it too: that one merges
+      const int seg = c.segbase + c.seg;
+      const int wf = (int)(((t0 + 1) * p.n_workers - 1) / total);
+      const int wl = (int)((t1 * p.n_workers - 1) / total);
+      const int b = c.b, sq = c.sq;
+      const int h = c.seg / c.nmb, mb = c.seg - h * c.nmb;
+      const int nrows = p.group * sq;
+      const float vscale = p.vs_vec ? p.vs_vec[h] : p.vs;
+      const int qr = c.qr;
+      // A worker between wf and wl whose range is empty (fewer tiles than workers) wrote nothing.
+      const bool all_have = total >= p.n_workers;
+      auto has_tiles = [&](int wi) {
+        return all_have || (long long)wi * total / p.n_workers < (long long)(wi + 1) * total / p.n_workers;
+      };
+      // one work item = 4 consecutive d of one query row; the partial loads of an item are independent
+      for (int item = threadIdx.x; item < p.rows_per_seg * kQuads; item += 128) {
+        const int rl = item / kQuads, d = (item - rl * kQuads) * 4;
+        const int row = mb * p.rows_per_seg + rl;
+        if (row >= nrows) continue;
+        float M = -INFINITY;
+        for (int wi = wf; wi <= wl; ++wi)
+          if (has_tiles(wi)) M = fmaxf(M, p.part_ml[((int64_t)seg + wi) * (kRowsPerSeg * 2) + rl * 2]);
+        float L = 0.f;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (M != -INFINITY) {
+          for (int wi = wf; wi <= wl; ++wi) {
+            if (!has_tiles(wi)) continue;
+            const int64_t slot = (int64_t)seg + wi;
+            const float2 ml = *reinterpret_cast<const float2*>(p.part_ml + slot * (kRowsPerSeg * 2) + rl * 2);
+            if (ml.x == -INFINITY) continue;
+            const float wgt = ex2(ml.x - M);
+            const float4 o = *reinterpret_cast<const float4*>(p.part_o + slot * (kRowsPerSeg * HD) + rl * HD + d);
+            L += wgt * ml.y;
+            acc.x += wgt * o.x; acc.y += wgt * o.y; acc.z += wgt * o.z; acc.w += wgt * o.w;
+          }
         }
+        const float inv = L > 0.f ? vscale / L : 0.f;
+        const int j = row / p.group, hq = h * p.group + row % p.group;
+        const float lse = L > 0.f ? M * kLn2 + logf(L) : -INFINITY;
+        const float4 r = make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
+        const int64_t oi = (int64_t)b * p.o_bs + (int64_t)(qr + j) * p.o_rs + (int64_t)hq * p.o_hs + d;
+        uint2 packed;
+        if (p.q_is_bf16) packed = make_uint2(pack2<true>(r.x, r.y), pack2<true>(r.z, r.w));
+        else packed = make_uint2(pack2<false>(r.x, r.y), pack2<false>(r.z, r.w));
+        *reinterpret_cast<uint2*>(p.out + 2 * oi) = packed;
+        if (p.lse && d == 0) p.lse[(int64_t)b * p.lse_bs + (int64_t)hq * p.lse_hs + qr + j] = lse;
       }
-      const float inv = L > 0.f ? vscale / L : 0.f;
-      const int j = row / p.group, hq = h * p.group + row % p.group;
+    }
+  }
+  // sequences with query rows but no visible keys: zeros
+  for (int b = blockIdx.x; b < p.batch; b += gridDim.x) {
+    const int sq = p.sq[b];
+    if (p.nt[b] > 0 || sq <= 0) continue;
+    const int qr = p.qrow0[b];
+    const int items = sq * p.hq * kQuads;
+    for (int item = threadIdx.x; item < items; item += 128) {
+      const int d = (item % kQuads) * 4, rh = item / kQuads;
+      const int hq = rh % p.hq, j = rh / p.hq;
       const int64_t oi = (int64_t)b * p.o_bs + (int64_t)(qr + j) * p.o_rs + (int64_t)hq * p.o_hs + d;
-      uint2 packed;
-      if (p.q_is_bf16) packed = make_uint2(pack2<true>(acc.x * inv, acc.y * inv), pack2<true>(acc.z * inv, acc.w * inv));
-      else packed = make_uint2(pack2<false>(acc.x * inv, acc.y * inv), pack2<false>(acc.z * inv, acc.w * inv));
-      *reinterpret_cast<uint2*>(p.out + 2 * oi) = packed;
-      if (p.lse && d == 0)
-        p.lse[(int64_t)b * p.lse_bs + (int64_t)hq * p.lse_hs + qr + j] = L > 0.f ? M * kLn2 + logf(L) : -INFINITY;
+      *reinterpret_cast<uint2*>(p.out + 2 * oi) = make_uint2(0u, 0u);   // +0.0 in either 16-bit type
+      if (p.lse && d == 0) p.lse[(int64_t)b * p.lse_bs + (int64_t)hq * p.lse_hs + qr + j] = -INFINITY;
     }
   }
 }
@@ -1407,7 +1534,7 @@ inline int attn_warps_for(int kv_dtype, int head_dim) {
 }
 
 struct AttnWorkspace {
-  size_t tile_cum, seg_cum, nt, tile0, sq, qrow0, klen, part_ml, part_o, total;
+  size_t tile_cum, seg_cum, nt, tile0, sq, qrow0, klen, bound_rec, part_ml, part_o, total;
 };
 
 inline int64_t attn_max_segments(int64_t batch, int64_t total_q, int hq, int hkv) {
@@ -1430,6 +1557,7 @@ inline AttnWorkspace attn_workspace_layout(int64_t batch, int64_t total_q, int h
   const int64_t slots = attn_max_segments(batch, total_q, hq, hkv) + n_workers;
   w.part_ml = off; off = up(off + sizeof(float) * slots * kRowsPerSeg * 2);
   w.part_o = off; off = up(off + sizeof(float) * slots * kRowsPerSeg * hd);
+  w.bound_rec = off; off = up(off + sizeof(int) * 8 * n_workers);   // (split-KV kernels only, like the partials)
   w.total = off;
   return w;
 }
@@ -1451,8 +1579,10 @@ inline int launch_attn_variant(const CUtensorMap& tmK, const CUtensorMap& tmV, c
   using T = AttnTile<KVB, HD, NW, NS>;
   auto kern = paged_attn_kernel<KVB, HD, BF16, NW, NS>;
   static SmemAttrOnce once;
-  if (int rc = once.ensure(kern, T::SMEM_BYTES, dev)) return rc;
-  KB200_CUDA_OK(launch_kernel(kern, dim3(grid), dim3(NW * 32), T::SMEM_BYTES, stream, tmK, tmV, p));
+  static_assert(T::SMEM_BYTES + plan_smem_bytes(kPlanSmemMaxBatch) <= 232448, "shared memory of the largest in-kernel plan");
+  if (int rc = once.ensure(kern, T::SMEM_BYTES + plan_smem_bytes(kPlanSmemMaxBatch), dev)) return rc;
+  const size_t smem = T::SMEM_BYTES + (p.plan_in_kernel ? plan_smem_bytes(p.batch) : 0);
+  KB200_CUDA_OK(launch_kernel(kern, dim3(grid), dim3(NW * 32), smem, stream, tmK, tmV, p));
   return KB200_OK;
 }
 
@@ -1462,16 +1592,18 @@ inline int launch_decode_variant(const CUtensorMap& tmK, const CUtensorMap& tmV,
   using T = AttnTile<KVB, HD, NW, NS>;
   auto kern = paged_attn_decode_kernel<KVB, HD, BF16, NW, NS>;
   static SmemAttrOnce once;
-  if (int rc = once.ensure(kern, T::SMEM_BYTES, dev)) return rc;
-  KB200_CUDA_OK(launch_kernel(kern, dim3(grid), dim3(NW * 32), T::SMEM_BYTES, stream, tmK, tmV, p));
+  static_assert(T::SMEM_BYTES + plan_smem_bytes(kPlanSmemMaxBatch) <= 232448, "shared memory of the largest in-kernel plan");
+  if (int rc = once.ensure(kern, T::SMEM_BYTES + plan_smem_bytes(kPlanSmemMaxBatch), dev)) return rc;
+  const size_t smem = T::SMEM_BYTES + (p.plan_in_kernel ? plan_smem_bytes(p.batch) : 0);
+  KB200_CUDA_OK(launch_kernel(kern, dim3(grid), dim3(NW * 32), smem, stream, tmK, tmV, p));
   return KB200_OK;
 }
 
 template <int KVB, bool BF16, int HD>
 inline int launch_decode_hd(int nw, const CUtensorMap& tmK, const CUtensorMap& tmV, const AttnParams& p, int grid,
                             int dev, cudaStream_t stream) {
-  if (nw == 12) return launch_decode_variant<KVB, HD, BF16, 12, 2>(tmK, tmV, p, grid, dev, stream);
-  return launch_decode_variant<KVB, HD, BF16, 8, 2>(tmK, tmV, p, grid, dev, stream);
+  (void)nw;   // e4m3 K/V only: 12 warps (attn_warps_for)
+  return launch_decode_variant<KVB, HD, BF16, 12, 2>(tmK, tmV, p, grid, dev, stream);
 }
 
 template <int KVB, bool BF16>
@@ -1484,8 +1616,9 @@ inline int launch_decode_dispatch(bool d128, int nw, const CUtensorMap& tmK, con
 template <int KVB, bool BF16, int HD>
 inline int launch_attn_hd(int nw, const CUtensorMap& tmK, const CUtensorMap& tmV, const AttnParams& p, int grid,
                           int dev, cudaStream_t stream) {
-  if (nw == 12) return launch_attn_variant<KVB, HD, BF16, 12, 2>(tmK, tmV, p, grid, dev, stream);
-  return launch_attn_variant<KVB, HD, BF16, 8, 2>(tmK, tmV, p, grid, dev, stream);
+  (void)nw;   // attn_warps_for: 12 warps for e4m3 K/V, 8 for 16-bit
+  if constexpr (KVB == 1) return launch_attn_variant<KVB, HD, BF16, 12, 2>(tmK, tmV, p, grid, dev, stream);
+  else return launch_attn_variant<KVB, HD, BF16, 8, 2>(tmK, tmV, p, grid, dev, stream);
 }
 
 template <int KVB, bool BF16>
@@ -1695,11 +1828,12 @@ inline int launch_shared_prefix_attention(const kb200_attn_args* a) {
   sp.pre.lse = reinterpret_cast<float*>(ws + sp.lse1);
   sp.pre.workspace = ws + sp.ws1;
   sp.pre.workspace_bytes = sp.ws2 - sp.ws1;
-  sp.rest.lse = a->lse ? a->lse : reinterpret_cast<float*>(ws + sp.lse2);
   sp.rest.workspace = ws + sp.ws2;
   sp.rest.workspace_bytes = sp.total - sp.ws2;
   const int klen_first = sp.pages_first * a->page_size;
   if (int rc = launch_attention_pass(&sp.pre, 0, klen_first, sp.n_split == 2 ? k_skip - klen_first : klen_first)) return rc;
+  const int64_t rows = a->batch * (int64_t)a->seqlen_q;
+  sp.rest.lse = a->lse ? a->lse : reinterpret_cast<float*>(ws + sp.lse2);
   if (int rc = launch_attention_pass(&sp.rest, k_skip, -1, -1)) return rc;
   CombineParams c;
   c.o1 = ws + sp.o1;
@@ -1707,7 +1841,7 @@ inline int launch_shared_prefix_attention(const kb200_attn_args* a) {
   c.lse1 = sp.pre.lse;
   c.lse2 = sp.rest.lse;
   c.o_bs = a->o_batch_stride; c.o_rs = a->o_row_stride; c.o_hs = a->o_head_stride;
-  c.rows = a->batch * (int64_t)a->seqlen_q;
+  c.rows = rows;
   c.sq = a->seqlen_q; c.hq = a->n_q_heads; c.hd = a->head_dim;
   c.q_is_bf16 = a->q_dtype == KB200_DTYPE_BF16;
   c.write_lse = a->lse != nullptr;
@@ -1841,6 +1975,7 @@ inline int launch_attention_pass(const kb200_attn_args* a, int k_skip, int fixed
   p.sq = reinterpret_cast<int*>(ws + wl.sq);
   p.qrow0 = reinterpret_cast<int*>(ws + wl.qrow0);
   p.klen = reinterpret_cast<int*>(ws + wl.klen);
+  p.bound_rec = reinterpret_cast<int*>(ws + wl.bound_rec);
   p.part_ml = reinterpret_cast<float*>(ws + wl.part_ml);
   p.part_o = reinterpret_cast<float*>(ws + wl.part_o);
   p.n_pages = a->n_pages;
@@ -1862,13 +1997,16 @@ inline int launch_attention_pass(const kb200_attn_args* a, int k_skip, int fixed
   p.fixed_klen = fixed_klen;
   p.fixed_klen_last = fixed_klen_last;
   p.merged_halves = merged ? 1 : 0;
+  p.total_q = a->total_q;
+  // the split-KV kernels build the plan themselves (every CTA, into shared memory) unless the batch is too large
+  p.plan_in_kernel = (!prefill && a->batch <= kPlanSmemMaxBatch) ? 1 : 0;
 
   cudaStream_t stream = static_cast<cudaStream_t>(a->stream);
   // sequences of fixed lengths on the prefill kernel (the prefix pass of a shared-prefix call) have
   // nothing to plan: the kernel derives its segments from the launch parameters
   const bool no_plan = prefill && fixed_klen >= 0 && p.uniform_nseg > 0;
   p.no_plan = no_plan ? 1 : 0;
-  if (!no_plan) KB200_CUDA_OK(launch_kernel(attn_plan_kernel, dim3(1), dim3(256), 0, stream, p));
+  if (!no_plan && !p.plan_in_kernel) KB200_CUDA_OK(launch_kernel(attn_plan_kernel, dim3(1), dim3(256), 0, stream, p));
 
   int rc;
   const bool d128 = a->head_dim == 128;
@@ -1903,7 +2041,9 @@ inline int launch_attention_pass(const kb200_attn_args* a, int k_skip, int fixed
   const int64_t max_seg = packed ? attn_max_segments(a->batch, a->total_q, a->n_q_heads, a->n_kv_heads)
                                  : a->batch * a->n_kv_heads * ((group * (int64_t)a->seqlen_q + p.rows_per_seg - 1) / p.rows_per_seg);
   KB200_REQUIRE(max_seg <= 0x7fffffff, "too many segments");
-  const int64_t merge_blocks = max_seg < (int64_t)sms * 16 ? max_seg : (int64_t)sms * 16;   // 16 x 128 threads fill an SM
+  // one block per range boundary (the only places where a segment can be cut), striding when there are more
+  int64_t merge_blocks = std::max<int64_t>(n_workers - 1, 1);
+  if (merge_blocks > (int64_t)sms * 16) merge_blocks = (int64_t)sms * 16;   // 16 x 128 threads fill an SM
   if (d128) KB200_CUDA_OK(launch_kernel(attn_merge_kernel<128>, dim3((unsigned)merge_blocks), dim3(128), 0, stream, p));
   else KB200_CUDA_OK(launch_kernel(attn_merge_kernel<64>, dim3((unsigned)merge_blocks), dim3(128), 0, stream, p));
   return KB200_OK;

@@ -710,6 +710,53 @@ def flash_attn_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *,
 
 
 # ---------------------------------------------------------------------------
+# sampling hand-off
+# ---------------------------------------------------------------------------
+
+def sample_step_from_logits(logits: torch.Tensor, temperatures: torch.Tensor, top_ps: torch.Tensor, *,
+                            out: Optional[torch.Tensor] = None, generator: Optional[torch.Generator] = None,
+                            logprobs_out: Optional[torch.Tensor] = None,
+                            uniforms: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """One token per row of ``logits [B, V]`` (fp32/fp16/bf16): temperature, top-p nucleus, one draw -- the call
+    the scheduler makes after the decoder stack (``kestrel/scheduler/scheduler.py:2986-2991``,
+    ``kestrel/scheduler/spatial.py:105-123``).
+
+    ``temperatures`` / ``top_ps`` fp32 ``[B]``; a temperature <= 1e-6 is greedy (arg-max, log-probability 0).
+    The row's random number comes from ``generator`` (one ``torch.rand`` of ``B`` values on the logits' device)
+    unless ``uniforms`` (fp32 ``[B]`` in [0, 1)) is given, which makes the call deterministic and allocation-free.
+    Returns ``out`` (int64 ``[B]``, allocated when absent); ``logprobs_out`` (fp32 ``[B]``) receives
+    ``logits[id] / T - logsumexp(logits / T)``.
+    """
+    dev = _require_cuda("logits", logits)
+    if logits.ndim != 2 or logits.stride(1) != 1:
+        raise ValueError("logits must have shape [batch, vocab], contiguous in the vocabulary")
+    dt = _TORCH_TO_DTYPE.get(logits.dtype)
+    if dt is None or logits.dtype in (torch.uint8, torch.float8_e4m3fn):
+        raise ValueError(f"unsupported logits dtype {logits.dtype}")
+    B, V = logits.shape
+    for nm, t in (("temperatures", temperatures), ("top_ps", top_ps)):
+        if _require_cuda(nm, t) != dev or t.dtype != torch.float32 or t.ndim != 1 or t.shape[0] < B or not t.is_contiguous():
+            raise ValueError(f"{nm} must be a contiguous fp32 [batch] tensor on the logits' device")
+    if out is None:
+        out = torch.empty(B, dtype=torch.int64, device=logits.device)
+    elif _require_cuda("out", out) != dev or out.dtype != torch.int64 or out.ndim != 1 or out.shape[0] < B or not out.is_contiguous():
+        raise ValueError("out must be a contiguous int64 [batch] tensor on the logits' device")
+    if logprobs_out is not None and (_require_cuda("logprobs_out", logprobs_out) != dev or logprobs_out.dtype != torch.float32
+                                     or logprobs_out.ndim != 1 or logprobs_out.shape[0] < B or not logprobs_out.is_contiguous()):
+        raise ValueError("logprobs_out must be a contiguous fp32 [batch] tensor on the logits' device")
+    if uniforms is None:
+        uniforms = torch.rand(B, generator=generator, device=logits.device, dtype=torch.float32)
+    elif _require_cuda("uniforms", uniforms) != dev or uniforms.dtype != torch.float32 or uniforms.shape[0] < B or not uniforms.is_contiguous():
+        raise ValueError("uniforms must be a contiguous fp32 [batch] tensor on the logits' device")
+    if B == 0:
+        return out
+    _native.check(_native.load().kb200_sample_step_from_logits(
+        logits.data_ptr(), dt, B, V, logits.stride(0), temperatures.data_ptr(), top_ps.data_ptr(), uniforms.data_ptr(),
+        out.data_ptr(), logprobs_out.data_ptr() if logprobs_out is not None else None, dev, _stream(dev)))
+    return out
+
+
+# ---------------------------------------------------------------------------
 # runtime object
 # ---------------------------------------------------------------------------
 
@@ -749,6 +796,13 @@ class _AttentionOps:
         raise NotImplementedError(f"kestrel_kernels.attention.{item} is outside the paged-KV path")
 
 
+class _SamplingOps:
+    sample_step_from_logits = staticmethod(sample_step_from_logits)
+
+    def __getattr__(self, item: str):
+        raise NotImplementedError(f"kestrel_kernels.sampling.{item} is outside the paged-KV path")
+
+
 class Runtime:
     """What ``kestrel_kernels.get_runtime()`` returns, restricted to the paged-KV path."""
 
@@ -756,7 +810,8 @@ class Runtime:
         self.cache = _CacheOps()
         self.attention = _AttentionOps()
         self.rotary = _RotaryOps()
-        for name in ("linear", "vision", "dense", "tau", "moe", "gated_delta", "sampling",
+        self.sampling = _SamplingOps()
+        for name in ("linear", "vision", "dense", "tau", "moe", "gated_delta",
                      "megakernel", "generated_decode", "linear_ops"):
             setattr(self, name, _Unavailable(name))
 
@@ -774,5 +829,14 @@ def get_runtime() -> Runtime:
 
 
 def install_as_kestrel_kernels() -> None:
-    """Register this module as ``kestrel_kernels`` so Kestrel's own modules bind to it."""
-    sys.modules["kestrel_kernels"] = sys.modules[__name__]
+    """Register this module as ``kestrel_kernels`` so Kestrel's own modules bind to it, and
+    ``kestrel_kernels.sampling`` for the scheduler's ``from kestrel_kernels.sampling import
+    sample_step_from_logits`` (``kestrel/scheduler/scheduler.py:47``)."""
+    import types
+
+    me = sys.modules[__name__]
+    sys.modules["kestrel_kernels"] = me
+    sampling = types.ModuleType("kestrel_kernels.sampling")
+    sampling.sample_step_from_logits = sample_step_from_logits
+    sys.modules["kestrel_kernels.sampling"] = sampling
+    me.sampling = sampling

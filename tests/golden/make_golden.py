@@ -18,6 +18,8 @@ take its torch path (``kestrel/kv_cache.py:216-220``) -- and records:
 * ``rope_vectors.npz``  the cos/sin table of ``kestrel/models/moondream/rope.py`` (Moondream's
                       geometry: 32 rotated of 64 head dims, theta 1.5e6) and fp32 rows rotated with
                       ``kestrel/ops/rotary.py:apply_rotary`` (both files loaded by path, unmodified);
+* ``pool_image.npz``   raw bytes of a small bf16 pool (reference torch path) and FP8 pool (oracle codes on the
+                      reference's slots) after a fixed append sequence: the pool layout / FP8 code contract;
 * ``page_table_traces.json``   random op sequences on the reference ``PageTable`` with every
                       return value and the resulting host state.
 
@@ -376,6 +378,69 @@ def rope_vectors(root: str) -> dict[str, np.ndarray]:
     return out
 
 
+def pool_image(kc) -> dict[str, np.ndarray]:
+    """The byte image of a small pool after a fixed append sequence: the contract a whole-model decode
+    kernel that reads and appends the same pool relies on (``kestrel/models/moondream/runtime.py:638-644``).
+
+    A 37-token and a 5-token prompt are appended out of fused q/k/v projections, then three batched decode
+    steps follow.  bf16: slots and pool bytes come from the reference's own ``PageTable.build_slot_mapping``
+    and ``PagedKVCache.update`` torch path.  FP8 e4m3: the reference's torch path refuses FP8
+    (``kestrel/kv_cache.py:212-215``), so the code image is the oracle's (``satfinite(rn(x / scale))`` with the
+    per-layer scalar scales the reference passes) on the reference's slots -- defined here, not pinned there.
+    """
+    sys.path.insert(0, str(HERE.parent.parent))
+    from oracle import paged_kv_oracle as O
+
+    n_pages, P, H, D, hq = 8, 16, 2, 64, 4
+    g = torch.Generator().manual_seed(404)
+    pt = kc.PageTable(n_pages=n_pages, page_size=P, max_batch_size=3, device="cpu")
+    pt.free_pages = [pt.free_pages[i] for i in torch.randperm(len(pt.free_pages), generator=g).tolist()]
+    cache = kc.PagedKVCache(pt, n_heads=H, head_dim=D, dtype=torch.bfloat16, pool=kc.KVMemoryPool(device="cpu"))
+    k8 = torch.zeros(n_pages, H, P, D, dtype=torch.uint8)
+    v8 = torch.zeros_like(k8)
+    ks, vs = 0.02, 0.03
+    out: dict[str, np.ndarray] = {"geometry": np.array([n_pages, P, H, D, hq], dtype=np.int64),
+                                  "scales": np.array([ks, vs], dtype=np.float32)}
+    rows = [pt.allocate(), pt.allocate()]
+    pt.reserve(rows[0], 40)
+    pt.reserve(rows[1], 8)
+    pt.commit_block_table(rows)
+    step = 0
+
+    def append(batch_rows, positions):
+        nonlocal step
+        B, S = positions.shape
+        fused = torch.randn(B, S, (hq + 2 * H) * D, generator=g).to(torch.bfloat16)
+        k = fused[..., hq * D:(hq + H) * D].unflatten(-1, (H, D))
+        v = fused[..., (hq + H) * D:].unflatten(-1, (H, D))
+        slots = pt.build_slot_mapping(torch.tensor(batch_rows), positions)
+        cache.update(input_pos=positions, k_val=k, v_val=v, slot_mapping=slots)
+        O.append(k8, v8, k.reshape(-1, H, D), v.reshape(-1, H, D), slots.reshape(-1),
+                 k_scale=torch.tensor([ks]), v_scale=torch.tensor([vs]))
+        out[f"step{step}_rows"] = np.array(batch_rows, dtype=np.int64)
+        out[f"step{step}_pos"] = positions.numpy().copy()
+        out[f"step{step}_fused"] = to_np(fused)
+        out[f"step{step}_slots"] = slots.numpy().copy()
+        step += 1
+
+    append([rows[0]], torch.arange(37).view(1, 37))
+    append([rows[1]], torch.arange(5).view(1, 5))
+    lens = [37, 5]
+    for _ in range(3):
+        for i, r in enumerate(rows):
+            pt.reserve(r, lens[i] + 1)
+        pt.commit_block_table(rows)
+        append(rows, torch.tensor(lens).view(2, 1))
+        lens = [n + 1 for n in lens]
+    out["n_steps"] = np.array([step], dtype=np.int64)
+    out["page_table"] = pt.page_table.numpy().copy()
+    out["k_bf16"] = cache.k_cache.contiguous().view(torch.uint8).numpy().copy()   # raw bytes, [n_pages, H, P, D * 2]
+    out["v_bf16"] = cache.v_cache.contiguous().view(torch.uint8).numpy().copy()
+    out["k_e4m3"] = k8.numpy().copy()
+    out["v_e4m3"] = v8.numpy().copy()
+    return out
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True, help="root of the m87-labs/kestrel source tree")
@@ -399,6 +464,7 @@ def main() -> None:
     (HERE / "page_table_traces.json").write_text(json.dumps(page_table_traces(kc)))
     (HERE / "radix_traces.json").write_text(json.dumps(radix_traces(args.reference)))
     np.savez_compressed(HERE / "rope_vectors.npz", **rope_vectors(args.reference))
+    np.savez_compressed(HERE / "pool_image.npz", **pool_image(kc))
     print("wrote", sorted(p.name for p in HERE.iterdir()))
 
 

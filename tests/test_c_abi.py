@@ -60,8 +60,9 @@ def test_runtime_object_has_the_reference_entry_points():
     assert callable(rt.cache.reshape_and_cache_flash)
     assert callable(rt.cache.build_paged_kv_metadata)
     assert callable(rt.attention.flash_attn_fwd)
+    assert callable(rt.sampling.sample_step_from_logits)
     with pytest.raises(NotImplementedError):
-        rt.sampling.sample_step_from_logits
+        rt.moe.topk_fwd
     assert rt.attention.block_bidirectional_mask is kernels.block_bidirectional_mask
     with pytest.raises(NotImplementedError):
         rt.attention.flash_attn_varlen_func

@@ -227,3 +227,20 @@ def test_decode_step_metadata_is_metadata_then_slot_mapping(vec):
     assert torch.equal(out_sk, torch.from_numpy(vec["meta_out_seqused"]))
     assert positions.tolist() == [[5, 6, 7], [6, 7, 8]]
     assert torch.equal(slots, O.build_slot_mapping(table, batch, positions, 4))
+
+
+def test_sampling_oracle_known_answers():
+    """Nucleus rule and inverse-CDF draw on a vocabulary of three: probabilities 0.5 / 0.3 / 0.2."""
+    from oracle import sampling_oracle as S
+
+    logits = torch.log(torch.tensor([[0.5, 0.3, 0.2]])).repeat(6, 1)
+    temps = torch.tensor([1.0, 1.0, 1.0, 1.0, 0.0, 1.0])
+    top_ps = torch.tensor([1.0, 1.0, 0.7, 0.7, 1.0, 0.0])
+    u = torch.tensor([0.49, 0.81, 0.62, 0.63, 0.99, 0.99])
+    ids, lps = S.sample_step_from_logits(logits, temps, top_ps, u)
+    # whole vocabulary: cdf 0.5 / 0.8 / 1.0; nucleus 0.7 -> {0, 1} with mass 0.8: cdf 0.5 / 0.8, target u * 0.8
+    assert ids.tolist() == [0, 2, 0, 1, 0, 0]
+    assert abs(float(lps[1]) - math.log(0.2)) < 1e-6 and float(lps[4]) == 0.0
+    assert S.check_sample(logits[2], 1.0, 0.7, 0.62, 0) is None
+    assert S.check_sample(logits[2], 1.0, 0.7, 0.62, 1) is not None
+    assert S.check_sample(logits[2], 1.0, 0.7, 0.9, 2) is not None      # outside the nucleus
