@@ -33,6 +33,7 @@
 
 #include <algorithm>
 #include <cstdlib>
+#include <cstring>
 #include <type_traits>
 #include <mutex>
 #include <unordered_map>
@@ -111,6 +112,14 @@ struct AttnParams {
   // (no plan launch; CTA 0 also stores it for the merge kernel); else attn_plan_kernel ran first
   int plan_in_kernel;
   long long total_q;     // rows of q (bounds the packed row ranges)
+  // gather: the (page, head) rows are too short for a TMA box (a box must be a multiple of 128 bytes in
+  // shared memory: page_size 1 with 64-byte e4m3 rows, the reference's own FP8 configuration,
+  // kestrel/models/moondream/runtime.py:645-663).  The warps then fetch their tiles 16 bytes at a time
+  // with cp.async, through these plain pointers and byte strides, into the same swizzled layout.
+  int gather;
+  const char* k_base;
+  const char* v_base;
+  long long kv_ps_b, kv_ts_b, kv_hs_b;
 };
 
 // Where the attention kernels read the plan from: shared memory (built by the CTA itself) or the
@@ -202,6 +211,16 @@ __device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap* tm,
       " [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
       ::"r"(dst), "l"(reinterpret_cast<uint64_t>(tm)), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
       : "memory");
+}
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+// the barrier gets one more pending arrival, which completes when this thread's cp.async so far have landed
+__device__ __forceinline__ void cp_async_mbar_arrive(uint32_t bar) {
+  asm volatile("cp.async.mbarrier.arrive.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_plain(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 __device__ __forceinline__ void ldsm_x4(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, uint32_t addr) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
@@ -461,7 +480,7 @@ __device__ __forceinline__ uint32_t swz(int row) {
 // one TMA box per (page, head, K|V, 128-byte half), page indices read one tile
 // before the copy that needs them.
 // ---------------------------------------------------------------------------
-template <typename T, int KVB>
+template <typename T, int KVB, bool GATHER>
 struct TileProducer {
   static constexpr int TILE_N = T::TILE_N;
   static constexpr int RB = T::RB;
@@ -487,7 +506,7 @@ struct TileProducer {
     nbox = (TILE_N >> box_shift) << (hb_shift + 1);
     cursor_locate(p, pv, pc, r0);
     enter_segment();
-    pg = lane < nbox ? page_for(lane) : 0;
+    pg = (!GATHER && lane < nbox) ? page_for(lane) : 0;
   }
   __device__ __forceinline__ void enter_segment() {
     h = pc.seg / pc.nmb;
@@ -499,7 +518,52 @@ struct TileProducer {
     if (key >= pc.L) return 0;
     return pt_row[key >> p_shift];
   }
+  // One tile, 16 bytes per cp.async: 256 chunks of K and 256 of V whatever the row length, eight of each per
+  // lane.  Lane l looks up the pages of tokens l and l + 32 of the tile; the chunks get them by shuffle.
+  __device__ __forceinline__ void issue_gather(int stage) {
+    constexpr int CPR = T::ROW_BYTES / 16;     // chunks per row
+    constexpr int CHUNKS = TILE_N * CPR;
+    static_assert(CHUNKS % 32 == 0 && TILE_N <= 64, "tile geometry of the gather path");
+    const uint32_t sbase = stage0 + (uint32_t)stage * T::STAGE_BYTES;
+    const uint32_t bar = bar0 + 8u * stage;
+    const int k0 = (pc.tile0 + pc.t) * TILE_N;
+    int nvalid = pc.L - k0;
+    if (nvalid > TILE_N) nvalid = TILE_N;
+    const int pg_a = lane < nvalid ? pt_row[(k0 + lane) >> p_shift] : 0;
+    const int pg_b = (TILE_N > 32 && lane + 32 < nvalid) ? pt_row[(k0 + lane + 32) >> p_shift] : 0;
+#pragma unroll
+    for (int c = lane; c < CHUNKS; c += 32) {
+      const int tk = c / CPR, c16 = c % CPR;
+      const int pa = __shfl_sync(0xffffffffu, pg_a, tk & 31), pb = __shfl_sync(0xffffffffu, pg_b, tk & 31);
+      const int page = tk < 32 ? pa : pb;
+      if (tk >= nvalid) continue;
+      if ((unsigned)page >= (unsigned long long)p.n_pages) {   // never dereferenced: the tile keeps stale bytes there
+        if (c16 == 0) report(KB200_STATUS_BAD_PAGE, page, KID_ATTN);
+        continue;
+      }
+      const long long off = (long long)page * p.kv_ps_b + (long long)((k0 + tk) & (p.page_size - 1)) * p.kv_ts_b +
+                            (long long)h * p.kv_hs_b + 16 * c16;
+      uint32_t dst;
+      if constexpr (NH == 2) dst = sbase + (uint32_t)(c16 >> 3) * (TILE_N * 128) + (uint32_t)tk * 128 + (uint32_t)(((c16 & 7) ^ (tk & 7)) << 4);
+      else dst = sbase + (uint32_t)tk * RB + (uint32_t)((c16 ^ (int)swz<RB>(tk)) << 4);
+      cp_async_16(dst, p.k_base + off);
+      cp_async_16(dst + T::KV_TILE_BYTES, p.v_base + off);
+    }
+    cp_async_mbar_arrive(bar);
+    __syncwarp();
+    if (lane == 0) mbar_arrive_plain(bar);   // the arrival the barrier was initialised for; the 32 above are extra
+    advance_after_issue();
+  }
+  __device__ __forceinline__ void advance_after_issue() {
+    ++issued;
+    if (issued < my_tiles) {
+      cursor_advance(p, pv, pc);
+      if (pc.t == 0) enter_segment();   // (a new segment, possibly of a new sequence)
+      if constexpr (!GATHER) pg = lane < nbox ? page_for(lane) : 0;
+    }
+  }
   __device__ __forceinline__ void issue(int stage) {
+    if constexpr (GATHER) { issue_gather(stage); return; }
     const uint32_t sbase = stage0 + (uint32_t)stage * T::STAGE_BYTES;
     const uint32_t bar = bar0 + 8u * stage;
     const int k0 = (pc.tile0 + pc.t) * TILE_N;
@@ -523,12 +587,7 @@ struct TileProducer {
       else
         tma_load_4d(dst, kv ? tmV : tmK, bar, half * (RB / KVB), key & (p.page_size - 1), h, page);
     }
-    ++issued;
-    if (issued < my_tiles) {
-      cursor_advance(p, pv, pc);
-      if (pc.t == 0) enter_segment();   // (a new segment, possibly of a new sequence)
-      pg = lane < nbox ? page_for(lane) : 0;
-    }
+    advance_after_issue();
   }
   __device__ __forceinline__ bool more() const { return issued < my_tiles; }
 };
@@ -537,7 +596,7 @@ struct TileProducer {
 // The attention kernel.  KVB: bytes per K/V element (2: bf16/f16, 1: e4m3);
 // BF16: operand type of the MMAs (bf16 when K/V are bf16, else f16).
 // ---------------------------------------------------------------------------
-template <int KVB, int HD, bool BF16, int NW, int NS>
+template <int KVB, int HD, bool BF16, int NW, int NS, bool GATHER>
 __global__ void __launch_bounds__(NW * 32, 1)
 paged_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                   const __grid_constant__ AttnParams p) {
@@ -585,7 +644,7 @@ paged_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
   }
   const int my_tiles = (int)(r1 - r0);
 
-  TileProducer<T, KVB> prod(p, plan, &tmK, &tmV, my_stage0, bar0, lane, r0, my_tiles);
+  TileProducer<T, KVB, GATHER> prod(p, plan, &tmK, &tmV, my_stage0, bar0, lane, r0, my_tiles);
   Cursor cc = prod.pc;   // consumer side: starts where the producer starts
   if (lane == 0 && w > 0) write_boundary_record(p, w, cc);
   for (int s = 0; s < NS && prod.more(); ++s) prod.issue(s);
@@ -952,7 +1011,7 @@ __device__ __forceinline__ void mma16816r(float (&d)[4], uint32_t a0, uint32_t a
   }
 }
 
-template <int KVB, int HD, bool BF16, int NW, int NS>
+template <int KVB, int HD, bool BF16, int NW, int NS, bool GATHER>
 __global__ void __launch_bounds__(NW * 32, 1)
 paged_attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                          const __grid_constant__ AttnParams p) {
@@ -995,7 +1054,7 @@ paged_attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
   }
   const int my_tiles = (int)(r1 - r0);
 
-  TileProducer<T, KVB> prod(p, plan, &tmK, &tmV, my_stage0, bar0, lane, r0, my_tiles);
+  TileProducer<T, KVB, GATHER> prod(p, plan, &tmK, &tmV, my_stage0, bar0, lane, r0, my_tiles);
   Cursor cc = prod.pc;   // consumer side: starts where the producer starts
   if (lane == 0 && w > 0) write_boundary_record(p, w, cc);
   for (int s = 0; s < NS && prod.more(); ++s) prod.issue(s);
@@ -1573,11 +1632,11 @@ inline int device_sm_count(int dev, int* sms) {
   return KB200_OK;
 }
 
-template <int KVB, int HD, bool BF16, int NW, int NS>
+template <int KVB, int HD, bool BF16, int NW, int NS, bool GATHER>
 inline int launch_attn_variant(const CUtensorMap& tmK, const CUtensorMap& tmV, const AttnParams& p, int grid,
                                int dev, cudaStream_t stream) {
   using T = AttnTile<KVB, HD, NW, NS>;
-  auto kern = paged_attn_kernel<KVB, HD, BF16, NW, NS>;
+  auto kern = paged_attn_kernel<KVB, HD, BF16, NW, NS, GATHER>;
   static SmemAttrOnce once;
   static_assert(T::SMEM_BYTES + plan_smem_bytes(kPlanSmemMaxBatch) <= 232448, "shared memory of the largest in-kernel plan");
   if (int rc = once.ensure(kern, T::SMEM_BYTES + plan_smem_bytes(kPlanSmemMaxBatch), dev)) return rc;
@@ -1586,11 +1645,11 @@ inline int launch_attn_variant(const CUtensorMap& tmK, const CUtensorMap& tmV, c
   return KB200_OK;
 }
 
-template <int KVB, int HD, bool BF16, int NW, int NS>
+template <int KVB, int HD, bool BF16, int NW, int NS, bool GATHER>
 inline int launch_decode_variant(const CUtensorMap& tmK, const CUtensorMap& tmV, const AttnParams& p, int grid,
                                  int dev, cudaStream_t stream) {
   using T = AttnTile<KVB, HD, NW, NS>;
-  auto kern = paged_attn_decode_kernel<KVB, HD, BF16, NW, NS>;
+  auto kern = paged_attn_decode_kernel<KVB, HD, BF16, NW, NS, GATHER>;
   static SmemAttrOnce once;
   static_assert(T::SMEM_BYTES + plan_smem_bytes(kPlanSmemMaxBatch) <= 232448, "shared memory of the largest in-kernel plan");
   if (int rc = once.ensure(kern, T::SMEM_BYTES + plan_smem_bytes(kPlanSmemMaxBatch), dev)) return rc;
@@ -1603,7 +1662,10 @@ template <int KVB, bool BF16, int HD>
 inline int launch_decode_hd(int nw, const CUtensorMap& tmK, const CUtensorMap& tmV, const AttnParams& p, int grid,
                             int dev, cudaStream_t stream) {
   (void)nw;   // e4m3 K/V only: 12 warps (attn_warps_for)
-  return launch_decode_variant<KVB, HD, BF16, 12, 2>(tmK, tmV, p, grid, dev, stream);
+  // only 64-byte rows (e4m3, head_dim 64) can be too short for a TMA box
+  if constexpr (KVB == 1 && HD == 64)
+    if (p.gather) return launch_decode_variant<KVB, HD, BF16, 12, 2, true>(tmK, tmV, p, grid, dev, stream);
+  return launch_decode_variant<KVB, HD, BF16, 12, 2, false>(tmK, tmV, p, grid, dev, stream);
 }
 
 template <int KVB, bool BF16>
@@ -1617,8 +1679,10 @@ template <int KVB, bool BF16, int HD>
 inline int launch_attn_hd(int nw, const CUtensorMap& tmK, const CUtensorMap& tmV, const AttnParams& p, int grid,
                           int dev, cudaStream_t stream) {
   (void)nw;   // attn_warps_for: 12 warps for e4m3 K/V, 8 for 16-bit
-  if constexpr (KVB == 1) return launch_attn_variant<KVB, HD, BF16, 12, 2>(tmK, tmV, p, grid, dev, stream);
-  else return launch_attn_variant<KVB, HD, BF16, 8, 2>(tmK, tmV, p, grid, dev, stream);
+  if constexpr (KVB == 1 && HD == 64)
+    if (p.gather) return launch_attn_variant<KVB, HD, BF16, 12, 2, true>(tmK, tmV, p, grid, dev, stream);
+  if constexpr (KVB == 1) return launch_attn_variant<KVB, HD, BF16, 12, 2, false>(tmK, tmV, p, grid, dev, stream);
+  else return launch_attn_variant<KVB, HD, BF16, 8, 2, false>(tmK, tmV, p, grid, dev, stream);
 }
 
 template <int KVB, bool BF16>
@@ -1640,11 +1704,22 @@ constexpr int kPrefillRowsPerSeg = 256, kPrefillTileKeys = 128, kPrefillMinPacke
 // (729 keys).
 inline int prefill_min_rows(int head_dim) { return head_dim == 128 ? 40 : 56; }
 
+// A TMA box must fill a multiple of 128 bytes of shared memory: page_size x min(row bytes, 128).  Pools
+// that cannot offer that (page size 1 with 64-byte e4m3 rows) are served by the split-KV kernels' cp.async
+// gather path.
+inline bool tma_boxes_possible(const kb200_attn_args* a, int tile_n) {
+  const int row_bytes = a->head_dim * dtype_size(a->kv_dtype);
+  const int rb = row_bytes > 128 ? 128 : row_bytes;
+  const int box_rows = a->page_size < tile_n ? a->page_size : tile_n;
+  return (box_rows * rb) % 128 == 0;
+}
+
 // Which kernel serves a call: many query rows per sequence with 16-bit K/V (or a block mask) go to
 // the tensor-memory prefill kernel, one CTA per 256 packed rows, no split over keys and no merge.
 inline bool use_prefill_kernel(const kb200_attn_args* a) {
   if (a->q_visible_until != nullptr) return true;
   if (!prefill_enabled() || a->n_kv_heads <= 0) return false;
+  if (!tma_boxes_possible(a, kPrefillTileKeys)) return false;   // (the prefill kernel has no gather path)
   // Packed rows: seqlen_q is only an upper bound (the reference's packed call passes none at all,
   // kestrel/ops/attention.py:69-86, and the shim then sets it to total_q); the mean rows per
   // sequence says which kernel has less work.
@@ -1925,22 +2000,27 @@ inline int launch_attention_pass(const kb200_attn_args* a, int k_skip, int fixed
   // is within a few percent of the HBM roofline with the general kernel already.
   const bool decode8 = !prefill && a->kv_dtype == KB200_DTYPE_E4M3 &&
                        (int64_t)group * a->seqlen_q <= kDecodeRows;
-  {
-    // every copy lands on a 128-byte boundary of shared memory
-    const int row_bytes = a->head_dim * es;
-    const int rb = row_bytes > 128 ? 128 : row_bytes;
-    const int box_rows = P < tile_n ? P : tile_n;
-    if ((box_rows * rb) % 128 != 0)
-      return fail(KB200_ERR_UNSUPPORTED, "page_size %d with %d-byte rows is not supported", P, row_bytes);
-  }
+  // every TMA copy must land on a 128-byte boundary of shared memory; pools that cannot offer that go
+  // through the split-KV kernels' cp.async gather path (the prefill kernel has none)
+  const bool gather = !tma_boxes_possible(a, tile_n);
+  if (gather && !(a->kv_dtype == KB200_DTYPE_E4M3 && a->head_dim == 64))
+    return fail(KB200_ERR_UNSUPPORTED, "page_size %d with %d-byte rows is not supported", P, a->head_dim * es);
+  if (gather && prefill)
+    return fail(KB200_ERR_UNSUPPORTED, "a block mask on a pool with page_size %d and %d-byte rows is not supported", P,
+                a->head_dim * es);
   TmapKey key{a->k_cache, a->kv_page_stride, a->kv_token_stride, a->kv_head_stride, a->n_pages,
               P, a->n_kv_heads, a->head_dim, a->kv_dtype, a->device};
   // 256-byte rows and pages at least a tile long: one box per (page, K|V) instead of one per half
   const bool merged = !prefill && a->head_dim * es == 256 && P >= tile_n;
   CUtensorMap tmK, tmV;
-  if (int rc = get_pool_tmap(key, tile_n, merged, &tmK)) return rc;
-  key.base = a->v_cache;
-  if (int rc = get_pool_tmap(key, tile_n, merged, &tmV)) return rc;
+  if (gather) {
+    memset(&tmK, 0, sizeof(tmK));
+    memset(&tmV, 0, sizeof(tmV));
+  } else {
+    if (int rc = get_pool_tmap(key, tile_n, merged, &tmK)) return rc;
+    key.base = a->v_cache;
+    if (int rc = get_pool_tmap(key, tile_n, merged, &tmV)) return rc;
+  }
 
   char* ws = static_cast<char*>(a->workspace);
   AttnParams p;
@@ -1998,6 +2078,12 @@ inline int launch_attention_pass(const kb200_attn_args* a, int k_skip, int fixed
   p.fixed_klen_last = fixed_klen_last;
   p.merged_halves = merged ? 1 : 0;
   p.total_q = a->total_q;
+  p.gather = gather ? 1 : 0;
+  p.k_base = static_cast<const char*>(a->k_cache);
+  p.v_base = static_cast<const char*>(a->v_cache);
+  p.kv_ps_b = a->kv_page_stride * es;
+  p.kv_ts_b = a->kv_token_stride * es;
+  p.kv_hs_b = a->kv_head_stride * es;
   // the split-KV kernels build the plan themselves (every CTA, into shared memory) unless the batch is too large
   p.plan_in_kernel = (!prefill && a->batch <= kPlanSmemMaxBatch) ? 1 : 0;
 

@@ -157,13 +157,30 @@ def test_sliding_window(window, kv, seqlen_q):
 
 
 @pytest.mark.parametrize("page_size", [1, 2, 4, 8, 32, 64, 128])
-@pytest.mark.parametrize("kv,head_dim", [("same", 128), ("same", 64), ("fp8", 128)])
+@pytest.mark.parametrize("kv,head_dim", [("same", 128), ("same", 64), ("fp8", 128), ("fp8", 64)])
 def test_page_sizes(page_size, kv, head_dim):
     lengths = [1, 2, 9, 63, 64, 65, 130, 257]
     p = make_paged_problem(seed=13, batch=len(lengths), len_lo=0, len_hi=0, n_q_heads=8, n_kv_heads=2,
                            head_dim=head_dim, page_size=page_size, dtype=torch.bfloat16, lengths=lengths)
     out, want = run_case(p, torch.bfloat16, kv=kv, scales=(0.02, 0.02) if kv == "fp8" else None)
     assert_close(out, want, f"P={page_size}")
+
+
+@pytest.mark.parametrize("heads_q,heads_kv,seqlen_q", [(32, 32, 1), (32, 8, 1), (32, 8, 4), (8, 8, 64), (32, 8, 3)])
+def test_fp8_pool_with_one_token_pages_and_64_byte_rows(heads_q, heads_kv, seqlen_q):
+    """The reference's own FP8 configuration (page size 1, head_dim 64, e4m3 with per-layer scalar scales,
+    kestrel/models/moondream/runtime.py:645-663; Moondream is MHA 32/32): a token row of one head is 64 bytes,
+    too short for a TMA box, so the warps gather their tiles with 16-byte asynchronous copies.  Decode
+    (transposed kernel), multi-query verify (16-row kernel) and a prefill-shaped call, which stays on the
+    split-KV kernels for such pools."""
+    lengths = [1, 2, 31, 63, 64, 65, 127, 129, 700, 2100]
+    p = make_paged_problem(seed=19, batch=len(lengths), len_lo=0, len_hi=0, n_q_heads=heads_q, n_kv_heads=heads_kv,
+                           head_dim=64, page_size=1, seqlen_q=seqlen_q, dtype=torch.bfloat16,
+                           lengths=[L + seqlen_q for L in lengths], outlier_frac=0.01)
+    ks = float(p["k_pool"].abs().max() / 448)
+    vs = float(p["v_pool"].abs().max() / 448)
+    out, want = run_case(p, torch.bfloat16, kv="fp8", scales=(ks, vs))
+    assert_close(out, want, f"P=1 D=64 e4m3, {heads_q}/{heads_kv} heads, Sq={seqlen_q}")
 
 
 @pytest.mark.parametrize("kv", ["same", "fp8"])

@@ -180,6 +180,20 @@ def test_reference_fp8_decode_step_with_per_layer_scalar_scales(ref):
     _status_clean()
 
 
+def test_reference_fp8_decode_step_in_the_references_own_fp8_geometry(ref):
+    """FP8 KV exists in the reference only with page size 1 (kestrel/models/moondream/runtime.py:645-663), on
+    Moondream's MHA 32/32 heads of 64: rows of 64 bytes.  Same flow as above through the reference's classes."""
+    kc, attn, _ = ref
+    pr = _decode_problem(kc, kv_dtype=torch.float8_e4m3fn, P=1, D=64, hq=32, hkv=32, lengths=[130, 17, 64, 700],
+                         seed=6, k_scale=0.0141, v_scale=0.0113)
+    out = attn.paged_attention(pr["q"].transpose(1, 2), paged_kv_layer=pr["cache"], page_table=pr["meta_pt"],
+                               paged_kv_seqlens_k=pr["meta_sk"], scaling=1.0 / math.sqrt(64))
+    want = O.paged_attention(pr["q"].cpu().float(), pr["mk"], pr["mv"], pr["meta_pt"].cpu(), pr["meta_sk"].cpu(),
+                             k_scale=pr["ks"], v_scale=pr["vs"])
+    _check(out, want)
+    _status_clean()
+
+
 def test_reference_multi_query_seqlens_q_packed_and_window_calls(ref):
     kc, attn, _ = ref
     D, sq = 128, 4
