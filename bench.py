@@ -73,7 +73,7 @@ def dram_traffic_ratio(kv: str) -> dict:
     m = re.search(r"DRAM traffic . algorithmic bytes[^0-9]*([0-9]+\.[0-9]+)", text)
     if m:
         out["ratio"] = float(m.group(1))
-    m = re.search(r"kernel source sha256[^0-9a-f]*([0-9a-f]{64})", text)
+    m = re.search(r"kernel source sha256[^=]*=\s*([0-9a-f]{64})", text)
     if m:
         now = hashlib.sha256((ROOT / KERNEL_SOURCE).read_bytes()).hexdigest()
         out["stale"] = now != m.group(1)
@@ -1193,14 +1193,8 @@ def measure_decode(name: str, args, device, rank: int, world: int, dist, *, step
         raise SystemExit(f"kernel diagnostics reported a problem in {name}: {flags}")
 
     # whole job: every rank's bytes over the slowest rank's time; per-rank figures alongside
-    stats = torch.tensor([elapsed_ms, float(total_bytes), e2e[0] if e2e else 0.0, float(e2e[1]) if e2e else 0.0],
-                         dtype=torch.float64, device=device)
-    if dist is not None:
-        gathered = [torch.empty_like(stats) for _ in range(world)]
-        dist.all_gather(gathered, stats)
-        per = torch.stack(gathered).cpu()
-    else:
-        per = stats.cpu().view(1, -1)
+    from kestrel_b200.sharding import gather_rank_stats, whole_job_rate
+    per = gather_rank_stats([elapsed_ms, total_bytes, e2e[0] if e2e else 0.0, e2e[1] if e2e else 0.0], device)
     h2d, d2h = wl.e2e_bytes()
     launches = wl.launches_per_step * steps
     n_pools, n_pages, shared_pages, layers_n, B, sq, D = wl.n_pools, wl.n_pages, wl.shared_pages, wl.layers_n, wl.B, wl.sq, wl.D
@@ -1214,9 +1208,8 @@ def measure_decode(name: str, args, device, rank: int, world: int, dist, *, step
         return None
 
     peak, peak_kind = measured_hbm_peak()
-    ms_all = float(per[:, 0].max())
-    bytes_all = float(per[:, 1].sum())
-    value = bytes_all / (ms_all * 1e-3) / 1e9
+    ms_all, rate_all, own_rates = whole_job_rate(per[:, 0], per[:, 1])
+    value = rate_all / 1e9
     ms_per_step = ms_all / steps
     logical = attn_bytes / (attn_avg_ms * 1e-3) / 1e9
     achieved = attn_unique / (attn_avg_ms * 1e-3) / 1e9
@@ -1226,7 +1219,7 @@ def measure_decode(name: str, args, device, rank: int, world: int, dist, *, step
         "tokens_per_s": world * B * sq / (ms_per_step * 1e-3),
         "pct_of_8TBps": 100.0 * value / world / NOMINAL_HBM_GBS, "pct_of_measured_hbm": 100.0 * value / world / peak,
         "bytes_per_step_per_gpu": float(per[0, 1]) / steps,
-        "per_rank": [{"ms_per_step": float(r[0]) / steps, "gbs": float(r[1]) / (float(r[0]) * 1e-3) / 1e9} for r in per],
+        "per_rank": [{"ms_per_step": float(r[0]) / steps, "gbs": g / 1e9} for r, g in zip(per, own_rates)],
         "dtype": "fp8_e4m3 KV, bf16 q/out, f16 mma, fp32 softmax" if cfg["kv"] == "fp8" else "bf16",
         "config": {"workload": f"{name}: {cfg['desc']}", "n_layer_pools": n_pools, "layers": layers_n,
                    "pool_pages": n_pages, "sequences_per_gpu": B, "context_lengths": "same draw on every rank",
@@ -1254,8 +1247,8 @@ def measure_decode(name: str, args, device, rank: int, world: int, dist, *, step
         rec["roofline"]["bytes"] = ("unique: the pages every request shares are counted once per launch, which is how "
                                     "often the kernel reads them; `value` counts them once per request (logical bytes)")
     if e2e is not None:
-        e_ms, e_bytes = float(per[:, 2].max()), float(per[:, 3].sum())
-        rec["e2e"] = {"value": e_bytes / (e_ms * 1e-3) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d,
+        e_ms, e_rate, _ = whole_job_rate(per[:, 2], per[:, 3])
+        rec["e2e"] = {"value": e_rate / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d,
                       "d2h_bytes_per_step": d2h, "ms_per_step": e_ms / e2e_steps, "steps": e2e_steps,
                       "tokens_per_s": world * B * sq / (e_ms / e2e_steps * 1e-3)}
     return rec

@@ -342,7 +342,7 @@ KB200_API int kb200_sample_step_from_logits(
  *
  * Limits and rules:
  *   - the problem must fit: kb200_attn_workspace_bytes_for(args) <=
- *     KB200_STATIC_SCRATCH_BYTES (decode batches of up to 188 sequences at
+ *     KB200_STATIC_SCRATCH_BYTES (decode batches of up to 187 sequences at
  *     32 query / 8 KV heads, head_dim 128), otherwise KB200_ERR_WORKSPACE with a message saying how
  *     much was needed;
  *   - the first call on each device looks up the array's device address (one

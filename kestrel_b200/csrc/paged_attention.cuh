@@ -1584,14 +1584,9 @@ inline int tile_n_for(int kv_dtype, int head_dim, int nw) {
   return raw > 64 ? 64 : raw;
 }
 
-// Worker warps per CTA.  One warp per scheduler (4 warps, 16 KB stages) cannot hide its own MMA/ALU
-// latencies.  bf16/f16 K/V is HBM-bound with 8 warps x 2 stages of 8 KB; e4m3 K/V carries twice the
-// tokens per byte plus the widening to f16, and is fastest with 12 warps x 2 stages of 8 KB.
-inline int attn_warps_for(int kv_dtype, int head_dim) {
-  (void)head_dim;
-  return kv_dtype == KB200_DTYPE_E4M3 ? 12 : 8;
-}
-
+// Worker warps per CTA: 8 (16-bit K/V on the 16-row kernel: HBM-bound with 2 stages of 8 KB per warp) or 12
+// (e4m3 K/V, and the transposed decode kernel: more warps to hide the MMA / conversion latencies); chosen in
+// launch_attention_pass.  One warp per scheduler (4 warps, 16 KB stages) cannot hide its own latencies.
 struct AttnWorkspace {
   size_t tile_cum, seg_cum, nt, tile0, sq, qrow0, klen, bound_rec, part_ml, part_o, total;
 };
@@ -1978,9 +1973,17 @@ inline int launch_attention_pass(const kb200_attn_args* a, int k_skip, int fixed
   int sms = 0;
   if (int rc = device_sm_count(a->device, &sms)) return rc;
   const int grid = sms;
-  const int nw = attn_warps_for(a->kv_dtype, a->head_dim);
-  const int n_workers = grid * nw;
   const int group = a->n_q_heads / a->n_kv_heads;
+  const bool prefill = use_prefill_kernel(a);
+  // Segments of at most 8 query rows run the transposed decode kernel where the math, not HBM, limits the
+  // 16-row kernel: e4m3 K/V (twice the keys per byte plus the widening), and 16-bit K/V with head_dim 64
+  // (the same MMAs and twice the exponentials per byte as head_dim 128: with 8 warps the 16-row kernel waits
+  // on its own dependent MMA / ALU chains there, 45 % of the DRAM rate on short contexts).  16-bit K/V with
+  // head_dim 128 is within a few percent of the HBM roofline with the 16-row kernel already.
+  const bool decode8 = !prefill && (int64_t)group * a->seqlen_q <= kDecodeRows &&
+                       (a->kv_dtype == KB200_DTYPE_E4M3 || a->head_dim == 64);
+  const int nw = (a->kv_dtype == KB200_DTYPE_E4M3 || decode8) ? 12 : 8;
+  const int n_workers = grid * nw;
   const AttnWorkspace wl = attn_workspace_layout(a->batch, a->total_q, a->n_q_heads, a->n_kv_heads, a->head_dim,
                                                  grid * kAttnMaxWarps);
   const uint64_t ws_need = attn_pass_workspace_need(a, sms);
@@ -1994,12 +1997,7 @@ inline int launch_attention_pass(const kb200_attn_args* a, int k_skip, int fixed
     KB200_REQUIRE(a->causal != 0 && a->window_left < 0, "the block-bidirectional mask extends the causal mask: "
                                                        "causal must be set and no window given");
   }
-  const bool prefill = use_prefill_kernel(a);
   const int tile_n = prefill ? kPrefillTileKeys : tile_n_for(a->kv_dtype, a->head_dim, nw);
-  // The transposed decode kernel pays off where the math is the limiter (e4m3 K/V); 16-bit K/V
-  // is within a few percent of the HBM roofline with the general kernel already.
-  const bool decode8 = !prefill && a->kv_dtype == KB200_DTYPE_E4M3 &&
-                       (int64_t)group * a->seqlen_q <= kDecodeRows;
   // every TMA copy must land on a 128-byte boundary of shared memory; pools that cannot offer that go
   // through the split-KV kernels' cp.async gather path (the prefill kernel has none)
   const bool gather = !tma_boxes_possible(a, tile_n);
@@ -2114,8 +2112,11 @@ inline int launch_attention_pass(const kb200_attn_args* a, int k_skip, int fixed
     }
     return rc;   // every segment is written by its own CTA: nothing to merge
   }
-  if (decode8)  // e4m3 only (the kernel template also covers 16-bit K/V; measured no faster there)
+  if (decode8 && a->kv_dtype == KB200_DTYPE_E4M3)
     rc = launch_decode_dispatch<1, false>(d128, nw, tmK, tmV, p, grid, a->device, stream);
+  else if (decode8)   // 16-bit K/V, head_dim 64
+    rc = a->kv_dtype == KB200_DTYPE_BF16 ? launch_decode_hd<2, true, 64>(nw, tmK, tmV, p, grid, a->device, stream)
+                                         : launch_decode_hd<2, false, 64>(nw, tmK, tmV, p, grid, a->device, stream);
   else if (a->kv_dtype == KB200_DTYPE_E4M3)
     rc = launch_attn_dispatch<1, false>(d128, nw, tmK, tmV, p, grid, a->device, stream);
   else if (a->kv_dtype == KB200_DTYPE_BF16)

@@ -6,11 +6,12 @@
 // from HBM once and from L2 on the later passes.  HBM-bound: batch x vocab x sizeof(logit) bytes.
 //
 //   pass 1  row maximum and its first index            -> greedy rows are done here
-//   pass 2  Z = sum exp((x - max) / T)
+//   pass 2  every thread sums exp((x - max) / T) over its contiguous slice of the vocabulary; a block scan
+//           gives Z and, with top_p >= 1, already the slice that holds u * Z
 //   pass 3  (top_p < 1) threshold tau of the nucleus {p >= tau}: radix select over the bit pattern of p,
-//           three rounds of 11 + 11 + 10 bits, each a histogram of probability MASS per digit
-//   pass 4  every thread sums the nucleus mass of its contiguous slice of the vocabulary, a block scan
-//           finds the slice that holds u * mass, its owner walks it to the token
+//           three rounds of 11 + 11 + 10 bits, each a histogram of probability MASS per digit; then the
+//           slice sums again, restricted to the nucleus
+//   last    the owner of the slice that holds u * mass walks it to the token
 //
 // Everything that decides the outcome is summed in 64-bit fixed point (p * 2^40, exact integer adds in any
 // order), so the result does not depend on the order in which threads or atomics arrive: the same logits
@@ -108,7 +109,9 @@ __device__ __forceinline__ unsigned long long block_exclusive_scan_u64(unsigned 
 
 template <typename LT>
 __global__ void __launch_bounds__(kSampleThreads, 1) sample_kernel(const SampleParams p) {
-  __shared__ unsigned long long hist[2048];
+  // mass per digit as two 32-bit halves: native 32-bit shared-memory atomics, the carry propagated by hand
+  __shared__ unsigned int hist_lo[2048];
+  __shared__ unsigned int hist_hi[2048];
   __shared__ unsigned long long scratch[32];
   __shared__ float red_v[32];
   __shared__ long long red_i[32];
@@ -159,14 +162,18 @@ __global__ void __launch_bounds__(kSampleThreads, 1) sample_kernel(const SampleP
   auto prob = [&](float x) { float y; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"((x - best) * c)); return y; };
   auto fixed = [&](float pr) { return (unsigned long long)__float2ull_rz(pr * kFix); };
 
-  // ---- pass 2: Z
-  unsigned long long zloc = 0;
-  for_strided<LT>(row, 0, V, tid, kSampleThreads, vec, [&](int64_t, float x) { zloc += fixed(prob(x)); });
-  const unsigned long long Z = block_sum_u64(zloc, scratch);
+  // ---- pass 2: slice sums over the whole vocabulary, Z
+  constexpr int N = SampleVec<LT>::N;
+  int64_t chunk = (V + kSampleThreads - 1) / kSampleThreads;
+  chunk = (chunk + N - 1) / N * N;
+  const int64_t lo = min((int64_t)tid * chunk, V), hi = min(lo + chunk, V);
+  unsigned long long local = 0;
+  for_strided<LT>(row, lo, hi, 0, 1, vec, [&](int64_t, float x) { local += fixed(prob(x)); });
+  unsigned long long Z, pre = block_exclusive_scan_u64(local, scratch, Z);
 
-  // ---- pass 3: nucleus threshold (bit pattern of p) and the nucleus mass
+  // ---- pass 3: nucleus threshold (bit pattern of p), then the slice sums restricted to the nucleus
   unsigned int tau = 0;
-  unsigned long long mass = Z;
+  unsigned long long total = Z;
   if (top_p < 1.f) {
     unsigned long long target = (unsigned long long)((double)fmaxf(top_p, 0.f) * (double)Z);
     if (target < 1) target = 1;
@@ -177,44 +184,47 @@ __global__ void __launch_bounds__(kSampleThreads, 1) sample_kernel(const SampleP
     for (int round = 0; round < 3; ++round) {
       const int width = round < 2 ? 11 : 10;
       shift -= width;
-      for (int i = tid; i < 2048; i += kSampleThreads) hist[i] = 0ull;
+      for (int i = tid; i < 2048; i += kSampleThreads) { hist_lo[i] = 0u; hist_hi[i] = 0u; }
       __syncthreads();
       const unsigned int dmask = (1u << width) - 1u;
       const int hi_shift = shift + width;
       for_strided<LT>(row, 0, V, tid, kSampleThreads, vec, [&](int64_t, float x) {
         const float pr = prob(x);
         const unsigned int bits = __float_as_uint(pr);
-        if (hi_shift >= 32 || (bits >> hi_shift) == prefix)
-          atomicAdd(&hist[(bits >> shift) & dmask], fixed(pr));
+        if (hi_shift >= 32 || (bits >> hi_shift) == prefix) {
+          const unsigned long long q = fixed(pr);
+          const unsigned int d = (bits >> shift) & dmask, ql = (unsigned int)q, qh = (unsigned int)(q >> 32);
+          if (q) {
+            const unsigned int old = atomicAdd(&hist_lo[d], ql);
+            const unsigned int carry = (old + ql < old) ? 1u : 0u;
+            if (qh + carry) atomicAdd(&hist_hi[d], qh + carry);
+          }
+        }
       });
       __syncthreads();
       // suffix sums from the top digit down; thread t owns digits 2t and 2t + 1
-      const unsigned long long h0 = hist[2 * tid], h1 = hist[2 * tid + 1];
-      unsigned long long total, excl = block_exclusive_scan_u64(h0 + h1, scratch, total);
-      const unsigned long long s_hi1 = total - excl - (h0 + h1);   // mass of digits above 2t + 1
+      const unsigned long long h0 = ((unsigned long long)hist_hi[2 * tid] << 32) + hist_lo[2 * tid];
+      const unsigned long long h1 = ((unsigned long long)hist_hi[2 * tid + 1] << 32) + hist_lo[2 * tid + 1];
+      unsigned long long tot, excl = block_exclusive_scan_u64(h0 + h1, scratch, tot);
+      const unsigned long long s_hi1 = tot - excl - (h0 + h1);     // mass of digits above 2t + 1
       const unsigned long long s1 = s_hi1 + h1, s0 = s1 + h0;      // mass of digits >= 2t + 1, >= 2t
       if (above + s1 >= target && above + s_hi1 < target) { sel_digit = 2 * tid + 1; sel_above = above + s_hi1; }
       else if (above + s0 >= target && above + s1 < target) { sel_digit = 2 * tid; sel_above = above + s1; }
       __syncthreads();
       prefix = (prefix << width) | sel_digit;
       above = sel_above;
-      if (round == 2) mass = above + hist[sel_digit];
       __syncthreads();
     }
     tau = prefix;
+    local = 0;
+    for_strided<LT>(row, lo, hi, 0, 1, vec, [&](int64_t, float x) {
+      const float pr = prob(x);
+      if (__float_as_uint(pr) >= tau) local += fixed(pr);
+    });
+    pre = block_exclusive_scan_u64(local, scratch, total);
   }
 
-  // ---- pass 4: the slice of the vocabulary that holds u * mass, then the token inside it
-  constexpr int N = SampleVec<LT>::N;
-  int64_t chunk = (V + kSampleThreads - 1) / kSampleThreads;
-  chunk = (chunk + N - 1) / N * N;
-  const int64_t lo = min((int64_t)tid * chunk, V), hi = min(lo + chunk, V);
-  unsigned long long local = 0;
-  for_strided<LT>(row, lo, hi, 0, 1, vec, [&](int64_t, float x) {
-    const float pr = prob(x);
-    if (__float_as_uint(pr) >= tau) local += fixed(pr);
-  });
-  unsigned long long total, pre = block_exclusive_scan_u64(local, scratch, total);
+  // ---- the slice of the vocabulary that holds u * mass, then the token inside it
   unsigned long long want = (unsigned long long)((double)p.uniforms[b] * (double)total);
   if (total > 0 && want >= total) want = total - 1;
   if (tid == 0) found_id = best_i;   // (only kept if no slice claims the target: an empty nucleus cannot happen)

@@ -44,3 +44,26 @@ def combine_step_stats(elapsed_ms: float, work_units: float, device: Optional[to
     dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
     dist.all_reduce(u, op=dist.ReduceOp.SUM, group=group)
     return t.item(), u.item()
+
+
+def gather_rank_stats(values, device: Optional[torch.device] = None, group=None) -> torch.Tensor:
+    """Every rank's measurements side by side: ``values`` (a sequence of floats, the same length on every
+    rank) -> float64 tensor ``[world, len(values)]`` on the CPU, row ``r`` from rank ``r``.  One all-gather,
+    outside any timed region; without an initialised process group a single row."""
+    import torch.distributed as dist
+
+    mine = torch.tensor([float(v) for v in values], dtype=torch.float64, device=device)
+    if not (dist.is_available() and dist.is_initialized()):
+        return mine.cpu().view(1, -1)
+    rows = [torch.empty_like(mine) for _ in range(dist.get_world_size(group))]
+    dist.all_gather(rows, mine, group=group)
+    return torch.stack(rows).cpu()
+
+
+def whole_job_rate(elapsed_ms: torch.Tensor, work_units: torch.Tensor) -> tuple[float, float, list[float]]:
+    """``(slowest rank's time in ms, work of all ranks per second, each rank's own rate per second)`` of a step
+    that every rank ran on its own shard: the job is as slow as its slowest rank and did everybody's work."""
+    t = float(elapsed_ms.max())
+    total = float(work_units.sum())
+    own = [float(u) / (float(ms) * 1e-3) if float(ms) > 0 else 0.0 for ms, u in zip(elapsed_ms.tolist(), work_units.tolist())]
+    return t, (total / (t * 1e-3) if t > 0 else 0.0), own
