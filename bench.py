@@ -1314,9 +1314,17 @@ def main() -> None:
                     help="cfg4: read the cached prefix once per request (plain calls) instead of once per batch")
     ap.add_argument("--only", action="store_true",
                     help="measure the named workload alone (no `workloads` map with the other configurations)")
+    ap.add_argument("--page-size", type=int, default=0, help="override the page size of the pools (default 16)")
     ap.add_argument("--batch", type=int, default=0, help="override the workload's batch (profiling on a small case)")
     ap.add_argument("--layers", type=int, default=0, help="override the workload's layer count (profiling)")
     args = ap.parse_args()
+    if args.page_size:
+        global PAGE
+        PAGE = args.page_size
+        args.only = True
+        for table in (WORKLOADS, PREFILL_WORKLOADS):
+            for cfg in table.values():
+                cfg["desc"] = cfg["desc"].replace("page 16", f"page {PAGE}")
     if args.impl == "flashinfer":
         run_yardstick(args)
         return

@@ -112,10 +112,12 @@ struct AttnParams {
   // (no plan launch; CTA 0 also stores it for the merge kernel); else attn_plan_kernel ran first
   int plan_in_kernel;
   long long total_q;     // rows of q (bounds the packed row ranges)
-  // gather: the (page, head) rows are too short for a TMA box (a box must be a multiple of 128 bytes in
-  // shared memory: page_size 1 with 64-byte e4m3 rows, the reference's own FP8 configuration,
-  // kestrel/models/moondream/runtime.py:645-663).  The warps then fetch their tiles 16 bytes at a time
-  // with cp.async, through these plain pointers and byte strides, into the same swizzled layout.
+  // gather: the warps fetch their tiles 16 bytes at a time with cp.async, through these plain pointers and
+  // byte strides, into the same swizzled layout as the TMA boxes would.  For pools whose (page, head) rows
+  // are too short for a box (a box must fill a multiple of 128 bytes of shared memory: page size 1 with
+  // 64-byte e4m3 rows, the reference's own FP8 configuration, kestrel/models/moondream/runtime.py:645-663)
+  // and for pages of one or two tokens (the reference's default page size is 1, kestrel/config.py:164),
+  // where a box per token costs more than it moves.
   int gather;
   const char* k_base;
   const char* v_base;
@@ -1657,9 +1659,7 @@ template <int KVB, bool BF16, int HD>
 inline int launch_decode_hd(int nw, const CUtensorMap& tmK, const CUtensorMap& tmV, const AttnParams& p, int grid,
                             int dev, cudaStream_t stream) {
   (void)nw;   // the transposed kernel runs 12 warps
-  // only 64-byte rows (e4m3, head_dim 64) can be too short for a TMA box
-  if constexpr (KVB == 1 && HD == 64)
-    if (p.gather) return launch_decode_variant<KVB, HD, BF16, 12, 2, true>(tmK, tmV, p, grid, dev, stream);
+  if (p.gather) return launch_decode_variant<KVB, HD, BF16, 12, 2, true>(tmK, tmV, p, grid, dev, stream);
   return launch_decode_variant<KVB, HD, BF16, 12, 2, false>(tmK, tmV, p, grid, dev, stream);
 }
 
@@ -1674,10 +1674,13 @@ template <int KVB, bool BF16, int HD>
 inline int launch_attn_hd(int nw, const CUtensorMap& tmK, const CUtensorMap& tmV, const AttnParams& p, int grid,
                           int dev, cudaStream_t stream) {
   (void)nw;   // 12 warps for e4m3 K/V, 8 for 16-bit
-  if constexpr (KVB == 1 && HD == 64)
+  if constexpr (KVB == 1) {
     if (p.gather) return launch_attn_variant<KVB, HD, BF16, 12, 2, true>(tmK, tmV, p, grid, dev, stream);
-  if constexpr (KVB == 1) return launch_attn_variant<KVB, HD, BF16, 12, 2, false>(tmK, tmV, p, grid, dev, stream);
-  else return launch_attn_variant<KVB, HD, BF16, 8, 2, false>(tmK, tmV, p, grid, dev, stream);
+    return launch_attn_variant<KVB, HD, BF16, 12, 2, false>(tmK, tmV, p, grid, dev, stream);
+  } else {
+    if (p.gather) return launch_attn_variant<KVB, HD, BF16, 8, 2, true>(tmK, tmV, p, grid, dev, stream);
+    return launch_attn_variant<KVB, HD, BF16, 8, 2, false>(tmK, tmV, p, grid, dev, stream);
+  }
 }
 
 template <int KVB, bool BF16>
@@ -2002,9 +2005,12 @@ inline int launch_attention_pass(const kb200_attn_args* a, int k_skip, int fixed
   const int tile_n = prefill ? kPrefillTileKeys : tile_n_for(a->kv_dtype, a->head_dim, nw);
   // every TMA copy must land on a 128-byte boundary of shared memory; pools that cannot offer that go
   // through the split-KV kernels' cp.async gather path (the prefill kernel has none)
-  const bool gather = !tma_boxes_possible(a, tile_n);
-  if (gather && !(a->kv_dtype == KB200_DTYPE_E4M3 && a->head_dim == 64))
-    return fail(KB200_ERR_UNSUPPORTED, "page_size %d with %d-byte rows is not supported", P, a->head_dim * es);
+  // Pages of one or two tokens are gathered as well: a box per token (or two) costs the issuing warp more than
+  // the sixteen 16-byte copies per lane of the gather.  Attention call, GB/s, boxes | gather, same GPU:
+  //   bf16 D=128, 64 sequences U[1k, 8k]:  P=1 2450 | 4460   P=2 4000 | 4640   P=4 5380 | 4920   P=8 6170 | 5000
+  //   e4m3 D=128, 32 sequences U[4k, 32k]: P=1 2970 | 4500   P=2 4620 | 5030   P=4 5800 | 5140   P=8 5430 | 5390
+  constexpr int kGatherMaxPage = 2;
+  const bool gather = !tma_boxes_possible(a, tile_n) || (!prefill && P <= kGatherMaxPage);
   if (gather && prefill)
     return fail(KB200_ERR_UNSUPPORTED, "a block mask on a pool with page_size %d and %d-byte rows is not supported", P,
                 a->head_dim * es);
@@ -2118,8 +2124,8 @@ inline int launch_attention_pass(const kb200_attn_args* a, int k_skip, int fixed
     rc = launch_decode_dispatch<1, false>(d128, nw, tmK, tmV, p, grid, a->device, stream);
   else if (decode8)   // 16-bit K/V, head_dim 64
     rc = a->kv_dtype == KB200_DTYPE_BF16
-             ? launch_decode_variant<2, 64, true, 12, 2, false>(tmK, tmV, p, grid, a->device, stream)
-             : launch_decode_variant<2, 64, false, 12, 2, false>(tmK, tmV, p, grid, a->device, stream);
+             ? launch_decode_hd<2, true, 64>(nw, tmK, tmV, p, grid, a->device, stream)
+             : launch_decode_hd<2, false, 64>(nw, tmK, tmV, p, grid, a->device, stream);
   else if (a->kv_dtype == KB200_DTYPE_E4M3)
     rc = launch_attn_dispatch<1, false>(d128, nw, tmK, tmV, p, grid, a->device, stream);
   else if (a->kv_dtype == KB200_DTYPE_BF16)
