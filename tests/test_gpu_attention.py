@@ -194,6 +194,21 @@ def test_single_long_sequence_is_split_across_warps_and_merged(kv):
     assert torch.allclose(lse.cpu(), want_lse, atol=2e-3, rtol=1e-3)
 
 
+def test_long_sequences_cut_by_dozens_of_ranges():
+    """270k keys in three sequences: every (sequence, head) segment is spread over dozens of warps' tile ranges
+    (more than one 32-lane ballot's worth for the longest), on the 16-bit and the FP8 kernels."""
+    p = make_paged_problem(seed=77, batch=3, len_lo=0, len_hi=0, n_q_heads=32, n_kv_heads=8, head_dim=128,
+                           page_size=16, dtype=torch.bfloat16, lengths=[150001, 70003, 49999])
+    out, want, lse, want_lse = run_case(p, torch.bfloat16, return_lse=True)
+    assert_close(out, want, "bf16")
+    assert torch.allclose(lse.cpu(), want_lse, atol=2e-3, rtol=1e-3)
+    out, want = run_case(p, torch.bfloat16, kv="fp8", scales=(0.03, 0.02))
+    assert_close(out, want, "fp8")
+    p["q"] = p["q"].repeat(1, 4, 1, 1)      # 4 query rows per sequence: the 16-row kernel on the FP8 pool
+    out, want = run_case(p, torch.bfloat16, kv="fp8", scales=(0.03, 0.02))
+    assert_close(out, want, "fp8 verify")
+
+
 def test_peaked_softmax_and_custom_scale():
     """Scores with a large dynamic range: one key dominates; softmax_scale=1.0 as Gemma passes."""
     p = make_paged_problem(seed=19, batch=4, len_lo=200, len_hi=900, n_q_heads=8, n_kv_heads=2, head_dim=64,
