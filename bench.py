@@ -1,6 +1,6 @@
 """Benchmark of the paged-KV hot path: append + paged decode attention over a KV stack.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload cfg2|cfg3|cfg4|cfg5] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload cfg2|cfg3|cfg4|cfg5|cfg5_sq8] [--impl reference]
 
 One *step* is one decode step of the whole KV stack of the workload: decode metadata and slot
 mapping once, then per layer the append of the new tokens' K/V rows (quantised to FP8 where the
@@ -94,6 +94,9 @@ WORKLOADS = {
                  desc="bf16, 24 layers, 256 sequences per GPU, ctx U[2048,16384], 4-token verify + 4-token append, "
                       "32/8 heads, D=128, page 16"),
 }
+WORKLOADS["cfg5_sq8"] = dict(WORKLOADS["cfg5"], sq=8,
+                             desc=WORKLOADS["cfg5"]["desc"].replace("4-token verify + 4-token append",
+                                                                    "8-token verify + 8-token append (32 packed rows per KV head)"))
 HQ, HKV, PAGE = 32, 8, 16
 
 PREFILL_WORKLOADS = {
@@ -223,7 +226,7 @@ class GpuWorkload:
         self.kv_bytes = 1 if cfg["kv"] == "fp8" else 2
         # context lengths and the page permutation are the same on every rank (the per-GPU work of a
         # weak-scaling run must not depend on the rank's draw); the K/V/Q data below is seeded per rank
-        g = torch.Generator().manual_seed(1000 + int(name[3:]))
+        g = torch.Generator().manual_seed(1000 + int(name[3]))
         prefix = cfg.get("prefix", 0)
         suffix = torch.randint(cfg["lo"], cfg["hi"] + 1, (self.B,), generator=g)
         self.len0 = suffix + prefix                      # context before the first timed/warm-up step
@@ -851,7 +854,7 @@ class CpuWorkload:
         self.D, self.sq = cfg["head_dim"], cfg["sq"]
         self.fp8 = cfg["kv"] == "fp8"
         self.kv_bytes = 1 if self.fp8 else 2
-        g = torch.Generator().manual_seed(1000 + int(name[3:]))
+        g = torch.Generator().manual_seed(1000 + int(name[3]))
         prefix = cfg.get("prefix", 0)
         full = torch.randint(cfg["lo"], cfg["hi"] + 1, (cfg["batch"],), generator=g) + prefix
         self.len0 = full[: self.B]
@@ -1366,7 +1369,7 @@ def main() -> None:
     # the other configurations, same process, same box: sub-records under "workloads"
     extra = {}
     if not args.only:
-        for name in ("cfg5", "cfg2", "cfg4"):
+        for name in ("cfg5", "cfg5_sq8", "cfg2", "cfg4"):
             if name == args.workload:
                 continue
             one_layer = WORKLOADS[name]["layers"] == 1

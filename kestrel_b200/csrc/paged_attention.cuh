@@ -97,7 +97,8 @@ struct AttnParams {
   float* part_o;        // [slots][16][HD] unnormalised
   int64_t n_pages;
   int batch, seqlen_q, hq, hkv, group, page_size, causal, window_left, q_is_bf16, n_workers, tile_n;
-  int rows_per_seg;  // query rows per segment: 16 (general kernel) or 8 (decode kernel)
+  int rows_per_seg;  // query rows per segment: 16 (general kernel), 8 (decode kernel) or 32 (32-row kernel)
+  int seg_blocks;    // 16-row partial slots per (segment, worker): 2 for 32-row segments, else 1
   int uniform_nseg;  // segments per sequence when that is the same for all (padded q, no seqused_q), else 0
   // Shared-prefix passes.  k_skip: the first k_skip keys of every sequence are served by another pass
   // (page_table already points past their pages; lengths are taken relative to them).
@@ -228,6 +229,9 @@ __device__ __forceinline__ void ldsm_x4(uint32_t& r0, uint32_t& r1, uint32_t& r2
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
                : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
                : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x2(uint32_t& r0, uint32_t& r1, uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0, %1}, [%2];" : "=r"(r0), "=r"(r1) : "r"(addr));
 }
 __device__ __forceinline__ void ldsm_x4_t(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, uint32_t addr) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
@@ -975,6 +979,10 @@ paged_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
   }
 }
 
+}  // namespace kb200
+#include "paged_attention_rows32.cuh"
+namespace kb200 {
+
 // ---------------------------------------------------------------------------
 // Decode kernel: segments of at most 8 query rows (GQA group x query positions),
 // computed in the transposed form so that the 16-wide MMA dimension carries keys
@@ -1432,18 +1440,20 @@ __global__ void __launch_bounds__(128) attn_merge_kernel(const AttnParams p) {
         const int row = mb * p.rows_per_seg + rl;
         if (row >= nrows) continue;
         float M = -INFINITY;
+        const int sub = rl >> 4, r16 = rl & 15;   // 16-row slot of the row (32-row segments have two per worker)
         for (int wi = wf; wi <= wl; ++wi)
-          if (has_tiles(wi)) M = fmaxf(M, p.part_ml[((int64_t)seg + wi) * (kRowsPerSeg * 2) + rl * 2]);
+          if (has_tiles(wi))
+            M = fmaxf(M, p.part_ml[(((int64_t)seg + wi) * p.seg_blocks + sub) * (kRowsPerSeg * 2) + r16 * 2]);
         float L = 0.f;
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
         if (M != -INFINITY) {
           for (int wi = wf; wi <= wl; ++wi) {
             if (!has_tiles(wi)) continue;
-            const int64_t slot = (int64_t)seg + wi;
-            const float2 ml = *reinterpret_cast<const float2*>(p.part_ml + slot * (kRowsPerSeg * 2) + rl * 2);
+            const int64_t slot = ((int64_t)seg + wi) * p.seg_blocks + sub;
+            const float2 ml = *reinterpret_cast<const float2*>(p.part_ml + slot * (kRowsPerSeg * 2) + r16 * 2);
             if (ml.x == -INFINITY) continue;
             const float wgt = ex2(ml.x - M);
-            const float4 o = *reinterpret_cast<const float4*>(p.part_o + slot * (kRowsPerSeg * HD) + rl * HD + d);
+            const float4 o = *reinterpret_cast<const float4*>(p.part_o + slot * (kRowsPerSeg * HD) + r16 * HD + d);
             L += wgt * ml.y;
             acc.x += wgt * o.x; acc.y += wgt * o.y; acc.z += wgt * o.z; acc.w += wgt * o.w;
           }
@@ -1599,7 +1609,9 @@ inline int64_t attn_max_segments(int64_t batch, int64_t total_q, int hq, int hkv
   return (int64_t)hkv * ((group * total_q + kDecodeRows - 1) / kDecodeRows + batch);  // smallest segment size
 }
 
-inline AttnWorkspace attn_workspace_layout(int64_t batch, int64_t total_q, int hq, int hkv, int hd, int n_workers) {
+// rows32: the call runs the 32-row kernel, whose (segment, worker) partials take two 16-row slots each.
+inline AttnWorkspace attn_workspace_layout(int64_t batch, int64_t total_q, int hq, int hkv, int hd, int n_workers,
+                                           bool rows32) {
   auto up = [](size_t x) { return (x + 255) & ~size_t(255); };
   AttnWorkspace w;
   size_t off = 0;
@@ -1610,7 +1622,9 @@ inline AttnWorkspace attn_workspace_layout(int64_t batch, int64_t total_q, int h
   w.sq = off; off = up(off + sizeof(int) * batch);
   w.qrow0 = off; off = up(off + sizeof(int) * batch);
   w.klen = off; off = up(off + sizeof(int) * batch);
-  const int64_t slots = attn_max_segments(batch, total_q, hq, hkv) + n_workers;
+  // 16-row kernel: slot = segment + worker.  32-row kernel: slot = 2 * (segment + worker) + block, with at most
+  // hkv * (group * total_q / 32 + batch) segments: twice that is within attn_max_segments + hkv * batch.
+  const int64_t slots = attn_max_segments(batch, total_q, hq, hkv) + (rows32 ? hkv * batch + 2 * (int64_t)n_workers : n_workers);
   w.part_ml = off; off = up(off + sizeof(float) * slots * kRowsPerSeg * 2);
   w.part_o = off; off = up(off + sizeof(float) * slots * kRowsPerSeg * hd);
   w.bound_rec = off; off = up(off + sizeof(int) * 8 * n_workers);   // (split-KV kernels only, like the partials)
@@ -1653,6 +1667,28 @@ inline int launch_decode_variant(const CUtensorMap& tmK, const CUtensorMap& tmV,
   const size_t smem = T::SMEM_BYTES + (p.plan_in_kernel ? plan_smem_bytes(p.batch) : 0);
   KB200_CUDA_OK(launch_kernel(kern, dim3(grid), dim3(NW * 32), smem, stream, tmK, tmV, p));
   return KB200_OK;
+}
+
+template <int KVB, int HD, bool BF16, bool GATHER>
+inline int launch_rows32_variant(const CUtensorMap& tmK, const CUtensorMap& tmV, const AttnParams& p, int grid,
+                                 int dev, cudaStream_t stream) {
+  using L = Rows32Smem<KVB, HD, 2>;
+  auto kern = paged_attn_rows32_kernel<KVB, HD, BF16, 2, GATHER>;
+  static SmemAttrOnce once;
+  static_assert(L::SMEM_BYTES + plan_smem_bytes(kPlanSmemMaxBatch) <= 232448, "shared memory of the largest in-kernel plan");
+  if (int rc = once.ensure(kern, L::SMEM_BYTES + plan_smem_bytes(kPlanSmemMaxBatch), dev)) return rc;
+  const size_t smem = L::SMEM_BYTES + (p.plan_in_kernel ? plan_smem_bytes(p.batch) : 0);
+  KB200_CUDA_OK(launch_kernel(kern, dim3(grid), dim3(256), smem, stream, tmK, tmV, p));
+  return KB200_OK;
+}
+
+template <int KVB, bool BF16>
+inline int launch_rows32_dispatch(bool d128, const CUtensorMap& tmK, const CUtensorMap& tmV, const AttnParams& p,
+                                  int grid, int dev, cudaStream_t stream) {
+  if (d128) return p.gather ? launch_rows32_variant<KVB, 128, BF16, true>(tmK, tmV, p, grid, dev, stream)
+                            : launch_rows32_variant<KVB, 128, BF16, false>(tmK, tmV, p, grid, dev, stream);
+  return p.gather ? launch_rows32_variant<KVB, 64, BF16, true>(tmK, tmV, p, grid, dev, stream)
+                  : launch_rows32_variant<KVB, 64, BF16, false>(tmK, tmV, p, grid, dev, stream);
 }
 
 template <int KVB, bool BF16, int HD>
@@ -1728,9 +1764,18 @@ inline bool use_prefill_kernel(const kb200_attn_args* a) {
 
 // Scratch bytes this very call needs: the plan arrays, plus the split-KV partials unless the prefill
 // kernel serves it.
+// Segments of 17 to 32 packed rows (and what is left of longer ones below the prefill kernel's threshold) run the
+// 32-row split-KV kernel: one pass over the keys per 32 rows instead of one per 16.
+inline bool use_rows32_kernel(const kb200_attn_args* a) {
+  if (a->n_kv_heads <= 0 || use_prefill_kernel(a)) return false;
+  int64_t rows = a->seqlen_q;
+  if (a->cu_seqlens_q && a->batch > 0) rows = std::min<int64_t>(rows, (a->total_q + a->batch - 1) / a->batch);
+  return (int64_t)(a->n_q_heads / a->n_kv_heads) * rows > kRowsPerSeg;
+}
+
 inline uint64_t attn_pass_workspace_need(const kb200_attn_args* a, int sms) {
   const AttnWorkspace wl = attn_workspace_layout(a->batch, a->total_q, a->n_q_heads, a->n_kv_heads, a->head_dim,
-                                                 sms * kAttnMaxWarps);
+                                                 sms * kAttnMaxWarps, use_rows32_kernel(a));
   return use_prefill_kernel(a) ? wl.part_ml : wl.total;
 }
 
@@ -1987,10 +2032,11 @@ inline int launch_attention_pass(const kb200_attn_args* a, int k_skip, int fixed
                        (a->kv_dtype == KB200_DTYPE_E4M3 || a->head_dim == 64);
   // (12 warps x 2 stages; 8 x 3 and 6 x 4 -- more tiles in flight per warp, fewer warps -- measured 2 % and
   // 13 % slower on the short contexts of a shared-prefix batch)
-  const int nw = (a->kv_dtype == KB200_DTYPE_E4M3 || decode8) ? 12 : 8;
+  const bool rows32 = use_rows32_kernel(a);   // (8 warps: two output accumulators per thread need the registers)
+  const int nw = rows32 ? 8 : (a->kv_dtype == KB200_DTYPE_E4M3 || decode8) ? 12 : 8;
   const int n_workers = grid * nw;
   const AttnWorkspace wl = attn_workspace_layout(a->batch, a->total_q, a->n_q_heads, a->n_kv_heads, a->head_dim,
-                                                 grid * kAttnMaxWarps);
+                                                 grid * kAttnMaxWarps, rows32);
   const uint64_t ws_need = attn_pass_workspace_need(a, sms);
   if (!a->workspace || a->workspace_bytes < ws_need)
     return fail(KB200_ERR_WORKSPACE, "workspace too small: need %llu bytes, got %llu", (unsigned long long)ws_need,
@@ -2076,7 +2122,8 @@ inline int launch_attention_pass(const kb200_attn_args* a, int k_skip, int fixed
   p.q_is_bf16 = a->q_dtype == KB200_DTYPE_BF16;
   p.n_workers = n_workers;
   p.tile_n = tile_n;
-  p.rows_per_seg = prefill ? kPrefillRowsPerSeg : decode8 ? kDecodeRows : kRowsPerSeg;
+  p.rows_per_seg = prefill ? kPrefillRowsPerSeg : decode8 ? kDecodeRows : rows32 ? 2 * kRowsPerSeg : kRowsPerSeg;
+  p.seg_blocks = rows32 ? 2 : 1;
   p.uniform_nseg = (packed || a->seqused_q) ? 0
                    : a->n_kv_heads * ((group * a->seqlen_q + p.rows_per_seg - 1) / p.rows_per_seg);
   p.k_skip = k_skip;
@@ -2120,7 +2167,12 @@ inline int launch_attention_pass(const kb200_attn_args* a, int k_skip, int fixed
     }
     return rc;   // every segment is written by its own CTA: nothing to merge
   }
-  if (decode8 && a->kv_dtype == KB200_DTYPE_E4M3)
+  if (rows32 && a->kv_dtype == KB200_DTYPE_E4M3)
+    rc = launch_rows32_dispatch<1, false>(d128, tmK, tmV, p, grid, a->device, stream);
+  else if (rows32)
+    rc = a->kv_dtype == KB200_DTYPE_BF16 ? launch_rows32_dispatch<2, true>(d128, tmK, tmV, p, grid, a->device, stream)
+                                         : launch_rows32_dispatch<2, false>(d128, tmK, tmV, p, grid, a->device, stream);
+  else if (decode8 && a->kv_dtype == KB200_DTYPE_E4M3)
     rc = launch_decode_dispatch<1, false>(d128, nw, tmK, tmV, p, grid, a->device, stream);
   else if (decode8)   // 16-bit K/V, head_dim 64
     rc = a->kv_dtype == KB200_DTYPE_BF16
