@@ -116,6 +116,16 @@ FALLBACK_BF16_TFLOPS = 1590.0
 # helpers
 # ----------------------------------------------------------------------------------------------
 
+def split_kv_kernel_name(cfg: dict) -> str:
+    """The split-KV kernel the library picks for a workload (rows = GQA group x query positions per KV head)."""
+    rows = (HQ // HKV) * cfg["sq"]
+    if rows > 16:
+        return "paged_attn_rows32_kernel"
+    if rows <= 8 and (cfg["kv"] == "fp8" or cfg["head_dim"] == 64):
+        return "paged_attn_decode_kernel"
+    return "paged_attn_kernel"
+
+
 def measured_hbm_peak() -> tuple[float, str]:
     f = ROOT / "MEASURED_PEAKS.json"
     if f.exists():
@@ -1232,8 +1242,7 @@ def measure_decode(name: str, args, device, rank: int, world: int, dist, *, step
                    "working set near L2 size; see tokens/s rather than GB/s"},
         "gpu_launches": launches, "clocks": clocks,
         "roofline": {"bound": "hbm",
-                     "kernel": ("paged_attn_decode_kernel" if cfg["kv"] == "fp8" and sq * 4 <= 8 else "paged_attn_kernel")
-                               + " (+ its merge launch" + (", the prefix pass on paged_prefill_kernel" if shared_pages else "") + ")",
+                     "kernel": split_kv_kernel_name(cfg) + " (+ its merge launch" + (", the prefix pass on paged_prefill_kernel" if shared_pages else "") + ")",
                      "achieved": achieved, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak,
                      "traffic": None if traffic["ratio"] is None else traffic["ratio"] * attn_unique,
                      "traffic_source": f"{traffic['profile']}: ncu dram__bytes_read+write of a reduced launch of the same "

@@ -120,7 +120,10 @@ uint64_t kb200_attn_workspace_bytes(int64_t batch, int64_t total_q, int32_t n_q_
   if (batch <= 0 || total_q <= 0 || n_q_heads <= 0 || n_kv_heads <= 0 || head_dim <= 0) return 0;
   int sms = 0;
   if (device_sm_count(device, &sms) != KB200_OK) return 0;
-  return attn_workspace_layout(batch, total_q, n_q_heads, n_kv_heads, head_dim, sms * kAttnMaxWarps, true).total;
+  // a call of these dimensions can reach the 32-row kernel (two partial slots per worker) only when a sequence
+  // brings more than 16 packed rows on average
+  const bool rows32_possible = (int64_t)(n_q_heads / n_kv_heads) * ((total_q + batch - 1) / batch) > kRowsPerSeg;
+  return attn_workspace_layout(batch, total_q, n_q_heads, n_kv_heads, head_dim, sms * kAttnMaxWarps, rows32_possible).total;
 }
 
 uint64_t kb200_attn_workspace_bytes_for(const kb200_attn_args* args) {

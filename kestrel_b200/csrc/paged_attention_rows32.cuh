@@ -319,7 +319,7 @@ paged_attn_rows32_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
           mk_lo = (2 * c4 < kv_left ? 0x0000ffffu : 0u) | (2 * c4 + 1 < kv_left ? 0xffff0000u : 0u);
           mk_hi = (2 * c4 + 8 < kv_left ? 0x0000ffffu : 0u) | (2 * c4 + 9 < kv_left ? 0xffff0000u : 0u);
         }
-        const int row = ks * 16 + ((lane >> 3) & 1) * 8 + (lane & 7);
+        [[maybe_unused]] const int row = ks * 16 + ((lane >> 3) & 1) * 8 + (lane & 7);
         if constexpr (KVB == 2) {
 #pragma unroll
           for (int q2 = 0; q2 < HD / 16; ++q2) {
