@@ -1397,10 +1397,14 @@ paged_attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
 // ---------------------------------------------------------------------------
 // Merge.  A segment that lies inside one warp's tile range was normalised and written by the
 // attention kernel.  Only a segment cut by a range boundary left partials, so the blocks stride
-// over the W - 1 boundaries, not over the segments: boundary w (the first tile of worker w) is
-// handled when it falls strictly inside a segment and is the first boundary to do so.  A second
-// loop zero-fills the rows of sequences without visible keys.
+// over the W - 1 boundaries, not over the segments: boundary w (the first tile of worker w) takes
+// part when it falls strictly inside a segment, and ALL the boundaries that cut one segment share
+// its work items (4 consecutive d of one query row each) -- a batch of a few long sequences has
+// few segments, each cut by a hundred boundaries, and must not be merged by a handful of blocks.
+// A second loop zero-fills the rows of sequences without visible keys.
 // ---------------------------------------------------------------------------
+constexpr int kMergeCoopParts = 8;   // from this many partials per segment on, a warp shares an item
+
 template <int HD>
 __global__ void __launch_bounds__(128) attn_merge_kernel(const AttnParams p) {
   pdl_wait();
@@ -1408,9 +1412,16 @@ __global__ void __launch_bounds__(128) attn_merge_kernel(const AttnParams p) {
   const long long total = p.tile_cum[p.batch];
   constexpr float kLn2 = 0.6931471805599453f;
   constexpr int kQuads = HD / 4;
+  const int lane = threadIdx.x & 31, wp = threadIdx.x >> 5;
+  // x * n_workers / total and w * total / n_workers: 32-bit divisions whenever the products fit (a 64-bit division
+  // is a call of a hundred instructions, and every block has a chain of them before its first load)
+  const bool narrow = total * p.n_workers < (1ll << 31);
+  auto muldiv = [&](long long a, long long b, long long c) -> long long {
+    return narrow ? (long long)((uint32_t)(a * b) / (uint32_t)c) : a * b / c;
+  };
   if (total > 0) {
     for (int w = blockIdx.x + 1; w < p.n_workers; w += gridDim.x) {
-      const long long g = (long long)w * total / p.n_workers;
+      const long long g = muldiv(w, total, p.n_workers);
       if (g <= 0 || g >= total) continue;
       // where tile g lies: the record the worker that starts there left (no search, one load)
       const int4* rec = reinterpret_cast<const int4*>(p.bound_rec + 8 * (size_t)w);
@@ -1420,10 +1431,13 @@ __global__ void __launch_bounds__(128) attn_merge_kernel(const AttnParams p) {
       c.sq = rb.x; c.qr = rb.y; c.segbase = rb.z; c.nmb = rb.w;
       if (c.t == 0) continue;       // the boundary coincides with the segment's first tile: not a cut
       const long long t0 = g - c.t, t1 = t0 + c.nt;   // the segment's tiles
-      if ((long long)(w - 1) * total / p.n_workers > t0) continue;   // an earlier boundary cuts it too: that one merges
       const int seg = c.segbase + c.seg;
-      const int wf = (int)(((t0 + 1) * p.n_workers - 1) / total);
-      const int wl = (int)((t1 * p.n_workers - 1) / total);
+      // workers wf .. wl hold the segment's tiles; the boundaries wf + 1 .. wl cut it, this one is number k of nb
+      const int wf = narrow ? (int)(((uint32_t)(t0 + 1) * (uint32_t)p.n_workers - 1u) / (uint32_t)total)
+                            : (int)(((t0 + 1) * p.n_workers - 1) / total);
+      const int wl = narrow ? (int)(((uint32_t)t1 * (uint32_t)p.n_workers - 1u) / (uint32_t)total)
+                            : (int)((t1 * p.n_workers - 1) / total);
+      const int nb = wl - wf, k = w - wf - 1;
       const int b = c.b, sq = c.sq;
       const int h = c.seg / c.nmb, mb = c.seg - h * c.nmb;
       const int nrows = p.group * sq;
@@ -1432,42 +1446,67 @@ __global__ void __launch_bounds__(128) attn_merge_kernel(const AttnParams p) {
       // A worker between wf and wl whose range is empty (fewer tiles than workers) wrote nothing.
       const bool all_have = total >= p.n_workers;
       auto has_tiles = [&](int wi) {
-        return all_have || (long long)wi * total / p.n_workers < (long long)(wi + 1) * total / p.n_workers;
+        return all_have || muldiv(wi, total, p.n_workers) < muldiv(wi + 1, total, p.n_workers);
       };
-      // one work item = 4 consecutive d of one query row; the partial loads of an item are independent
-      for (int item = threadIdx.x; item < p.rows_per_seg * kQuads; item += 128) {
+      auto ml_of = [&](int wi, int sub, int r16) {
+        return p.part_ml + (((int64_t)seg + wi) * p.seg_blocks + sub) * (kRowsPerSeg * 2) + r16 * 2;
+      };
+      auto o_of = [&](int wi, int sub, int r16, int d) {
+        return p.part_o + (((int64_t)seg + wi) * p.seg_blocks + sub) * (kRowsPerSeg * HD) + r16 * HD + d;
+      };
+      const int n_items = p.rows_per_seg * kQuads;
+      // Few partials: one thread per item.  Many: one warp per item (the item is then uniform over the warp), its
+      // lanes striding over the partials.  One loop serves both: the kernel is a chain of latencies, and a second
+      // copy of the loop body costs more in instruction fetches than it saves.
+      const bool coop = nb + 1 >= kMergeCoopParts;
+      const int item_step = coop ? nb * 4 : nb * 128;
+      const int wi0 = coop ? wf + lane : wf, wi_step = coop ? 32 : 1;
+      for (int item = coop ? k * 4 + wp : k * 128 + threadIdx.x; item < n_items; item += item_step) {
         const int rl = item / kQuads, d = (item - rl * kQuads) * 4;
         const int row = mb * p.rows_per_seg + rl;
         if (row >= nrows) continue;
-        float M = -INFINITY;
         const int sub = rl >> 4, r16 = rl & 15;   // 16-row slot of the row (32-row segments have two per worker)
-        for (int wi = wf; wi <= wl; ++wi)
-          if (has_tiles(wi))
-            M = fmaxf(M, p.part_ml[(((int64_t)seg + wi) * p.seg_blocks + sub) * (kRowsPerSeg * 2) + r16 * 2]);
+        float M = -INFINITY;
+        for (int wi = wi0; wi <= wl; wi += wi_step)
+          if (has_tiles(wi)) M = fmaxf(M, *ml_of(wi, sub, r16));
+        if (coop) {
+#pragma unroll
+          for (int s = 16; s > 0; s >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, s));
+        }
         float L = 0.f;
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
         if (M != -INFINITY) {
-          for (int wi = wf; wi <= wl; ++wi) {
+          for (int wi = wi0; wi <= wl; wi += wi_step) {   // the partial loads of an item are independent
             if (!has_tiles(wi)) continue;
-            const int64_t slot = ((int64_t)seg + wi) * p.seg_blocks + sub;
-            const float2 ml = *reinterpret_cast<const float2*>(p.part_ml + slot * (kRowsPerSeg * 2) + r16 * 2);
+            const float2 ml = *reinterpret_cast<const float2*>(ml_of(wi, sub, r16));
             if (ml.x == -INFINITY) continue;
             const float wgt = ex2(ml.x - M);
-            const float4 o = *reinterpret_cast<const float4*>(p.part_o + slot * (kRowsPerSeg * HD) + r16 * HD + d);
+            const float4 o = *reinterpret_cast<const float4*>(o_of(wi, sub, r16, d));
             L += wgt * ml.y;
             acc.x += wgt * o.x; acc.y += wgt * o.y; acc.z += wgt * o.z; acc.w += wgt * o.w;
           }
         }
+        if (coop) {
+#pragma unroll
+          for (int s = 16; s > 0; s >>= 1) {
+            L += __shfl_xor_sync(0xffffffffu, L, s);
+            acc.x += __shfl_xor_sync(0xffffffffu, acc.x, s);
+            acc.y += __shfl_xor_sync(0xffffffffu, acc.y, s);
+            acc.z += __shfl_xor_sync(0xffffffffu, acc.z, s);
+            acc.w += __shfl_xor_sync(0xffffffffu, acc.w, s);
+          }
+          if (lane != 0) continue;
+        }
         const float inv = L > 0.f ? vscale / L : 0.f;
         const int j = row / p.group, hq = h * p.group + row % p.group;
-        const float lse = L > 0.f ? M * kLn2 + logf(L) : -INFINITY;
         const float4 r = make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
         const int64_t oi = (int64_t)b * p.o_bs + (int64_t)(qr + j) * p.o_rs + (int64_t)hq * p.o_hs + d;
         uint2 packed;
         if (p.q_is_bf16) packed = make_uint2(pack2<true>(r.x, r.y), pack2<true>(r.z, r.w));
         else packed = make_uint2(pack2<false>(r.x, r.y), pack2<false>(r.z, r.w));
         *reinterpret_cast<uint2*>(p.out + 2 * oi) = packed;
-        if (p.lse && d == 0) p.lse[(int64_t)b * p.lse_bs + (int64_t)hq * p.lse_hs + qr + j] = lse;
+        if (p.lse && d == 0)
+          p.lse[(int64_t)b * p.lse_bs + (int64_t)hq * p.lse_hs + qr + j] = L > 0.f ? M * kLn2 + logf(L) : -INFINITY;
       }
     }
   }
@@ -1732,11 +1771,17 @@ template <int HD, bool BF16, bool KV8>
 int launch_prefill_variant(const CUtensorMap& tmK, const CUtensorMap& tmV, const AttnParams& p, int grid, int dev,
                            cudaStream_t stream);
 constexpr int kPrefillRowsPerSeg = 256, kPrefillTileKeys = 128, kPrefillMinPackedRows = 64;
-// Packed query rows per sequence from which the prefill kernel serves a call.  The split-KV kernels
-// read a sequence's K/V once per 16 rows, the prefill kernel once per 256 but with a fixed cost per
-// CTA: measured break-even at 32 rows for head_dim 128 (4096 keys) and near 56 for head_dim 64
-// (729 keys).
-inline int prefill_min_rows(int head_dim) { return head_dim == 128 ? 40 : 56; }
+// Packed query rows per sequence (per KV head) from which the prefill kernel serves a call.  Below, the split-KV
+// kernels read a sequence's keys once per 32 rows and balance any mix of lengths over all SMs; the prefill kernel
+// reads them once per 256 rows, but one CTA walks all keys of its rows and pays a fixed cost per CTA.  Measured
+// (256 / 64 / 8 sequences of U[2k, 16k] keys, 32/8 heads, per call, prefill | split-KV):
+//   16-bit pools, head_dim 128, 36 rows: 1.46 | 3.28 ms, 0.28 | 0.48 ms, 0.156 | 0.157 ms  (two passes of the
+//     32-row kernel against the key-split prefill kernel at the HBM rate); 32 rows: 1.77 | 1.67, 0.28 | 0.28,
+//     0.148 | 0.154; on contexts of a few hundred keys the split-KV side wins at 32 rows by a third  -> 33.
+//   16-bit pools, head_dim 64 (512 sequences of ~900 keys): 36 rows 0.33 | 0.27 ms                     -> 56.
+//   e4m3 pools (the prefill kernel widens tiles through shared memory and has no key split): 64 rows
+//     2.69 | 2.44 ms, 0.84 | 0.71, 0.33 | 0.14; 128 rows 2.73 | 4.92, 0.85 | 1.36, 0.33 | 0.19          -> 65.
+inline int prefill_min_rows(int head_dim, bool kv8) { return kv8 ? 65 : head_dim == 128 ? 33 : 56; }
 
 // A TMA box must fill a multiple of 128 bytes of shared memory: page_size x min(row bytes, 128).  Pools
 // that cannot offer that (page size 1 with 64-byte e4m3 rows) are served by the split-KV kernels' cp.async
@@ -1759,7 +1804,7 @@ inline bool use_prefill_kernel(const kb200_attn_args* a) {
   // sequence says which kernel has less work.
   int64_t rows = a->seqlen_q;
   if (a->cu_seqlens_q && a->batch > 0) rows = std::min<int64_t>(rows, (a->total_q + a->batch - 1) / a->batch);
-  return (int64_t)(a->n_q_heads / a->n_kv_heads) * rows >= prefill_min_rows(a->head_dim);
+  return (int64_t)(a->n_q_heads / a->n_kv_heads) * rows >= prefill_min_rows(a->head_dim, a->kv_dtype == KB200_DTYPE_E4M3);
 }
 
 // Scratch bytes this very call needs: the plan arrays, plus the split-KV partials unless the prefill

@@ -2,7 +2,7 @@
 // cores: many query rows per sequence (a prompt chunk), K/V gathered through the
 // page table.  This is the compute-bound mode of the same op the decode kernels
 // serve (paged_attention.cuh); it is chosen when a sequence brings at least
-// 40 packed query rows (56 with head_dim 64).  K/V pools are 16-bit or FP8 e4m3 (see KV8 below).
+// 33 packed query rows per KV head (56 with head_dim 64, 65 on e4m3 pools).  K/V pools are 16-bit or FP8 e4m3 (see KV8 below).
 //
 // One CTA = one (sequence, KV head, block of 256 packed query rows) = two Q tiles of
 // 128 rows; packed row r = j * group + g is query position j of head h * group + g,
@@ -56,7 +56,8 @@ struct PrefillSmem {
   static constexpr int OFF_KV = 2 * Q_TILE;
   static constexpr int OFF_STG = OFF_KV + RING * KV_TILE;
   static constexpr int OFF_BAR = OFF_STG + NSTG * STG_TILE;
-  static constexpr int N_BARS = 2 * RING + 6 + 2 * NSTG;
+  static constexpr int RINGB = RING + 1;                        // barrier pairs: the key split borrows Q tile B as one more ring slot
+  static constexpr int N_BARS = 2 * RINGB + 6 + 2 * NSTG;
   static constexpr int OFF_TMEM = OFF_BAR + 8 * N_BARS;
   static constexpr int BYTES = OFF_TMEM + 16 + 1024;            // + alignment slack
 };
@@ -218,7 +219,9 @@ __host__ __device__ constexpr uint32_t umma_idesc(bool bf16, bool b_mn_major, in
 // BF16: dtype of q and out.  KV8: K/V pools hold e4m3 codes; the tiles are widened to f16 in shared memory
 // (exact), the tensor core then runs on f16 operands (q is converted once, as in the decode kernels)
 // and the dequantisation scales are folded into the softmax scale (K) and the final normalisation (V).
-template <int HD, bool BF16, bool KV8>
+// SPLIT: no sequence of the launch brings more than 128 packed rows per KV head, so no CTA has rows in its
+// second Q tile and the key split (below) is open to every CTA; the ring then has one slot more.
+template <int HD, bool BF16, bool KV8, bool SPLIT>
 __global__ void __launch_bounds__(pf_threads(KV8), 1)
 paged_prefill_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                      const __grid_constant__ AttnParams p) {
@@ -226,6 +229,13 @@ paged_prefill_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
   constexpr bool MMA_BF16 = BF16 && !KV8;   // operand type of both products
   constexpr int NH = SM::NH;
   constexpr int RING = SM::RING;
+  static_assert(!(SPLIT && KV8), "the key split is for 16-bit pools");
+  // Under the key split Q tile B is unused and lies directly below the K/V ring: it becomes one more ring slot
+  // (every key tile feeds one pipeline instead of two, so tiles are consumed twice as fast and the copies have
+  // to run further ahead).
+  static_assert(SM::Q_TILE == SM::KV_TILE && SM::OFF_KV == SM::OFF_Q + 2 * SM::Q_TILE, "Q tile B adjoins the ring");
+  constexpr int RINGN = SPLIT ? RING + 1 : RING;
+  constexpr uint32_t RING_OFF = SPLIT ? SM::OFF_Q + SM::Q_TILE : SM::OFF_KV;
   constexpr int BN = kPrefillKeys;
   constexpr float kLog2e = 1.4426950408889634f;
   constexpr float kRescaleStep = 8.f;   // the running maximum is only raised when it grew by 2^8
@@ -244,12 +254,13 @@ paged_prefill_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
   // barrier map
   const uint32_t bar = sbase + SM::OFF_BAR;
   auto B_FULL = [&](int s) { return bar + 8u * s; };
-  auto B_EMPTY = [&](int s) { return bar + 8u * (RING + s); };
-  auto B_SREADY = [&](int x) { return bar + 8u * (2 * RING + x); };
-  auto B_PREADY = [&](int x) { return bar + 8u * (2 * RING + 2 + x); };
-  auto B_PVDONE = [&](int x) { return bar + 8u * (2 * RING + 4 + x); };
-  auto B_SFULL = [&](int s) { return bar + 8u * (2 * RING + 6 + s); };               // e4m3 staging tiles
-  auto B_SEMPTY = [&](int s) { return bar + 8u * (2 * RING + 6 + SM::NSTG + s); };
+  constexpr int RINGB = SM::RINGB;
+  auto B_EMPTY = [&](int s) { return bar + 8u * (RINGB + s); };
+  auto B_SREADY = [&](int x) { return bar + 8u * (2 * RINGB + x); };
+  auto B_PREADY = [&](int x) { return bar + 8u * (2 * RINGB + 2 + x); };
+  auto B_PVDONE = [&](int x) { return bar + 8u * (2 * RINGB + 4 + x); };
+  auto B_SFULL = [&](int s) { return bar + 8u * (2 * RINGB + 6 + s); };               // e4m3 staging tiles
+  auto B_SEMPTY = [&](int s) { return bar + 8u * (2 * RINGB + 6 + SM::NSTG + s); };
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(sgen + SM::OFF_TMEM);
 
   pdl_launch_dependents();
@@ -299,6 +310,14 @@ paged_prefill_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
     n_x[x] = k_end > tile_begin * BN ? (k_end - tile_begin * BN + BN - 1) / BN : 0;
   }
   const int n_tiles = max(n_x[0], n_x[1]);   // n_x[0] <= n_x[1] whenever tile B has rows (limits grow with the row)
+  // Key split.  A CTA whose second Q tile has no rows (at most 128 packed rows per KV head: short chunks with few
+  // heads per group, a verify step of a few dozen tokens) would run one dependent chain Q K^T -> softmax -> P V per
+  // key tile with half of its warps and tensor memory idle.  Instead the two pipelines both work on Q tile A:
+  // stream 0 takes the even key tiles, stream 1 the odd ones, each with its own S, P, O, maximum and sum, and the
+  // two partial results are combined at the end.  (16-bit pools: the f16 ring of an e4m3 pool holds three tiles,
+  // one fewer than K_{i+2} next to V_i needs.)
+  const bool split = SPLIT && n_x[0] >= 2;
+  const int n_s[2] = {split ? (n_tiles + 1) >> 1 : n_x[0], split ? n_tiles >> 1 : n_x[1]};   // key tiles per pipeline
 
   // ---- set-up.  The TMA warp starts on the K/V tiles at once, so that they are in flight while the
   // other warps bring Q in and tensor memory is allocated.
@@ -315,7 +334,7 @@ paged_prefill_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
   const int64_t pt_row = (int64_t)b * p.pt_rs;
   const int n_slots = (L + page_sz - 1) >> p_shift;   // table entries that hold pages of this sequence
   auto produce = [&](int idx) -> bool {   // warp-wide; false when the ring slot never came free
-    constexpr int NSLOT = KV8 ? SM::NSTG : RING;
+    constexpr int NSLOT = KV8 ? SM::NSTG : RINGN;
     const int s = idx % NSLOT;
     if (idx >= NSLOT && !mbar_wait_bounded(KV8 ? B_SEMPTY(s) : B_EMPTY(s), (uint32_t)((idx / NSLOT) - 1) & 1u)) {
       if (lane == 0) report(KB200_STATUS_WAIT_TIMEOUT, idx, KID_PREFILL);
@@ -338,7 +357,7 @@ paged_prefill_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
     if (lane == 0) mbar_expect_tx(full, (uint32_t)((nvb << box_shift) * HD * (KV8 ? 1 : 2)));
     __syncwarp();
     const uint32_t dst0 = KV8 ? sbase + SM::OFF_STG + (uint32_t)s * SM::STG_TILE
-                              : sbase + SM::OFF_KV + (uint32_t)s * SM::KV_TILE;
+                              : sbase + RING_OFF + (uint32_t)s * SM::KV_TILE;
     for (int j0 = 0; j0 < boxes_per_tile * NHB; j0 += 32) {   // uniform trip count: the shuffle below is warp-wide
       const int j = j0 + lane;
       const int i = j / NHB, half = j - i * NHB;
@@ -354,7 +373,7 @@ paged_prefill_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
     return true;
   };
   if (tid == 0) {
-    for (int s = 0; s < RING; ++s) {
+    for (int s = 0; s < RINGB; ++s) {
       mbar_init(B_FULL(s), KV8 ? 128 : 1);   // filled by the TMA unit, or by the 128 widening threads
       mbar_init(B_EMPTY(s), 1);
     }
@@ -448,7 +467,7 @@ paged_prefill_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
 #pragma unroll
     for (int u = 0; u < PER; ++u) {
       const int i = qt + u * NCOPY;
-      if (i < kPfCtaRows * CH) {
+      if (i < kPfCtaRows * CH && !(SPLIT && i >= kPfTileRows * CH)) {   // (Q tile B is a ring slot under the key split)
         const int rr = i / CH, c = i - rr * CH;
         const int x = rr >> 7, r = rr & 127;
         const uint32_t off = SM::OFF_Q + (uint32_t)x * SM::Q_TILE + (uint32_t)(c >> 3) * SM::SLAB + (uint32_t)r * 128 +
@@ -472,9 +491,9 @@ paged_prefill_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
     constexpr uint32_t IDESC_QK = umma_idesc(MMA_BF16, false, BN);
     constexpr uint32_t IDESC_PV = umma_idesc(MMA_BF16, true, HD);
     bool ok = true;
-    auto kv_addr = [&](int idx) { return sbase + SM::OFF_KV + (uint32_t)(idx % RING) * SM::KV_TILE; };
+    auto kv_addr = [&](int idx) { return sbase + RING_OFF + (uint32_t)(idx % RINGN) * SM::KV_TILE; };
     auto kv_wait = [&](int idx) {
-      ok = ok && mbar_wait_bounded(B_FULL(idx % RING), (uint32_t)(idx / RING) & 1u);
+      ok = ok && mbar_wait_bounded(B_FULL(idx % RINGN), (uint32_t)(idx / RINGN) & 1u);
     };
     // Descriptors differ only in their start-address field (low 14 bits, units of 16 bytes): the
     // high word and the layout bits are built once, the per-step offsets are compile-time constants.
@@ -482,10 +501,10 @@ paged_prefill_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
     constexpr uint32_t kLboK = (16u >> 4) << 16;                 // K-major operands: unused leading offset
     constexpr uint32_t kLboV = ((uint32_t)(BN * 128) >> 4) << 16;  // V (MN-major): distance between 64-column slabs
     auto mk = [](uint32_t lo) { return ((uint64_t)kDescHi << 32) | lo; };
-    auto qk = [&](int x, int i) {   // S_x = Q_x K_i^T
+    auto qk = [&](int x, int xq, int i) {   // S_x = Q_xq K_i^T
       tc_fence_after();
       if (lane == 0) {
-        const uint32_t q_lo = ((sbase + SM::OFF_Q + (uint32_t)x * SM::Q_TILE) >> 4) | kLboK;
+        const uint32_t q_lo = ((sbase + SM::OFF_Q + (uint32_t)xq * SM::Q_TILE) >> 4) | kLboK;
         const uint32_t k_lo = (kv_addr(2 * i) >> 4) | kLboK;
         const uint32_t s_tmem = tmem_base + S_COL + (uint32_t)x * BN;
 #pragma unroll
@@ -499,7 +518,7 @@ paged_prefill_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
       __syncwarp();
     };
     auto wait_p = [&](int x, int i) { ok = ok && mbar_wait_bounded(B_PREADY(x), (uint32_t)i & 1u); };
-    auto pv = [&](int x, int i, int ksteps) {   // O_x (+)= P_x V_i
+    auto pv = [&](int x, int i, int ksteps, bool acc) {   // O_x (+)= P_x V_i; acc: O_x holds earlier tiles
       if (!ok) return;
       tc_fence_after();
       if (lane == 0) {
@@ -510,46 +529,93 @@ paged_prefill_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
 #pragma unroll
           for (int k = 0; k < BN / 16; ++k)
             umma_f16_ts(o_tmem, p_tmem + (uint32_t)k * 8, mk(v_lo + (uint32_t)k * (2048 >> 4)), IDESC_PV,
-                        (i > 0 || k > 0) ? 1u : 0u);
+                        (acc || k > 0) ? 1u : 0u);
         } else {
           for (int k = 0; k < ksteps; ++k)
             umma_f16_ts(o_tmem, p_tmem + (uint32_t)k * 8, mk(v_lo + (uint32_t)k * (2048 >> 4)), IDESC_PV,
-                        (i > 0 || k > 0) ? 1u : 0u);
+                        (acc || k > 0) ? 1u : 0u);
         }
         tc_commit(B_PVDONE(x));
       }
       __syncwarp();
     };
-    if (n_tiles > 0) {
+    // V rows between the sequence end and the end of its 16-key block may hold anything (NaN bit patterns
+    // included) and would poison 0 * V: zero them (whole rows, so the swizzle does not matter)
+    auto zero_v_tail = [&](int i, int nvalid, int ksteps) {
+      const uint32_t v_off = kv_addr(2 * i + 1) - sbase;
+      const int r0 = nvalid, r1 = ksteps << 4;
+      for (int t = lane; t < (r1 - r0) * NH * 8; t += 32) {
+        const int r = r0 + t / (NH * 8), c = t % (NH * 8);
+        *reinterpret_cast<uint4*>(sgen + v_off + (uint32_t)(c >> 3) * (BN * 128) + (uint32_t)r * 128 +
+                                  (uint32_t)((c & 7) << 4)) = make_uint4(0u, 0u, 0u, 0u);
+      }
+      fence_proxy_async();
+      __syncwarp();
+    };
+    if (split) {
+      // pipeline x = i & 1 owns key tile i; per tile: P V of the tile, then Q K^T of the pipeline's next tile
+      // (the other way round when P has columns of its own), while the other pipeline's softmax runs
       kv_wait(0);
       if (ok) {
-        if (n_x[0] > 0) qk(0, 0);
-        if (n_x[1] > 0) qk(1, 0);
+        qk(0, 0, 0);
+        if (lane == 0) tc_commit(B_EMPTY(0));
+        __syncwarp();
+        kv_wait(2);
+      }
+      if (ok) {
+        qk(1, 0, 1);
+        if (lane == 0) tc_commit(B_EMPTY(2 % RINGN));
+        __syncwarp();
+      }
+      for (int i = 0; i < n_tiles && ok; ++i) {
+        const int x = i & 1, li = i >> 1;
+        kv_wait(2 * i + 1);
+        if (!ok) break;
+        int nvalid = L - (tile_begin + i) * BN;
+        if (nvalid > BN) nvalid = BN;
+        const int ksteps = (nvalid + 15) >> 4;
+        if (nvalid & 15) zero_v_tail(i, nvalid, ksteps);
+        const bool more = i + 2 < n_tiles;
+        wait_p(x, li);
+        if (!ok) break;
+        if constexpr (PSEP) {
+          if (more) {
+            kv_wait(2 * (i + 2));
+            if (!ok) break;
+            qk(x, 0, i + 2);
+          }
+          pv(x, i, ksteps, li > 0);
+        } else {
+          pv(x, i, ksteps, li > 0);
+          if (more) {
+            kv_wait(2 * (i + 2));
+            if (!ok) break;
+            qk(x, 0, i + 2);
+          }
+        }
+        if (lane == 0) {
+          tc_commit(B_EMPTY((2 * i + 1) % RINGN));
+          if (more) tc_commit(B_EMPTY((2 * i + 4) % RINGN));
+        }
+        __syncwarp();
+      }
+    } else if (n_tiles > 0) {
+      kv_wait(0);
+      if (ok) {
+        if (n_x[0] > 0) qk(0, 0, 0);
+        if (n_x[1] > 0) qk(1, 1, 0);
         if (lane == 0) tc_commit(B_EMPTY(0));
         __syncwarp();
       }
     }
-    for (int i = 0; i < n_tiles && ok; ++i) {
+    for (int i = 0; i < n_tiles && ok && !split; ++i) {
       kv_wait(2 * i + 1);
       if (!ok) break;
       const int key0 = (tile_begin + i) * BN;
       int nvalid = L - key0;
       if (nvalid > BN) nvalid = BN;
       const int ksteps = (nvalid + 15) >> 4;
-      if (nvalid & 15) {
-        // rows of V between the sequence end and the end of its 16-key block may hold anything
-        // (NaN bit patterns included) and would poison 0 * V: zero them (whole rows, so the
-        // swizzle does not matter)
-        const uint32_t v_off = kv_addr(2 * i + 1) - sbase;
-        const int r0 = nvalid, r1 = ksteps << 4;
-        for (int t = lane; t < (r1 - r0) * NH * 8; t += 32) {
-          const int r = r0 + t / (NH * 8), c = t % (NH * 8);
-          *reinterpret_cast<uint4*>(sgen + v_off + (uint32_t)(c >> 3) * (BN * 128) + (uint32_t)r * 128 +
-                                    (uint32_t)((c & 7) << 4)) = make_uint4(0u, 0u, 0u, 0u);
-        }
-        fence_proxy_async();
-        __syncwarp();
-      }
+      if (nvalid & 15) zero_v_tail(i, nvalid, ksteps);
       const bool more = i + 1 < n_tiles;
       if constexpr (PSEP) {
         // P_x has columns of its own: once the softmax has let go of S_x the next Q K^T goes first
@@ -559,28 +625,28 @@ paged_prefill_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
           if (i < n_x[x]) {
             wait_p(x, i);
             if (!ok) break;
-            if (i + 1 < n_x[x]) qk(x, i + 1);
-            pv(x, i, ksteps);
+            if (i + 1 < n_x[x]) qk(x, x, i + 1);
+            pv(x, i, ksteps, i > 0);
           }
         }
         if (!ok) break;
         if (lane == 0) {
-          tc_commit(B_EMPTY((2 * i + 1) % RING));             // V_i has been read by both tiles
-          if (more) tc_commit(B_EMPTY((2 * i + 2) % RING));   // K_{i+1} likewise
+          tc_commit(B_EMPTY((2 * i + 1) % RINGN));             // V_i has been read by both tiles
+          if (more) tc_commit(B_EMPTY((2 * i + 2) % RINGN));   // K_{i+1} likewise
         }
         __syncwarp();
       } else {
-        if (i < n_x[0]) { wait_p(0, i); pv(0, i, ksteps); }
+        if (i < n_x[0]) { wait_p(0, i); pv(0, i, ksteps, i > 0); }
         if (more) kv_wait(2 * (i + 1));
         if (!ok) break;
-        if (i + 1 < n_x[0]) qk(0, i + 1);
-        if (i < n_x[1]) { wait_p(1, i); pv(1, i, ksteps); }
+        if (i + 1 < n_x[0]) qk(0, 0, i + 1);
+        if (i < n_x[1]) { wait_p(1, i); pv(1, i, ksteps, i > 0); }
         if (!ok) break;
-        if (lane == 0) tc_commit(B_EMPTY((2 * i + 1) % RING));   // V_i has been read by both tiles
+        if (lane == 0) tc_commit(B_EMPTY((2 * i + 1) % RINGN));   // V_i has been read by both tiles
         __syncwarp();
         if (more) {
-          if (i + 1 < n_x[1]) qk(1, i + 1);
-          if (lane == 0) tc_commit(B_EMPTY((2 * i + 2) % RING));  // K_{i+1} likewise
+          if (i + 1 < n_x[1]) qk(1, 1, i + 1);
+          if (lane == 0) tc_commit(B_EMPTY((2 * i + 2) % RINGN));  // K_{i+1} likewise
           __syncwarp();
         }
       }
@@ -588,16 +654,19 @@ paged_prefill_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
     if (!ok && lane == 0) report(KB200_STATUS_WAIT_TIMEOUT, seg, KID_PREFILL);
   } else {
     // =========================== softmax: one row per thread, one warpgroup per Q tile ===========================
-    const int x = warp >> 2;                 // Q tile
+    const int x = warp >> 2;                 // Q tile (pipeline of the key split)
     const int r = tid & 127;                 // row inside the tile == tensor-memory lane
-    const int row = row_first + x * kPfTileRows + r;
+    const int row = row_first + (split ? 0 : x * kPfTileRows) + r;
     const bool valid = row < nrows;
     const int j = valid ? row / p.group : 0;
     const int g = valid ? row - j * p.group : 0;
     int jv = j;   // last row of this sequence whose key this row sees
     if (valid && p.q_vis) jv = max(j, min(sq - 1, p.q_vis[(int64_t)b * p.q_vis_bs + qrow0 + j]));
-    const int lim = valid ? (upper ? L - sq + jv : L - 1) : -1;         // last visible key
-    const int lo = p.window_left >= 0 ? lim - p.window_left : 0;         // first visible key
+    // Rows past the segment's end are never written, and their tile must not hold the others back: no mask for
+    // them (their Q rows are zero: every score is 0), and a warp without any row skips the arithmetic altogether.
+    const int lim = valid ? (upper ? L - sq + jv : L - 1) : 0x3fffffff;             // last visible key
+    const int lo = (valid && p.window_left >= 0) ? lim - p.window_left : 0;         // first visible key
+    const bool warp_has_rows = row - lane < nrows;                                   // (the warp's first row)
     const float ksc = p.ks_vec ? p.ks_vec[h] : p.ks;
     const float vscale = p.vs_vec ? p.vs_vec[h] : p.vs;
     const float sl2 = p.softmax_scale * ksc * kLog2e;
@@ -605,14 +674,24 @@ paged_prefill_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
     const uint32_t s_tmem = tmem_base + lane_base + S_COL + (uint32_t)x * BN;
     const uint32_t o_tmem = tmem_base + lane_base + O_COL + (uint32_t)x * 128;
     const uint32_t p_st = tmem_base + lane_base + P_OFF + (uint32_t)x * 128;   // where this row's weights go
-    const int n_mine = n_x[x];
+    const int n_mine = n_s[x];
     float m = -INFINITY, l = 0.f;
     bool ok = true;
     for (int it = 0; it < n_mine; ++it) {
       ok = mbar_wait_bounded(B_SREADY(x), (uint32_t)it & 1u);
       if (!ok) break;
       tc_fence_after();
-      const int key0 = (tile_begin + it) * BN;
+      if (!warp_has_rows) {   // whatever S and P hold on these lanes only reaches rows of O that nobody reads
+        // (still in step with the others on every barrier: a wait by parity must not fall two phases behind)
+        if (it > 0) {
+          ok = mbar_wait_bounded(B_PVDONE(x), (uint32_t)(it - 1) & 1u);
+          if (!ok) break;
+        }
+        tc_fence_before();
+        mbar_arrive(B_PREADY(x));
+        continue;
+      }
+      const int key0 = (tile_begin + (split ? 2 * it + x : it)) * BN;
       const bool masked = key0 + BN - 1 > lim || key0 < lo;
       const int c_hi = lim - key0, c_lo = lo - key0;   // visible columns of this tile: c_lo <= column <= c_hi
       // pass 1: the row maximum; eight independent chains of three-input maxima (one chain of 128
@@ -753,7 +832,65 @@ paged_prefill_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
       ok = mbar_wait_bounded(B_PVDONE(x), (uint32_t)(n_mine - 1) & 1u);
       if (ok) tc_fence_after();
     }
-    if (!ok) {
+    if (split) {
+      // Combine the two pipelines.  Pipeline 1 parks its row (maximum in log2 units, sum, unnormalised O) in the
+      // K/V ring, which is at rest once the last P V of both pipelines has completed; element (row, 4 columns c)
+      // sits at (c * 128 + row) * 16 so that a warp's rows are side by side.
+      uint8_t* xbuf = sgen + SM::OFF_KV;
+      static_assert(HD * 512 + 128 * 8 <= RING * SM::KV_TILE, "the exchange buffer fits the K/V ring");
+      const float m_own = (m == -INFINITY) ? -INFINITY : m * sl2;
+      if (x == 1) {
+        if (ok) ok = mbar_wait_bounded(B_PVDONE(0), (uint32_t)(n_s[0] - 1) & 1u);
+        if (ok) {
+          tc_fence_after();
+#pragma unroll
+          for (int c = 0; c < HD / 32; ++c) {
+            float v[32];
+            tmem_ld32(o_tmem + c * 32, v);
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+              *reinterpret_cast<float4*>(xbuf + ((c * 8 + q) * 128 + r) * 16) =
+                  make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+          }
+          *reinterpret_cast<float2*>(xbuf + HD * 512 + r * 8) = make_float2(m_own, l);
+        }
+      }
+      if (!ok && lane == 0) report(KB200_STATUS_WAIT_TIMEOUT, seg, KID_PREFILL);
+      asm volatile("bar.sync 2, 256;" ::: "memory");   // both softmax warpgroups, whatever happened above
+      if (x == 0 && ok) {
+        const float2 other = *reinterpret_cast<const float2*>(xbuf + HD * 512 + r * 8);
+        const float M = fmaxf(m_own, other.x);
+        const float w0 = (m_own == -INFINITY) ? 0.f : ex2(m_own - M);
+        const float w1 = (other.x == -INFINITY) ? 0.f : ex2(other.x - M);
+        const float lt = l * w0 + other.y * w1;
+        const float inv = lt > 0.f ? vscale / lt : 0.f;
+        const float f0 = w0 * inv, f1 = w1 * inv;
+        const int hq = h * p.group + g;
+        char* dst = p.out + 2 * ((int64_t)b * p.o_bs + (int64_t)(qrow0 + j) * p.o_rs + (int64_t)hq * p.o_hs);
+#pragma unroll
+        for (int c = 0; c < HD / 32; ++c) {
+          float v[32];
+          tmem_ld32(o_tmem + c * 32, v);
+          if (valid) {
+#pragma unroll
+            for (int q8 = 0; q8 < 4; ++q8) {
+              const float4 a = *reinterpret_cast<const float4*>(xbuf + ((c * 8 + 2 * q8) * 128 + r) * 16);
+              const float4 bq = *reinterpret_cast<const float4*>(xbuf + ((c * 8 + 2 * q8 + 1) * 128 + r) * 16);
+              uint4 w;
+              w.x = pack2<BF16>(v[8 * q8 + 0] * f0 + a.x * f1, v[8 * q8 + 1] * f0 + a.y * f1);
+              w.y = pack2<BF16>(v[8 * q8 + 2] * f0 + a.z * f1, v[8 * q8 + 3] * f0 + a.w * f1);
+              w.z = pack2<BF16>(v[8 * q8 + 4] * f0 + bq.x * f1, v[8 * q8 + 5] * f0 + bq.y * f1);
+              w.w = pack2<BF16>(v[8 * q8 + 6] * f0 + bq.z * f1, v[8 * q8 + 7] * f0 + bq.w * f1);
+              *reinterpret_cast<uint4*>(dst + 64 * c + 16 * q8) = w;
+            }
+          }
+        }
+        if (valid && p.lse) {
+          constexpr float kLn2 = 0.6931471805599453f;
+          p.lse[(int64_t)b * p.lse_bs + (int64_t)hq * p.lse_hs + qrow0 + j] = lt > 0.f ? M * kLn2 + logf(lt) : -INFINITY;
+        }
+      }
+    } else if (!ok) {
       if (lane == 0) report(KB200_STATUS_WAIT_TIMEOUT, seg, KID_PREFILL);
     } else if (row_first + x * kPfTileRows < nrows) {   // uniform per warpgroup: tensor-memory loads are warp-wide
       const float inv = l > 0.f ? vscale / l : 0.f;
@@ -805,15 +942,27 @@ inline bool prefill_enabled() {
   return on;
 }
 
-template <int HD, bool BF16, bool KV8>
-inline int launch_prefill_variant(const CUtensorMap& tmK, const CUtensorMap& tmV, const AttnParams& p, int grid,
-                                  int dev, cudaStream_t stream) {
+template <int HD, bool BF16, bool KV8, bool SPLIT>
+inline int launch_prefill_split(const CUtensorMap& tmK, const CUtensorMap& tmV, const AttnParams& p, int grid,
+                                int dev, cudaStream_t stream) {
   using SM = PrefillSmem<HD, KV8>;
-  auto kern = paged_prefill_kernel<HD, BF16, KV8>;
+  auto kern = paged_prefill_kernel<HD, BF16, KV8, SPLIT>;
   static SmemAttrOnce once;
   if (int rc = once.ensure(kern, SM::BYTES, dev)) return rc;
   KB200_CUDA_OK(launch_kernel(kern, dim3(grid), dim3(pf_threads(KV8)), SM::BYTES, stream, tmK, tmV, p));
   return KB200_OK;
+}
+
+template <int HD, bool BF16, bool KV8>
+inline int launch_prefill_variant(const CUtensorMap& tmK, const CUtensorMap& tmV, const AttnParams& p, int grid,
+                                  int dev, cudaStream_t stream) {
+  // seqlen_q bounds the rows of every sequence (padded and packed layouts alike): at most 128 packed rows per
+  // KV head means no CTA of the launch uses its second Q tile, and the key-split variant serves it
+  if constexpr (!KV8) {
+    if ((long long)p.group * p.seqlen_q <= kPfTileRows)
+      return launch_prefill_split<HD, BF16, KV8, true>(tmK, tmV, p, grid, dev, stream);
+  }
+  return launch_prefill_split<HD, BF16, KV8, false>(tmK, tmV, p, grid, dev, stream);
 }
 
 }  // namespace kb200

@@ -42,12 +42,24 @@ def test_prefill_shapes_and_gqa(seqlen_q, group, heads_kv, head_dim):
 
 
 # packed rows on either side of the switch between the split-KV kernels and the prefill kernel
-# (40 rows with head_dim 128, 56 with head_dim 64)
-@pytest.mark.parametrize("seqlen_q,group,heads_kv,head_dim", [(9, 4, 2, 128), (10, 4, 2, 128), (12, 4, 2, 128), (15, 4, 2, 128),
-                                                               (39, 1, 3, 128), (40, 1, 3, 128), (13, 4, 2, 64), (14, 4, 2, 64),
+# (33 rows with head_dim 128, 56 with head_dim 64, 65 on FP8 pools)
+@pytest.mark.parametrize("seqlen_q,group,heads_kv,head_dim", [(8, 4, 2, 128), (9, 4, 2, 128), (10, 4, 2, 128), (12, 4, 2, 128),
+                                                               (32, 1, 3, 128), (33, 1, 3, 128), (39, 1, 3, 128), (40, 1, 3, 128),
+                                                               (13, 4, 2, 64), (14, 4, 2, 64),
                                                                (55, 1, 4, 64), (56, 1, 4, 64), (63, 1, 4, 64)])
 def test_rows_around_the_kernel_switch(seqlen_q, group, heads_kv, head_dim):
     _shapes_case(seqlen_q, group, heads_kv, head_dim)
+
+
+@pytest.mark.parametrize("seqlen_q,group,heads_kv,head_dim", [(16, 4, 2, 128), (64, 1, 2, 128), (65, 1, 2, 128), (17, 4, 2, 64),
+                                                               (33, 2, 1, 128)])
+def test_rows_around_the_kernel_switch_fp8_pools(seqlen_q, group, heads_kv, head_dim):
+    lengths = [seqlen_q, seqlen_q + 1, seqlen_q + 15, seqlen_q + 113, 3 * seqlen_q + 500, max(1, seqlen_q - 5), 7]
+    p = make_paged_problem(seed=70 + seqlen_q, batch=len(lengths), len_lo=0, len_hi=0, n_q_heads=group * heads_kv,
+                           n_kv_heads=heads_kv, head_dim=head_dim, page_size=16, seqlen_q=seqlen_q,
+                           dtype=torch.bfloat16, lengths=lengths)
+    out, want = run_case(p, torch.bfloat16, kv="fp8", scales=(0.02, 0.03))
+    assert_close(out, want, f"fp8 Sq={seqlen_q} G={group} Hkv={heads_kv} D={head_dim}")
 
 
 def _shapes_case(seqlen_q, group, heads_kv, head_dim):
@@ -131,6 +143,71 @@ def test_prefill_ignores_garbage_past_the_sequence_end():
                                     seqused_k=p["seqused_k"].to(DEV), causal=True)
     want = O.paged_attention(p["q"].to(torch.bfloat16).float(), p["k_pool"], p["v_pool"], p["page_table"], p["seqused_k"])
     assert_close(out, want, "garbage past the end")
+
+
+# ---- key split: a CTA whose second Q tile has no rows (at most 128 packed rows per KV head) runs its two
+# pipelines on the even and the odd key tiles of the same rows and combines them at the end
+
+@pytest.mark.parametrize("seqlen_q,group,heads_kv,head_dim", [(40, 1, 2, 128), (128, 1, 2, 128), (16, 4, 2, 128), (10, 8, 1, 128),
+                                                               (56, 1, 3, 64), (32, 4, 1, 64), (100, 1, 2, 64), (129, 1, 2, 128)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_key_split_of_a_single_q_tile(seqlen_q, group, heads_kv, head_dim, dtype):
+    # 2 to 40 key tiles, odd and even counts, a sequence that is all chunk, one just past a tile boundary
+    lengths = [seqlen_q, seqlen_q + 129, 256, 257, 385, 1000, 2049, 5000, max(seqlen_q, 130)]
+    p = make_paged_problem(seed=61 + seqlen_q, batch=len(lengths), len_lo=0, len_hi=0, n_q_heads=group * heads_kv,
+                           n_kv_heads=heads_kv, head_dim=head_dim, page_size=16, seqlen_q=seqlen_q, dtype=dtype,
+                           lengths=lengths)
+    out, want, lse, want_lse = run_case(p, dtype, return_lse=True)
+    assert_close(out, want, f"key split Sq={seqlen_q} G={group} D={head_dim} {dtype}")
+    assert torch.allclose(lse.cpu(), want_lse, atol=2e-3, rtol=1e-3)
+
+
+@pytest.mark.parametrize("causal,window", [(False, None), (True, 63), (True, 200), (True, 1000), (True, 0)])
+@pytest.mark.parametrize("head_dim", [128, 64])
+def test_key_split_non_causal_and_sliding_window(causal, window, head_dim):
+    lengths = [130, 400, 1500, 3000]
+    p = make_paged_problem(seed=62, batch=len(lengths), len_lo=0, len_hi=0, n_q_heads=16, n_kv_heads=4, head_dim=head_dim,
+                           page_size=16, seqlen_q=24, dtype=torch.bfloat16, lengths=lengths)
+    out, want = run_case(p, torch.bfloat16, causal=causal, window=window)
+    assert_close(out, want, f"key split causal={causal} window={window} D={head_dim}")
+
+
+def test_key_split_seqused_q_and_garbage_past_the_sequence_end():
+    lengths = [500, 333, 1031, 300]
+    p = make_paged_problem(seed=63, batch=len(lengths), len_lo=0, len_hi=0, n_q_heads=8, n_kv_heads=8, head_dim=64,
+                           page_size=16, seqlen_q=64, dtype=torch.bfloat16, lengths=lengths)
+    k = p["k_pool"].to(torch.bfloat16).to(DEV)
+    v = p["v_pool"].to(torch.bfloat16).to(DEV)
+    for b, L in enumerate(lengths):   # NaN patterns behind the last key of every sequence
+        page, off = int(p["page_table"][b, (L - 1) // 16]), L % 16
+        if off:
+            k[page, :, off:, :] = float("nan")
+            v[page, :, off:, :] = float("nan")
+    sq = torch.tensor([64, 57, 1, 60], dtype=torch.int32)
+    out, _ = kernels.flash_attn_fwd(p["q"].to(torch.bfloat16).to(DEV), k.permute(0, 2, 1, 3), v.permute(0, 2, 1, 3),
+                                    page_table=p["page_table"].to(DEV), seqused_k=p["seqused_k"].to(DEV),
+                                    seqused_q=sq.to(DEV), causal=True)
+    want = O.paged_attention(p["q"].to(torch.bfloat16).float(), p["k_pool"], p["v_pool"], p["page_table"],
+                             p["seqused_k"], seqused_q=sq)
+    for b, n in enumerate(sq.tolist()):
+        assert_close(out[b, :n], want[b, :n], f"key split, seqused_q row {b}")
+
+
+def test_key_split_block_mask_on_a_short_chunk():
+    # 100 query rows (one Q tile) on a cached prefix, an image block inside the chunk
+    Sq, L = 100, 100 + 700
+    ids = _image_prompt_ids(1, Sq, [[(10, 60, 0)]])
+    p = make_paged_problem(seed=64, batch=1, len_lo=0, len_hi=0, n_q_heads=4, n_kv_heads=4, head_dim=128, page_size=16,
+                           seqlen_q=Sq, dtype=torch.bfloat16, lengths=[L])
+    rt = kernels.get_runtime()
+    out, _ = rt.attention.flash_attn_fwd(
+        p["q"].to(torch.bfloat16).to(DEV), p["k_pool"].to(torch.bfloat16).to(DEV).permute(0, 2, 1, 3),
+        p["v_pool"].to(torch.bfloat16).to(DEV).permute(0, 2, 1, 3), page_table=p["page_table"].to(DEV),
+        seqused_k=p["seqused_k"].to(DEV), paged_kv_non_tma=True, causal=False, pack_gqa=False,
+        mask_mod=rt.attention.block_bidirectional_mask, aux_tensors=[ids.to(DEV)])
+    want = O.paged_attention(p["q"].to(torch.bfloat16).float(), p["k_pool"], p["v_pool"], p["page_table"], p["seqused_k"],
+                             block_ids=ids)
+    assert_close(out, want, "key split with a block mask")
 
 
 def _image_prompt_ids(B, Sq, layouts):
