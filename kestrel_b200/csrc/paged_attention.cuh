@@ -946,30 +946,32 @@ paged_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
           if (valid1) p.lse[(int64_t)cc.b * p.lse_bs + (int64_t)hq1 * p.lse_hs + qr + j1] = lse1;
         }
       } else {
+        // (rows past the segment's end are neither written here nor read by the merge: with one query token
+        // and four heads per group that is three quarters of the partial)
         const int64_t slot = (int64_t)seg_id + w;
         float* po = p.part_o + slot * (kRowsPerSeg * HD);
         float* pml = p.part_ml + slot * (kRowsPerSeg * 2);
         if (c4 == 0) {
-          pml[g8 * 2 + 0] = (m0 == -INFINITY) ? -INFINITY : m0 * sl2;
-          pml[g8 * 2 + 1] = l0;
-          pml[(g8 + 8) * 2 + 0] = (m1 == -INFINITY) ? -INFINITY : m1 * sl2;
-          pml[(g8 + 8) * 2 + 1] = l1;
+          if (valid0) *reinterpret_cast<float2*>(pml + g8 * 2) = make_float2((m0 == -INFINITY) ? -INFINITY : m0 * sl2, l0);
+          if (valid1) *reinterpret_cast<float2*>(pml + (g8 + 8) * 2) = make_float2((m1 == -INFINITY) ? -INFINITY : m1 * sl2, l1);
         }
         if constexpr (KVB == 2) {
 #pragma unroll
           for (int i = 0; i < NOT; ++i) {
             const int d = 8 * i + 2 * c4;
-            *reinterpret_cast<float2*>(po + g8 * HD + d) = make_float2(o[i][0], o[i][1]);
-            *reinterpret_cast<float2*>(po + (g8 + 8) * HD + d) = make_float2(o[i][2], o[i][3]);
+            if (valid0) *reinterpret_cast<float2*>(po + g8 * HD + d) = make_float2(o[i][0], o[i][1]);
+            if (valid1) *reinterpret_cast<float2*>(po + (g8 + 8) * HD + d) = make_float2(o[i][2], o[i][3]);
           }
         } else {
 #pragma unroll
           for (int ch = 0; ch < HD / 16; ++ch) {
             const int d = 16 * ch + 4 * c4;
-            *reinterpret_cast<float4*>(po + g8 * HD + d) =
-                make_float4(o[2 * ch][0], o[2 * ch + 1][0], o[2 * ch][1], o[2 * ch + 1][1]);
-            *reinterpret_cast<float4*>(po + (g8 + 8) * HD + d) =
-                make_float4(o[2 * ch][2], o[2 * ch + 1][2], o[2 * ch][3], o[2 * ch + 1][3]);
+            if (valid0)
+              *reinterpret_cast<float4*>(po + g8 * HD + d) =
+                  make_float4(o[2 * ch][0], o[2 * ch + 1][0], o[2 * ch][1], o[2 * ch + 1][1]);
+            if (valid1)
+              *reinterpret_cast<float4*>(po + (g8 + 8) * HD + d) =
+                  make_float4(o[2 * ch][2], o[2 * ch + 1][2], o[2 * ch][3], o[2 * ch + 1][3]);
           }
         }
       }
@@ -1368,23 +1370,28 @@ paged_attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
         float* po = p.part_o + slot * (kRowsPerSeg * HD);
         float* pml = p.part_ml + slot * (kRowsPerSeg * 2);
         const int rl0 = 2 * c4, rl1 = rl0 + 1;  // row inside the segment
+        // (rows past the segment's end are neither written here nor read by the merge)
+        const int nrows_seg = p.group * cc.sq - mb * kDecodeRows;
+        const bool wv0 = rl0 < nrows_seg, wv1 = rl1 < nrows_seg;
         if (g8 == 0) {
-          pml[rl0 * 2 + 0] = (m0 == -INFINITY) ? -INFINITY : m0 * sl2;
-          pml[rl0 * 2 + 1] = l0;
-          pml[rl1 * 2 + 0] = (m1 == -INFINITY) ? -INFINITY : m1 * sl2;
-          pml[rl1 * 2 + 1] = l1;
+          if (wv0) *reinterpret_cast<float2*>(pml + rl0 * 2) = make_float2((m0 == -INFINITY) ? -INFINITY : m0 * sl2, l0);
+          if (wv1) *reinterpret_cast<float2*>(pml + rl1 * 2) = make_float2((m1 == -INFINITY) ? -INFINITY : m1 * sl2, l1);
         }
 #pragma unroll
         for (int i = 0; i < NDT; ++i) {
           const int d = KVB == 2 ? 16 * i + g8 : 16 * i + 2 * g8;
           if constexpr (KVB == 2) {
-            po[rl0 * HD + d] = o[i][0];
-            po[rl0 * HD + d + dstep] = o[i][2];
-            po[rl1 * HD + d] = o[i][1];
-            po[rl1 * HD + d + dstep] = o[i][3];
+            if (wv0) {
+              po[rl0 * HD + d] = o[i][0];
+              po[rl0 * HD + d + dstep] = o[i][2];
+            }
+            if (wv1) {
+              po[rl1 * HD + d] = o[i][1];
+              po[rl1 * HD + d + dstep] = o[i][3];
+            }
           } else {
-            *reinterpret_cast<float2*>(po + rl0 * HD + d) = make_float2(o[i][0], o[i][2]);
-            *reinterpret_cast<float2*>(po + rl1 * HD + d) = make_float2(o[i][1], o[i][3]);
+            if (wv0) *reinterpret_cast<float2*>(po + rl0 * HD + d) = make_float2(o[i][0], o[i][2]);
+            if (wv1) *reinterpret_cast<float2*>(po + rl1 * HD + d) = make_float2(o[i][1], o[i][3]);
           }
         }
       }

@@ -436,27 +436,28 @@ paged_attn_rows32_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
           const int64_t slot = ((int64_t)seg_id + w) * 2 + blk;
           float* po = p.part_o + slot * (kRowsPerSeg * HD);
           float* pml = p.part_ml + slot * (kRowsPerSeg * 2);
+          const bool wv0 = valid[blk][0], wv1 = valid[blk][1];   // rows past the end: not written, not read by the merge
           if (c4 == 0) {
-            pml[g8 * 2 + 0] = (m0 == -INFINITY) ? -INFINITY : m0 * sl2;
-            pml[g8 * 2 + 1] = l0;
-            pml[(g8 + 8) * 2 + 0] = (m1 == -INFINITY) ? -INFINITY : m1 * sl2;
-            pml[(g8 + 8) * 2 + 1] = l1;
+            if (wv0) *reinterpret_cast<float2*>(pml + g8 * 2) = make_float2((m0 == -INFINITY) ? -INFINITY : m0 * sl2, l0);
+            if (wv1) *reinterpret_cast<float2*>(pml + (g8 + 8) * 2) = make_float2((m1 == -INFINITY) ? -INFINITY : m1 * sl2, l1);
           }
           if constexpr (KVB == 2) {
 #pragma unroll
             for (int i = 0; i < NOT; ++i) {
               const int d = 8 * i + 2 * c4;
-              *reinterpret_cast<float2*>(po + g8 * HD + d) = make_float2(o[blk][i][0], o[blk][i][1]);
-              *reinterpret_cast<float2*>(po + (g8 + 8) * HD + d) = make_float2(o[blk][i][2], o[blk][i][3]);
+              if (wv0) *reinterpret_cast<float2*>(po + g8 * HD + d) = make_float2(o[blk][i][0], o[blk][i][1]);
+              if (wv1) *reinterpret_cast<float2*>(po + (g8 + 8) * HD + d) = make_float2(o[blk][i][2], o[blk][i][3]);
             }
           } else {
 #pragma unroll
             for (int ch = 0; ch < HD / 16; ++ch) {
               const int d = 16 * ch + 4 * c4;
-              *reinterpret_cast<float4*>(po + g8 * HD + d) =
-                  make_float4(o[blk][2 * ch][0], o[blk][2 * ch + 1][0], o[blk][2 * ch][1], o[blk][2 * ch + 1][1]);
-              *reinterpret_cast<float4*>(po + (g8 + 8) * HD + d) =
-                  make_float4(o[blk][2 * ch][2], o[blk][2 * ch + 1][2], o[blk][2 * ch][3], o[blk][2 * ch + 1][3]);
+              if (wv0)
+                *reinterpret_cast<float4*>(po + g8 * HD + d) =
+                    make_float4(o[blk][2 * ch][0], o[blk][2 * ch + 1][0], o[blk][2 * ch][1], o[blk][2 * ch + 1][1]);
+              if (wv1)
+                *reinterpret_cast<float4*>(po + (g8 + 8) * HD + d) =
+                    make_float4(o[blk][2 * ch][2], o[blk][2 * ch + 1][2], o[blk][2 * ch][3], o[blk][2 * ch + 1][3]);
             }
           }
         }
