@@ -1,6 +1,6 @@
 """Benchmark of the paged-KV hot path: append + paged decode attention over a KV stack.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload cfg2|cfg3|cfg4|cfg5|cfg5_sq8] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload cfg2|cfg3|cfg4|cfg5|cfg5_sq8|cfg5_sq16] [--impl reference]
 
 One *step* is one decode step of the whole KV stack of the workload: decode metadata and slot
 mapping once, then per layer the append of the new tokens' K/V rows (quantised to FP8 where the
@@ -97,6 +97,10 @@ WORKLOADS = {
 WORKLOADS["cfg5_sq8"] = dict(WORKLOADS["cfg5"], sq=8,
                              desc=WORKLOADS["cfg5"]["desc"].replace("4-token verify + 4-token append",
                                                                     "8-token verify + 8-token append (32 packed rows per KV head)"))
+WORKLOADS["cfg5_sq16"] = dict(WORKLOADS["cfg5"], sq=16,
+                              desc=WORKLOADS["cfg5"]["desc"].replace("4-token verify + 4-token append",
+                                                                     "16-token verify + 16-token append (64 packed rows per KV head: "
+                                                                     "the tensor-memory kernel with its key split)"))
 HQ, HKV, PAGE = 32, 8, 16
 
 PREFILL_WORKLOADS = {
@@ -119,6 +123,8 @@ FALLBACK_BF16_TFLOPS = 1590.0
 def split_kv_kernel_name(cfg: dict) -> str:
     """The split-KV kernel the library picks for a workload (rows = GQA group x query positions per KV head)."""
     rows = (HQ // HKV) * cfg["sq"]
+    if rows >= (65 if cfg["kv"] == "fp8" else 33 if cfg["head_dim"] == 128 else 56):
+        return "paged_prefill_kernel"
     if rows > 16:
         return "paged_attn_rows32_kernel"
     if rows <= 8 and (cfg["kv"] == "fp8" or cfg["head_dim"] == 64):
@@ -1242,7 +1248,7 @@ def measure_decode(name: str, args, device, rank: int, world: int, dist, *, step
                    "working set near L2 size; see tokens/s rather than GB/s"},
         "gpu_launches": launches, "clocks": clocks,
         "roofline": {"bound": "hbm",
-                     "kernel": split_kv_kernel_name(cfg) + " (+ its merge launch" + (", the prefix pass on paged_prefill_kernel" if shared_pages else "") + ")",
+                     "kernel": split_kv_kernel_name(cfg) + (" (no merge launch" if split_kv_kernel_name(cfg) == "paged_prefill_kernel" else " (+ its merge launch") + (", the prefix pass on paged_prefill_kernel" if shared_pages else "") + ")",
                      "achieved": achieved, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak,
                      "traffic": None if traffic["ratio"] is None else traffic["ratio"] * attn_unique,
                      "traffic_source": f"{traffic['profile']}: ncu dram__bytes_read+write of a reduced launch of the same "
@@ -1378,7 +1384,7 @@ def main() -> None:
     # the other configurations, same process, same box: sub-records under "workloads"
     extra = {}
     if not args.only:
-        for name in ("cfg5", "cfg5_sq8", "cfg2", "cfg4"):
+        for name in ("cfg5", "cfg5_sq8", "cfg5_sq16", "cfg2", "cfg4"):
             if name == args.workload:
                 continue
             one_layer = WORKLOADS[name]["layers"] == 1
