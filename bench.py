@@ -55,28 +55,32 @@ FALLBACK_HBM_GBS = 6650.0
 # DRAM read+write bytes of one attention launch divided by its algorithmic bytes come from the ncu captures
 # summarised under profiles/ (each summary states the ratio and the sha256 of the kernel source it was taken
 # with).  Traffic grows with the tokens attended, so a full launch is that ratio times its algorithmic bytes.
-TRAFFIC_PROFILES = {"fp8": "profiles/paged_attn_decode_kernel_fp8_cfg3_reduced.md",
-                    "bf16": "profiles/paged_attn_kernel_bf16_cfg2.md"}
-KERNEL_SOURCE = "kestrel_b200/csrc/paged_attention.cuh"
+# ncu summary that holds the DRAM-traffic ratio of each attention kernel (a reduced launch of the same kernel)
+TRAFFIC_PROFILES = {
+    ("paged_attn_decode_kernel", "fp8"): "profiles/paged_attn_decode_kernel_fp8_cfg3_reduced.md",
+    ("paged_attn_decode_kernel", "bf16"): "profiles/cfg4_shared_prefix_step.md",
+    ("paged_attn_kernel", "bf16"): "profiles/paged_attn_kernel_bf16_cfg2.md",
+    ("paged_attn_rows32_kernel", "bf16"): "profiles/paged_attn_rows32_kernel_bf16_cfg5_sq8_reduced.md",
+    ("paged_prefill_kernel", "bf16"): "profiles/paged_prefill_kernel_bf16_key_split_cfg5_sq16_reduced.md",
+}
 
 
-def dram_traffic_ratio(kv: str) -> dict:
+def dram_traffic_ratio(kernel: str, kv: str) -> dict:
     """{"ratio", "profile", "stale"}: the ratio a profile summary records, and whether the kernel source
-    changed since (the summary names the sha256 of the source it was captured with)."""
+    changed since (the summary names the source file and the sha256 it was captured with)."""
     import hashlib
     import re
-    path = ROOT / TRAFFIC_PROFILES[kv]
-    out = {"ratio": None, "profile": TRAFFIC_PROFILES[kv], "stale": None}
-    if not path.exists():
+    rel = TRAFFIC_PROFILES.get((kernel, kv))
+    out = {"ratio": None, "profile": rel, "stale": None}
+    if rel is None or not (ROOT / rel).exists():
         return out
-    text = path.read_text()
+    text = (ROOT / rel).read_text()
     m = re.search(r"DRAM traffic . algorithmic bytes[^0-9]*([0-9]+\.[0-9]+)", text)
     if m:
         out["ratio"] = float(m.group(1))
-    m = re.search(r"kernel source sha256[^=]*=\s*([0-9a-f]{64})", text)
-    if m:
-        now = hashlib.sha256((ROOT / KERNEL_SOURCE).read_bytes()).hexdigest()
-        out["stale"] = now != m.group(1)
+    m = re.search(r"kernel source sha256 \(`([^`]+)`\)\s*=\s*([0-9a-f]{64})", text)
+    if m and (ROOT / m.group(1)).exists():
+        out["stale"] = hashlib.sha256((ROOT / m.group(1)).read_bytes()).hexdigest() != m.group(2)
     return out
 
 
@@ -96,7 +100,8 @@ WORKLOADS = {
 }
 WORKLOADS["cfg5_sq8"] = dict(WORKLOADS["cfg5"], sq=8,
                              desc=WORKLOADS["cfg5"]["desc"].replace("4-token verify + 4-token append",
-                                                                    "8-token verify + 8-token append (32 packed rows per KV head)"))
+                                                                    "8-token verify + 8-token append (32 packed rows per KV head: at this batch "
+                                                                    "the tensor-memory kernel with its key split)"))
 WORKLOADS["cfg5_sq16"] = dict(WORKLOADS["cfg5"], sq=16,
                               desc=WORKLOADS["cfg5"]["desc"].replace("4-token verify + 4-token append",
                                                                      "16-token verify + 16-token append (64 packed rows per KV head: "
@@ -121,13 +126,15 @@ FALLBACK_BF16_TFLOPS = 1590.0
 # ----------------------------------------------------------------------------------------------
 
 def split_kv_kernel_name(cfg: dict) -> str:
-    """The split-KV kernel the library picks for a workload (rows = GQA group x query positions per KV head)."""
+    """The attention kernel the library picks for a decode / verify workload (rows = GQA group x query positions per
+    KV head; the rule of ``use_prefill_kernel`` in csrc/paged_attention.cuh, 148 SMs)."""
     rows = (HQ // HKV) * cfg["sq"]
-    if rows >= (65 if cfg["kv"] == "fp8" else 33 if cfg["head_dim"] == 128 else 56):
+    fp8 = cfg["kv"] == "fp8"
+    if rows >= (65 if fp8 else 33) or (not fp8 and cfg["head_dim"] == 128 and rows > 16 and cfg["batch"] * HKV >= 148):
         return "paged_prefill_kernel"
     if rows > 16:
         return "paged_attn_rows32_kernel"
-    if rows <= 8 and (cfg["kv"] == "fp8" or cfg["head_dim"] == 64):
+    if rows <= 8 and (fp8 or cfg["head_dim"] == 64):
         return "paged_attn_decode_kernel"
     return "paged_attn_kernel"
 
@@ -1232,7 +1239,7 @@ def measure_decode(name: str, args, device, rank: int, world: int, dist, *, step
     ms_per_step = ms_all / steps
     logical = attn_bytes / (attn_avg_ms * 1e-3) / 1e9
     achieved = attn_unique / (attn_avg_ms * 1e-3) / 1e9
-    traffic = dram_traffic_ratio(cfg["kv"])
+    traffic = dram_traffic_ratio(split_kv_kernel_name(cfg), cfg["kv"])
     rec = {
         "value": value, "unit": "GB/s", "ms_per_step": ms_per_step, "steps": steps,
         "tokens_per_s": world * B * sq / (ms_per_step * 1e-3),
@@ -1384,7 +1391,7 @@ def main() -> None:
     # the other configurations, same process, same box: sub-records under "workloads"
     extra = {}
     if not args.only:
-        for name in ("cfg5", "cfg5_sq8", "cfg5_sq16", "cfg2", "cfg4"):
+        for name in ("cfg5", "cfg5_sq8", "cfg2", "cfg4"):
             if name == args.workload:
                 continue
             one_layer = WORKLOADS[name]["layers"] == 1

@@ -1781,14 +1781,20 @@ constexpr int kPrefillRowsPerSeg = 256, kPrefillTileKeys = 128, kPrefillMinPacke
 // Packed query rows per sequence (per KV head) from which the prefill kernel serves a call.  Below, the split-KV
 // kernels read a sequence's keys once per 32 rows and balance any mix of lengths over all SMs; the prefill kernel
 // reads them once per 256 rows, but one CTA walks all keys of its rows and pays a fixed cost per CTA.  Measured
-// (256 / 64 / 8 sequences of U[2k, 16k] keys, 32/8 heads, per call, prefill | split-KV):
-//   16-bit pools, head_dim 128, 36 rows: 1.46 | 3.28 ms, 0.28 | 0.48 ms, 0.156 | 0.157 ms  (two passes of the
-//     32-row kernel against the key-split prefill kernel at the HBM rate); 32 rows: 1.77 | 1.67, 0.28 | 0.28,
-//     0.148 | 0.154; on contexts of a few hundred keys the split-KV side wins at 32 rows by a third  -> 33.
-//   16-bit pools, head_dim 64 (512 sequences of ~900 keys): 36 rows 0.33 | 0.27 ms                     -> 56.
-//   e4m3 pools (the prefill kernel widens tiles through shared memory and has no key split): 64 rows
-//     2.69 | 2.44 ms, 0.84 | 0.71, 0.33 | 0.14; 128 rows 2.73 | 4.92, 0.85 | 1.36, 0.33 | 0.19          -> 65.
-inline int prefill_min_rows(int head_dim, bool kv8) { return kv8 ? 65 : head_dim == 128 ? 33 : 56; }
+// per call, prefill | split-KV (32/8 heads unless noted; U[a, b] = context lengths):
+//   16-bit pools, head_dim 128
+//     36 rows: 256 x U[2k,16k] 1.46 | 3.28 ms, 64 x U[1k,8k] 0.28 | 0.48, 8 x U[2k,16k] 0.156 | 0.157          -> 33
+//     20 .. 32 rows: 256 x U[2k,16k] 1.46 | 1.65, 64 x U[2k,4k] 0.154 | 0.174 .. 0.187, 128 x U[300,1200]
+//       0.116 | 0.120 .. 0.139, 32 x U[300,1200] 0.036 | 0.081 .. 0.110, 512 x U[300,1200] 0.420 | 0.388 .. 0.429;
+//       16 x U[2k,16k] 0.153 | 0.145, 8 x U[2k,16k] 0.150 | 0.120   -> 17 once there is a CTA (sequence x KV head) per SM
+//   16-bit pools, head_dim 64
+//     20 .. 32 rows: 512 x U[760,1000] 0.353 | 0.208 .. 0.219, 256 x U[2k,16k] 0.986 | 0.840 .. 0.850
+//     48 rows: 512 x U[760,1000] 0.367 | 0.392, 64 x U[2k,16k] 0.318 | 0.427, 256 x U[2k,16k] 1.13 | 1.69;
+//       32/32 heads, 64 x U[2k,16k] 1.08 | 1.63                                                                  -> 33
+//   e4m3 pools (the prefill kernel widens tiles through shared memory and has no key split)
+//     64 rows: 256 x U[2k,16k] 2.69 | 2.44, 64 x: 0.84 | 0.71, 8 x: 0.33 | 0.14; 128 rows: 2.73 | 4.92, 0.85 | 1.36,
+//       0.33 | 0.19                                                                                              -> 65
+inline int prefill_min_rows(bool kv8) { return kv8 ? 65 : 33; }
 
 // A TMA box must fill a multiple of 128 bytes of shared memory: page_size x min(row bytes, 128).  Pools
 // that cannot offer that (page size 1 with 64-byte e4m3 rows) are served by the split-KV kernels' cp.async
@@ -1811,7 +1817,14 @@ inline bool use_prefill_kernel(const kb200_attn_args* a) {
   // sequence says which kernel has less work.
   int64_t rows = a->seqlen_q;
   if (a->cu_seqlens_q && a->batch > 0) rows = std::min<int64_t>(rows, (a->total_q + a->batch - 1) / a->batch);
-  return (int64_t)(a->n_q_heads / a->n_kv_heads) * rows >= prefill_min_rows(a->head_dim, a->kv_dtype == KB200_DTYPE_E4M3);
+  const int64_t packed_rows = (int64_t)(a->n_q_heads / a->n_kv_heads) * rows;
+  const bool kv8 = a->kv_dtype == KB200_DTYPE_E4M3;
+  if (packed_rows >= prefill_min_rows(kv8)) return true;
+  if (!kv8 && a->head_dim == 128 && packed_rows > kRowsPerSeg) {   // 17 .. 32 rows: with a CTA per SM at least
+    int sms = 0;
+    return device_sm_count(a->device, &sms) == KB200_OK && a->batch * (int64_t)a->n_kv_heads >= sms;
+  }
+  return false;
 }
 
 // Scratch bytes this very call needs: the plan arrays, plus the split-KV partials unless the prefill

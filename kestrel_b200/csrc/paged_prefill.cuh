@@ -2,7 +2,7 @@
 // cores: many query rows per sequence (a prompt chunk), K/V gathered through the
 // page table.  This is the compute-bound mode of the same op the decode kernels
 // serve (paged_attention.cuh); it is chosen when a sequence brings at least
-// 33 packed query rows per KV head (56 with head_dim 64, 65 on e4m3 pools).  K/V pools are 16-bit or FP8 e4m3 (see KV8 below).
+// 33 packed query rows per KV head (65 on e4m3 pools; 17 with 16-bit head_dim-128 pools and a CTA per SM).  K/V pools are 16-bit or FP8 e4m3 (see KV8 below).
 //
 // One CTA = one (sequence, KV head, block of 256 packed query rows) = two Q tiles of
 // 128 rows; packed row r = j * group + g is query position j of head h * group + g,

@@ -97,10 +97,12 @@ def test_packed_rows_of_mixed_lengths():
     assert_close(out, torch.cat([want[b, :n] for b, n in enumerate(qlens)]), "packed")
 
 
-def test_verify_batch_at_full_size():
-    """64 sequences, contexts U[2048, 16384], 8-token verify at GQA 4: the 4-token verify configuration's shape
-    with twice the tokens per step."""
-    p = make_paged_problem(seed=56, batch=64, len_lo=2048, len_hi=16384, n_q_heads=32, n_kv_heads=8, head_dim=128,
+@pytest.mark.parametrize("batch", [16, 64])
+def test_verify_batch_at_full_size(batch):
+    """Contexts U[2048, 16384], 8-token verify at GQA 4 (the 4-token verify configuration's shape with twice the
+    tokens per step).  16 sequences x 8 KV heads stay on the 32-row kernel; 64 x 8 reach the SM count and go to the
+    tensor-memory kernel with its key split."""
+    p = make_paged_problem(seed=56, batch=batch, len_lo=2048, len_hi=16384, n_q_heads=32, n_kv_heads=8, head_dim=128,
                            page_size=16, seqlen_q=8, dtype=torch.bfloat16, pool_factor=1.02)
     out, want = run_case(p, torch.bfloat16)
     assert_close(out, want, "verify batch")
