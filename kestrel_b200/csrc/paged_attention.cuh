@@ -1410,7 +1410,7 @@ paged_attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
 // few segments, each cut by a hundred boundaries, and must not be merged by a handful of blocks.
 // A second loop zero-fills the rows of sequences without visible keys.
 // ---------------------------------------------------------------------------
-constexpr int kMergeCoopParts = 8;   // from this many partials per segment on, a warp shares an item
+constexpr int kMergeCoopParts = 32;   // from this many partials per segment on, a warp shares an item
 
 template <int HD>
 __global__ void __launch_bounds__(128) attn_merge_kernel(const AttnParams p) {
@@ -1474,7 +1474,7 @@ __global__ void __launch_bounds__(128) attn_merge_kernel(const AttnParams p) {
         if (row >= nrows) continue;
         const int sub = rl >> 4, r16 = rl & 15;   // 16-row slot of the row (32-row segments have two per worker)
         float M = -INFINITY;
-        for (int wi = wi0; wi <= wl; wi += wi_step)
+        for (int wi = wi0; wi <= wl; wi += wi_step)   // (not unrolled: measured slower, the kernel is a chain of fetches)
           if (has_tiles(wi)) M = fmaxf(M, *ml_of(wi, sub, r16));
         if (coop) {
 #pragma unroll
