@@ -120,6 +120,11 @@ struct AttnParams {
   // and for pages of one or two tokens (the reference's default page size is 1, kestrel/config.py:164),
   // where a box per token costs more than it moves.
   int gather;
+  // head_pack > 1: `head_pack` KV heads whose rows lie side by side in the pool are read as ONE head of
+  // head_pack * real_hd elements (hkv, group and the kernel's head_dim are those of that wide head); a query
+  // row is zero outside the real_hd-wide slice of its own KV head and owns only that slice of the output.
+  // For pools with tiny pages and rows: page size 1 or 2 with 64- or 128-byte e4m3 rows.
+  int head_pack, real_hd;
   const char* k_base;
   const char* v_base;
   long long kv_ps_b, kv_ts_b, kv_hs_b;
@@ -1034,6 +1039,17 @@ paged_attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
   constexpr int NDT = HD / 16;      // 16-wide head_dim slices
   constexpr float kLog2e = 1.4426950408889634f;
   static_assert(TILE_N % 16 == 0, "tile must hold whole 16-key blocks");
+  // head_dim 256 only exists as several KV heads read as one (AttnParams::head_pack): e4m3 rows of 64 or 128
+  // bytes in pools with pages of one or two tokens.  The products run over the wide head with block-sparse Q:
+  // S^T = [K_0 | K_1 | ..] [Q_0^T ; Q_1^T ; ..] where Q_g^T is zero outside the rows of head g, so every column
+  // of S^T is the score of its own head, and of O^T = [V_0 | V_1 | ..]^T P^T a column owns the slice of its head.
+  constexpr bool PACKED = HD == 256;
+  static_assert(!PACKED || KVB == 1, "packed heads: e4m3 pools");
+  // e4m3 tile rows are RB bytes per 128-byte slab (two slabs when the row has 256 bytes)
+  auto kv8_off = [](int r, int ch) -> uint32_t {
+    if constexpr (T::NH == 2) return (uint32_t)(ch >> 3) * (TILE_N * 128) + (uint32_t)r * 128 + ((uint32_t)((ch & 7) ^ (r & 7)) << 4);
+    else return (uint32_t)r * RB + ((uint32_t)(ch ^ (int)swz<RB>(r)) << 4);
+  };
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -1108,8 +1124,10 @@ paged_attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
       // B fragments of Q^T: this thread supplies row (mb*8 + g8)
       const int qr = mb * kDecodeRows + g8;
       const bool qvalid = qr < nrows;
+      // (h * group + g is the index of the query head with packed heads too: both count KV head by KV head)
       const char* qrow = p.q + 2 * ((int64_t)cc.b * p.q_bs + (int64_t)(cc.qr + qr / p.group) * p.q_rs +
                                     (int64_t)(h * p.group + qr % p.group) * p.q_hs);
+      [[maybe_unused]] const int q_slice = PACKED ? (qr % p.group) / (p.group / p.head_pack) : 0;   // KV head inside the pack
       if constexpr (KVB == 2) {
 #pragma unroll
         for (int ks = 0; ks < NDT; ++ks) {
@@ -1120,8 +1138,13 @@ paged_attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
       } else {
 #pragma unroll
         for (int ch = 0; ch < NDT; ++ch) {
-          const int d = 16 * ch + 4 * c4;
-          uint2 a = qvalid ? *reinterpret_cast<const uint2*>(qrow + 2 * d) : make_uint2(0u, 0u);
+          int d = 16 * ch + 4 * c4;
+          bool mine = qvalid;
+          if constexpr (PACKED) {   // zero outside the slice of the row's own KV head
+            mine = qvalid && (16 * ch) / p.real_hd == q_slice;
+            d -= q_slice * p.real_hd;
+          }
+          uint2 a = mine ? *reinterpret_cast<const uint2*>(qrow + 2 * d) : make_uint2(0u, 0u);
           if (p.q_is_bf16) {
             a.x = pack2<false>(bf16_bits_to_float(a.x & 0xffffu), bf16_bits_to_float(a.x >> 16));
             a.y = pack2<false>(bf16_bits_to_float(a.y & 0xffffu), bf16_bits_to_float(a.y >> 16));
@@ -1134,7 +1157,7 @@ paged_attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
 
     // Last tile of this segment and the next segment belongs to the same sequence: pull its Q row
     // into L1 now, so that the loads at the segment switch do not wait for L2.
-    if (cc.t == cc.nt - 1 && cc.seg + 1 < cc.nseg && it + 1 < my_tiles && (c4 == 0 || (HD == 128 && c4 == 1))) {
+    if (!PACKED && cc.t == cc.nt - 1 && cc.seg + 1 < cc.nseg && it + 1 < my_tiles && (c4 == 0 || (HD == 128 && c4 == 1))) {
       const int ns = cc.seg + 1, nh = ns / cc.nmb;
       const int r = (ns - nh * cc.nmb) * kDecodeRows + g8;
       if (r < p.group * cc.sq)
@@ -1181,7 +1204,7 @@ paged_attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
         for (int mt = 0; mt < NMT; ++mt) {
           const int r = mt * 16 + k_row;
           const int ch = 2 * cp + k_chunk;
-          const uint32_t addr = kbase + (uint32_t)r * RB + ((uint32_t)(ch ^ swz<RB>(r)) << 4);
+          const uint32_t addr = kbase + kv8_off(r, ch);
           uint32_t x0, x1, x2, x3;  // (keys lo, ch) (keys hi, ch) (keys lo, ch+1) (keys hi, ch+1)
           ldsm_x4(x0, x1, x2, x3, addr);
           uint32_t a0, a1, a2, a3;
@@ -1285,7 +1308,7 @@ paged_attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
 #pragma unroll
           for (int cp = 0; cp < NDT / 2; ++cp) {
             const int ch = 2 * cp + v_chunk;
-            const uint32_t addr = vbase + (uint32_t)row * RB + ((uint32_t)(ch ^ swz<RB>(row)) << 4);
+            const uint32_t addr = vbase + kv8_off(row, ch);
             uint32_t x0, x1, x2, x3;  // (keys lo, ch) (keys hi, ch) (keys lo, ch+1) (keys hi, ch+1)
             ldsm_x4_t(x0, x1, x2, x3, addr);
             if constexpr (MASKED) { x0 &= mk_lo; x1 &= mk_hi; x2 &= mk_lo; x3 &= mk_hi; }
@@ -1344,7 +1367,14 @@ paged_attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
         {
 #pragma unroll
           for (int i = 0; i < NDT; ++i) {
-            const int d = KVB == 2 ? 16 * i + g8 : 16 * i + 2 * g8;
+            int d = KVB == 2 ? 16 * i + g8 : 16 * i + 2 * g8;
+            bool w0 = v0, w1 = v1;
+            if constexpr (PACKED) {   // a column owns the slice of its KV head (both columns of a thread: the same pack)
+              const int per = p.group / p.head_pack, sl = (16 * i) / p.real_hd;
+              w0 = v0 && (q0 % p.group) / per == sl;
+              w1 = v1 && (q1 % p.group) / per == sl;
+              d -= sl * p.real_hd;
+            }
             const float a0 = o[i][0] * i0, a2 = o[i][2] * i0, b1 = o[i][1] * i1, b3 = o[i][3] * i1;
             if constexpr (KVB == 2) {
               if (v0) {
@@ -1356,8 +1386,8 @@ paged_attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
                 *reinterpret_cast<uint16_t*>(out1 + 2 * (d + dstep)) = (uint16_t)(pack2<BF16>(b3, 0.f) & 0xffffu);
               }
             } else {
-              if (v0) *reinterpret_cast<uint32_t*>(out0 + 2 * d) = obf ? pack2<true>(a0, a2) : pack2<false>(a0, a2);
-              if (v1) *reinterpret_cast<uint32_t*>(out1 + 2 * d) = obf ? pack2<true>(b1, b3) : pack2<false>(b1, b3);
+              if (w0) *reinterpret_cast<uint32_t*>(out0 + 2 * d) = obf ? pack2<true>(a0, a2) : pack2<false>(a0, a2);
+              if (w1) *reinterpret_cast<uint32_t*>(out1 + 2 * d) = obf ? pack2<true>(b1, b3) : pack2<false>(b1, b3);
             }
           }
         }
@@ -1472,6 +1502,12 @@ __global__ void __launch_bounds__(128) attn_merge_kernel(const AttnParams p) {
         const int rl = item / kQuads, d = (item - rl * kQuads) * 4;
         const int row = mb * p.rows_per_seg + rl;
         if (row >= nrows) continue;
+        int d_out = d;
+        if (HD == 256) {   // packed heads: a row owns the slice of its own KV head
+          const int sl = (row % p.group) / (p.group / p.head_pack);
+          if (d / p.real_hd != sl) continue;
+          d_out = d - sl * p.real_hd;
+        }
         const int sub = rl >> 4, r16 = rl & 15;   // 16-row slot of the row (32-row segments have two per worker)
         float M = -INFINITY;
         for (int wi = wi0; wi <= wl; wi += wi_step)   // (not unrolled: measured slower, the kernel is a chain of fetches)
@@ -1507,12 +1543,12 @@ __global__ void __launch_bounds__(128) attn_merge_kernel(const AttnParams p) {
         const float inv = L > 0.f ? vscale / L : 0.f;
         const int j = row / p.group, hq = h * p.group + row % p.group;
         const float4 r = make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
-        const int64_t oi = (int64_t)b * p.o_bs + (int64_t)(qr + j) * p.o_rs + (int64_t)hq * p.o_hs + d;
+        const int64_t oi = (int64_t)b * p.o_bs + (int64_t)(qr + j) * p.o_rs + (int64_t)hq * p.o_hs + d_out;
         uint2 packed;
         if (p.q_is_bf16) packed = make_uint2(pack2<true>(r.x, r.y), pack2<true>(r.z, r.w));
         else packed = make_uint2(pack2<false>(r.x, r.y), pack2<false>(r.z, r.w));
         *reinterpret_cast<uint2*>(p.out + 2 * oi) = packed;
-        if (p.lse && d == 0)
+        if (p.lse && d_out == 0)
           p.lse[(int64_t)b * p.lse_bs + (int64_t)hq * p.lse_hs + qr + j] = L > 0.f ? M * kLn2 + logf(L) : -INFINITY;
       }
     }
@@ -1522,9 +1558,10 @@ __global__ void __launch_bounds__(128) attn_merge_kernel(const AttnParams p) {
     const int sq = p.sq[b];
     if (p.nt[b] > 0 || sq <= 0) continue;
     const int qr = p.qrow0[b];
-    const int items = sq * p.hq * kQuads;
+    const int zq = (HD == 256 ? p.real_hd : HD) / 4;   // (a query head's row has real_hd elements with packed heads too)
+    const int items = sq * p.hq * zq;
     for (int item = threadIdx.x; item < items; item += 128) {
-      const int d = (item % kQuads) * 4, rh = item / kQuads;
+      const int d = (item % zq) * 4, rh = item / zq;
       const int hq = rh % p.hq, j = rh / p.hq;
       const int64_t oi = (int64_t)b * p.o_bs + (int64_t)(qr + j) * p.o_rs + (int64_t)hq * p.o_hs + d;
       *reinterpret_cast<uint2*>(p.out + 2 * oi) = make_uint2(0u, 0u);   // +0.0 in either 16-bit type
@@ -1829,6 +1866,21 @@ inline bool use_prefill_kernel(const kb200_attn_args* a) {
 
 // Scratch bytes this very call needs: the plan arrays, plus the split-KV partials unless the prefill
 // kernel serves it.
+// Several KV heads read as one wide head (AttnParams::head_pack): for e4m3 pools with pages of one or two tokens
+// whose (token, head) rows have 64 or 128 bytes -- the reference's own FP8 geometry is page size 1, 32 KV heads of 64
+// (kestrel/models/moondream/runtime.py:645-663, kestrel/models/moondream/config.py:25-31).  Per head, a tile is
+// 64-byte pieces scattered over the pool, one page-table look-up per piece; four heads side by side make 256
+// contiguous bytes per look-up.  Needs: one scale per layer (the reference's), heads side by side in the pool,
+// at most 8 packed rows for the wide head.  Returns the number of heads per pack (1: none).
+inline int attn_head_pack(const kb200_attn_args* a) {
+  if (a->kv_dtype != KB200_DTYPE_E4M3 || a->page_size > 2 || a->k_scale_per_head || a->v_scale_per_head) return 1;
+  if (a->q_visible_until != nullptr || a->n_kv_heads <= 0) return 1;
+  const int pack = a->head_dim == 64 ? 4 : a->head_dim == 128 ? 2 : 1;
+  if (pack == 1 || a->n_kv_heads % pack != 0 || a->kv_head_stride != a->head_dim) return 1;
+  if ((int64_t)(a->n_q_heads / a->n_kv_heads) * pack * a->seqlen_q > kDecodeRows) return 1;
+  return pack;
+}
+
 // Segments of 17 to 32 packed rows (and what is left of longer ones below the prefill kernel's threshold) run the
 // 32-row split-KV kernel: one pass over the keys per 32 rows instead of one per 16.
 inline bool use_rows32_kernel(const kb200_attn_args* a) {
@@ -1839,8 +1891,9 @@ inline bool use_rows32_kernel(const kb200_attn_args* a) {
 }
 
 inline uint64_t attn_pass_workspace_need(const kb200_attn_args* a, int sms) {
-  const AttnWorkspace wl = attn_workspace_layout(a->batch, a->total_q, a->n_q_heads, a->n_kv_heads, a->head_dim,
-                                                 sms * kAttnMaxWarps, use_rows32_kernel(a));
+  const int pack = use_prefill_kernel(a) ? 1 : attn_head_pack(a);
+  const AttnWorkspace wl = attn_workspace_layout(a->batch, a->total_q, a->n_q_heads, a->n_kv_heads / pack,
+                                                 a->head_dim * pack, sms * kAttnMaxWarps, use_rows32_kernel(a));
   return use_prefill_kernel(a) ? wl.part_ml : wl.total;
 }
 
@@ -2086,22 +2139,24 @@ inline int launch_attention_pass(const kb200_attn_args* a, int k_skip, int fixed
   int sms = 0;
   if (int rc = device_sm_count(a->device, &sms)) return rc;
   const int grid = sms;
-  const int group = a->n_q_heads / a->n_kv_heads;
   const bool prefill = use_prefill_kernel(a);
+  // several KV heads read as one wide head (see attn_head_pack): from here on hkv, group and hd are the wide head's
+  const int pack = prefill ? 1 : attn_head_pack(a);
+  const int hkv = a->n_kv_heads / pack, hd = a->head_dim * pack;
+  const int group = a->n_q_heads / hkv;
   // Segments of at most 8 query rows run the transposed decode kernel where the math, not HBM, limits the
   // 16-row kernel: e4m3 K/V (twice the keys per byte plus the widening), and 16-bit K/V with head_dim 64
   // (the same MMAs and twice the exponentials per byte as head_dim 128: with 8 warps the 16-row kernel waits
   // on its own dependent MMA / ALU chains there, 45 % of the DRAM rate on short contexts).  16-bit K/V with
   // head_dim 128 is within a few percent of the HBM roofline with the 16-row kernel already.
   const bool decode8 = !prefill && (int64_t)group * a->seqlen_q <= kDecodeRows &&
-                       (a->kv_dtype == KB200_DTYPE_E4M3 || a->head_dim == 64);
+                       (a->kv_dtype == KB200_DTYPE_E4M3 || hd == 64);
   // (12 warps x 2 stages; 8 x 3 and 6 x 4 -- more tiles in flight per warp, fewer warps -- measured 2 % and
   // 13 % slower on the short contexts of a shared-prefix batch)
   const bool rows32 = use_rows32_kernel(a);   // (8 warps: two output accumulators per thread need the registers)
   const int nw = rows32 ? 8 : (a->kv_dtype == KB200_DTYPE_E4M3 || decode8) ? 12 : 8;
   const int n_workers = grid * nw;
-  const AttnWorkspace wl = attn_workspace_layout(a->batch, a->total_q, a->n_q_heads, a->n_kv_heads, a->head_dim,
-                                                 grid * kAttnMaxWarps, rows32);
+  const AttnWorkspace wl = attn_workspace_layout(a->batch, a->total_q, a->n_q_heads, hkv, hd, grid * kAttnMaxWarps, rows32);
   const uint64_t ws_need = attn_pass_workspace_need(a, sms);
   if (!a->workspace || a->workspace_bytes < ws_need)
     return fail(KB200_ERR_WORKSPACE, "workspace too small: need %llu bytes, got %llu", (unsigned long long)ws_need,
@@ -2113,7 +2168,7 @@ inline int launch_attention_pass(const kb200_attn_args* a, int k_skip, int fixed
     KB200_REQUIRE(a->causal != 0 && a->window_left < 0, "the block-bidirectional mask extends the causal mask: "
                                                        "causal must be set and no window given");
   }
-  const int tile_n = prefill ? kPrefillTileKeys : tile_n_for(a->kv_dtype, a->head_dim, nw);
+  const int tile_n = prefill ? kPrefillTileKeys : tile_n_for(a->kv_dtype, hd, nw);
   // every TMA copy must land on a 128-byte boundary of shared memory; pools that cannot offer that go
   // through the split-KV kernels' cp.async gather path (the prefill kernel has none)
   // Pages of one or two tokens are gathered as well: a box per token (or two) costs the issuing warp more than
@@ -2179,8 +2234,10 @@ inline int launch_attention_pass(const kb200_attn_args* a, int k_skip, int fixed
   p.batch = (int)a->batch;
   p.seqlen_q = a->seqlen_q;
   p.hq = a->n_q_heads;
-  p.hkv = a->n_kv_heads;
+  p.hkv = hkv;
   p.group = group;
+  p.head_pack = pack;
+  p.real_hd = a->head_dim;
   p.page_size = P;
   p.causal = a->causal != 0;
   p.window_left = a->window_left;
@@ -2190,7 +2247,7 @@ inline int launch_attention_pass(const kb200_attn_args* a, int k_skip, int fixed
   p.rows_per_seg = prefill ? kPrefillRowsPerSeg : decode8 ? kDecodeRows : rows32 ? 2 * kRowsPerSeg : kRowsPerSeg;
   p.seg_blocks = rows32 ? 2 : 1;
   p.uniform_nseg = (packed || a->seqused_q) ? 0
-                   : a->n_kv_heads * ((group * a->seqlen_q + p.rows_per_seg - 1) / p.rows_per_seg);
+                   : hkv * ((group * a->seqlen_q + p.rows_per_seg - 1) / p.rows_per_seg);
   p.k_skip = k_skip;
   p.fixed_klen = fixed_klen;
   p.fixed_klen_last = fixed_klen_last;
@@ -2201,7 +2258,7 @@ inline int launch_attention_pass(const kb200_attn_args* a, int k_skip, int fixed
   p.v_base = static_cast<const char*>(a->v_cache);
   p.kv_ps_b = a->kv_page_stride * es;
   p.kv_ts_b = a->kv_token_stride * es;
-  p.kv_hs_b = a->kv_head_stride * es;
+  p.kv_hs_b = a->kv_head_stride * es * pack;
   // the split-KV kernels build the plan themselves (every CTA, into shared memory) unless the batch is too large
   p.plan_in_kernel = (!prefill && a->batch <= kPlanSmemMaxBatch) ? 1 : 0;
 
@@ -2232,7 +2289,9 @@ inline int launch_attention_pass(const kb200_attn_args* a, int k_skip, int fixed
     }
     return rc;   // every segment is written by its own CTA: nothing to merge
   }
-  if (rows32 && a->kv_dtype == KB200_DTYPE_E4M3)
+  if (pack > 1)   // (e4m3, gather, at most 8 rows: the transposed kernel on the wide head)
+    rc = launch_decode_variant<1, 256, false, 12, 2, true>(tmK, tmV, p, grid, a->device, stream);
+  else if (rows32 && a->kv_dtype == KB200_DTYPE_E4M3)
     rc = launch_rows32_dispatch<1, false>(d128, tmK, tmV, p, grid, a->device, stream);
   else if (rows32)
     rc = a->kv_dtype == KB200_DTYPE_BF16 ? launch_rows32_dispatch<2, true>(d128, tmK, tmV, p, grid, a->device, stream)
@@ -2251,13 +2310,14 @@ inline int launch_attention_pass(const kb200_attn_args* a, int k_skip, int fixed
     rc = launch_attn_dispatch<2, false>(d128, nw, tmK, tmV, p, grid, a->device, stream);
   if (rc) return rc;
 
-  const int64_t max_seg = packed ? attn_max_segments(a->batch, a->total_q, a->n_q_heads, a->n_kv_heads)
-                                 : a->batch * a->n_kv_heads * ((group * (int64_t)a->seqlen_q + p.rows_per_seg - 1) / p.rows_per_seg);
+  const int64_t max_seg = packed ? attn_max_segments(a->batch, a->total_q, a->n_q_heads, hkv)
+                                 : a->batch * hkv * ((group * (int64_t)a->seqlen_q + p.rows_per_seg - 1) / p.rows_per_seg);
   KB200_REQUIRE(max_seg <= 0x7fffffff, "too many segments");
   // one block per range boundary (the only places where a segment can be cut), striding when there are more
   int64_t merge_blocks = std::max<int64_t>(n_workers - 1, 1);
   if (merge_blocks > (int64_t)sms * 16) merge_blocks = (int64_t)sms * 16;   // 16 x 128 threads fill an SM
-  if (d128) KB200_CUDA_OK(launch_kernel(attn_merge_kernel<128>, dim3((unsigned)merge_blocks), dim3(128), 0, stream, p));
+  if (pack > 1) KB200_CUDA_OK(launch_kernel(attn_merge_kernel<256>, dim3((unsigned)merge_blocks), dim3(128), 0, stream, p));
+  else if (d128) KB200_CUDA_OK(launch_kernel(attn_merge_kernel<128>, dim3((unsigned)merge_blocks), dim3(128), 0, stream, p));
   else KB200_CUDA_OK(launch_kernel(attn_merge_kernel<64>, dim3((unsigned)merge_blocks), dim3(128), 0, stream, p));
   return KB200_OK;
 }

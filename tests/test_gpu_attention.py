@@ -183,6 +183,48 @@ def test_fp8_pool_with_one_token_pages_and_64_byte_rows(heads_q, heads_kv, seqle
     assert_close(out, want, f"P=1 D=64 e4m3, {heads_q}/{heads_kv} heads, Sq={seqlen_q}")
 
 
+@pytest.mark.parametrize("heads_q,heads_kv,head_dim,seqlen_q,page_size", [
+    (32, 32, 64, 1, 1),    # the reference's own FP8 geometry: four KV heads read as one wide head of 256
+    (32, 32, 64, 2, 1),    # two query tokens: all 8 rows of the wide head's segment
+    (16, 8, 64, 1, 1),     # GQA 2 x four heads
+    (12, 12, 64, 1, 2),    # pages of two tokens, twelve heads = three packs
+    (32, 8, 128, 1, 1),    # 128-byte rows: two KV heads per pack, GQA 4
+    (8, 4, 128, 2, 2),
+    (6, 6, 64, 1, 1),      # six heads are not a multiple of four: no packing
+])
+@pytest.mark.parametrize("qdtype", [torch.bfloat16, torch.float16])
+def test_fp8_pools_with_tiny_pages_read_several_heads_as_one(heads_q, heads_kv, head_dim, seqlen_q, page_size, qdtype):
+    """e4m3 pools with pages of one or two tokens and per-layer scalar scales: KV heads whose rows lie side by
+    side are read as one head of 256 bytes.  Edge lengths, an empty sequence, one sequence long enough to be cut
+    by many tile ranges (the merge on the wide head), log-sum-exp."""
+    lengths = [1, 2, 15, 16, 17, 63, 64, 65, 129, 700, 0, 9000]
+    p = make_paged_problem(seed=91, batch=len(lengths), len_lo=0, len_hi=0, n_q_heads=heads_q, n_kv_heads=heads_kv,
+                           head_dim=head_dim, page_size=page_size, seqlen_q=seqlen_q, dtype=qdtype,
+                           lengths=[L + seqlen_q if L else 0 for L in lengths], outlier_frac=0.01)
+    ks = float(p["k_pool"].abs().max() / 448)
+    vs = float(p["v_pool"].abs().max() / 448)
+    out, want, lse, want_lse = run_case(p, qdtype, kv="fp8", scales=(ks, vs), return_lse=True)
+    for b, L in enumerate(lengths):
+        if L == 0:
+            assert (out[b] == 0).all() and torch.isinf(lse[b]).all()
+            continue
+        assert_close(out[b], want[b], f"packed heads {heads_q}/{heads_kv} D={head_dim} P={page_size} sequence {b}")
+        fin = torch.isfinite(want_lse[b])
+        assert torch.allclose(lse[b].cpu()[fin], want_lse[b][fin], atol=3e-3, rtol=1e-3)
+
+
+@pytest.mark.parametrize("window,causal", [(None, False), (0, True), (40, True), (1000, True)])
+def test_fp8_packed_heads_masks_and_seqused_q(window, causal):
+    lengths = [5, 64, 130, 700, 2500]
+    p = make_paged_problem(seed=92, batch=len(lengths), len_lo=0, len_hi=0, n_q_heads=16, n_kv_heads=16, head_dim=64,
+                           page_size=1, seqlen_q=2, dtype=torch.bfloat16, lengths=lengths)
+    sq = torch.tensor([2, 1, 2, 0, 2], dtype=torch.int32)
+    out, want = run_case(p, torch.bfloat16, kv="fp8", scales=(0.02, 0.03), causal=causal, window=window, seqused_q=sq)
+    for b, n in enumerate(sq.tolist()):
+        if n:
+            assert_close(out[b, :n], want[b, :n], f"packed heads window={window} causal={causal} sequence {b}")
+
+
 @pytest.mark.parametrize("kv", ["same", "fp8"])
 def test_single_long_sequence_is_split_across_warps_and_merged(kv):
     """One sequence of 20k keys: every (head) segment is cut into many partials that the merge combines."""

@@ -298,7 +298,8 @@ def test_prefill_calls_need_only_the_plan_arrays_as_scratch():
     a.kv_dtype = _native.DTYPE_E4M3                 # FP8 pools: the same kernel, tiles widened on the fly
     assert int(lib.kb200_attn_workspace_bytes_for(C.byref(a))) == need
     a.kv_dtype, a.seqlen_q, a.total_q = _native.DTYPE_BF16, 1, 64  # decode
-    assert int(lib.kb200_attn_workspace_bytes_for(C.byref(a))) == int(lib.kb200_attn_workspace_bytes(64, 64, 32, 8, 128, a.device))
+    # (the bound also covers e4m3 pools with one-token pages, whose partials are wider)
+    assert 64 * 1024 < int(lib.kb200_attn_workspace_bytes_for(C.byref(a))) <= int(lib.kb200_attn_workspace_bytes(64, 64, 32, 8, 128, a.device))
 
 
 @pytest.mark.parametrize("head_dim", [128, 64])

@@ -131,6 +131,19 @@ def test_static_scratch_rejects_problems_that_do_not_fit():
     msg = lib.kb200_last_error().decode()
     assert "built-in buffer" in msg and "kb200_paged_attention" in msg
     # largest decode batch (8 KV heads, head_dim 128) the built-in buffer serves
-    fit = max(b for b in range(1, 400) if int(lib.kb200_attn_workspace_bytes(b, b, 32, 8, 128, dev)) <= _native.STATIC_SCRATCH_BYTES)
+    # (sized as the entry point sizes it, for the call at hand; the bound over all calls of these dimensions is
+    # larger: it also covers e4m3 pools with one-token pages, whose partials are twice as wide)
+    a = _native.AttnArgs()
+    a.struct_bytes = C.sizeof(_native.AttnArgs)
+    a.device = dev
+    a.seqlen_q, a.n_q_heads, a.n_kv_heads, a.head_dim, a.page_size = 1, 32, 8, 128, 16
+    a.q_dtype = a.kv_dtype = _native.DTYPE_BF16
+
+    def need(b):
+        a.batch = a.total_q = b
+        return int(lib.kb200_attn_workspace_bytes_for(C.byref(a)))
+
+    fit = max(b for b in range(1, 400) if need(b) <= _native.STATIC_SCRATCH_BYTES)
     assert fit >= 128
+    assert need(fit) <= int(lib.kb200_attn_workspace_bytes(fit, fit, 32, 8, 128, dev))
     print(f"static scratch serves decode batches up to {fit} (32 q / 8 kv heads, head_dim 128)")
