@@ -126,10 +126,10 @@ uint64_t kb200_attn_workspace_bytes(int64_t batch, int64_t total_q, int32_t n_q_
   uint64_t need = attn_workspace_layout(batch, total_q, n_q_heads, n_kv_heads, head_dim, sms * kAttnMaxWarps, rows32_possible).total;
   // e4m3 pools with pages of one or two tokens read several KV heads as one wide head of 256 (attn_head_pack):
   // fewer segments, wider partials
-  const int pack = head_dim == 64 ? 4 : head_dim == 128 ? 2 : 1;
-  if (pack > 1 && n_kv_heads % pack == 0)
-    need = std::max<uint64_t>(need, attn_workspace_layout(batch, total_q, n_q_heads, n_kv_heads / pack, head_dim * pack,
-                                                          sms * kAttnMaxWarps, false).total);
+  for (int pack = 2; pack <= (head_dim == 64 ? 4 : head_dim == 128 ? 2 : 1); pack *= 2)
+    if (n_kv_heads % pack == 0)
+      need = std::max<uint64_t>(need, attn_workspace_layout(batch, total_q, n_q_heads, n_kv_heads / pack, head_dim * pack,
+                                                            sms * kAttnMaxWarps, false).total);
   return need;
 }
 

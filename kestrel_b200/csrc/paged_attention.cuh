@@ -1043,8 +1043,9 @@ paged_attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
   // bytes in pools with pages of one or two tokens.  The products run over the wide head with block-sparse Q:
   // S^T = [K_0 | K_1 | ..] [Q_0^T ; Q_1^T ; ..] where Q_g^T is zero outside the rows of head g, so every column
   // of S^T is the score of its own head, and of O^T = [V_0 | V_1 | ..]^T P^T a column owns the slice of its head.
-  constexpr bool PACKED = HD == 256;
-  static_assert(!PACKED || KVB == 1, "packed heads: e4m3 pools");
+  // (the same for 16-bit pools with 128-byte rows: two heads of 64 as one of 128; plain 16-bit head_dim-128 pools
+  // never run this kernel)
+  constexpr bool PACKED = HD == 256 || (KVB == 2 && HD == 128);
   // e4m3 tile rows are RB bytes per 128-byte slab (two slabs when the row has 256 bytes)
   auto kv8_off = [](int r, int ch) -> uint32_t {
     if constexpr (T::NH == 2) return (uint32_t)(ch >> 3) * (TILE_N * 128) + (uint32_t)r * 128 + ((uint32_t)((ch & 7) ^ (r & 7)) << 4);
@@ -1131,9 +1132,14 @@ paged_attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
       if constexpr (KVB == 2) {
 #pragma unroll
         for (int ks = 0; ks < NDT; ++ks) {
-          const int d = 16 * ks + 2 * c4;
-          qb[ks][0] = qvalid ? *reinterpret_cast<const uint32_t*>(qrow + 2 * d) : 0u;
-          qb[ks][1] = qvalid ? *reinterpret_cast<const uint32_t*>(qrow + 2 * (d + 8)) : 0u;
+          int d = 16 * ks + 2 * c4;
+          bool mine = qvalid;
+          if constexpr (PACKED) {   // zero outside the slice of the row's own KV head
+            mine = qvalid && (16 * ks) / p.real_hd == q_slice;
+            d -= q_slice * p.real_hd;
+          }
+          qb[ks][0] = mine ? *reinterpret_cast<const uint32_t*>(qrow + 2 * d) : 0u;
+          qb[ks][1] = mine ? *reinterpret_cast<const uint32_t*>(qrow + 2 * (d + 8)) : 0u;
         }
       } else {
 #pragma unroll
@@ -1377,11 +1383,11 @@ paged_attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
             }
             const float a0 = o[i][0] * i0, a2 = o[i][2] * i0, b1 = o[i][1] * i1, b3 = o[i][3] * i1;
             if constexpr (KVB == 2) {
-              if (v0) {
+              if (w0) {
                 *reinterpret_cast<uint16_t*>(out0 + 2 * d) = (uint16_t)(pack2<BF16>(a0, 0.f) & 0xffffu);
                 *reinterpret_cast<uint16_t*>(out0 + 2 * (d + dstep)) = (uint16_t)(pack2<BF16>(a2, 0.f) & 0xffffu);
               }
-              if (v1) {
+              if (w1) {
                 *reinterpret_cast<uint16_t*>(out1 + 2 * d) = (uint16_t)(pack2<BF16>(b1, 0.f) & 0xffffu);
                 *reinterpret_cast<uint16_t*>(out1 + 2 * (d + dstep)) = (uint16_t)(pack2<BF16>(b3, 0.f) & 0xffffu);
               }
@@ -1503,7 +1509,7 @@ __global__ void __launch_bounds__(128) attn_merge_kernel(const AttnParams p) {
         const int row = mb * p.rows_per_seg + rl;
         if (row >= nrows) continue;
         int d_out = d;
-        if (HD == 256) {   // packed heads: a row owns the slice of its own KV head
+        if (p.head_pack > 1) {   // packed heads: a row owns the slice of its own KV head
           const int sl = (row % p.group) / (p.group / p.head_pack);
           if (d / p.real_hd != sl) continue;
           d_out = d - sl * p.real_hd;
@@ -1558,7 +1564,7 @@ __global__ void __launch_bounds__(128) attn_merge_kernel(const AttnParams p) {
     const int sq = p.sq[b];
     if (p.nt[b] > 0 || sq <= 0) continue;
     const int qr = p.qrow0[b];
-    const int zq = (HD == 256 ? p.real_hd : HD) / 4;   // (a query head's row has real_hd elements with packed heads too)
+    const int zq = (p.head_pack > 1 ? p.real_hd : HD) / 4;   // (a query head's row has real_hd elements with packed heads too)
     const int items = sq * p.hq * zq;
     for (int item = threadIdx.x; item < items; item += 128) {
       const int d = (item % zq) * 4, rh = item / zq;
@@ -1873,9 +1879,12 @@ inline bool use_prefill_kernel(const kb200_attn_args* a) {
 // contiguous bytes per look-up.  Needs: one scale per layer (the reference's), heads side by side in the pool,
 // at most 8 packed rows for the wide head.  Returns the number of heads per pack (1: none).
 inline int attn_head_pack(const kb200_attn_args* a) {
-  if (a->kv_dtype != KB200_DTYPE_E4M3 || a->page_size > 2 || a->k_scale_per_head || a->v_scale_per_head) return 1;
+  const bool kv8 = a->kv_dtype == KB200_DTYPE_E4M3;
+  if (a->page_size > 2 || (kv8 && (a->k_scale_per_head || a->v_scale_per_head))) return 1;
   if (a->q_visible_until != nullptr || a->n_kv_heads <= 0) return 1;
-  const int pack = a->head_dim == 64 ? 4 : a->head_dim == 128 ? 2 : 1;
+  // wide rows of 256 bytes: four e4m3 heads of 64, two of 128, or two 16-bit heads of 64 (the reference's default
+  // pools: page size 1, kestrel/config.py:164, MHA heads of 64)
+  const int pack = kv8 ? (a->head_dim == 64 ? 4 : a->head_dim == 128 ? 2 : 1) : (a->head_dim == 64 ? 2 : 1);
   if (pack == 1 || a->n_kv_heads % pack != 0 || a->kv_head_stride != a->head_dim) return 1;
   if ((int64_t)(a->n_q_heads / a->n_kv_heads) * pack * a->seqlen_q > kDecodeRows) return 1;
   return pack;
@@ -2150,7 +2159,7 @@ inline int launch_attention_pass(const kb200_attn_args* a, int k_skip, int fixed
   // on its own dependent MMA / ALU chains there, 45 % of the DRAM rate on short contexts).  16-bit K/V with
   // head_dim 128 is within a few percent of the HBM roofline with the 16-row kernel already.
   const bool decode8 = !prefill && (int64_t)group * a->seqlen_q <= kDecodeRows &&
-                       (a->kv_dtype == KB200_DTYPE_E4M3 || hd == 64);
+                       (a->kv_dtype == KB200_DTYPE_E4M3 || hd == 64 || pack > 1);
   // (12 warps x 2 stages; 8 x 3 and 6 x 4 -- more tiles in flight per warp, fewer warps -- measured 2 % and
   // 13 % slower on the short contexts of a shared-prefix batch)
   const bool rows32 = use_rows32_kernel(a);   // (8 warps: two output accumulators per thread need the registers)
@@ -2289,8 +2298,11 @@ inline int launch_attention_pass(const kb200_attn_args* a, int k_skip, int fixed
     }
     return rc;   // every segment is written by its own CTA: nothing to merge
   }
-  if (pack > 1)   // (e4m3, gather, at most 8 rows: the transposed kernel on the wide head)
+  if (pack > 1 && a->kv_dtype == KB200_DTYPE_E4M3)   // (gather, at most 8 rows: the transposed kernel on the wide head)
     rc = launch_decode_variant<1, 256, false, 12, 2, true>(tmK, tmV, p, grid, a->device, stream);
+  else if (pack > 1)
+    rc = a->kv_dtype == KB200_DTYPE_BF16 ? launch_decode_variant<2, 128, true, 12, 2, true>(tmK, tmV, p, grid, a->device, stream)
+                                         : launch_decode_variant<2, 128, false, 12, 2, true>(tmK, tmV, p, grid, a->device, stream);
   else if (rows32 && a->kv_dtype == KB200_DTYPE_E4M3)
     rc = launch_rows32_dispatch<1, false>(d128, tmK, tmV, p, grid, a->device, stream);
   else if (rows32)
@@ -2316,8 +2328,8 @@ inline int launch_attention_pass(const kb200_attn_args* a, int k_skip, int fixed
   // one block per range boundary (the only places where a segment can be cut), striding when there are more
   int64_t merge_blocks = std::max<int64_t>(n_workers - 1, 1);
   if (merge_blocks > (int64_t)sms * 16) merge_blocks = (int64_t)sms * 16;   // 16 x 128 threads fill an SM
-  if (pack > 1) KB200_CUDA_OK(launch_kernel(attn_merge_kernel<256>, dim3((unsigned)merge_blocks), dim3(128), 0, stream, p));
-  else if (d128) KB200_CUDA_OK(launch_kernel(attn_merge_kernel<128>, dim3((unsigned)merge_blocks), dim3(128), 0, stream, p));
+  if (pack > 1 && hd == 256) KB200_CUDA_OK(launch_kernel(attn_merge_kernel<256>, dim3((unsigned)merge_blocks), dim3(128), 0, stream, p));
+  else if (d128 || hd == 128) KB200_CUDA_OK(launch_kernel(attn_merge_kernel<128>, dim3((unsigned)merge_blocks), dim3(128), 0, stream, p));
   else KB200_CUDA_OK(launch_kernel(attn_merge_kernel<64>, dim3((unsigned)merge_blocks), dim3(128), 0, stream, p));
   return KB200_OK;
 }

@@ -213,6 +213,25 @@ def test_fp8_pools_with_tiny_pages_read_several_heads_as_one(heads_q, heads_kv, 
         assert torch.allclose(lse[b].cpu()[fin], want_lse[b][fin], atol=3e-3, rtol=1e-3)
 
 
+@pytest.mark.parametrize("heads_q,heads_kv,seqlen_q,page_size", [(32, 32, 1, 1), (32, 32, 4, 1), (16, 8, 1, 2), (6, 6, 2, 1), (5, 5, 1, 1)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_16_bit_pools_with_tiny_pages_read_two_heads_as_one(heads_q, heads_kv, seqlen_q, page_size, dtype):
+    """The reference's default pools (page size 1, kestrel/config.py:164; MHA heads of 64): a (token, head) row has
+    128 bytes, two heads side by side are read as one of 256.  Five heads cannot pair up and stay single."""
+    lengths = [1, 2, 15, 16, 17, 63, 64, 65, 129, 700, 0, 9000]
+    p = make_paged_problem(seed=93, batch=len(lengths), len_lo=0, len_hi=0, n_q_heads=heads_q, n_kv_heads=heads_kv,
+                           head_dim=64, page_size=page_size, seqlen_q=seqlen_q, dtype=dtype,
+                           lengths=[L + seqlen_q if L else 0 for L in lengths])
+    out, want, lse, want_lse = run_case(p, dtype, return_lse=True)
+    for b, L in enumerate(lengths):
+        if L == 0:
+            assert (out[b] == 0).all() and torch.isinf(lse[b]).all()
+            continue
+        assert_close(out[b], want[b], f"paired heads {heads_q}/{heads_kv} P={page_size} Sq={seqlen_q} sequence {b}")
+        fin = torch.isfinite(want_lse[b])
+        assert torch.allclose(lse[b].cpu()[fin], want_lse[b][fin], atol=3e-3, rtol=1e-3)
+
+
 @pytest.mark.parametrize("window,causal", [(None, False), (0, True), (40, True), (1000, True)])
 def test_fp8_packed_heads_masks_and_seqused_q(window, causal):
     lengths = [5, 64, 130, 700, 2500]
