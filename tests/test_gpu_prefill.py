@@ -72,12 +72,15 @@ def _shapes_case(seqlen_q, group, heads_kv, head_dim):
 
 
 @pytest.mark.parametrize("page_size", [1, 2, 8, 16, 64, 256])
-def test_prefill_page_sizes(page_size):
-    lengths = [300, 64, 65, 1, 513]
-    p = make_paged_problem(seed=13, batch=len(lengths), len_lo=0, len_hi=0, n_q_heads=8, n_kv_heads=2, head_dim=128,
-                           page_size=page_size, seqlen_q=32, dtype=torch.bfloat16, lengths=lengths)
+@pytest.mark.parametrize("head_dim,seqlen_q", [(128, 32), (64, 32), (128, 96), (64, 130)])
+def test_prefill_page_sizes(page_size, head_dim, seqlen_q):
+    """TMA boxes of one token (page size 1) up to a whole 128-key tile (page size 256); 32 query tokens at GQA 4 fill
+    one Q tile (key split), 96 and 130 two and more."""
+    lengths = [300, 64, 65, 1, 513, 1300]
+    p = make_paged_problem(seed=13, batch=len(lengths), len_lo=0, len_hi=0, n_q_heads=8, n_kv_heads=2, head_dim=head_dim,
+                           page_size=page_size, seqlen_q=seqlen_q, dtype=torch.bfloat16, lengths=lengths)
     out, want = run_case(p, torch.bfloat16)
-    assert_close(out, want, f"page_size={page_size}")
+    assert_close(out, want, f"page_size={page_size} D={head_dim} Sq={seqlen_q}")
 
 
 @pytest.mark.parametrize("causal,window", [(False, None), (True, 63), (True, 200), (True, 0)])
