@@ -1,6 +1,6 @@
 """Benchmark of the paged-KV hot path: append + paged decode attention over a KV stack.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload cfg2|cfg3|cfg4|cfg5|cfg5_sq8|cfg5_sq16] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload cfg2|cfg3|cfg4|cfg5|cfg5_sq8|cfg5_sq16|ref_mha64_p1] [--impl reference]
 
 One *step* is one decode step of the whole KV stack of the workload: decode metadata and slot
 mapping once, then per layer the append of the new tokens' K/V rows (quantised to FP8 where the
@@ -106,6 +106,13 @@ WORKLOADS["cfg5_sq16"] = dict(WORKLOADS["cfg5"], sq=16,
                               desc=WORKLOADS["cfg5"]["desc"].replace("4-token verify + 4-token append",
                                                                      "16-token verify + 16-token append (64 packed rows per KV head: "
                                                                      "the tensor-memory kernel with its key split)"))
+# The reference's own pools: page size 1 (kestrel/config.py:164), MHA with 32 heads of 64
+# (kestrel/models/moondream/config.py:25-31), 24 layers, bf16.  `heads` / `page` override the module's geometry
+# while this workload is measured.
+WORKLOADS["ref_mha64_p1"] = dict(batch=64, lo=1024, hi=8192, layers=24, kv="bf16", head_dim=64, sq=1, outliers=0.0,
+                                 pool=1.25, heads=(32, 32), page=1,
+                                 desc="the reference's own geometry: bf16, 24 layers, batch 64, ctx U[1024,8192], "
+                                      "32/32 heads (MHA), D=64, page 1, pool 1.25x")
 HQ, HKV, PAGE = 32, 8, 16
 
 PREFILL_WORKLOADS = {
@@ -249,7 +256,7 @@ class GpuWorkload:
         self.kv_bytes = 1 if cfg["kv"] == "fp8" else 2
         # context lengths and the page permutation are the same on every rank (the per-GPU work of a
         # weak-scaling run must not depend on the rank's draw); the K/V/Q data below is seeded per rank
-        g = torch.Generator().manual_seed(1000 + int(name[3]))
+        g = torch.Generator().manual_seed(1000 + (int(name[3]) if name[3].isdigit() else 6))
         prefix = cfg.get("prefix", 0)
         suffix = torch.randint(cfg["lo"], cfg["hi"] + 1, (self.B,), generator=g)
         self.len0 = suffix + prefix                      # context before the first timed/warm-up step
@@ -877,7 +884,7 @@ class CpuWorkload:
         self.D, self.sq = cfg["head_dim"], cfg["sq"]
         self.fp8 = cfg["kv"] == "fp8"
         self.kv_bytes = 1 if self.fp8 else 2
-        g = torch.Generator().manual_seed(1000 + int(name[3]))
+        g = torch.Generator().manual_seed(1000 + (int(name[3]) if name[3].isdigit() else 6))
         prefix = cfg.get("prefix", 0)
         full = torch.randint(cfg["lo"], cfg["hi"] + 1, (cfg["batch"],), generator=g) + prefix
         self.len0 = full[: self.B]
@@ -1159,6 +1166,21 @@ def measure_decode(name: str, args, device, rank: int, world: int, dist, *, step
     from kestrel_b200 import _native
     local = device.index
     cfg = WORKLOADS[name]
+    global HQ, HKV, PAGE
+    saved_geometry = (HQ, HKV, PAGE)
+    if "heads" in cfg:
+        HQ, HKV = cfg["heads"]
+    if "page" in cfg:
+        PAGE = cfg["page"]
+    try:
+        return _measure_decode(name, cfg, args, device, rank, world, dist, steps=steps, e2e_steps=e2e_steps)
+    finally:
+        HQ, HKV, PAGE = saved_geometry
+
+
+def _measure_decode(name: str, cfg: dict, args, device, rank: int, world: int, dist, *, steps: int, e2e_steps: int) -> dict | None:
+    from kestrel_b200 import _native
+    local = device.index
     warm = max(3, args.warmup)
     total_steps = 3 * warm + steps + e2e_steps + 4
     wl = GpuWorkload(name, device, rank, total_steps, share_prefix=not args.no_shared_prefix)
@@ -1240,6 +1262,8 @@ def measure_decode(name: str, args, device, rank: int, world: int, dist, *, step
     logical = attn_bytes / (attn_avg_ms * 1e-3) / 1e9
     achieved = attn_unique / (attn_avg_ms * 1e-3) / 1e9
     traffic = dram_traffic_ratio(split_kv_kernel_name(cfg), cfg["kv"])
+    if "page" in cfg:   # (no capture of the gather path on one-token pages: no traffic figure for it)
+        traffic = {"ratio": None, "profile": None, "stale": None}
     rec = {
         "value": value, "unit": "GB/s", "ms_per_step": ms_per_step, "steps": steps,
         "tokens_per_s": world * B * sq / (ms_per_step * 1e-3),
@@ -1391,7 +1415,7 @@ def main() -> None:
     # the other configurations, same process, same box: sub-records under "workloads"
     extra = {}
     if not args.only:
-        for name in ("cfg5", "cfg5_sq8", "cfg2", "cfg4"):
+        for name in ("cfg5", "cfg5_sq8", "cfg2", "cfg4", "ref_mha64_p1"):
             if name == args.workload:
                 continue
             one_layer = WORKLOADS[name]["layers"] == 1
