@@ -36,7 +36,8 @@ import os
 
 HERE = Path(__file__).resolve().parent
 DEST = HERE / "_ref"
-DEFAULT_REFERENCE = os.environ.get("KESTREL_REFERENCE_DIR", "/root/reference")
+# a checkout named "reference" beside this repository, unless the environment names another place
+DEFAULT_REFERENCE = os.environ.get("KESTREL_REFERENCE_DIR", str(HERE.parent.parent / "reference"))
 
 MODULES = (
     "kestrel/kv_cache.py",
