@@ -65,12 +65,12 @@ TRAFFIC_PROFILES = {
 }
 
 
-def dram_traffic_ratio(kernel: str, kv: str) -> dict:
+def dram_traffic_ratio(kernel: str, kv: str, rel: str | None = None) -> dict:
     """{"ratio", "profile", "stale"}: the ratio a profile summary records, and whether the kernel source
     changed since (the summary names the source file and the sha256 it was captured with)."""
     import hashlib
     import re
-    rel = TRAFFIC_PROFILES.get((kernel, kv))
+    rel = rel or TRAFFIC_PROFILES.get((kernel, kv))
     out = {"ratio": None, "profile": rel, "stale": None}
     if rel is None or not (ROOT / rel).exists():
         return out
@@ -111,6 +111,7 @@ WORKLOADS["cfg5_sq16"] = dict(WORKLOADS["cfg5"], sq=16,
 # while this workload is measured.
 WORKLOADS["ref_mha64_p1"] = dict(batch=64, lo=1024, hi=8192, layers=24, kv="bf16", head_dim=64, sq=1, outliers=0.0,
                                  pool=1.25, heads=(32, 32), page=1,
+                                 traffic_profile="profiles/paged_attn_decode_kernel_bf16_ref_mha64_p1_reduced.md",
                                  desc="the reference's own geometry: bf16, 24 layers, batch 64, ctx U[1024,8192], "
                                       "32/32 heads (MHA), D=64, page 1, pool 1.25x")
 HQ, HKV, PAGE = 32, 8, 16
@@ -1262,8 +1263,8 @@ def _measure_decode(name: str, cfg: dict, args, device, rank: int, world: int, d
     logical = attn_bytes / (attn_avg_ms * 1e-3) / 1e9
     achieved = attn_unique / (attn_avg_ms * 1e-3) / 1e9
     traffic = dram_traffic_ratio(split_kv_kernel_name(cfg), cfg["kv"])
-    if "page" in cfg:   # (no capture of the gather path on one-token pages: no traffic figure for it)
-        traffic = {"ratio": None, "profile": None, "stale": None}
+    if "traffic_profile" in cfg:   # (a capture of this very geometry)
+        traffic = dram_traffic_ratio(split_kv_kernel_name(cfg), cfg["kv"], rel=cfg["traffic_profile"])
     rec = {
         "value": value, "unit": "GB/s", "ms_per_step": ms_per_step, "steps": steps,
         "tokens_per_s": world * B * sq / (ms_per_step * 1e-3),
