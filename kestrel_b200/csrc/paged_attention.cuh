@@ -1863,7 +1863,10 @@ inline bool use_prefill_kernel(const kb200_attn_args* a) {
   const int64_t packed_rows = (int64_t)(a->n_q_heads / a->n_kv_heads) * rows;
   const bool kv8 = a->kv_dtype == KB200_DTYPE_E4M3;
   if (packed_rows >= prefill_min_rows(kv8)) return true;
-  if (!kv8 && a->head_dim == 128 && packed_rows > kRowsPerSeg) {   // 17 .. 32 rows: with a CTA per SM at least
+  // 17 .. 32 rows: with a CTA per SM at least, and only when the launch will get the key-split variant (seqlen_q
+  // bounds every sequence's rows; a packed call without a bound keeps the 32-row kernel)
+  if (!kv8 && a->head_dim == 128 && packed_rows > kRowsPerSeg &&
+      (int64_t)(a->n_q_heads / a->n_kv_heads) * a->seqlen_q <= 128 /* rows of one Q tile */) {
     int sms = 0;
     return device_sm_count(a->device, &sms) == KB200_OK && a->batch * (int64_t)a->n_kv_heads >= sms;
   }

@@ -106,3 +106,27 @@ def test_verify_batch_at_full_size(batch):
                            page_size=16, seqlen_q=8, dtype=torch.bfloat16, pool_factor=1.02)
     out, want = run_case(p, torch.bfloat16)
     assert_close(out, want, "verify batch")
+
+
+@pytest.mark.parametrize("bound", [None, 8])
+def test_packed_rows_with_and_without_a_row_bound_at_a_batch_that_fills_the_sms(bound):
+    """40 sequences x 4 KV heads (a CTA per SM), 5 to 8 packed query tokens at GQA 4.  With ``max_seqlen_q`` the call
+    may take the tensor-memory kernel's key split; without it (the reference's packed call passes none,
+    kestrel/ops/attention.py:69-86) nothing bounds a sequence's rows and the 32-row kernel keeps the call."""
+    import random
+    rng = random.Random(5)
+    batch = 40
+    lengths = [rng.randint(40, 900) for _ in range(batch)]
+    qlens = [rng.randint(5, 8) for _ in range(batch)]
+    p = make_paged_problem(seed=57, batch=batch, len_lo=0, len_hi=0, n_q_heads=16, n_kv_heads=4, head_dim=128, page_size=16,
+                           seqlen_q=8, dtype=torch.bfloat16, lengths=lengths)
+    packed = torch.cat([p["q"][b, :n] for b, n in enumerate(qlens)]).to(torch.bfloat16).to(DEV)
+    cu = torch.tensor([0] + list(torch.tensor(qlens).cumsum(0)), dtype=torch.int32, device=DEV)
+    kw = {} if bound is None else {"max_seqlen_q": bound}
+    out, _ = kernels.flash_attn_fwd(packed, p["k_pool"].to(torch.bfloat16).to(DEV).permute(0, 2, 1, 3),
+                                    p["v_pool"].to(torch.bfloat16).to(DEV).permute(0, 2, 1, 3),
+                                    page_table=p["page_table"].to(DEV), cu_seqlens_q=cu,
+                                    seqused_k=p["seqused_k"].to(DEV), causal=True, **kw)
+    want = O.paged_attention(p["q"].to(torch.bfloat16).float(), p["k_pool"], p["v_pool"], p["page_table"],
+                             p["seqused_k"], seqused_q=torch.tensor(qlens))
+    assert_close(out, torch.cat([want[b, :n] for b, n in enumerate(qlens)]), f"packed, bound={bound}")
