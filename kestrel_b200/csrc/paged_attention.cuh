@@ -1834,9 +1834,12 @@ constexpr int kPrefillRowsPerSeg = 256, kPrefillTileKeys = 128, kPrefillMinPacke
 //     20 .. 32 rows: 512 x U[760,1000] 0.353 | 0.208 .. 0.219, 256 x U[2k,16k] 0.986 | 0.840 .. 0.850
 //     48 rows: 512 x U[760,1000] 0.367 | 0.392, 64 x U[2k,16k] 0.318 | 0.427, 256 x U[2k,16k] 1.13 | 1.69;
 //       32/32 heads, 64 x U[2k,16k] 1.08 | 1.63                                                                  -> 33
-//   e4m3 pools (the prefill kernel widens tiles through shared memory and has no key split)
-//     64 rows: 256 x U[2k,16k] 2.69 | 2.44, 64 x: 0.84 | 0.71, 8 x: 0.33 | 0.14; 128 rows: 2.73 | 4.92, 0.85 | 1.36,
-//       0.33 | 0.19                                                                                              -> 65
+//   e4m3 pools, head_dim 128 (the prefill kernel widens tiles through shared memory)
+//     without the key split (more than 128 rows per KV head somewhere in the launch): 64 rows: 256 x U[2k,16k]
+//       2.69 | 2.44, 64 x: 0.84 | 0.71, 8 x: 0.33 | 0.14; 128 rows: 2.73 | 4.92, 0.85 | 1.36, 0.33 | 0.19           -> 65
+//     with it: 40 rows: 256 x U[2k,16k] 1.77 | 2.39, 16 x: 0.206 | 0.171; 64 rows: 1.78 | 2.44, 0.204 | 0.179;
+//       128 rows: 256 x 1.83, 16 x 0.210                            -> 33 once there is a CTA per SM (32 rows and
+//       fewer stay with the 32-row kernel, which reads the keys once as well and spreads them over all SMs)
 inline int prefill_min_rows(bool kv8) { return kv8 ? 65 : 33; }
 
 // A TMA box must fill a multiple of 128 bytes of shared memory: page_size x min(row bytes, 128).  Pools
@@ -1863,9 +1866,9 @@ inline bool use_prefill_kernel(const kb200_attn_args* a) {
   const int64_t packed_rows = (int64_t)(a->n_q_heads / a->n_kv_heads) * rows;
   const bool kv8 = a->kv_dtype == KB200_DTYPE_E4M3;
   if (packed_rows >= prefill_min_rows(kv8)) return true;
-  // 17 .. 32 rows: with a CTA per SM at least, and only when the launch will get the key-split variant (seqlen_q
-  // bounds every sequence's rows; a packed call without a bound keeps the 32-row kernel)
-  if (!kv8 && a->head_dim == 128 && packed_rows > kRowsPerSeg &&
+  // 17 .. 32 rows (33 .. 64 on e4m3 pools): with a CTA per SM at least, and only when the launch will get the
+  // key-split variant (seqlen_q bounds every sequence's rows; a packed call without a bound keeps the 32-row kernel)
+  if (a->head_dim == 128 && packed_rows > (kv8 ? 2 * kRowsPerSeg : kRowsPerSeg) &&
       (int64_t)(a->n_q_heads / a->n_kv_heads) * a->seqlen_q <= 128 /* rows of one Q tile */) {
     int sms = 0;
     return device_sm_count(a->device, &sms) == KB200_OK && a->batch * (int64_t)a->n_kv_heads >= sms;

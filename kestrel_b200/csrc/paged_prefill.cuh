@@ -229,7 +229,6 @@ paged_prefill_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
   constexpr bool MMA_BF16 = BF16 && !KV8;   // operand type of both products
   constexpr int NH = SM::NH;
   constexpr int RING = SM::RING;
-  static_assert(!(SPLIT && KV8), "the key split is for 16-bit pools");
   // Under the key split Q tile B is unused and lies directly below the K/V ring: it becomes one more ring slot
   // (every key tile feeds one pipeline instead of two, so tiles are consumed twice as fast and the copies have
   // to run further ahead).
@@ -314,8 +313,8 @@ paged_prefill_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
   // heads per group, a verify step of a few dozen tokens) would run one dependent chain Q K^T -> softmax -> P V per
   // key tile with half of its warps and tensor memory idle.  Instead the two pipelines both work on Q tile A:
   // stream 0 takes the even key tiles, stream 1 the odd ones, each with its own S, P, O, maximum and sum, and the
-  // two partial results are combined at the end.  (16-bit pools: the f16 ring of an e4m3 pool holds three tiles,
-  // one fewer than K_{i+2} next to V_i needs.)
+  // two partial results are combined at the end.  Ring entries V_i to K_{i+2} (four in a row) are live at
+  // once: the f16 ring of an e4m3 pool (three tiles) gets there with the borrowed Q tile.
   const bool split = SPLIT && n_x[0] >= 2;
   const int n_s[2] = {split ? (n_tiles + 1) >> 1 : n_x[0], split ? n_tiles >> 1 : n_x[1]};   // key tiles per pipeline
 
@@ -406,15 +405,15 @@ paged_prefill_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
     constexpr int NSTG = SM::NSTG > 0 ? SM::NSTG : 1;   // (this branch is only taken with a staging ring)
     const int r = (warp - 10) * 32 + lane;
     for (int idx = 0; idx < 2 * n_tiles; ++idx) {
-      const int s8 = idx % NSTG, c = idx % RING;
+      const int s8 = idx % NSTG, c = idx % RINGN;
       bool got = mbar_wait_bounded(B_SFULL(s8), (uint32_t)(idx / NSTG) & 1u);
-      if (got && idx >= RING) got = mbar_wait_bounded(B_EMPTY(c), (uint32_t)((idx / RING) - 1) & 1u);
+      if (got && idx >= RINGN) got = mbar_wait_bounded(B_EMPTY(c), (uint32_t)((idx / RINGN) - 1) & 1u);
       if (!got) {
         if (lane == 0) report(KB200_STATUS_WAIT_TIMEOUT, idx, KID_PREFILL);
         break;
       }
       const uint8_t* src = sgen + SM::OFF_STG + s8 * SM::STG_TILE + r * RB8;
-      uint8_t* dst = sgen + SM::OFF_KV + c * SM::KV_TILE + r * 128;
+      uint8_t* dst = sgen + RING_OFF + c * SM::KV_TILE + r * 128;
 #pragma unroll
       for (int ch = 0; ch < RB8 / 16; ++ch) {
         const uint4 x = *reinterpret_cast<const uint4*>(src + ((ch ^ (int)swz<RB8>(r)) << 4));
@@ -958,10 +957,8 @@ inline int launch_prefill_variant(const CUtensorMap& tmK, const CUtensorMap& tmV
                                   int dev, cudaStream_t stream) {
   // seqlen_q bounds the rows of every sequence (padded and packed layouts alike): at most 128 packed rows per
   // KV head means no CTA of the launch uses its second Q tile, and the key-split variant serves it
-  if constexpr (!KV8) {
-    if ((long long)p.group * p.seqlen_q <= kPfTileRows)
-      return launch_prefill_split<HD, BF16, KV8, true>(tmK, tmV, p, grid, dev, stream);
-  }
+  if ((long long)p.group * p.seqlen_q <= kPfTileRows)
+    return launch_prefill_split<HD, BF16, KV8, true>(tmK, tmV, p, grid, dev, stream);
   return launch_prefill_split<HD, BF16, KV8, false>(tmK, tmV, p, grid, dev, stream);
 }
 

@@ -42,7 +42,7 @@ def test_prefill_shapes_and_gqa(seqlen_q, group, heads_kv, head_dim):
 
 
 # packed rows on either side of the switch between the split-KV kernels and the prefill kernel
-# (33 rows, 65 on FP8 pools; 17 with head_dim 128 once there is a CTA per SM)
+# (33 rows, 65 on FP8 pools; 17, 33 on FP8 pools, with head_dim 128 once there is a CTA per SM)
 @pytest.mark.parametrize("seqlen_q,group,heads_kv,head_dim", [(8, 4, 2, 128), (9, 4, 2, 128), (10, 4, 2, 128), (12, 4, 2, 128),
                                                                (32, 1, 3, 128), (33, 1, 3, 128), (39, 1, 3, 128), (40, 1, 3, 128),
                                                                (13, 4, 2, 64), (14, 4, 2, 64),
@@ -163,6 +163,31 @@ def test_key_split_of_a_single_q_tile(seqlen_q, group, heads_kv, head_dim, dtype
     out, want, lse, want_lse = run_case(p, dtype, return_lse=True)
     assert_close(out, want, f"key split Sq={seqlen_q} G={group} D={head_dim} {dtype}")
     assert torch.allclose(lse.cpu(), want_lse, atol=2e-3, rtol=1e-3)
+
+
+@pytest.mark.parametrize("seqlen_q,group,heads_kv,head_dim", [(65, 1, 2, 128), (128, 1, 2, 128), (17, 4, 2, 128), (10, 8, 1, 128),
+                                                               (70, 1, 3, 64), (32, 4, 1, 64)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_key_split_on_fp8_pools(seqlen_q, group, heads_kv, head_dim, dtype):
+    # e4m3 tiles are widened into a ring of four f16 tiles (three and the unused second Q tile)
+    lengths = [seqlen_q, seqlen_q + 129, 256, 257, 385, 1000, 2049, 5000, max(seqlen_q, 130)]
+    p = make_paged_problem(seed=64 + seqlen_q, batch=len(lengths), len_lo=0, len_hi=0, n_q_heads=group * heads_kv,
+                           n_kv_heads=heads_kv, head_dim=head_dim, page_size=16, seqlen_q=seqlen_q, dtype=dtype,
+                           lengths=lengths)
+    out, want, lse, want_lse = run_case(p, dtype, kv="fp8", scales=(0.02, 0.03), return_lse=True)
+    assert_close(out, want, f"fp8 key split Sq={seqlen_q} G={group} D={head_dim} {dtype}")
+    assert torch.allclose(lse.cpu(), want_lse, atol=3e-3, rtol=1e-3)
+
+
+def test_key_split_on_fp8_pools_from_33_rows_with_a_cta_per_sm():
+    # 40 sequences x 4 KV heads reach the SM count: 40 and 64 packed rows of an e4m3 pool go to the key split
+    rng = torch.Generator().manual_seed(65)
+    for seqlen_q in (10, 16):
+        lengths = torch.randint(seqlen_q, 900, (40,), generator=rng).tolist()
+        p = make_paged_problem(seed=66 + seqlen_q, batch=40, len_lo=0, len_hi=0, n_q_heads=16, n_kv_heads=4, head_dim=128,
+                               page_size=16, seqlen_q=seqlen_q, dtype=torch.bfloat16, lengths=lengths)
+        out, want = run_case(p, torch.bfloat16, kv="fp8", scales=(0.02, 0.03))
+        assert_close(out, want, f"fp8 key split, {4 * seqlen_q} rows, 160 CTAs")
 
 
 @pytest.mark.parametrize("causal,window", [(False, None), (True, 63), (True, 200), (True, 1000), (True, 0)])
